@@ -1,0 +1,401 @@
+"""Block-sparse prefill attention wrapper (drop-in for flashomni/attention.py:194-869).
+
+`plan()` does the host work once per shape (indptrs to the host, list capacities, workspace carving);
+`run()` enqueues two steps on the current stream: the mask compaction (packed bits -> work lists) and
+the tcgen05 attention kernel over those lists. Nothing in `run()` synchronises or allocates besides
+`out` / `lse` when the caller does not pass them (as in the reference, attention.py:778-781).
+"""
+
+from __future__ import annotations
+
+import functools
+import logging
+import math
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _native
+from .utils import (MaskMode, PosEncodingMode, TensorLayout, _check_cached_qkv_data_type, _check_kv_layout,
+                    _check_pos_encoding_mode, _check_shape_dtype_device, canonicalize_torch_dtype, native_dtype)
+
+
+def _compute_sparse_info_indptr(qo_indptr: torch.Tensor, num_qo_heads, sparse_block_size_for_q: int,
+                                device: torch.device = "cuda") -> torch.Tensor:
+    """Unpacked (bit count) indptr of sparse_info (reference: flashomni/attention.py:165-176)."""
+    out = torch.empty_like(qo_indptr, device=device)
+    out[0] = 0
+    out[1:] = torch.cumsum(
+        torch.ceil((qo_indptr[1:] - qo_indptr[:-1]) / sparse_block_size_for_q) * num_qo_heads, 0)
+    return out
+
+
+def _compute_sparse_kv_info_indptr(qo_indptr: torch.Tensor, kv_indptr: torch.Tensor, num_qo_heads,
+                                   sparse_block_size_for_q: int, sparse_block_size_for_kv: int,
+                                   device: torch.device = "cuda") -> torch.Tensor:
+    """Unpacked (bit count) indptr of sparse_kv_info (reference: flashomni/attention.py:178-191)."""
+    out = torch.empty_like(qo_indptr, device=device)
+    out[0] = 0
+    out[1:] = torch.cumsum(
+        torch.ceil((qo_indptr[1:] - qo_indptr[:-1]) / sparse_block_size_for_q)
+        * torch.ceil((kv_indptr[1:] - kv_indptr[:-1]) / sparse_block_size_for_kv) * num_qo_heads, 0)
+    return out
+
+
+class BatchFlashOmniFAWithRaggedKVWrapper:
+    r"""Prefill attention over ragged q/k/v with two bit-packed block masks: `sparse_info` selects the
+    (q-block, head) pairs that are computed at all, `sparse_kv_info` the kv-blocks each of them attends
+    to. Same constructor / plan / run surface as the reference class (flashomni/attention.py:194-869).
+
+    Extensions (keyword-only in `plan`, default = reference behaviour): `mask_num_heads` and
+    `mask_head_begin` describe a head window when the tensors hold only heads
+    [mask_head_begin, mask_head_begin + num_qo_heads) of a mask laid out for `mask_num_heads` heads
+    (used when heads are partitioned over GPUs).
+    """
+
+    def __init__(
+        self,
+        float_workspace_buffer: torch.Tensor,
+        kv_layout: str = "NHD",
+        use_cuda_graph: bool = False,
+        qo_indptr_buf: Optional[torch.Tensor] = None,
+        kv_indptr_buf: Optional[torch.Tensor] = None,
+        custom_mask_buf: Optional[torch.Tensor] = None,
+        mask_indptr_buf: Optional[torch.Tensor] = None,
+        backend: str = "auto",
+    ) -> None:
+        _check_kv_layout(kv_layout)
+        if not float_workspace_buffer.is_cuda:
+            raise RuntimeError("flashomni_b200: the workspace must live on a CUDA device (no CPU path exists)")
+        self._kv_layout = kv_layout
+        self._float_workspace_buffer = float_workspace_buffer
+        self.device = float_workspace_buffer.device
+        self._int_workspace_buffer = None  # carved in plan(); sized from the planned shapes
+        self._use_cuda_graph = use_cuda_graph
+        if use_cuda_graph:
+            if not torch.is_tensor(qo_indptr_buf):
+                raise ValueError("qo_indptr_buf should be a torch.Tensor in cuda graph mode")
+            if not torch.is_tensor(kv_indptr_buf):
+                raise ValueError("kv_indptr_buf should be a torch.Tensor in cuda graph mode")
+            self._fixed_batch_size = len(qo_indptr_buf) - 1
+            if len(kv_indptr_buf) != self._fixed_batch_size + 1:
+                raise ValueError(
+                    "The length of kv_indptr_buf ({}) should be the same as qo_indptr_buf ({}).".format(
+                        len(kv_indptr_buf), self._fixed_batch_size))
+        self._qo_indptr_buf = qo_indptr_buf
+        self._kv_indptr_buf = kv_indptr_buf
+        self._custom_mask_buf = custom_mask_buf
+        self._mask_indptr_buf = mask_indptr_buf
+        self._max_total_num_rows = None
+        self._backend = backend
+        self._planned = False
+
+    @property
+    def is_cuda_graph_enabled(self) -> bool:
+        return self._use_cuda_graph
+
+    def reset_workspace_buffer(self, float_workspace_buffer: torch.Tensor, int_workspace_buffer) -> None:
+        """Reference: flashomni/attention.py:384-406. The int workspace, if given and large enough, is
+        used for the work lists at the next plan()."""
+        self._float_workspace_buffer = float_workspace_buffer
+        self._int_workspace_buffer = int_workspace_buffer
+        self._planned = False
+
+    # ------------------------------------------------------------------------------------------ plan
+    def plan(
+        self,
+        qo_indptr: torch.Tensor,
+        kv_indptr: torch.Tensor,
+        num_qo_heads: int,
+        num_kv_heads: int,
+        head_dim_qk: int,
+        sparse_block_size_for_q: int = 128,
+        sparse_block_size_for_kv: int = 128,
+        head_dim_vo: Optional[int] = None,
+        custom_mask: Optional[torch.Tensor] = None,
+        packed_custom_mask: Optional[torch.Tensor] = None,
+        causal: bool = False,
+        pos_encoding_mode: str = "NONE",
+        use_fp16_qk_reduction: bool = False,
+        logits_soft_cap: Optional[float] = None,
+        sm_scale: Optional[float] = None,
+        rope_scale: Optional[float] = None,
+        rope_theta: Optional[float] = None,
+        q_data_type: Union[str, torch.dtype] = "float16",
+        kv_data_type: Optional[Union[str, torch.dtype]] = None,
+        *,
+        mask_num_heads: Optional[int] = None,
+        mask_head_begin: int = 0,
+    ) -> None:
+        """Reference: flashomni/attention.py:408-642. Host-only; must not be captured in a CUDA graph."""
+        q_data_type = canonicalize_torch_dtype(q_data_type)
+        if kv_data_type is None:
+            kv_data_type = q_data_type
+        kv_data_type = canonicalize_torch_dtype(kv_data_type)
+        if head_dim_vo is None:
+            head_dim_vo = head_dim_qk
+        if logits_soft_cap is None:
+            logits_soft_cap = 0.0
+        _check_pos_encoding_mode(pos_encoding_mode)
+
+        batch_size = len(qo_indptr) - 1
+        if len(kv_indptr) != batch_size + 1:
+            raise ValueError("The kv_indptr length should be equal to mask_indptr length.")
+        # Features of the FlashInfer lineage that the DiT path never enables (the reference's AOT build
+        # only instantiates mask_mode 0, setup.py:38; pos-enc and fp16-qk-reduction are forced off,
+        # csrc/batch_sparseFA_config.inc:42-43):
+        if custom_mask is not None or packed_custom_mask is not None:
+            raise NotImplementedError("flashomni_b200: custom attention masks are not implemented")
+        if causal:
+            raise NotImplementedError("flashomni_b200: causal masking is not implemented (DiT path is non-causal)")
+        if PosEncodingMode[pos_encoding_mode] != PosEncodingMode.NONE:
+            raise NotImplementedError("flashomni_b200: in-kernel positional encoding is not implemented")
+        if logits_soft_cap > 0:
+            raise NotImplementedError("flashomni_b200: logits soft cap is not implemented")
+        if q_data_type != kv_data_type:
+            raise NotImplementedError("flashomni_b200: q and kv must share a dtype")
+        native_dtype(q_data_type)
+        if num_qo_heads != num_kv_heads:
+            raise NotImplementedError("flashomni_b200: grouped-query attention is not implemented")
+        if head_dim_qk != 128 or head_dim_vo != 128:
+            raise NotImplementedError("flashomni_b200: only head_dim 128 is implemented")
+        if sparse_block_size_for_q != 128 or sparse_block_size_for_kv != 128:
+            raise NotImplementedError("flashomni_b200: only 128-row sparse blocks are implemented")
+
+        qo_indptr_host = qo_indptr.to("cpu")
+        kv_indptr_host = kv_indptr.to("cpu")
+        total_num_rows = int(qo_indptr_host[-1])
+
+        if self.is_cuda_graph_enabled:
+            if self._max_total_num_rows is None:
+                self._max_total_num_rows = total_num_rows
+            elif total_num_rows > self._max_total_num_rows:
+                raise ValueError(
+                    "The total number of rows in qo_indptr {} in cuda graph mode cannot "
+                    "exceed the number of rows set during initialization {}.".format(
+                        total_num_rows, self._max_total_num_rows))
+            if batch_size != self._fixed_batch_size:
+                raise ValueError(
+                    "The batch size should be fixed in cudagraph mode, the runtime batch size {} "
+                    " mismatches the batch size set during initialization {}.".format(
+                        batch_size, self._fixed_batch_size))
+            self._qo_indptr_buf.copy_(qo_indptr)
+            self._kv_indptr_buf.copy_(kv_indptr)
+        else:
+            self._qo_indptr_buf = qo_indptr.to(self.device, dtype=torch.int32)
+            self._kv_indptr_buf = kv_indptr.to(self.device, dtype=torch.int32)
+
+        self._cached_q_data_type = q_data_type
+        self._cached_kv_data_type = kv_data_type
+
+        if mask_num_heads is None:
+            mask_num_heads = num_qo_heads
+        if mask_head_begin < 0 or mask_head_begin + num_qo_heads > mask_num_heads:
+            raise ValueError("mask head window out of range")
+
+        ql = (qo_indptr_host[1:] - qo_indptr_host[:-1]).to(torch.int64)
+        kl = (kv_indptr_host[1:] - kv_indptr_host[:-1]).to(torch.int64)
+        if bool((ql < 0).any()) or bool((kl < 0).any()):
+            raise ValueError("indptr arrays must be non-decreasing")
+        nq = (ql + sparse_block_size_for_q - 1) // sparse_block_size_for_q
+        nkv = (kl + sparse_block_size_for_kv - 1) // sparse_block_size_for_kv
+        self._n_cand = int((nq * num_qo_heads).sum())
+        self._max_nkv = int(nkv.max()) if batch_size > 0 else 0
+        self._max_kept = int((nq * nkv * num_qo_heads).sum())
+        self._batch_size = batch_size
+        self._num_qo_heads = num_qo_heads
+        self._num_kv_heads = num_kv_heads
+        self._head_dim = head_dim_qk
+        self._mask_num_heads = mask_num_heads
+        self._mask_head_begin = mask_head_begin
+        self._total_q = total_num_rows
+        self._total_kv = int(kv_indptr_host[-1])
+        self._carve_workspace()
+
+        self._sparse_block_size_for_q = sparse_block_size_for_q
+        self._sparse_block_size_for_kv = sparse_block_size_for_kv
+        self._causal = causal
+        self._pos_encoding_mode = pos_encoding_mode
+        self._use_fp16_qk_reduction = use_fp16_qk_reduction
+        self._logits_soft_cap = logits_soft_cap
+        self._sm_scale = sm_scale
+        self._rope_scale = rope_scale
+        self._rope_theta = rope_theta
+        self._sparse_info_indptr_base = _compute_sparse_info_indptr(
+            self._qo_indptr_buf, num_qo_heads, sparse_block_size_for_q, device=self.device)
+        self._sparse_kv_info_indptr_base = _compute_sparse_kv_info_indptr(
+            self._qo_indptr_buf, self._kv_indptr_buf, num_qo_heads, sparse_block_size_for_q,
+            sparse_block_size_for_kv, device=self.device)
+        self._planned = True
+
+    begin_forward = plan
+
+    def _carve_workspace(self) -> None:
+        """Lays the work lists out in one int32 buffer: counters[4] | status[4] | items | kv_ptr | order |
+        kv_idx | scratch."""
+        lib = _native.load()
+        n, kept = max(self._n_cand, 1), max(self._max_kept, 1)
+        scratch_bytes = lib.fo_mask_compact_scratch_bytes(n, self._max_nkv)
+
+        def al(words):  # 16-byte aligned word counts
+            return (words + 3) // 4 * 4
+
+        offs, cur = {}, 0
+        for name, words in (("counters", 4), ("status", 4), ("items", 4 * n), ("kv_ptr", n + 1), ("order", n),
+                            ("kv_idx", kept), ("scratch", (scratch_bytes + 3) // 4)):
+            offs[name] = cur
+            cur += al(words)
+        need = cur * 4
+        buf = self._int_workspace_buffer
+        if buf is None or buf.numel() * buf.element_size() < need or buf.device != self.device:
+            buf = torch.zeros(need, dtype=torch.uint8, device=self.device)
+            self._int_workspace_buffer = buf
+        words = buf.view(torch.uint8)[: need].view(torch.int32)
+        self._ws = {k: words[v:] for k, v in offs.items()}
+        self._ws_words = words
+        self._ws_offs = offs
+        self._scratch_bytes = scratch_bytes
+
+    # ------------------------------------------------------------------------------------------ run
+    def run(
+        self,
+        q: torch.Tensor,
+        k: torch.Tensor,
+        v: torch.Tensor,
+        sparse_info: torch.Tensor = None,
+        sparse_kv_info: torch.Tensor = None,
+        sparse_info_indptr: torch.Tensor = None,
+        sparse_kv_info_indptr: torch.Tensor = None,
+        is_full: bool = False,
+        *args,
+        out: Optional[torch.Tensor] = None,
+        lse: Optional[torch.Tensor] = None,
+        return_lse: bool = False,
+    ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+        """q [qo_indptr[-1], H, D]; k, v [kv_indptr[-1], H, D] (NHD) or [H, kv_indptr[-1], D] (HND).
+        `sparse_info` / `sparse_kv_info` are the packed uint8 masks and their *byte* indptrs as returned
+        by `segment_packbits(..., bitorder="little")`. q-blocks whose bit is 0 keep the contents of `out`
+        (zeros when `out` is allocated here). Reference: flashomni/attention.py:709-835."""
+        if not self._planned:
+            raise RuntimeError("plan() must be called before run()")
+        _native.require_cuda(q, k, v)
+        _check_cached_qkv_data_type(q, k, self._cached_q_data_type, self._cached_kv_data_type)
+        sm_scale = self._sm_scale
+        if sm_scale is None:
+            sm_scale = 1.0 / math.sqrt(q.size(-1))
+        if q.dim() != 3 or q.size(0) != self._total_q or q.size(1) != self._num_qo_heads or q.size(2) != self._head_dim:
+            raise ValueError(f"q has shape {tuple(q.shape)}, planned [{self._total_q}, {self._num_qo_heads}, {self._head_dim}]")
+        if return_lse:
+            if lse is None:
+                lse = torch.empty((q.size(0), q.size(1)), dtype=torch.float32, device=q.device)
+            else:
+                _check_shape_dtype_device(lse, (q.size(0), q.size(1)), torch.float32, q.device, "lse")
+        if out is None:
+            out = torch.zeros(q.shape[:-1] + v.shape[-1:], dtype=q.dtype, device=q.device)
+        else:
+            _check_shape_dtype_device(out, q.shape[:-1] + v.shape[-1:], q.dtype, q.device, "out")
+        if not is_full:
+            # the reference dereferences null masks here (csrc/batch_sparseFA.cu:123-131); raise instead
+            if sparse_info is None or sparse_kv_info is None or sparse_info_indptr is None \
+                    or sparse_kv_info_indptr is None:
+                raise ValueError("sparse_info, sparse_kv_info and their indptrs are required unless is_full=True")
+            for name, t in (("sparse_info", sparse_info), ("sparse_kv_info", sparse_kv_info)):
+                if t.dtype != torch.uint8 or not t.is_cuda or not t.is_contiguous():
+                    raise ValueError(f"{name} must be a contiguous uint8 CUDA tensor")
+            if len(sparse_info_indptr) != self._batch_size + 1 or len(sparse_kv_info_indptr) != self._batch_size + 1:
+                raise ValueError("mask indptr length must be batch_size + 1")
+            if sparse_info_indptr.dtype != torch.int32:
+                sparse_info_indptr = sparse_info_indptr.to(torch.int32)
+            if sparse_kv_info_indptr.dtype != torch.int32:
+                sparse_kv_info_indptr = sparse_kv_info_indptr.to(torch.int32)
+        if self._kv_layout == "NHD":
+            kn, kh, vn, vh = k.stride(0), k.stride(1), v.stride(0), v.stride(1)
+            total_kv, hkv = k.size(0), k.size(1)
+        else:
+            kh, kn, vh, vn = k.stride(0), k.stride(1), v.stride(0), v.stride(1)
+            total_kv, hkv = k.size(1), k.size(0)
+        if total_kv != self._total_kv or hkv != self._num_kv_heads:
+            raise ValueError("k/v shape does not match the plan")
+        if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or out.stride(2) != 1:
+            raise ValueError("the head dimension of q/k/v/out must be contiguous")
+        if out.stride(1) % 8 != 0 or out.stride(0) % 8 != 0:
+            raise ValueError("out strides must be multiples of 8 elements")
+
+        lib = _native.load()
+        ws = self._ws
+        stream = _native.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            rc = lib.fo_mask_compact(
+                _native.ptr(sparse_info), 0 if sparse_info is None else sparse_info.numel(),
+                _native.ptr(sparse_kv_info), 0 if sparse_kv_info is None else sparse_kv_info.numel(),
+                _native.ptr(sparse_info_indptr), _native.ptr(sparse_kv_info_indptr),
+                _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
+                self._batch_size, self._mask_num_heads, self._mask_head_begin, self._num_qo_heads,
+                self._sparse_block_size_for_q, self._sparse_block_size_for_kv, 1 if is_full else 0,
+                self._n_cand, self._max_nkv, max(self._n_cand, 1), max(self._max_kept, 1),
+                _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
+                _native.ptr(ws["order"]), _native.ptr(ws["counters"]), _native.ptr(ws["scratch"]),
+                self._scratch_bytes, stream)
+            _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper.run (mask compaction)")
+            rc = lib.fo_sparse_attn_fwd(
+                _native.ptr(q), _native.ptr(k), _native.ptr(v), _native.ptr(out), _native.ptr(lse),
+                native_dtype(q.dtype), self._total_q, self._total_kv, self._num_qo_heads, self._num_kv_heads,
+                self._head_dim, q.stride(0), q.stride(1), kn, kh, vn, vh, out.stride(0), out.stride(1),
+                _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
+                self._sparse_block_size_for_q, self._sparse_block_size_for_kv,
+                _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
+                _native.ptr(ws["order"]), _native.ptr(ws["counters"]), max(self._n_cand, 1),
+                self._mask_head_begin, float(sm_scale), _native.ptr(ws["status"]), stream)
+            _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper.run")
+        if _native.debug_checks():
+            self.check_status()
+        return (out, lse) if return_lse else out
+
+    run_return_lse = functools.partialmethod(run, return_lse=True)
+
+    # ------------------------------------------------------------------------------------------ extras
+    def check_status(self) -> None:
+        """Synchronises and raises if the last run() recorded a device-side problem."""
+        w = self._ws_words[:8].cpu()
+        if int(w[2]) != 0 or int(w[4]) != 0:
+            raise RuntimeError(f"flashomni_b200 attention: device status compaction={int(w[2])} kernel={int(w[4])}")
+
+    def work_lists(self) -> dict:
+        """Host copies of the lists of the last run() (synchronises; for tests and FLOP accounting)."""
+        w = self._ws
+        c = w["counters"][:4].cpu()
+        n, kept = int(c[0]), int(c[1])
+        return {
+            "n_items": n, "total_kept": kept, "status": int(c[2]),
+            "items": w["items"][: 4 * n].cpu().view(-1, 4).numpy(),
+            "kv_indptr": w["kv_ptr"][: n + 1].cpu().numpy(),
+            "kv_idx": w["kv_idx"][: kept].cpu().numpy(),
+            "order": w["order"][: n].cpu().numpy(),
+        }
+
+    def forward(self, q, k, v, sparse_info=None, sparse_kv_info=None, sparse_info_indptr=None,
+                sparse_kv_info_indptr=None, is_full: bool = False, causal: bool = False,
+                pos_encoding_mode: str = "NONE", use_fp16_qk_reduction: bool = False,
+                logits_soft_cap: Optional[float] = None, sm_scale: Optional[float] = None,
+                rope_scale: Optional[float] = None, rope_theta: Optional[float] = None) -> torch.Tensor:
+        """Deprecated alias kept for source compatibility (reference: flashomni/attention.py:647-673)."""
+        if causal or pos_encoding_mode != "NONE" or (logits_soft_cap or 0) > 0:
+            raise NotImplementedError("flashomni_b200: causal / pos-encoding / soft-cap are not implemented")
+        self._sm_scale = sm_scale
+        return self.run(q, k, v, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full)
+
+    def forward_return_lse(self, q, k, v, sparse_info=None, sparse_kv_info=None, sparse_info_indptr=None,
+                           sparse_kv_info_indptr=None, is_full: bool = False, causal: bool = False,
+                           pos_encoding_mode: str = "NONE", use_fp16_qk_reduction: bool = False,
+                           logits_soft_cap: Optional[float] = None, sm_scale: Optional[float] = None,
+                           rope_scale: Optional[float] = None, rope_theta: Optional[float] = None):
+        """Deprecated alias (reference: flashomni/attention.py:839-865)."""
+        if causal or pos_encoding_mode != "NONE" or (logits_soft_cap or 0) > 0:
+            raise NotImplementedError("flashomni_b200: causal / pos-encoding / soft-cap are not implemented")
+        self._sm_scale = sm_scale
+        return self.run_return_lse(q, k, v, sparse_info, sparse_kv_info, sparse_info_indptr,
+                                   sparse_kv_info_indptr, is_full)
+
+    def end_forward(self) -> None:
+        """Deprecated, no effect (reference: flashomni/attention.py:867-869)."""
+        pass

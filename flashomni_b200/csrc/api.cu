@@ -1,0 +1,456 @@
+// C ABI of libflashomni_b200.so: argument validation, tensor-map encoding, launches.
+// See include/flashomni_b200.h for the contract of every entry point.
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+
+#include "../../include/flashomni_b200.h"
+#include "internal.h"
+
+namespace fo {
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+int fail_cuda(const char* what, cudaError_t e) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return FO_ERR_CUDA;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+int sm_count() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[5];
+  cuuint32_t bdim[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) gstr[i - 1] = strides_bytes[i];
+  }
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
+                        gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+}  // namespace fo
+
+using namespace fo;
+
+extern "C" {
+
+const char* fo_last_error(void) { return g_last_error.c_str(); }
+int fo_abi_version(void) { return FO_ABI_VERSION; }
+
+// ------------------------------------------------------------------------------------------ packbits
+int fo_packbits(const uint8_t* x, int64_t n, int little, uint8_t* y, void* stream) {
+  if (n < 0) return fail(FO_ERR_INVALID_ARG, "fo_packbits: n < 0");
+  if (n == 0) return FO_OK;
+  if (x == nullptr || y == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_packbits: null pointer");
+  const cudaError_t e = launch_packbits(x, n, little, y, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_packbits", e);
+}
+
+int fo_segment_packbits(const uint8_t* x, const int32_t* indptr, const int32_t* new_indptr, int32_t num_segments,
+                        int64_t out_bytes, int little, uint8_t* y, void* stream) {
+  if (num_segments < 0 || out_bytes < 0) return fail(FO_ERR_INVALID_ARG, "fo_segment_packbits: negative size");
+  if (num_segments == 0 || out_bytes == 0) return FO_OK;
+  if (x == nullptr || y == nullptr || indptr == nullptr || new_indptr == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_segment_packbits: null pointer");
+  const cudaError_t e = launch_segment_packbits(x, indptr, new_indptr, num_segments, out_bytes, little, y,
+                                                static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_segment_packbits", e);
+}
+
+// ------------------------------------------------------------------------------------------ compaction
+size_t fo_mask_compact_scratch_bytes(int64_t n_cand, int32_t max_nkv) {
+  if (n_cand < 0) n_cand = 0;
+  if (max_nkv < 0) max_nkv = 0;
+  // cnt int32[n] | item_pos int32[n] | kv_off int64[n] | hist int32[max_nkv+1], each 16-byte aligned
+  const size_t n = static_cast<size_t>(n_cand);
+  size_t b = 0;
+  b += (n * 4 + 15) & ~static_cast<size_t>(15);
+  b += (n * 4 + 15) & ~static_cast<size_t>(15);
+  b += (n * 8 + 15) & ~static_cast<size_t>(15);
+  b += ((static_cast<size_t>(max_nkv) + 1) * 4 + 15) & ~static_cast<size_t>(15);
+  return b + 16;
+}
+
+int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes, const uint8_t* sparse_kv_info,
+                    int64_t sparse_kv_info_bytes, const int32_t* sparse_info_indptr,
+                    const int32_t* sparse_kv_info_indptr, const int32_t* qo_indptr, const int32_t* kv_indptr,
+                    int32_t batch, int32_t num_heads, int32_t head_begin, int32_t head_count, int32_t sbq,
+                    int32_t sbkv, int32_t is_full, int64_t n_cand, int32_t max_nkv, int64_t max_items,
+                    int64_t max_kept, int32_t* items, int32_t* kv_ptr, int32_t* kv_idx, int32_t* order,
+                    int32_t* counters, void* scratch, size_t scratch_bytes, void* stream) {
+  if (batch <= 0 || num_heads <= 0 || head_count <= 0 || head_begin < 0 || head_begin + head_count > num_heads)
+    return fail(FO_ERR_INVALID_ARG, "fo_mask_compact: bad batch / head window");
+  if (sbq <= 0 || sbkv <= 0) return fail(FO_ERR_INVALID_ARG, "fo_mask_compact: block sizes must be positive");
+  if (qo_indptr == nullptr || kv_indptr == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_mask_compact: null indptr");
+  if (!is_full && (sparse_info == nullptr || sparse_kv_info == nullptr || sparse_info_indptr == nullptr ||
+                   sparse_kv_info_indptr == nullptr))
+    return fail(FO_ERR_INVALID_ARG,
+                "fo_mask_compact: sparse_info / sparse_kv_info / their indptrs are required unless is_full");
+  if (items == nullptr || kv_ptr == nullptr || kv_idx == nullptr || order == nullptr || counters == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_mask_compact: null output");
+  if (n_cand < 0 || max_nkv < 0 || max_items < n_cand || max_kept < 0)
+    return fail(FO_ERR_INVALID_ARG, "fo_mask_compact: capacities must cover n_cand");
+  if (batch > 1024) return fail(FO_ERR_UNSUPPORTED, "fo_mask_compact: batch > 1024");
+  if (scratch == nullptr || scratch_bytes < fo_mask_compact_scratch_bytes(n_cand, max_nkv) || !aligned16(scratch))
+    return fail(FO_ERR_WORKSPACE, "fo_mask_compact: scratch too small or misaligned");
+  CompactArgs a;
+  memset(&a, 0, sizeof(a));
+  a.sparse_info = sparse_info;
+  a.sparse_kv_info = sparse_kv_info;
+  a.info_indptr = sparse_info_indptr;
+  a.kv_info_indptr = sparse_kv_info_indptr;
+  a.qo_indptr = qo_indptr;
+  a.kv_indptr = kv_indptr;
+  a.info_bytes = sparse_info_bytes;
+  a.kv_info_bytes = sparse_kv_info_bytes;
+  a.batch = batch;
+  a.num_heads = num_heads;
+  a.head_begin = head_begin;
+  a.head_count = head_count;
+  a.sbq = sbq;
+  a.sbkv = sbkv;
+  a.is_full = is_full;
+  a.max_nkv = max_nkv;
+  a.n_cand = n_cand;
+  a.max_items = max_items;
+  a.max_kept = max_kept;
+  a.items = items;
+  a.kv_ptr = kv_ptr;
+  a.kv_idx = kv_idx;
+  a.order = order;
+  a.counters = counters;
+  uint8_t* p = static_cast<uint8_t*>(scratch);
+  const size_t n = static_cast<size_t>(n_cand);
+  a.cnt = reinterpret_cast<int32_t*>(p);
+  p += (n * 4 + 15) & ~static_cast<size_t>(15);
+  a.item_pos = reinterpret_cast<int32_t*>(p);
+  p += (n * 4 + 15) & ~static_cast<size_t>(15);
+  a.kv_off = reinterpret_cast<long long*>(p);
+  p += (n * 8 + 15) & ~static_cast<size_t>(15);
+  a.hist = reinterpret_cast<int32_t*>(p);
+  const cudaError_t e = launch_attn_compact(a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_mask_compact", e);
+}
+
+// ------------------------------------------------------------------------------------------ attention
+int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                       int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                       int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                       int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t sbq,
+                       int32_t sbkv, const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx,
+                       const int32_t* order, const int32_t* counters, int64_t max_items, int32_t head_begin,
+                       float sm_scale, int32_t* status, void* stream) {
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: null q/k/v/o");
+  if (qo_indptr == nullptr || kv_indptr == nullptr || items == nullptr || kv_ptr == nullptr ||
+      kv_idx == nullptr || order == nullptr || counters == nullptr || status == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: null work list / indptr / status");
+  if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: bad dtype");
+  if (head_dim != 128) return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: only head_dim 128 is implemented");
+  if (sbq != 128 || sbkv != 128)
+    return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: only 128-row q and kv sparse blocks are implemented");
+  if (num_qo_heads <= 0 || num_kv_heads <= 0 || num_qo_heads % num_kv_heads != 0)
+    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: num_qo_heads must be a multiple of num_kv_heads");
+  if (total_q <= 0 || total_kv <= 0 || max_items <= 0) return FO_OK;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
+    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: q/k/v/o must be 16-byte aligned");
+  const int64_t strides[] = {q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h};
+  for (int64_t s : strides)
+    if (s <= 0 || (s % 8) != 0)
+      return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: strides must be positive multiples of 8 elements");
+
+  AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  {
+    const uint32_t box[3] = {64, 1, 128};
+    const uint64_t qd[3] = {128, static_cast<uint64_t>(num_qo_heads), static_cast<uint64_t>(total_q)};
+    const uint64_t qs[3] = {0, static_cast<uint64_t>(q_stride_h) * 2, static_cast<uint64_t>(q_stride_n) * 2};
+    const uint64_t kd[3] = {128, static_cast<uint64_t>(num_kv_heads), static_cast<uint64_t>(total_kv)};
+    const uint64_t ks[3] = {0, static_cast<uint64_t>(k_stride_h) * 2, static_cast<uint64_t>(k_stride_n) * 2};
+    const uint64_t vs[3] = {0, static_cast<uint64_t>(v_stride_h) * 2, static_cast<uint64_t>(v_stride_n) * 2};
+    int r = encode_tmap_16bit(&a.tmap_q, q, 3, qd, qs, box);
+    if (r == 0) r = encode_tmap_16bit(&a.tmap_k, k, 3, kd, ks, box);
+    if (r == 0) r = encode_tmap_16bit(&a.tmap_v, v, 3, kd, vs, box);
+    if (r != 0) {
+      char buf[96];
+      snprintf(buf, sizeof(buf), "fo_sparse_attn_fwd: cuTensorMapEncodeTiled failed (%d)", r);
+      return fail(FO_ERR_CUDA, buf);
+    }
+  }
+  a.o = o;
+  a.lse = lse;
+  a.o_stride_n = o_stride_n;
+  a.o_stride_h = o_stride_h;
+  a.lse_stride_n = num_qo_heads;
+  a.qo_indptr = qo_indptr;
+  a.kv_indptr = kv_indptr;
+  a.items = items;
+  a.kv_ptr = kv_ptr;
+  a.kv_idx = kv_idx;
+  a.order = order;
+  a.counters = counters;
+  a.head_begin = head_begin;
+  a.group_size = num_qo_heads / num_kv_heads;
+  a.is_bf16 = dtype == FO_DTYPE_BF16;
+  a.sm_scale_log2 = sm_scale * 1.4426950408889634f;
+  a.status = status;
+  int64_t ctas = 2 * static_cast<int64_t>(sm_count());
+  if (ctas > max_items) ctas = max_items;
+  const cudaError_t e = launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_sparse_attn_fwd", e);
+}
+
+// ------------------------------------------------------------------------------------------ GEMMs
+size_t fo_gemm_workspace_bytes(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim) {
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0 || head_dim <= 0) return 64;
+  const size_t mt = static_cast<size_t>(m) / 128, nt = static_cast<size_t>(n) / 128;
+  const size_t rows = static_cast<size_t>(batch) * mt;
+  const size_t lh = static_cast<size_t>(k) / static_cast<size_t>(head_dim);
+  const size_t words_q = 8 + 3 * rows * nt;
+  const size_t words_o = 8 + (rows + 1) + rows * (lh > 0 ? lh : 1) + rows;
+  const size_t words = words_q > words_o ? words_q : words_o;
+  return ((words * 4 + 255) / 256) * 256;
+}
+
+namespace {
+
+struct GemmShape {
+  int32_t batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens;
+};
+
+int check_lists_common(const char* who, const GemmShape& s, bool need_mask, const uint8_t* sparse_info,
+                       const int32_t* indptr, void* ws, size_t ws_bytes) {
+  if (s.batch <= 0 || s.m <= 0 || s.n <= 0 || s.k <= 0) return fail(FO_ERR_INVALID_ARG, std::string(who) + ": empty shape");
+  if (s.m % 128 != 0 || s.n % 128 != 0)
+    return fail(FO_ERR_INVALID_ARG, std::string(who) + ": m and n must be multiples of 128");
+  if (s.num_heads <= 0 || s.head_dim <= 0 || s.head_begin < 0 || s.sparse_q_size <= 0 || s.num_text_tokens < 0)
+    return fail(FO_ERR_INVALID_ARG, std::string(who) + ": bad head / block parameters");
+  if (need_mask && (sparse_info == nullptr || indptr == nullptr))
+    return fail(FO_ERR_INVALID_ARG, std::string(who) + ": sparse_info and sparse_info_indptr are required");
+  if (ws == nullptr || !aligned16(ws) ||
+      ws_bytes < fo_gemm_workspace_bytes(s.batch, s.m, s.n, s.k, s.head_dim))
+    return fail(FO_ERR_WORKSPACE, std::string(who) + ": workspace too small or misaligned");
+  return FO_OK;
+}
+
+GemmListArgs make_list_args(const GemmShape& s, const uint8_t* sparse_info, int64_t info_bytes,
+                            const int32_t* indptr, void* ws) {
+  GemmListArgs a;
+  memset(&a, 0, sizeof(a));
+  a.sparse_info = sparse_info;
+  a.info_indptr = indptr;
+  a.info_bytes = info_bytes;
+  a.batch = s.batch;
+  a.m = s.m;
+  a.n = s.n;
+  a.k = s.k;
+  a.num_heads = s.num_heads;
+  a.head_begin = s.head_begin;
+  a.head_dim = s.head_dim;
+  a.sparse_q_size = s.sparse_q_size;
+  a.num_text_tokens = s.num_text_tokens;
+  int32_t* w = static_cast<int32_t*>(ws);
+  a.counters = w;
+  const int rows = s.batch * (s.m / 128);
+  const int lh = s.k / s.head_dim;
+  a.tiles = w + 8;
+  a.max_tiles = rows * (s.n / 128);
+  a.row_indptr = w + 8;
+  a.row_heads = w + 8 + rows + 1;
+  a.row_order = w + 8 + rows + 1 + rows * (lh > 0 ? lh : 1);
+  return a;
+}
+
+}  // namespace
+
+int fo_gemm_q_worklist(int32_t batch, int32_t m, int32_t n, int32_t num_heads, int32_t head_begin,
+                       int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full,
+                       const uint8_t* sparse_info, int64_t sparse_info_bytes, const int32_t* sparse_info_indptr,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  const GemmShape s = {batch, m, n, head_dim > 0 ? head_dim : 1, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens};
+  int rc = check_lists_common("fo_gemm_q_worklist", s, !is_full, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
+  if (rc != FO_OK) return rc;
+  if (128 % head_dim != 0 && head_dim % 128 != 0)
+    return fail(FO_ERR_UNSUPPORTED, "fo_gemm_q_worklist: head_dim must divide or be a multiple of 128");
+  GemmListArgs a = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
+  a.is_full = is_full;
+  const cudaError_t e = launch_gemm_q_tiles(a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_q_worklist", e);
+}
+
+int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_heads, int32_t head_begin,
+                       int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_for_cache,
+                       const uint8_t* sparse_info, int64_t sparse_info_bytes, const int32_t* sparse_info_indptr,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  const GemmShape s = {batch, m, 128, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens};
+  int rc = check_lists_common("fo_gemm_o_worklist", s, true, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
+  if (rc != FO_OK) return rc;
+  if (k % head_dim != 0) return fail(FO_ERR_INVALID_ARG, "fo_gemm_o_worklist: k must be a multiple of head_dim");
+  GemmListArgs a = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
+  a.is_for_cache = is_for_cache;
+  const cudaError_t e = launch_gemm_o_rows(a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_o_worklist", e);
+}
+
+namespace {
+
+int encode_gemm_maps(const char* who, GemmArgs& g, const void* x, const void* w, int64_t rows_a, int64_t n, int64_t k) {
+  const uint32_t box[2] = {64, 128};
+  const uint64_t ad[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(rows_a)};
+  const uint64_t bd[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+  const uint64_t st[2] = {0, static_cast<uint64_t>(k) * 2};
+  int r = encode_tmap_16bit(&g.tmap_a, x, 2, ad, st, box);
+  if (r == 0) r = encode_tmap_16bit(&g.tmap_b, w, 2, bd, st, box);
+  if (r != 0) {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "%s: cuTensorMapEncodeTiled failed (%d)", who, r);
+    return fail(FO_ERR_CUDA, buf);
+  }
+  return FO_OK;
+}
+
+}  // namespace
+
+int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch, int32_t m,
+              int32_t n, int32_t k, int32_t num_heads, int32_t head_begin, int32_t head_dim,
+              int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full, const uint8_t* sparse_info,
+              int64_t sparse_info_bytes, const int32_t* sparse_info_indptr, void* workspace,
+              size_t workspace_bytes, void* stream) {
+  if (x == nullptr || w == nullptr || y == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_gemm_q: null x/w/y");
+  if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_gemm_q: bad dtype");
+  const GemmShape s = {batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens};
+  int rc = check_lists_common("fo_gemm_q", s, !is_full, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
+  if (rc != FO_OK) return rc;
+  if (k % 64 != 0) return fail(FO_ERR_UNSUPPORTED, "fo_gemm_q: k must be a multiple of 64");
+  if (128 % head_dim != 0 && head_dim % 128 != 0)
+    return fail(FO_ERR_UNSUPPORTED, "fo_gemm_q: head_dim must divide or be a multiple of 128");
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (bias != nullptr && !aligned16(bias)))
+    return fail(FO_ERR_INVALID_ARG, "fo_gemm_q: pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t* wsw = static_cast<int32_t*>(workspace);
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  rc = encode_gemm_maps("fo_gemm_q", g, x, w, static_cast<int64_t>(batch) * m, n, k);
+  if (rc != FO_OK) return rc;
+  cudaError_t e;
+  if (!is_full) {
+    GemmListArgs la = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
+    la.is_full = 0;
+    e = launch_gemm_q_tiles(la, st);
+    if (e != cudaSuccess) return fail_cuda("fo_gemm_q (work list)", e);
+    g.tiles = la.tiles;
+    g.n_tiles_ptr = la.counters;
+  }
+  e = cudaMemsetAsync(wsw + 4, 0, sizeof(int32_t), st);
+  if (e != cudaSuccess) return fail_cuda("fo_gemm_q (status reset)", e);
+  g.y = y;
+  g.init = bias;
+  g.init_mode = bias != nullptr ? kInitBias1D : kInitNone;
+  g.mode = kGemmQ;
+  g.is_bf16 = dtype == FO_DTYPE_BF16;
+  g.batch = batch;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.kb_per_head = 1;
+  g.status = wsw + 4;
+  e = launch_gemm(g, sm_count(), st);
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_q", e);
+}
+
+int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t init_is_full, int32_t dtype,
+              int32_t batch, int32_t m, int32_t n, int32_t k, int32_t num_heads, int32_t head_begin,
+              int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_for_cache,
+              const uint8_t* sparse_info, int64_t sparse_info_bytes, const int32_t* sparse_info_indptr,
+              void* workspace, size_t workspace_bytes, void* stream) {
+  if (x == nullptr || w == nullptr || y == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_gemm_o: null x/w/y");
+  if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_gemm_o: bad dtype");
+  const GemmShape s = {batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens};
+  int rc = check_lists_common("fo_gemm_o", s, true, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
+  if (rc != FO_OK) return rc;
+  if (head_dim % 64 != 0) return fail(FO_ERR_UNSUPPORTED, "fo_gemm_o: head_dim must be a multiple of 64");
+  if (k % head_dim != 0) return fail(FO_ERR_INVALID_ARG, "fo_gemm_o: k must be a multiple of head_dim");
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (init != nullptr && !aligned16(init)))
+    return fail(FO_ERR_INVALID_ARG, "fo_gemm_o: pointers must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t* wsw = static_cast<int32_t*>(workspace);
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  rc = encode_gemm_maps("fo_gemm_o", g, x, w, static_cast<int64_t>(batch) * m, n, k);
+  if (rc != FO_OK) return rc;
+  GemmListArgs la = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
+  la.is_for_cache = is_for_cache;
+  cudaError_t e = launch_gemm_o_rows(la, st);
+  if (e != cudaSuccess) return fail_cuda("fo_gemm_o (work list)", e);
+  e = cudaMemsetAsync(wsw + 4, 0, sizeof(int32_t), st);
+  if (e != cudaSuccess) return fail_cuda("fo_gemm_o (status reset)", e);
+  g.y = y;
+  g.init = init;
+  g.init_mode = init == nullptr ? kInitNone : (init_is_full ? kInitFull : kInitBias1D);
+  g.mode = kGemmO;
+  g.is_bf16 = dtype == FO_DTYPE_BF16;
+  g.batch = batch;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.kb_per_head = head_dim / 64;
+  g.row_indptr = la.row_indptr;
+  g.row_heads = la.row_heads;
+  g.row_order = la.row_order;
+  g.status = wsw + 4;
+  e = launch_gemm(g, sm_count(), st);
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_o", e);
+}
+
+}  // extern "C"

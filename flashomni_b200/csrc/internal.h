@@ -1,0 +1,115 @@
+// Internal declarations shared by the translation units of libflashomni_b200.so.
+// Nothing in this header is part of the C ABI (see include/flashomni_b200.h for that).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace fo {
+
+// ------------------------------------------------------------------ mask path
+struct CompactArgs {
+  const uint8_t* sparse_info;
+  const uint8_t* sparse_kv_info;
+  const int32_t* info_indptr;      // byte offsets per request
+  const int32_t* kv_info_indptr;   // byte offsets per request
+  const int32_t* qo_indptr;        // token offsets per request
+  const int32_t* kv_indptr;
+  int64_t info_bytes;              // readable bytes of sparse_info
+  int64_t kv_info_bytes;           // readable bytes of sparse_kv_info
+  int batch, num_heads, head_begin, head_count, sbq, sbkv, is_full;
+  int max_nkv;                     // upper bound of kv-blocks per request (histogram size - 1)
+  int64_t n_cand;                  // sum_b nq(b) * head_count
+  int64_t max_items, max_kept;     // capacities of the output lists
+  // outputs
+  int32_t* items;                  // [max_items, 4] (b, h, qb, n_kept)
+  int32_t* kv_ptr;                 // [max_items + 1]
+  int32_t* kv_idx;                 // [max_kept]
+  int32_t* order;                  // [max_items]
+  int32_t* counters;               // [4]: n_items, total_kept, status, max_nkv
+  // scratch
+  int32_t* cnt;                    // [n_cand]
+  int32_t* item_pos;               // [n_cand]
+  long long* kv_off;               // [n_cand]
+  int32_t* hist;                   // [max_nkv + 1]
+};
+
+struct GemmListArgs {
+  const uint8_t* sparse_info;
+  const int32_t* info_indptr;
+  int64_t info_bytes;
+  int batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens;
+  int is_full, is_for_cache;
+  int32_t* tiles;                  // GEMM-Q: [max_tiles, 3] (b, iy, ix)
+  int max_tiles;
+  int32_t* row_indptr;             // GEMM-O: [rows + 1]
+  int32_t* row_heads;              // GEMM-O: [rows * local_heads]
+  int32_t* row_order;              // GEMM-O: [rows]
+  int32_t* counters;               // [4]
+};
+
+cudaError_t launch_packbits(const uint8_t* x, int64_t n, int little, uint8_t* y, cudaStream_t stream);
+cudaError_t launch_segment_packbits(const uint8_t* x, const int32_t* indptr, const int32_t* new_indptr,
+                                    int num_segments, int64_t out_bytes, int little, uint8_t* y,
+                                    cudaStream_t stream);
+cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream);
+cudaError_t launch_gemm_q_tiles(const GemmListArgs& a, cudaStream_t stream);
+cudaError_t launch_gemm_o_rows(const GemmListArgs& a, cudaStream_t stream);
+
+// ------------------------------------------------------------------ GEMM
+enum GemmMode : int { kGemmQ = 0, kGemmO = 1 };
+enum GemmInit : int { kInitNone = 0, kInitBias1D = 1, kInitFull = 2 };
+
+struct GemmArgs {
+  CUtensorMap tmap_a;              // X as [batch*m, k], box 64 x 128, 128B swizzle
+  CUtensorMap tmap_b;              // W as [n, k],       box 64 x 128, 128B swizzle
+  void* y;                         // [batch, m, n]
+  const void* init;                // bias [n] or cache [batch, m, n] or null
+  int init_mode;
+  int mode;
+  int is_bf16;
+  int batch, m, n, k;
+  int kb_per_head;                 // GEMM-O: head_dim / 64
+  const int32_t* tiles;            // GEMM-Q work list (b, iy, ix); null = every tile (dense)
+  const int32_t* n_tiles_ptr;      // device count of GEMM-Q tiles
+  const int32_t* row_indptr;       // GEMM-O lists
+  const int32_t* row_heads;
+  const int32_t* row_order;
+  int32_t* status;                 // device status word (DevStatus)
+};
+cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream);
+
+// ------------------------------------------------------------------ attention
+struct AttnArgs {
+  CUtensorMap tmap_q;              // [D, H, Tq]   box 64 x 1 x 128
+  CUtensorMap tmap_k;              // [D, Hkv, Tkv]
+  CUtensorMap tmap_v;
+  void* o;                         // [Tq, H, D] (strides below, in elements)
+  float* lse;                      // [Tq, H] or null
+  int64_t o_stride_n, o_stride_h;
+  int64_t lse_stride_n;
+  const int32_t* qo_indptr;
+  const int32_t* kv_indptr;
+  const int32_t* items;            // (b, h_mask, qb, n_kept)
+  const int32_t* kv_ptr;
+  const int32_t* kv_idx;
+  const int32_t* order;
+  const int32_t* counters;         // counters[0] = n_items
+  int head_begin;                  // tensor head = item head - head_begin
+  int group_size;                  // H / Hkv
+  int is_bf16;
+  float sm_scale_log2;             // sm_scale * log2(e)
+  int32_t* status;
+};
+cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream);
+
+// ------------------------------------------------------------------ host helpers
+// Encodes a tiled tensor map (bf16/f16 elements, 128-byte swizzle). dims/strides innermost first;
+// strides in bytes for dims 1..rank-1. Returns 0 on success.
+int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box);
+
+}  // namespace fo

@@ -1,0 +1,534 @@
+// Mask path: bit packing (packbits / segment_packbits) and the compaction of the packed
+// block masks into the work lists the attention and GEMM kernels consume.
+//
+// Bit layout (same as include/flashomni/attention/prefill.cuh:1284-1294,1385-1394 and
+// include/flashomni/gemm/w16a16/gemm.cuh:50-58 of the reference): per request b the segment starts
+// at byte `indptr[b]`; q-block bit index = qb*H + h; kv-block bit index = (qb*H + h)*nkv + kvb;
+// bit i of a segment = (seg[i >> 3] >> (i & 7)) & 1.
+//
+// All kernels here are integer / byte work bound by HBM and launch latency; they never touch
+// memory outside the extents given (reads are clamped to the packed buffers' byte sizes) and
+// report malformed input through a status word instead of faulting.
+#include "internal.h"
+
+namespace fo {
+
+// ---------------------------------------------------------------------------------------------
+// packbits
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack8(const uint8_t* p, int64_t avail, bool little, bool aligned8) {
+  // Packs up to 8 input bytes (non-zero -> 1). `avail` = number of valid inputs (1..8).
+  uint32_t out = 0;
+  if (aligned8 && avail >= 8) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const uint32_t w[2] = {v.x, v.y};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t byte = (w[i >> 2] >> ((i & 3) * 8)) & 0xFFu;
+      const uint32_t bit = byte != 0u;
+      out |= bit << (little ? i : 7 - i);
+    }
+  } else {
+    const int n = avail < 8 ? static_cast<int>(avail) : 8;
+    for (int i = 0; i < n; ++i) {
+      const uint32_t bit = p[i] != 0;
+      out |= bit << (little ? i : 7 - i);
+    }
+  }
+  return out;
+}
+
+__global__ void packbits_kernel(const uint8_t* __restrict__ x, int64_t n, int little, uint8_t* __restrict__ y) {
+  const int64_t nbytes = (n + 7) >> 3;
+  const bool base_aligned = (reinterpret_cast<uintptr_t>(x) & 7u) == 0;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nbytes;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    y[i] = static_cast<uint8_t>(pack8(x + i * 8, n - i * 8, little != 0, base_aligned));
+  }
+}
+
+// One thread per output byte; the segment of a byte is found by binary search over the byte indptr.
+__global__ void segment_packbits_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ indptr,
+                                        const int32_t* __restrict__ new_indptr, int num_segments,
+                                        int64_t out_bytes, int little, uint8_t* __restrict__ y) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < out_bytes;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int lo = 0, hi = num_segments;  // find seg with new_indptr[seg] <= i < new_indptr[seg+1]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (static_cast<int64_t>(new_indptr[mid]) <= i) lo = mid; else hi = mid;
+    }
+    const int64_t seg_in0 = indptr[lo], seg_in1 = indptr[lo + 1];
+    const int64_t k = i - new_indptr[lo];
+    const int64_t src = seg_in0 + k * 8;
+    const int64_t avail = seg_in1 - src;
+    if (avail <= 0) { y[i] = 0; continue; }
+    const bool aligned = (reinterpret_cast<uintptr_t>(x + src) & 7u) == 0;
+    y[i] = static_cast<uint8_t>(pack8(x + src, avail, little != 0, aligned));
+  }
+}
+
+cudaError_t launch_packbits(const uint8_t* x, int64_t n, int little, uint8_t* y, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  const int64_t nbytes = (n + 7) >> 3;
+  const int threads = 256;
+  int64_t blocks = (nbytes + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  packbits_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(x, n, little, y);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_segment_packbits(const uint8_t* x, const int32_t* indptr, const int32_t* new_indptr,
+                                    int num_segments, int64_t out_bytes, int little, uint8_t* y,
+                                    cudaStream_t stream) {
+  if (out_bytes <= 0 || num_segments <= 0) return cudaSuccess;
+  const int threads = 256;
+  int64_t blocks = (out_bytes + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  segment_packbits_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(x, indptr, new_indptr, num_segments,
+                                                                            out_bytes, little, y);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bit-stream helpers
+// ---------------------------------------------------------------------------------------------
+// 32 bits of the little-endian bit stream `seg` starting at bit `pos`; bytes at or beyond `limit`
+// (the number of readable bytes from `seg`) read as zero.
+__device__ __forceinline__ uint32_t load_bits32(const uint8_t* seg, int64_t pos, int64_t limit) {
+  const int64_t byte0 = pos >> 3;
+  const int sh = static_cast<int>(pos & 7);
+  uint64_t acc = 0;
+#pragma unroll
+  for (int i = 0; i < 5; ++i) {
+    const int64_t bi = byte0 + i;
+    const uint64_t v = (bi < limit) ? seg[bi] : 0u;
+    acc |= v << (8 * i);
+  }
+  return static_cast<uint32_t>(acc >> sh);
+}
+__device__ __forceinline__ int get_bit(const uint8_t* seg, int64_t pos, int64_t limit) {
+  const int64_t bi = pos >> 3;
+  if (bi >= limit) return 0;
+  return (seg[bi] >> (pos & 7)) & 1;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention mask compaction
+// ---------------------------------------------------------------------------------------------
+// Candidate c enumerates (b, qb, hl) in ascending (b, qb, hl) order, hl in [0, head_count).
+struct Cand {
+  int b, qb, h;       // h = head_begin + hl (index used for mask bits)
+  int nq, nkv;
+  bool valid;
+};
+
+constexpr int kMaxBatchSmem = 1024;
+
+// Fills smem prefix of candidates per request. Thread 0 computes (B is small), all read after sync.
+__device__ __forceinline__ void build_cand_prefix(const CompactArgs& a, int64_t* s_prefix) {
+  if (threadIdx.x == 0) {
+    int64_t acc = 0;
+    s_prefix[0] = 0;
+    for (int b = 0; b < a.batch; ++b) {
+      const int64_t ql = static_cast<int64_t>(a.qo_indptr[b + 1]) - a.qo_indptr[b];
+      const int64_t nq = ql > 0 ? (ql + a.sbq - 1) / a.sbq : 0;
+      acc += nq * a.head_count;
+      s_prefix[b + 1] = acc;
+    }
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ Cand decode_cand(const CompactArgs& a, const int64_t* s_prefix, int64_t c) {
+  Cand r;
+  int lo = 0, hi = a.batch;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (s_prefix[mid] <= c) lo = mid; else hi = mid;
+  }
+  r.b = lo;
+  const int64_t local = c - s_prefix[lo];
+  r.qb = static_cast<int>(local / a.head_count);
+  r.h = a.head_begin + static_cast<int>(local % a.head_count);
+  const int64_t ql = static_cast<int64_t>(a.qo_indptr[lo + 1]) - a.qo_indptr[lo];
+  const int64_t kl = static_cast<int64_t>(a.kv_indptr[lo + 1]) - a.kv_indptr[lo];
+  r.nq = static_cast<int>((ql + a.sbq - 1) / a.sbq);
+  r.nkv = kl > 0 ? static_cast<int>((kl + a.sbkv - 1) / a.sbkv) : 0;
+  r.valid = c < s_prefix[a.batch];
+  return r;
+}
+
+// Pass 1: one warp per candidate. cnt[c] = number of kept kv-blocks if the q-block is active, else -1.
+__global__ void compact_count_kernel(CompactArgs a) {
+  __shared__ int64_t s_prefix[kMaxBatchSmem + 1];
+  build_cand_prefix(a, s_prefix);
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_per_grid = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t c = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5); c < a.n_cand;
+       c += warps_per_grid) {
+    const Cand cd = decode_cand(a, s_prefix, c);
+    int result;
+    if (a.is_full) {
+      result = cd.nkv;
+    } else {
+      const int64_t ioff = a.info_indptr[cd.b];
+      const int64_t koff = a.kv_info_indptr[cd.b];
+      const int64_t qbit = static_cast<int64_t>(cd.qb) * a.num_heads + cd.h;
+      const int active = get_bit(a.sparse_info + ioff, qbit, a.info_bytes - ioff);
+      if (!active) {
+        result = -1;
+      } else {
+        const int64_t row0 = qbit * cd.nkv;
+        int cnt = 0;
+        for (int w = lane * 32; w < cd.nkv; w += 32 * 32) {
+          uint32_t bits = load_bits32(a.sparse_kv_info + koff, row0 + w, a.kv_info_bytes - koff);
+          const int rem = cd.nkv - w;
+          if (rem < 32) bits &= (1u << rem) - 1u;
+          cnt += __popc(bits);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+        result = cnt;
+      }
+    }
+    if (lane == 0) a.cnt[c] = result;
+  }
+}
+
+// Pass 2: single CTA. Exclusive scans of the active flags (item index) and of the kept counts
+// (offset into kv_idx), then the longest-first permutation by a stable counting sort.
+__global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a) {
+  __shared__ int s_warp_items[32];
+  __shared__ long long s_warp_kept[32];
+  __shared__ int s_carry_items;
+  __shared__ long long s_carry_kept;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) { s_carry_items = 0; s_carry_kept = 0; }
+  // zero the histogram (one bucket per kept count 0..max_nkv)
+  for (int i = tid; i <= a.max_nkv; i += blockDim.x) a.hist[i] = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < a.n_cand; base += blockDim.x) {
+    const int64_t c = base + tid;
+    const int v = (c < a.n_cand) ? a.cnt[c] : -1;
+    const int flag = v >= 0;
+    const int kept = flag ? v : 0;
+    int xi = flag;
+    long long xk = kept;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int yi = __shfl_up_sync(0xffffffffu, xi, o);
+      const long long yk = __shfl_up_sync(0xffffffffu, xk, o);
+      if (lane >= o) { xi += yi; xk += yk; }
+    }
+    if (lane == 31) { s_warp_items[warp] = xi; s_warp_kept[warp] = xk; }
+    __syncthreads();
+    if (warp == 0) {
+      int wi = s_warp_items[lane];
+      long long wk = s_warp_kept[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int yi = __shfl_up_sync(0xffffffffu, wi, o);
+        const long long yk = __shfl_up_sync(0xffffffffu, wk, o);
+        if (lane >= o) { wi += yi; wk += yk; }
+      }
+      s_warp_items[lane] = wi;  // inclusive over warps
+      s_warp_kept[lane] = wk;
+    }
+    __syncthreads();
+    const int pre_i = s_carry_items + (warp ? s_warp_items[warp - 1] : 0) + xi - flag;
+    const long long pre_k = s_carry_kept + (warp ? s_warp_kept[warp - 1] : 0) + xk - kept;
+    if (c < a.n_cand) {
+      a.item_pos[c] = flag ? pre_i : -1;
+      a.kv_off[c] = pre_k;
+      if (flag) atomicAdd(&a.hist[kept], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      s_carry_items += s_warp_items[31];
+      s_carry_kept += s_warp_kept[31];
+    }
+    __syncthreads();
+  }
+  const int n_items = s_carry_items;
+  const long long total_kept = s_carry_kept;
+  if (tid == 0) {
+    a.counters[0] = n_items;
+    a.counters[1] = static_cast<int>(total_kept > 0x7fffffffLL ? 0x7fffffff : total_kept);
+    a.counters[3] = a.max_nkv;
+    if (total_kept > a.max_kept || n_items > a.max_items) a.counters[2] = kDevBadIndex;
+    a.kv_ptr[n_items <= a.max_items ? n_items : 0] = static_cast<int>(total_kept);
+  }
+  __threadfence_block();
+  __syncthreads();
+  // Bucket starts for descending kept order: start[k] = number of items with kept > k.
+  // Serial suffix scan by one warp in chunks of 32 (max_nkv is a few hundred at most in practice).
+  if (warp == 0) {
+    int carry = 0;
+    for (int hi = a.max_nkv; hi >= 0; hi -= 32) {
+      const int k = hi - lane;
+      const int v = (k >= 0) ? a.hist[k] : 0;
+      int x = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      if (k >= 0) a.hist[k] = carry + x - v;  // exclusive start of bucket k
+      carry += __shfl_sync(0xffffffffu, x, 31);
+    }
+    __syncwarp();
+    // Stable placement: candidates visited in ascending index, 32 at a time.
+    for (int64_t base = 0; base < a.n_cand; base += 32) {
+      const int64_t c = base + lane;
+      const int v = (c < a.n_cand) ? a.cnt[c] : -1;
+      const bool flag = v >= 0;
+      const unsigned grp = __match_any_sync(0xffffffffu, flag ? v : -1 - lane);
+      const int rank_in_grp = __popc(grp & ((1u << lane) - 1u));
+      const int leader = __ffs(grp) - 1;
+      int start = 0;
+      if (flag && lane == leader) {
+        start = a.hist[v];
+        a.hist[v] = start + __popc(grp);
+      }
+      start = __shfl_sync(0xffffffffu, start, leader);
+      if (flag) {
+        const int pos = start + rank_in_grp;
+        if (pos < a.max_items) a.order[pos] = a.item_pos[c];
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// Pass 3: one warp per candidate; writes the item record and expands its kept kv-blocks (ascending).
+__global__ void compact_fill_kernel(CompactArgs a) {
+  __shared__ int64_t s_prefix[kMaxBatchSmem + 1];
+  build_cand_prefix(a, s_prefix);
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_per_grid = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t c = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5); c < a.n_cand;
+       c += warps_per_grid) {
+    const int pos = a.item_pos[c];
+    if (pos < 0 || pos >= a.max_items) continue;
+    const Cand cd = decode_cand(a, s_prefix, c);
+    const long long off = a.kv_off[c];
+    const int kept = a.cnt[c];
+    if (off + kept > a.max_kept) continue;  // flagged by the scan pass
+    if (lane == 0) {
+      a.items[4 * pos + 0] = cd.b;
+      a.items[4 * pos + 1] = cd.h;
+      a.items[4 * pos + 2] = cd.qb;
+      a.items[4 * pos + 3] = kept;
+      a.kv_ptr[pos] = static_cast<int>(off);
+    }
+    int written = 0;
+    if (a.is_full) {
+      for (int j = lane; j < cd.nkv; j += 32) a.kv_idx[off + j] = j;
+    } else {
+      const int64_t koff = a.kv_info_indptr[cd.b];
+      const int64_t row0 = (static_cast<int64_t>(cd.qb) * a.num_heads + cd.h) * cd.nkv;
+      for (int w0 = 0; w0 < cd.nkv; w0 += 32 * 32) {
+        const int w = w0 + lane * 32;
+        uint32_t bits = 0;
+        if (w < cd.nkv) {
+          bits = load_bits32(a.sparse_kv_info + koff, row0 + w, a.kv_info_bytes - koff);
+          const int rem = cd.nkv - w;
+          if (rem < 32) bits &= (1u << rem) - 1u;
+        }
+        const int pc = __popc(bits);
+        int x = pc;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, x, o);
+          if (lane >= o) x += y;
+        }
+        int dst = written + x - pc;
+        while (bits) {
+          const int bpos = __ffs(bits) - 1;
+          bits &= bits - 1;
+          a.kv_idx[off + dst++] = w + bpos;
+        }
+        written += __shfl_sync(0xffffffffu, x, 31);
+      }
+    }
+  }
+}
+
+cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
+  if (a.batch > kMaxBatchSmem) return cudaErrorInvalidValue;
+  if (a.n_cand <= 0) {
+    return cudaMemsetAsync(a.counters, 0, 4 * sizeof(int), stream);
+  }
+  const int threads = 256, wpb = threads / 32;
+  int64_t blocks = (a.n_cand + wpb - 1) / wpb;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  cudaError_t e = cudaMemsetAsync(a.counters, 0, 4 * sizeof(int), stream);
+  if (e != cudaSuccess) return e;
+  compact_count_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(a);
+  compact_scan_kernel<<<1, 1024, 0, stream>>>(a);
+  compact_fill_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// GEMM work lists (single CTA: the candidate counts are a few thousand at most)
+// ---------------------------------------------------------------------------------------------
+// GEMM-Q: ascending list of active (b, iy, ix) tiles; count in counters[0].
+__global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) s_carry = 0;
+  __syncthreads();
+  const int mt = a.m / 128, nt = a.n / 128;
+  const int64_t n_cand = static_cast<int64_t>(a.batch) * mt * nt;
+  for (int64_t base = 0; base < n_cand; base += blockDim.x) {
+    const int64_t c = base + tid;
+    int flag = 0, b = 0, iy = 0, ix = 0;
+    if (c < n_cand) {
+      b = static_cast<int>(c / (static_cast<int64_t>(mt) * nt));
+      const int rem = static_cast<int>(c % (static_cast<int64_t>(mt) * nt));
+      iy = rem / nt;
+      ix = rem % nt;
+      if (a.is_full) {
+        flag = 1;
+      } else {
+        const int64_t ioff = a.info_indptr[b];
+        const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
+        const int64_t bit = qb * a.num_heads + a.head_begin + (ix * 128) / a.head_dim;
+        flag = get_bit(a.sparse_info + ioff, bit, a.info_bytes - ioff);
+      }
+    }
+    int x = flag;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) s_warp[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    const int pos = s_carry + (warp ? s_warp[warp - 1] : 0) + x - flag;
+    if (flag && pos < a.max_tiles) {
+      a.tiles[3 * pos + 0] = b;
+      a.tiles[3 * pos + 1] = iy;
+      a.tiles[3 * pos + 2] = ix;
+    }
+    __syncthreads();
+    if (tid == 0) s_carry += s_warp[31];
+    __syncthreads();
+  }
+  if (tid == 0) {
+    a.counters[0] = s_carry;
+    a.counters[1] = 0;
+    a.counters[2] = s_carry > a.max_tiles ? kDevBadIndex : kDevOk;
+  }
+}
+
+// GEMM-O: per 128-row block the ascending list of selected local heads, plus the row blocks sorted
+// by descending list length (stable). counters[0] = number of row blocks, counters[1] = total heads.
+__global__ void __launch_bounds__(1024) gemm_o_rows_kernel(GemmListArgs a) {
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  extern __shared__ int s_hist[];  // local_heads + 2 buckets
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int mt = a.m / 128;
+  const int rows = a.batch * mt;
+  const int local_heads = a.k / a.head_dim;
+  const int want = a.is_for_cache ? 0 : 1;
+  if (tid == 0) s_carry = 0;
+  for (int i = tid; i <= local_heads; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  for (int base = 0; base < rows; base += blockDim.x) {
+    const int r = base + tid;
+    int cnt = 0;
+    if (r < rows) {
+      const int b = r / mt, iy = r % mt;
+      const int64_t ioff = a.info_indptr[b];
+      const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
+      const int64_t bit0 = qb * a.num_heads + a.head_begin;
+      for (int h = 0; h < local_heads; ++h)
+        cnt += get_bit(a.sparse_info + ioff, bit0 + h, a.info_bytes - ioff) == want;
+    }
+    int x = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) s_warp[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    const int off = s_carry + (warp ? s_warp[warp - 1] : 0) + x - cnt;
+    if (r < rows) {
+      a.row_indptr[r] = off;
+      atomicAdd(&s_hist[cnt], 1);
+      const int b = r / mt, iy = r % mt;
+      const int64_t ioff = a.info_indptr[b];
+      const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
+      const int64_t bit0 = qb * a.num_heads + a.head_begin;
+      int w = off;
+      for (int h = 0; h < local_heads; ++h)
+        if (get_bit(a.sparse_info + ioff, bit0 + h, a.info_bytes - ioff) == want) a.row_heads[w++] = h;
+    }
+    __syncthreads();
+    if (tid == 0) s_carry += s_warp[31];
+    __syncthreads();
+  }
+  if (tid == 0) {
+    a.row_indptr[rows] = s_carry;
+    a.counters[0] = rows;
+    a.counters[1] = s_carry;
+    a.counters[2] = kDevOk;
+    // bucket starts, descending count
+    int acc = 0;
+    for (int k = local_heads; k >= 0; --k) { const int v = s_hist[k]; s_hist[k] = acc; acc += v; }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    for (int base = 0; base < rows; base += 32) {
+      const int r = base + lane;
+      const bool ok = r < rows;
+      const int cnt = ok ? (a.row_indptr[r + 1] - a.row_indptr[r]) : -1 - lane;
+      const unsigned grp = __match_any_sync(0xffffffffu, cnt);
+      const int rank = __popc(grp & ((1u << lane) - 1u));
+      const int leader = __ffs(grp) - 1;
+      int start = 0;
+      if (ok && lane == leader) { start = s_hist[cnt]; s_hist[cnt] = start + __popc(grp); }
+      start = __shfl_sync(0xffffffffu, start, leader);
+      if (ok) a.row_order[start + rank] = r;
+      __syncwarp();
+    }
+  }
+}
+
+cudaError_t launch_gemm_q_tiles(const GemmListArgs& a, cudaStream_t stream) {
+  gemm_q_tiles_kernel<<<1, 1024, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t launch_gemm_o_rows(const GemmListArgs& a, cudaStream_t stream) {
+  const int local_heads = a.k / a.head_dim;
+  gemm_o_rows_kernel<<<1, 1024, (local_heads + 2) * sizeof(int), stream>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace fo

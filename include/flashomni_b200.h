@@ -1,0 +1,154 @@
+/*
+ * flashomni_b200 -- C ABI of the B200 (sm_100a) sparse-DiT hot path.
+ *
+ * One entry point per native op that the reference binds under torch.ops.flashomni_kernels
+ * (csrc/flashomni_ops.cu:20-68), plus the mask-compaction step that replaces the reference's
+ * in-kernel bit scanning. Conventions:
+ *   - plain pointers and sizes only; every pointer that is not marked "host" is a DEVICE pointer
+ *     owned by the caller; nothing here allocates or frees device memory;
+ *   - the caller selects the device (cudaSetDevice / a torch device guard) before the call;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and no call
+ *     synchronises the device;
+ *   - return value: FO_OK or an error code; fo_last_error() returns a thread-local message;
+ *   - malformed device-side data (bad indptr, list overflow, a wait that ran out) never faults:
+ *     the kernels record a code in the status word the call was given (see each function).
+ *   - dtype: FO_DTYPE_F16 or FO_DTYPE_BF16 (inputs and outputs share it; accumulation is fp32).
+ *
+ * Bit layout of the packed masks (reference: include/flashomni/attention/prefill.cuh:1284-1294,
+ * 1385-1394; include/flashomni/gemm/w16a16/gemm.cuh:50-58): request b's segment starts at byte
+ * indptr[b]; q-block bit = qb*H + h; kv-block bit = (qb*H + h)*nkv + kvb; bit i = (seg[i>>3] >> (i&7)) & 1.
+ */
+#ifndef FLASHOMNI_B200_H_
+#define FLASHOMNI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FO_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define FO_API __attribute__((visibility("default")))
+#else
+#define FO_API
+#endif
+
+enum {
+  FO_OK = 0,
+  FO_ERR_INVALID_ARG = 1,  /* null / misaligned / inconsistent argument (the reference TORCH_CHECKs) */
+  FO_ERR_UNSUPPORTED = 2,  /* shape or dtype outside what this build implements */
+  FO_ERR_CUDA = 3,         /* a CUDA runtime / driver call failed; message has the CUDA error string */
+  FO_ERR_WORKSPACE = 4     /* workspace / scratch too small */
+};
+enum { FO_DTYPE_F16 = 0, FO_DTYPE_BF16 = 1 };
+
+/* Device status codes (written into status words by the kernels). */
+enum { FO_DEV_OK = 0, FO_DEV_WAIT_TIMEOUT = 1, FO_DEV_BAD_INDEX = 2 };
+
+/* Thread-local description of the last error returned on this thread ("" if none). */
+FO_API const char* fo_last_error(void);
+FO_API int fo_abi_version(void);
+
+/* ---- mask packing -------------------------------------------------------------------------
+ * Replaces torch.ops.flashomni_kernels.packbits / segment_packbits (csrc/flashomni_ops.cu:46-51,
+ * csrc/quantization.cu:24-57; kernels include/flashomni/quantization.cuh:39-109).
+ * x: n bytes, non-zero = 1. y: (n+7)/8 bytes. little != 0 selects bitorder="little". */
+FO_API int fo_packbits(const uint8_t* x, int64_t n, int little, uint8_t* y, void* stream);
+/* indptr / new_indptr: int32 [num_segments+1] (element and byte offsets); out_bytes = new_indptr[-1]
+ * as known to the host (flashomni/quantization.py:148-152). */
+FO_API int fo_segment_packbits(const uint8_t* x, const int32_t* indptr, const int32_t* new_indptr,
+                        int32_t num_segments, int64_t out_bytes, int little, uint8_t* y, void* stream);
+
+/* ---- attention mask compaction (new step; no counterpart op in the reference, which re-reads
+ * the bits in the kernel: prefill.cuh:1284-1294,1380-1460) -------------------------------------
+ * Turns the packed masks into work lists, restricted to heads [head_begin, head_begin+head_count):
+ *   items   int32 [max_items,4]  (b, h, qb, n_kept) of every active q-block, ascending (b, qb, h)
+ *   kv_ptr  int32 [max_items+1]  offsets into kv_idx
+ *   kv_idx  int32 [max_kept]     ascending kept kv-block indices per item
+ *   order   int32 [max_items]    item indices by descending n_kept (stable): the schedule
+ *   counters int32 [4]           n_items, total_kept, status (FO_DEV_*), max_nkv
+ * n_cand = sum over requests of ceil(qo_len/sbq)*head_count and max_nkv = max ceil(kv_len/sbkv) are
+ * host-known (plan time). is_full != 0 ignores the masks (they may be null). scratch must hold
+ * fo_mask_compact_scratch_bytes(n_cand, max_nkv) bytes. */
+FO_API size_t fo_mask_compact_scratch_bytes(int64_t n_cand, int32_t max_nkv);
+FO_API int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes, const uint8_t* sparse_kv_info,
+                    int64_t sparse_kv_info_bytes, const int32_t* sparse_info_indptr,
+                    const int32_t* sparse_kv_info_indptr, const int32_t* qo_indptr, const int32_t* kv_indptr,
+                    int32_t batch, int32_t num_heads, int32_t head_begin, int32_t head_count, int32_t sbq,
+                    int32_t sbkv, int32_t is_full, int64_t n_cand, int32_t max_nkv, int64_t max_items,
+                    int64_t max_kept, int32_t* items, int32_t* kv_ptr, int32_t* kv_idx, int32_t* order,
+                    int32_t* counters, void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- block-sparse attention ------------------------------------------------------------------
+ * Replaces torch.ops.flashomni_kernels.batch_sparseFA_with_ragged_kv_run
+ * (csrc/batch_sparseFA.cu:67-201 -> include/flashomni/attention/prefill.cuh:1203-1636), consuming
+ * the work lists of fo_mask_compact. q [total_q, Hq, D], k/v [total_kv, Hkv, D], o [total_q, Hq, D]
+ * with element strides (row, head); the innermost dimension is contiguous. lse (optional, may be
+ * null): float32 [total_q, Hq], base 2. Hq here is the number of heads IN THE TENSORS; item head
+ * indices are mask heads and map to tensor head (h - head_begin). q-blocks that are not listed are
+ * not written. status: int32 device word, set to FO_DEV_WAIT_TIMEOUT if a bounded wait ran out.
+ * This build implements D = 128 with 128-row q and kv blocks. */
+FO_API int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                       int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                       int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                       int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr,
+                       int32_t sbq, int32_t sbkv, const int32_t* items, const int32_t* kv_ptr,
+                       const int32_t* kv_idx, const int32_t* order, const int32_t* counters,
+                       int64_t max_items, int32_t head_begin, float sm_scale, int32_t* status,
+                       void* stream);
+
+/* ---- GEMM-Q / GEMM-O ---------------------------------------------------------------------------
+ * Workspace (device, caller-owned, 16-byte aligned) of fo_gemm_workspace_bytes(...) bytes, laid out
+ * as int32 words: [0..3] counters (count, aux, list status, 0), [4] kernel status (FO_DEV_*),
+ * [8...] the work list built from the mask. */
+FO_API size_t fo_gemm_workspace_bytes(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim);
+
+/* Replaces torch.ops.flashomni_kernels.flashomni_gemm (csrc/gemm.cu:24-59 ->
+ * include/flashomni/gemm/w16a16/gemm.cuh:27-357). x [batch, m, k], w [n, k], y [batch, m, n], all
+ * contiguous; bias [n] or null. Output tile (iy, ix) of batch b is computed iff is_full or bit
+ * ((num_text_tokens + iy*128)/sparse_q_size)*num_heads + head_begin + (ix*128)/head_dim of b's
+ * segment is 1; other tiles of y are left untouched. head_dim = n/num_heads in the reference
+ * (pass that, with head_begin = 0, for the reference behaviour). m, n multiples of 128; k of 64. */
+FO_API int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch,
+              int32_t m, int32_t n, int32_t k, int32_t num_heads, int32_t head_begin, int32_t head_dim,
+              int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full, const uint8_t* sparse_info,
+              int64_t sparse_info_bytes, const int32_t* sparse_info_indptr, void* workspace,
+              size_t workspace_bytes, void* stream);
+
+/* Replaces torch.ops.flashomni_kernels.flashomni_gemm_reduction (csrc/gemm_reduction.cu:24-57 ->
+ * include/flashomni/gemm/w16a16/gemm_reduction.cuh:27-406). Every tile of y is written:
+ * y = init + sum over selected heads h of x[:, :, h*head_dim:(h+1)*head_dim] w[:, same]^T, selected =
+ * bit 1 (is_for_cache = 0) or bit 0 (is_for_cache != 0) of bit ((num_text_tokens + iy*128)/
+ * sparse_q_size)*num_heads + head_begin + h. init: null, or bias [n] (init_is_full = 0), or the cached
+ * tensor [batch, m, n] (init_is_full != 0). head_dim = n/num_heads in the reference; k/head_dim local
+ * heads are visited. m, n multiples of 128; head_dim a multiple of 64. */
+FO_API int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t init_is_full, int32_t dtype,
+              int32_t batch, int32_t m, int32_t n, int32_t k, int32_t num_heads, int32_t head_begin,
+              int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_for_cache,
+              const uint8_t* sparse_info, int64_t sparse_info_bytes, const int32_t* sparse_info_indptr,
+              void* workspace, size_t workspace_bytes, void* stream);
+
+/* The list builders that fo_gemm_q / fo_gemm_o run first (exposed so that the lists can be checked
+ * bit for bit). They fill the same workspace layout: GEMM-Q: words [8 + 3*i ..] = (b, iy, ix) of the
+ * i-th active tile, counters[0] = tile count. GEMM-O with R = batch*m/128 row blocks and
+ * L = k/head_dim local heads: words [8 .. 8+R] row_indptr, then [8+R+1 ..] row_heads (R*L words
+ * reserved), then row_order (R words): row blocks by descending list length (stable). */
+FO_API int fo_gemm_q_worklist(int32_t batch, int32_t m, int32_t n, int32_t num_heads, int32_t head_begin,
+                       int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full,
+                       const uint8_t* sparse_info, int64_t sparse_info_bytes,
+                       const int32_t* sparse_info_indptr, void* workspace, size_t workspace_bytes,
+                       void* stream);
+FO_API int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_heads, int32_t head_begin,
+                       int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens,
+                       int32_t is_for_cache, const uint8_t* sparse_info, int64_t sparse_info_bytes,
+                       const int32_t* sparse_info_indptr, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHOMNI_B200_H_ */

@@ -1,0 +1,189 @@
+"""CPU oracle (test infrastructure): bit packing, bit addressing and the canonical outputs of
+the mask-compaction step. Integer work only; every comparison against it is bit-exact.
+
+Follows:
+  * packbits / segment_packbits: flashomni/quantization.py:68-159 (same semantics as numpy.packbits;
+    per-segment packing, padding bits of a segment's last byte are zero, new indptr = cumsum of
+    ceil(len/8) bytes, :148-152).
+  * bit addressing used by all three kernels: include/flashomni/attention/prefill.cuh:1284-1294
+    (q-block bit `qb*H + h`), :1385-1394 (kv-block bit `(qb*H + h)*nkv + kvb`),
+    include/flashomni/gemm/w16a16/gemm.cuh:50-58 and gemm_reduction.cuh:128-145 (GEMM row block ->
+    q-block `(num_text_tokens + iy*128) // sparse_q_size`). Bits are little-endian inside a byte.
+  * unpacked indptrs: flashomni/attention.py:165-191.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+
+def packbits(x: np.ndarray, bitorder: str = "big") -> np.ndarray:
+    """flashomni/quantization.py:68-99."""
+    if bitorder not in ("big", "little"):
+        raise ValueError("bitorder must be 'big' or 'little'")
+    x = np.asarray(x).reshape(-1)
+    return np.packbits(x.astype(bool), bitorder=bitorder)
+
+
+def segment_packbits(x: np.ndarray, indptr: np.ndarray, bitorder: str = "big"):
+    """flashomni/quantization.py:102-159. Returns (packed uint8, new byte indptr int32)."""
+    if bitorder not in ("big", "little"):
+        raise ValueError("bitorder must be 'big' or 'little'")
+    x = np.asarray(x).reshape(-1)
+    indptr = np.asarray(indptr, dtype=np.int64)
+    seglen = indptr[1:] - indptr[:-1]
+    packed_len = (seglen + 7) // 8
+    new_indptr = np.zeros(len(indptr), dtype=np.int64)
+    new_indptr[1:] = np.cumsum(packed_len)
+    out = np.zeros(int(new_indptr[-1]), dtype=np.uint8)
+    for i in range(len(indptr) - 1):
+        seg = x[indptr[i]:indptr[i + 1]].astype(bool)
+        out[new_indptr[i]:new_indptr[i + 1]] = np.packbits(seg, bitorder=bitorder)
+    return out, new_indptr.astype(np.int32)
+
+
+def sparse_info_indptr(qo_indptr, num_heads: int, sbq: int) -> np.ndarray:
+    """Unpacked (bit-count) indptr of `sparse_info`: flashomni/attention.py:165-176."""
+    qo = np.asarray(qo_indptr, dtype=np.int64)
+    nq = -(-(qo[1:] - qo[:-1]) // sbq)
+    out = np.zeros(len(qo), dtype=np.int64)
+    out[1:] = np.cumsum(nq * num_heads)
+    return out
+
+
+def sparse_kv_info_indptr(qo_indptr, kv_indptr, num_heads: int, sbq: int, sbkv: int) -> np.ndarray:
+    """Unpacked (bit-count) indptr of `sparse_kv_info`: flashomni/attention.py:178-191."""
+    qo = np.asarray(qo_indptr, dtype=np.int64)
+    kv = np.asarray(kv_indptr, dtype=np.int64)
+    nq = -(-(qo[1:] - qo[:-1]) // sbq)
+    nkv = -(-(kv[1:] - kv[:-1]) // sbkv)
+    out = np.zeros(len(qo), dtype=np.int64)
+    out[1:] = np.cumsum(nq * nkv * num_heads)
+    return out
+
+
+def get_bit(seg: np.ndarray, i: int) -> int:
+    """Little-endian bit i of a packed segment (prefill.cuh:1288-1290)."""
+    return (int(seg[i >> 3]) >> (i & 7)) & 1
+
+
+def unpack_segment(packed: np.ndarray, byte_off: int, nbits: int) -> np.ndarray:
+    nbytes = (nbits + 7) // 8
+    seg = np.asarray(packed[byte_off:byte_off + nbytes], dtype=np.uint8)
+    return np.unpackbits(seg, bitorder="little")[:nbits]
+
+
+def unpack_masks(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr, kv_indptr,
+                 num_heads: int, sbq: int, sbkv: int):
+    """Per request b: (q_active[nq, H], kv_kept[nq, H, nkv]) as uint8 arrays, decoded from the packed
+    byte streams with the byte indptrs (the form the kernels receive)."""
+    qo = np.asarray(qo_indptr, dtype=np.int64)
+    kv = np.asarray(kv_indptr, dtype=np.int64)
+    out = []
+    for b in range(len(qo) - 1):
+        nq = int(-(-(qo[b + 1] - qo[b]) // sbq))
+        nkv = int(-(-(kv[b + 1] - kv[b]) // sbkv))
+        qa = unpack_segment(sparse_info, int(info_indptr[b]), nq * num_heads).reshape(nq, num_heads)
+        kk = unpack_segment(sparse_kv_info, int(kv_info_indptr[b]), nq * num_heads * nkv)
+        out.append((qa, kk.reshape(nq, num_heads, nkv)))
+    return out
+
+
+def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr, kv_indptr,
+            num_heads: int, sbq: int, sbkv: int, head_begin: int = 0, head_count: int | None = None,
+            is_full: bool = False):
+    """Canonical outputs of the attention mask-compaction step (the work lists the CUDA attention
+    kernel consumes).
+
+    Returns a dict of numpy arrays:
+      items      int32 [n, 4]  (b, h, qb, n_kept) for every active (b, qb, h) with h in the head window,
+                               ascending in (b, qb, h)
+      kv_indptr  int32 [n+1]   offsets of each item's kept list inside kv_idx
+      kv_idx     int32 [total] ascending kept kv-block indices of each item
+      order      int32 [n]     item indices sorted by n_kept descending, ties in ascending item index
+                               (the scheduling permutation: longest first)
+    With `is_full` every q-block is active and every kv-block kept (prefill.cuh:1284,1383,1434).
+    """
+    if head_count is None:
+        head_count = num_heads - head_begin
+    qo = np.asarray(qo_indptr, dtype=np.int64)
+    kv = np.asarray(kv_indptr, dtype=np.int64)
+    B = len(qo) - 1
+    items, kv_ptr, kv_idx = [], [0], []
+    for b in range(B):
+        nq = int(-(-(qo[b + 1] - qo[b]) // sbq))
+        nkv = int(-(-(kv[b + 1] - kv[b]) // sbkv))
+        if is_full:
+            qa = np.ones((nq, num_heads), dtype=np.uint8)
+            kk = np.ones((nq, num_heads, nkv), dtype=np.uint8)
+        else:
+            qa = unpack_segment(sparse_info, int(info_indptr[b]), nq * num_heads).reshape(nq, num_heads)
+            kk = unpack_segment(sparse_kv_info, int(kv_info_indptr[b]),
+                                nq * num_heads * nkv).reshape(nq, num_heads, nkv)
+        for qb in range(nq):
+            for h in range(head_begin, head_begin + head_count):
+                if qa[qb, h]:
+                    kept = np.nonzero(kk[qb, h])[0]
+                    items.append((b, h, qb, len(kept)))
+                    kv_idx.extend(int(v) for v in kept)
+                    kv_ptr.append(len(kv_idx))
+    items_a = np.asarray(items, dtype=np.int32).reshape(-1, 4)
+    n_kept = items_a[:, 3] if len(items) else np.zeros(0, dtype=np.int32)
+    order = np.argsort(-n_kept.astype(np.int64), kind="stable").astype(np.int32)
+    return {
+        "items": items_a,
+        "kv_indptr": np.asarray(kv_ptr, dtype=np.int32),
+        "kv_idx": np.asarray(kv_idx, dtype=np.int32),
+        "order": order,
+    }
+
+
+def gemm_q_tiles(sparse_info, info_indptr, batch: int, m: int, n: int, num_heads: int,
+                 sparse_q_size: int = 128, num_text_tokens: int = 0, is_full: bool = False,
+                 head_begin: int = 0, head_dim: int | None = None) -> np.ndarray:
+    """Active 128x128 output tiles of GEMM-Q as int32 [n_tiles, 3] = (b, iy, ix), ascending.
+    Tile (iy, ix) of batch b is active iff bit `qb*H + head_begin + (ix*128)//head_dim` of b's segment
+    is 1, `qb = (num_text_tokens + iy*128)//sparse_q_size`, `head_dim = N//H` unless given
+    (gemm.cuh:50-58, csrc/gemm.cu:26-30)."""
+    if head_dim is None:
+        head_dim = n // num_heads
+    tiles = []
+    for b in range(batch):
+        for iy in range(m // 128):
+            qb = (num_text_tokens + iy * 128) // sparse_q_size
+            for ix in range(n // 128):
+                if is_full:
+                    tiles.append((b, iy, ix))
+                    continue
+                bit = qb * num_heads + head_begin + (ix * 128) // head_dim
+                seg = sparse_info[int(info_indptr[b]):]
+                if get_bit(seg, bit):
+                    tiles.append((b, iy, ix))
+    return np.asarray(tiles, dtype=np.int32).reshape(-1, 3)
+
+
+def gemm_o_rows(sparse_info, info_indptr, batch: int, m: int, k: int, num_heads: int,
+                sparse_q_size: int = 128, num_text_tokens: int = 0, is_for_cache: bool = False,
+                head_begin: int = 0, head_dim: int | None = None):
+    """Per 128-row block (b, iy) of GEMM-O: ascending list of the local heads whose K-slice is
+    accumulated. Head h (local index, global = head_begin + h) is selected iff its bit equals 1
+    (`is_for_cache=False`) or 0 (`is_for_cache=True`), gemm_reduction.cuh:128-145,199-218.
+    Returns (row_indptr int32[R+1], row_heads int32[...], order int32[R]) with R = batch*m/128 and
+    `order` = row blocks by descending list length, ties ascending."""
+    if head_dim is None:
+        head_dim = k // num_heads
+    local_heads = k // head_dim
+    indptr, heads = [0], []
+    for b in range(batch):
+        seg = sparse_info[int(info_indptr[b]):]
+        for iy in range(m // 128):
+            qb = (num_text_tokens + iy * 128) // sparse_q_size
+            for h in range(local_heads):
+                bit = get_bit(seg, qb * num_heads + head_begin + h)
+                if bit == (0 if is_for_cache else 1):
+                    heads.append(h)
+            indptr.append(len(heads))
+    indptr_a = np.asarray(indptr, dtype=np.int32)
+    cnt = (indptr_a[1:] - indptr_a[:-1]).astype(np.int64)
+    order = np.argsort(-cnt, kind="stable").astype(np.int32)
+    return indptr_a, np.asarray(heads, dtype=np.int32), order

@@ -1,0 +1,132 @@
+"""GPU: block-sparse attention through the wrapper against the fp32 oracle."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import flashomni_b200 as fo
+from flashomni_b200 import workloads as wl
+from oracle import attention as oa
+from helpers import assert_close_bf16, dev, masks_to_device
+
+pytestmark = pytest.mark.gpu
+
+
+def _wrapper(device, qo, kv, H, dtype=torch.bfloat16, layout="NHD", **kw):
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=device), layout)
+    w.plan(dev(np.asarray(qo, np.int32), device), dev(np.asarray(kv, np.int32), device), H, H, 128,
+           q_data_type=dtype, **kw)
+    return w
+
+
+def _run(device, w, q, k, v, m, **kw):
+    si, skv, ip, kp = masks_to_device(m, device)
+    r = w.run(dev(q, device), dev(k, device), dev(v, device), si, skv, ip, kp, **kw)
+    w.check_status()
+    return r
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("seq,H,density", [(128, 1, 1.0), (256, 2, 1.0), (512, 2, 0.6), (1024, 4, 0.5)])
+def test_small_uniform(cuda_device, dtype, seq, H, density):
+    inp = wl.attention_inputs(1, H, seq, 128, density, seed=40 + seq, dtype=dtype)
+    w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, H, dtype)
+    prior = wl.randn_bf16(inp.q.shape, 99, dtype=dtype)
+    out = dev(prior, cuda_device).clone()
+    o = _run(cuda_device, w, inp.q, inp.k, inp.v, inp.masks, out=out)
+    m = inp.masks
+    ref = oa.sparse_attention(inp.q, inp.k, inp.v, inp.qo_indptr.numpy(), inp.kv_indptr.numpy(), m.sparse_info,
+                              m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, out_prior=prior)
+    assert_close_bf16(o, ref, f"attention S={seq} H={H} {dtype}")
+    # skipped q-blocks are never written
+    oc = o.cpu()
+    for qb in range(seq // 128):
+        for h in range(H):
+            if not m.q_active[0][qb, h]:
+                assert torch.equal(oc[qb * 128:(qb + 1) * 128, h], prior[qb * 128:(qb + 1) * 128, h])
+
+
+def test_ragged_batch_with_empty_rows_and_lse(cuda_device):
+    H = 3
+    lens_q, lens_kv = [300, 128, 1000, 77], [256, 700, 1300, 129]
+    qo = np.concatenate([[0], np.cumsum(lens_q)]); kv = np.concatenate([[0], np.cumsum(lens_kv)])
+    rng = np.random.default_rng(5)
+    qa = [(rng.random((-(-a // 128), H)) < 0.7).astype(np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // 128), H, -(-b // 128))) < 0.5).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    qa[0][0, 0] = 1; kk[0][0, 0, :] = 0       # an active q-block that keeps nothing -> zeros, lse = -5e4
+    qa[2][7, 1] = 1; kk[2][7, 1, :] = 0; kk[2][7, 1, 10] = 1   # only the ragged last kv-block kept
+    m = wl.pack_masks(qa, kk)
+    q = wl.randn_bf16((int(qo[-1]), H, 128), 1); k = wl.randn_bf16((int(kv[-1]), H, 128), 2); v = wl.randn_bf16((int(kv[-1]), H, 128), 3)
+    w = _wrapper(cuda_device, qo, kv, H)
+    prior = wl.randn_bf16(q.shape, 4)
+    lse_prior = torch.full((q.shape[0], H), 3.0)
+    o, lse = _run(cuda_device, w, q, k, v, m, out=dev(prior, cuda_device).clone(), lse=dev(lse_prior, cuda_device).clone(),
+                  return_lse=True)
+    ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                                       out_prior=prior, lse_prior=lse_prior, return_lse=True)
+    assert_close_bf16(o, ref, "ragged attention")
+    assert torch.all(o[:128, 0] == 0)
+    assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-4)
+
+
+def test_is_full_matches_dense_sdpa_and_default_zero_out(cuda_device):
+    H, S = 2, 640
+    q = wl.randn_bf16((S, H, 128), 1); k = wl.randn_bf16((S, H, 128), 2); v = wl.randn_bf16((S, H, 128), 3)
+    w = _wrapper(cuda_device, [0, S], [0, S], H)
+    o = w.run(dev(q, cuda_device), dev(k, cuda_device), dev(v, cuda_device), is_full=True)
+    w.check_status()
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float().transpose(0, 1), k.float().transpose(0, 1),
+                                                           v.float().transpose(0, 1)).transpose(0, 1)
+    assert_close_bf16(o, ref, "is_full attention")
+    with pytest.raises(ValueError):
+        w.run(dev(q, cuda_device), dev(k, cuda_device), dev(v, cuda_device))  # masks missing, is_full False
+
+
+def test_hnd_layout_sm_scale_and_head_window(cuda_device):
+    Htot, hb, hc, S = 6, 2, 3, 512
+    inp = wl.attention_inputs(1, Htot, S, 128, 0.6, seed=7)
+    q, k, v = inp.q[:, hb:hb + hc].contiguous(), inp.k[:, hb:hb + hc].contiguous(), inp.v[:, hb:hb + hc].contiguous()
+    w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, hc, layout="HND", sm_scale=0.05, mask_num_heads=Htot,
+                 mask_head_begin=hb)
+    si, skv, ip, kp = masks_to_device(inp.masks, cuda_device)
+    o = w.run(dev(q, cuda_device), dev(k, cuda_device).transpose(0, 1).contiguous(),
+              dev(v, cuda_device).transpose(0, 1).contiguous(), si, skv, ip, kp)
+    w.check_status()
+    m = inp.masks
+    ref = oa.sparse_attention(q, k, v, inp.qo_indptr.numpy(), inp.kv_indptr.numpy(), m.sparse_info, m.sparse_kv_info,
+                              m.info_indptr, m.kv_info_indptr, sm_scale=0.05, head_begin=hb, num_mask_heads=Htot)
+    assert_close_bf16(o, ref, "HND + window attention")
+
+
+def test_flux_layer_size_sampled_heads(cuda_device):
+    """Config-1 size (B=1, H=24, S=4608, D=128, density 0.5). The whole layer runs on the GPU; three heads
+    are compared with the CPU oracle (bounded CPU time) and every head with an fp32 blockwise
+    computation on the GPU."""
+    H, S = 24, 4608
+    inp = wl.attention_inputs(1, H, S, 128, 0.5, seed=8)
+    w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, H)
+    prior = wl.randn_bf16(inp.q.shape, 9)
+    o = _run(cuda_device, w, inp.q, inp.k, inp.v, inp.masks, out=dev(prior, cuda_device).clone())
+    lists = w.work_lists()
+    assert lists["total_kept"] == wl.executed_attention_tiles(inp.masks)
+    m = inp.masks
+    for h in (0, 11, 23):
+        mh = wl.pack_masks([m.q_active[0][:, h:h + 1]], [m.kv_kept[0][:, h:h + 1]])
+        ref = oa.sparse_attention(inp.q[:, h:h + 1], inp.k[:, h:h + 1], inp.v[:, h:h + 1], [0, S], [0, S], mh.sparse_info,
+                                  mh.sparse_kv_info, mh.info_indptr, mh.kv_info_indptr, out_prior=prior[:, h:h + 1])
+        assert_close_bf16(o[:, h:h + 1], ref, f"flux layer head {h}")
+    # all heads, fp32 on the GPU with a dense element mask
+    qd, kd, vd = (dev(t, cuda_device).float().transpose(0, 1) for t in (inp.q, inp.k, inp.v))
+    kept = torch.from_numpy(m.kv_kept[0]).to(cuda_device).bool().permute(1, 0, 2)  # [H, nq, nkv]
+    act = torch.from_numpy(m.q_active[0]).to(cuda_device).bool().T                 # [H, nq]
+    worst = 0.0
+    for h in range(H):
+        s = (qd[h] @ kd[h].T) / math.sqrt(128)
+        el = kept[h].repeat_interleave(128, 0).repeat_interleave(128, 1)
+        p = torch.softmax(s.masked_fill(~el, float("-inf")), -1).nan_to_num(0.0)
+        ref = p @ vd[h]
+        rows = act[h].repeat_interleave(128)
+        ref = torch.where(rows[:, None], ref, dev(prior, cuda_device)[:, h].float())
+        assert_close_bf16(o[:, h], ref, f"flux layer head {h} (gpu fp32)")

@@ -1,0 +1,102 @@
+"""CPU: the mask oracle against the reference's known-answer vectors and against numpy."""
+
+import numpy as np
+import pytest
+
+from oracle import masks as om
+from flashomni_b200 import workloads as wl
+
+
+def test_packbits_kat_from_reference_docstring():
+    # flashomni/quantization.py:90-93
+    x = np.array([1, 0, 1, 1, 0, 0, 1, 1], dtype=np.uint8)
+    assert om.packbits(x, "big").tolist() == [0b10110011]
+    assert om.packbits(x, "little").tolist() == [0b11001101]
+
+
+def test_segment_packbits_kat_from_reference_docstring():
+    # flashomni/quantization.py:133-138
+    x = np.array([1, 0, 1, 1, 0, 0, 1, 1, 1, 0, 1], dtype=np.uint8)
+    y, ip = om.segment_packbits(x, np.array([0, 4, 7, 11]), "big")
+    assert y.tolist() == [0b10110000, 0b100000, 0b11010000]
+    assert ip.tolist() == [0, 1, 2, 3]
+
+
+@pytest.mark.parametrize("order", ["big", "little"])
+def test_segment_packbits_matches_numpy(order):
+    rng = np.random.default_rng(0)
+    lens = [0, 1, 7, 8, 9, 63, 64, 65, 1000]
+    indptr = np.concatenate([[0], np.cumsum(lens)])
+    x = rng.integers(0, 2, indptr[-1]).astype(np.uint8)
+    y, ip = om.segment_packbits(x, indptr, order)
+    for i, n in enumerate(lens):
+        ref = np.packbits(x[indptr[i]:indptr[i + 1]].astype(bool), bitorder=order)
+        assert np.array_equal(y[ip[i]:ip[i + 1]], ref)
+        assert ip[i + 1] - ip[i] == (n + 7) // 8
+
+
+def test_bad_bitorder():
+    with pytest.raises(ValueError):
+        om.packbits(np.zeros(8, np.uint8), "middle")
+
+
+def test_indptr_formulas_match_reference_convention():
+    qo = np.array([0, 300, 300 + 129])
+    kv = np.array([0, 256, 256 + 1000])
+    assert om.sparse_info_indptr(qo, 3, 128).tolist() == [0, 9, 15]
+    assert om.sparse_kv_info_indptr(qo, kv, 3, 128, 128).tolist() == [0, 18, 18 + 2 * 8 * 3]
+
+
+def test_compact_handmade():
+    # one request, 2 q-blocks, 2 heads, 3 kv-blocks
+    qa = np.array([[1, 0], [1, 1]], dtype=np.uint8)
+    kk = np.zeros((2, 2, 3), dtype=np.uint8)
+    kk[0, 0] = [1, 0, 1]
+    kk[1, 0] = [0, 0, 0]
+    kk[1, 1] = [1, 1, 1]
+    m = wl.pack_masks([qa], [kk])
+    qo = kv = np.array([0, 256]); kv = np.array([0, 384])
+    c = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, kv, 2, 128, 128)
+    assert c["items"].tolist() == [[0, 0, 0, 2], [0, 0, 1, 0], [0, 1, 1, 3]]
+    assert c["kv_indptr"].tolist() == [0, 2, 2, 5]
+    assert c["kv_idx"].tolist() == [0, 2, 0, 1, 2]
+    assert c["order"].tolist() == [2, 0, 1]
+    # head window and is_full
+    c1 = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, kv, 2, 128, 128,
+                    head_begin=1, head_count=1)
+    assert c1["items"].tolist() == [[0, 1, 1, 3]]
+    cf = om.compact(None, None, None, None, qo, kv, 2, 128, 128, is_full=True)
+    assert len(cf["items"]) == 4 and cf["kv_idx"].tolist() == [0, 1, 2] * 4
+
+
+def test_compact_counts_match_unpacked_masks():
+    m = wl.flux_masks(2, 5, 7, 9, 0.5, seed=3, text_blocks=2)
+    qo = np.array([0, 7 * 128, 14 * 128]); kv = np.array([0, 9 * 128, 18 * 128])
+    c = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, kv, 5, 128, 128)
+    assert len(c["items"]) == sum(int(q.sum()) for q in m.q_active)
+    assert len(c["kv_idx"]) == wl.executed_attention_tiles(m)
+    assert sorted(c["order"].tolist()) == list(range(len(c["items"])))
+    kept = c["items"][:, 3][c["order"]]
+    assert np.all(kept[:-1] >= kept[1:])
+
+
+def test_gemm_lists():
+    m = wl.flux_masks(2, 4, 6, 6, 0.5, seed=5, text_blocks=1)
+    tiles = om.gemm_q_tiles(m.sparse_info, m.info_indptr, 2, 6 * 128, 4 * 128, 4)
+    exp = [(b, iy, ix) for b in range(2) for iy in range(6) for ix in range(4) if m.q_active[b][iy, ix]]
+    assert tiles.tolist() == [list(t) for t in exp]
+    # a row offset (num_text_tokens) shifts the q-block a row tile maps to
+    tiles2 = om.gemm_q_tiles(m.sparse_info, m.info_indptr, 2, 4 * 128, 4 * 128, 4, num_text_tokens=256)
+    exp2 = [(b, iy, ix) for b in range(2) for iy in range(4) for ix in range(4) if m.q_active[b][iy + 2, ix]]
+    assert tiles2.tolist() == [list(t) for t in exp2]
+    ip, heads, order = om.gemm_o_rows(m.sparse_info, m.info_indptr, 2, 6 * 128, 4 * 128, 4)
+    ipc, headsc, _ = om.gemm_o_rows(m.sparse_info, m.info_indptr, 2, 6 * 128, 4 * 128, 4, is_for_cache=True)
+    r = 0
+    for b in range(2):
+        for iy in range(6):
+            a = set(heads[ip[r]:ip[r + 1]].tolist()); c = set(headsc[ipc[r]:ipc[r + 1]].tolist())
+            assert a == {h for h in range(4) if m.q_active[b][iy, h]}
+            assert a | c == set(range(4)) and not (a & c)
+            r += 1
+    cnt = (ip[1:] - ip[:-1])[order]
+    assert np.all(cnt[:-1] >= cnt[1:])
