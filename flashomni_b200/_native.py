@@ -42,6 +42,11 @@ SIGNATURES = {
     "fo_gemm_o": (c_int32, [_P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                             c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                             _P, c_int64, _P, _P, c_size_t, _P]),
+    "fo_gemm_q_static_max_bytes": (c_size_t, []),
+    "fo_gemm_q_static_last_error": (c_char_p, []),
+    "fo_gemm_q_static": (c_int32, [_P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                   c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                   _P, c_int64, _P, _P]),
     "fo_gemm_q_worklist": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                      c_int32, _P, c_int64, _P, _P, c_size_t, _P]),
     "fo_gemm_o_worklist": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,

@@ -148,6 +148,26 @@ FO_API int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_h
                        const int32_t* sparse_info_indptr, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* ---- GEMM-Q without a caller workspace ------------------------------------------------------------
+ * No counterpart in the reference. Same arguments and result as fo_gemm_q minus the workspace: the
+ * tile list, counters and status word live in a 1 MiB array that is part of the library image (one
+ * copy per GPU that loads the library, kept until exit), so this path performs no device allocation
+ * of any kind. It is meant for hosts that may not allocate when the op runs -- a server whose arena
+ * owns all device memory, a plugin that must stay out of its framework's allocator, a latency-bound
+ * loop that cannot risk the synchronisation an allocation can cause.
+ * Problems whose fo_gemm_workspace_bytes(...) exceeds fo_gemm_q_static_max_bytes() are refused with
+ * FO_ERR_WORKSPACE. The first call on a device looks up the array's device address; issue it before
+ * starting any stream capture. All calls on a device share the array: do not let two of them overlap
+ * on the GPU. Errors of this entry point are described by fo_gemm_q_static_last_error(); the kernel
+ * status word is not readable by the caller (use fo_gemm_q where that matters). */
+FO_API size_t fo_gemm_q_static_max_bytes(void);
+FO_API const char* fo_gemm_q_static_last_error(void);
+FO_API int fo_gemm_q_static(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch,
+                     int32_t m, int32_t n, int32_t k, int32_t num_heads, int32_t head_begin, int32_t head_dim,
+                     int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full,
+                     const uint8_t* sparse_info, int64_t sparse_info_bytes, const int32_t* sparse_info_indptr,
+                     void* stream);
+
 #ifdef __cplusplus
 }
 #endif
