@@ -245,7 +245,7 @@ int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   a.is_bf16 = dtype == FO_DTYPE_BF16;
   a.sm_scale_log2 = sm_scale * 1.4426950408889634f;
   a.status = status;
-  int64_t ctas = 2 * static_cast<int64_t>(sm_count());
+  int64_t ctas = static_cast<int64_t>(sm_count());  // one persistent CTA per SM
   if (ctas > max_items) ctas = max_items;
   const cudaError_t e = launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_sparse_attn_fwd", e);
@@ -257,7 +257,7 @@ size_t fo_gemm_workspace_bytes(int32_t batch, int32_t m, int32_t n, int32_t k, i
   const size_t mt = static_cast<size_t>(m) / 128, nt = static_cast<size_t>(n) / 128;
   const size_t rows = static_cast<size_t>(batch) * mt;
   const size_t lh = static_cast<size_t>(k) / static_cast<size_t>(head_dim);
-  const size_t words_q = 8 + 3 * rows * nt;
+  const size_t words_q = 8 + 4 * rows * ((nt + 1) / 2);
   const size_t words_o = 8 + (rows + 1) + rows * (lh > 0 ? lh : 1) + rows;
   const size_t words = words_q > words_o ? words_q : words_o;
   return ((words * 4 + 255) / 256) * 256;
@@ -305,7 +305,7 @@ GemmListArgs make_list_args(const GemmShape& s, const uint8_t* sparse_info, int6
   const int rows = s.batch * (s.m / 128);
   const int lh = s.k / s.head_dim;
   a.tiles = w + 8;
-  a.max_tiles = rows * (s.n / 128);
+  a.max_tiles = rows * ((s.n / 128 + 1) / 2);
   a.row_indptr = w + 8;
   a.row_heads = w + 8 + rows + 1;
   a.row_order = w + 8 + rows + 1 + rows * (lh > 0 ? lh : 1);
@@ -345,13 +345,17 @@ int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_heads, i
 
 namespace {
 
-int encode_gemm_maps(const char* who, GemmArgs& g, const void* x, const void* w, int64_t rows_a, int64_t n, int64_t k) {
+int encode_gemm_maps(const char* who, GemmArgs& g, const void* x, const void* w, const void* y, int64_t rows_a,
+                     int64_t n, int64_t k) {
   const uint32_t box[2] = {64, 128};
   const uint64_t ad[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(rows_a)};
   const uint64_t bd[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+  const uint64_t yd[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(rows_a)};
   const uint64_t st[2] = {0, static_cast<uint64_t>(k) * 2};
+  const uint64_t yst[2] = {0, static_cast<uint64_t>(n) * 2};
   int r = encode_tmap_16bit(&g.tmap_a, x, 2, ad, st, box);
   if (r == 0) r = encode_tmap_16bit(&g.tmap_b, w, 2, bd, st, box);
+  if (r == 0) r = encode_tmap_16bit(&g.tmap_y, y, 2, yd, yst, box);
   if (r != 0) {
     char buf[96];
     snprintf(buf, sizeof(buf), "%s: cuTensorMapEncodeTiled failed (%d)", who, r);
@@ -381,7 +385,7 @@ int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t d
   int32_t* wsw = static_cast<int32_t*>(workspace);
   GemmArgs g;
   memset(&g, 0, sizeof(g));
-  rc = encode_gemm_maps("fo_gemm_q", g, x, w, static_cast<int64_t>(batch) * m, n, k);
+  rc = encode_gemm_maps("fo_gemm_q", g, x, w, y, static_cast<int64_t>(batch) * m, n, k);
   if (rc != FO_OK) return rc;
   cudaError_t e;
   if (!is_full) {
@@ -391,9 +395,10 @@ int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t d
     if (e != cudaSuccess) return fail_cuda("fo_gemm_q (work list)", e);
     g.tiles = la.tiles;
     g.n_tiles_ptr = la.counters;
+  } else {
+    e = cudaMemsetAsync(wsw + 4, 0, sizeof(int32_t), st);  // the list kernel does this on the sparse path
+    if (e != cudaSuccess) return fail_cuda("fo_gemm_q (status reset)", e);
   }
-  e = cudaMemsetAsync(wsw + 4, 0, sizeof(int32_t), st);
-  if (e != cudaSuccess) return fail_cuda("fo_gemm_q (status reset)", e);
   g.y = y;
   g.init = bias;
   g.init_mode = bias != nullptr ? kInitBias1D : kInitNone;
@@ -427,14 +432,12 @@ int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t i
   int32_t* wsw = static_cast<int32_t*>(workspace);
   GemmArgs g;
   memset(&g, 0, sizeof(g));
-  rc = encode_gemm_maps("fo_gemm_o", g, x, w, static_cast<int64_t>(batch) * m, n, k);
+  rc = encode_gemm_maps("fo_gemm_o", g, x, w, y, static_cast<int64_t>(batch) * m, n, k);
   if (rc != FO_OK) return rc;
   GemmListArgs la = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
   la.is_for_cache = is_for_cache;
   cudaError_t e = launch_gemm_o_rows(la, st);
   if (e != cudaSuccess) return fail_cuda("fo_gemm_o (work list)", e);
-  e = cudaMemsetAsync(wsw + 4, 0, sizeof(int32_t), st);
-  if (e != cudaSuccess) return fail_cuda("fo_gemm_o (status reset)", e);
   g.y = y;
   g.init = init;
   g.init_mode = init == nullptr ? kInitNone : (init_is_full ? kInitFull : kInitBias1D);

@@ -6,85 +6,145 @@
 // base-2 online softmax, output rounded to the input dtype. q-blocks that are not in the list are
 // never written. An item with an empty list writes zeros (lse = -5e4), like the reference.
 //
-// CTA = 192 threads, two CTAs per SM: warps 0-3 softmax / correction / epilogue (one thread per
-// q row, TMEM lane = row), warp 4 TMA producer, warp 5 MMA issuer. TMEM per CTA: S (128 fp32
-// columns, P in bf16 aliases its first 64 columns) + O (128 fp32 columns). Shared memory per
-// CTA: Q tile 32 KB + a two-slot ring of 32 KB tiles that K and V blocks alternate through.
-// While one CTA of the SM is in its softmax, the other one's MMAs keep the tensor pipe busy.
-// CTAs are persistent; items are dealt round-robin in longest-first order.
+// One persistent CTA per SM walks its items (dealt round-robin in longest-first order) as ONE
+// sequence of kv blocks g = 0, 1, 2, ... and software-pipelines it three deep:
+//
+//   round r:   tensor pipe   S[(r+1)&1] = Q K_{r+1}^T   interleaved with   O += P[(r-1)&1] V_{r-1}
+//              softmax warps block r: S[r&1] -> P[r&1]
+//
+// TMEM (512 columns): S0, S1 (fp32, 128 each), O (fp32, 128), P0, P1 (16 bit, 64 each). Because S is
+// double-buffered and P does not alias S, the QK and PV batches of a round are independent of each
+// other and of the softmax of the block in between; they are issued by two different threads, because
+// a thread that issues a batch is held until the batch has drained.
+// Warps: 0-15 softmax / O-rescale / epilogue (4 threads per q row: TMEM lane = row, 32 columns
+// each), 16 TMA producer (double-buffered Q tile + two-slot FIFOs of 32 KB K and V tiles, K running two
+// blocks ahead of V), 17 QK issuer, 18 PV issuer. Every mbarrier wait is bounded.
 #include <cuda_fp16.h>
 
 #include "internal.h"
+
+#ifndef FO_POLY_EVERY
+#define FO_POLY_EVERY 4
+#endif
 
 namespace fo {
 namespace {
 
 constexpr int kBQ = 128, kBKV = 128, kD = 128;
-constexpr int kTileBytes = 128 * kD * 2;   // 32 KB: a 128-row tile of Q, K or V
-constexpr int kHalfBytes = kTileBytes / 2; // one 64-column half (one swizzle-atom column)
-constexpr int kRing = 2;
-constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColO = 128;
+constexpr int kTileBytes = 128 * kD * 2;    // 32 KB: a 128-row tile of Q, K or V
+constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half (one swizzle-atom column)
+constexpr int kRingK = 2, kRingV = 2;  // separate FIFOs of 32 KB tiles for K and V
+constexpr int kRing = kRingK + kRingV;
+constexpr int kQBufs = 2;
+constexpr int kSoftmaxWarps = 16;
+constexpr int kWarpProducer = kSoftmaxWarps;
+constexpr int kWarpQK = kSoftmaxWarps + 1;      // issues S = Q K^T
+constexpr int kWarpPV = kSoftmaxWarps + 2;      // issues O += P V
+constexpr int kWarpMma = kWarpQK;               // owner of the TMEM allocation
+constexpr int kThreads = (kWarpPV + 1) * 32;    // 608
+constexpr int kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
+constexpr int kPolyEvery = FO_POLY_EVERY;   // 1 in (2 * kPolyEvery) exponentials is computed by polynomial
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: keep the old max while exp2 stays <= 2^8
 
 struct Tail {
-  uint64_t q_full, q_empty;
-  uint64_t ring_full[kRing], ring_empty[kRing];
-  uint64_t s_full, p_full, o_full;
+  uint64_t q_full[kQBufs], q_empty[kQBufs];
+  uint64_t k_full[kRingK], k_empty[kRingK], v_full[kRingV], v_empty[kRingV];
+  uint64_t s_full[2];
+  uint64_t p_full[2], pv_done[2];  // indexed by block parity, so that no waiter can fall two phases behind
+  uint64_t o_full, o_free;
+  uint64_t xbar;          // barrier among the softmax warps (bounded, unlike bar.sync)
   uint32_t tmem_base;
   int abort_flag;
+  float xmax[2][4][128];  // [block parity][column quarter][row]: partial row maxima
+  float xsum[4][128];     // [column quarter][row]: partial row sums
 };
-constexpr int kSmemBytes = (1 + kRing) * kTileBytes + 1024 + static_cast<int>(sizeof(Tail));
+constexpr int kSmemBytes = (kQBufs + kRing) * kTileBytes + 1024 + static_cast<int>(sizeof(Tail));
 
-struct Item {
-  int b, h, qb, n;
-  const int32_t* kv;
-};
-
-__device__ __forceinline__ Item load_item(const AttnArgs& a, int i) {
-  const int it = a.order[i];
-  Item r;
-  r.b = a.items[4 * it + 0];
-  r.h = a.items[4 * it + 1];
-  r.qb = a.items[4 * it + 2];
-  r.n = a.items[4 * it + 3];
-  r.kv = a.kv_idx + a.kv_ptr[it];
-  return r;
+#ifdef FO_ATTN_TRACE
+// Development aid (only with -DFO_ATTN_TRACE): CTA 0 records clock64() at pipeline events.
+__device__ long long g_trace[8][512];
+__device__ __forceinline__ void trace(int ev, int idx) {
+  if (blockIdx.x == 0 && idx >= 0 && idx < 512) g_trace[ev][idx] = clock64();
 }
+#define FO_TRACE(ev, idx) trace(ev, idx)
+#else
+#define FO_TRACE(ev, idx)
+#endif
+
+
+// Walks the CTA's share of the schedule as a flat sequence of kv blocks.
+struct BlockSeq {
+  int pos, stride, n_items;
+  int item_no;   // index among this CTA's non-empty items (selects the Q buffer, o_full / o_free phases)
+  int b, h, qb, n, j;
+  int kvb, kvb_next;  // kv-block index of the current block; the next one is fetched a block early
+  const int32_t* kv;
+  __device__ __forceinline__ void init(int start, int stride_, int n_items_) {
+    pos = start; stride = stride_; n_items = n_items_; item_no = -1; n = 0; j = 0; kv = nullptr;
+    b = h = qb = 0; kvb = kvb_next = 0;
+  }
+  // Advances to the next block; `on_empty(b, h, qb)` is called for every item without kv blocks that
+  // is passed on the way. Returns false at the end of the sequence.
+  template <class F>
+  __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
+    if (j + 1 < n) {
+      ++j;
+      kvb = kvb_next;
+      if (j + 1 < n) kvb_next = kv[j + 1];
+      return true;
+    }
+    while (pos < n_items) {
+      const int it = a.order[pos];
+      pos += stride;
+      const int4 rec = *reinterpret_cast<const int4*>(a.items + 4 * it);
+      if (rec.w <= 0) { on_empty(rec.x, rec.y, rec.z); continue; }
+      b = rec.x; h = rec.y; qb = rec.z; n = rec.w; j = 0;
+      kv = a.kv_idx + a.kv_ptr[it];
+      kvb = kv[0];
+      if (n > 1) kvb_next = kv[1];
+      ++item_no;
+      return true;
+    }
+    n = 0; j = 0;
+    return false;
+  }
+  __device__ __forceinline__ bool first() const { return j == 0; }
+  __device__ __forceinline__ bool last() const { return j == n - 1; }
+};
 
 template <bool kBf16>
-__global__ void __launch_bounds__(kThreads, 2) attention_kernel(const __grid_constant__ AttnArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
-  uint8_t* smem_q = smem;
-  uint8_t* smem_ring = smem + kTileBytes;
-  Tail* tail = reinterpret_cast<Tail*>(smem + (1 + kRing) * kTileBytes);
+  uint8_t* smem_q = smem;                           // kQBufs tiles
+  uint8_t* smem_ring = smem + kQBufs * kTileBytes;  // kRing tiles
+  Tail* tail = reinterpret_cast<Tail*>(smem + (kQBufs + kRing) * kTileBytes);
   volatile int* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    mbar_init(&tail->q_full, 1);
-    mbar_init(&tail->q_empty, 1);
-    for (int s = 0; s < kRing; ++s) {
-      mbar_init(&tail->ring_full[s], 1);
-      mbar_init(&tail->ring_empty[s], 1);
-    }
-    mbar_init(&tail->s_full, 1);
-    mbar_init(&tail->p_full, 4);
+    for (int i = 0; i < kQBufs; ++i) { mbar_init(&tail->q_full[i], 1); mbar_init(&tail->q_empty[i], 1); }
+    for (int i = 0; i < kRingK; ++i) { mbar_init(&tail->k_full[i], 1); mbar_init(&tail->k_empty[i], 1); }
+    for (int i = 0; i < kRingV; ++i) { mbar_init(&tail->v_full[i], 1); mbar_init(&tail->v_empty[i], 1); }
+    mbar_init(&tail->s_full[0], 1);
+    mbar_init(&tail->s_full[1], 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&tail->p_full[i], kSoftmaxWarps); mbar_init(&tail->pv_done[i], 1); }
     mbar_init(&tail->o_full, 1);
+    mbar_init(&tail->o_free, kSoftmaxWarps);
+    mbar_init(&tail->xbar, kSoftmaxWarps);
     tail->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kWarpProducer && lane == 0) {
     tma_prefetch_desc(&a.tmap_q);
     tma_prefetch_desc(&a.tmap_k);
     tma_prefetch_desc(&a.tmap_v);
   }
-  if (warp == 5) {
+  if (warp == kWarpMma) {
     tmem_alloc(&tail->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -95,222 +155,343 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const __grid_con
 
   int n_items = a.counters[0];
   if (n_items < 0) n_items = 0;
+  const int sched_start = static_cast<int>(blockIdx.x), sched_stride = static_cast<int>(gridDim.x);
+  auto ignore_empty = [](int, int, int) {};
 
-  if (warp == 4) {
+  if (warp == kWarpProducer) {
     // ------------------------------------------------------------------ TMA producer
+    // Push order: K_0, K_1, then (K_t, V_{t-2}) for t = 2, 3, ... and the last two V (K runs two blocks ahead).
     if (lane == 0) {
-      int slot = 0;
-      uint32_t ring_phase = 0, q_phase = 0;
+      BlockSeq seq;
+      seq.init(sched_start, sched_stride, n_items);
+      uint32_t nk = 0, nv = 0;           // K / V tiles pushed so far
+      uint32_t q_uses[kQBufs] = {0, 0};  // loads issued per Q buffer
+      int hist_row[3] = {0, 0, 0}, hist_head[3] = {0, 0, 0};  // kv row / kv head of blocks t, t-1, t-2
+      int pending_v = 0;                 // number of blocks whose V has not been pushed yet (0..2)
+      int kv_row0 = 0;                   // first kv row of the current item's request
       bool ok = true;
-      for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
-        const Item it = load_item(a, i);
-        if (it.n <= 0) continue;
-        const int hq = it.h - a.head_begin;
-        const int hk = hq / a.group_size;
-        const int q_row = a.qo_indptr[it.b] + it.qb * kBQ;
-        const int kv_row0 = a.kv_indptr[it.b];
-        if (!mbar_wait(&tail->q_empty, q_phase ^ 1u, abort_flag)) { ok = false; break; }
-        q_phase ^= 1u;
-        mbar_expect_tx(&tail->q_full, kTileBytes);
-        tma_load_3d(smem_q, &a.tmap_q, &tail->q_full, 0, hq, q_row);
-        tma_load_3d(smem_q + kHalfBytes, &a.tmap_q, &tail->q_full, 64, hq, q_row);
-        for (int j = 0; j < it.n && ok; ++j) {
-          const int row = kv_row0 + it.kv[j] * kBKV;
-#pragma unroll
-          for (int which = 0; which < 2; ++which) {  // 0: K block, 1: V block
-            if (!mbar_wait(&tail->ring_empty[slot], ring_phase ^ 1u, abort_flag)) { ok = false; break; }
-            uint8_t* dst = smem_ring + slot * kTileBytes;
-            const CUtensorMap* tm = which == 0 ? &a.tmap_k : &a.tmap_v;
-            mbar_expect_tx(&tail->ring_full[slot], kTileBytes);
-            tma_load_3d(dst, tm, &tail->ring_full[slot], 0, hk, row);
-            tma_load_3d(dst + kHalfBytes, tm, &tail->ring_full[slot], 64, hk, row);
-            if (++slot == kRing) { slot = 0; ring_phase ^= 1u; }
+      auto push = [&](bool is_v, int head, int row) -> bool {
+        const uint32_t n = is_v ? nv : nk;
+        const int slot = static_cast<int>(n % (is_v ? kRingV : kRingK));
+        const uint32_t phase = (n / (is_v ? kRingV : kRingK)) & 1u;
+        uint64_t* empty = is_v ? &tail->v_empty[slot] : &tail->k_empty[slot];
+        uint64_t* full = is_v ? &tail->v_full[slot] : &tail->k_full[slot];
+        if (!mbar_wait(empty, phase ^ 1u, abort_flag)) return false;
+        uint8_t* dst = smem_ring + (is_v ? kRingK + slot : slot) * kTileBytes;
+        const CUtensorMap* tm = is_v ? &a.tmap_v : &a.tmap_k;
+        mbar_expect_tx(full, kTileBytes);
+        tma_load_3d(dst, tm, full, 0, head, row);
+        tma_load_3d(dst + kHalfBytes, tm, full, 64, head, row);
+        if (is_v) ++nv; else ++nk;
+        return true;
+      };
+      while (ok) {
+        const bool have = seq.next(a, ignore_empty);
+        if (have) {
+          const int hq = seq.h - a.head_begin;
+          const int hk = hq / a.group_size;
+          if (seq.first()) kv_row0 = a.kv_indptr[seq.b];
+          if (seq.first()) {  // new item: its Q tile goes to buffer item_no & 1
+            const int qb_i = seq.item_no & 1;
+            if (!mbar_wait(&tail->q_empty[qb_i], (q_uses[qb_i] & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+            ++q_uses[qb_i];
+            const int q_row = a.qo_indptr[seq.b] + seq.qb * kBQ;
+            uint8_t* dst = smem_q + qb_i * kTileBytes;
+            mbar_expect_tx(&tail->q_full[qb_i], kTileBytes);
+            tma_load_3d(dst, &a.tmap_q, &tail->q_full[qb_i], 0, hq, q_row);
+            tma_load_3d(dst + kHalfBytes, &a.tmap_q, &tail->q_full[qb_i], 64, hq, q_row);
           }
+          hist_row[2] = hist_row[1]; hist_row[1] = hist_row[0];
+          hist_head[2] = hist_head[1]; hist_head[1] = hist_head[0];
+          hist_row[0] = kv_row0 + seq.kvb * kBKV;
+          hist_head[0] = hk;
+          if (!push(false, hist_head[0], hist_row[0])) { ok = false; break; }
+          if (pending_v == 2) {
+            if (!push(true, hist_head[2], hist_row[2])) { ok = false; break; }
+          } else {
+            ++pending_v;
+          }
+        } else {
+          // drain: V of the last (up to two) blocks, oldest first
+          if (pending_v == 2) ok = push(true, hist_head[1], hist_row[1]);
+          if (ok && pending_v >= 1) ok = push(true, hist_head[0], hist_row[0]);
+          break;
         }
       }
     }
-  } else if (warp == 5) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kWarpQK) {
+    // ------------------------------------------------------------------ QK issuer: S[g&1] = Q K_g^T
+    // Two threads feed the tensor pipe (this one and the PV issuer): an issuing thread is blocked while
+    // its batch drains, so with a single issuer the pipe would idle during that thread's bookkeeping.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_f16(kBQ, kBKV, kBf16, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc_f16(kBQ, kD, kBf16, 0, 1);
-      const uint32_t tmem_s = tmem_base + kColS;
-      const uint32_t tmem_o = tmem_base + kColO;
-      const uint32_t q_addr = smem_u32(smem_q);
-      int slot = 0;
-      uint32_t ring_phase = 0, q_phase = 0, p_phase = 0;
+      // descriptors: constant high word (K-major, 128-byte swizzle), low word holds the address
+      const uint64_t d0 = make_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
+      const uint32_t hi = static_cast<uint32_t>(d0 >> 32);
+      const uint32_t q_lo0 = static_cast<uint32_t>(d0);
+      const uint32_t k_lo0 = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(smem_ring), 16, 1024));
+      BlockSeq seq;
+      seq.init(sched_start, sched_stride, n_items);
+      uint32_t g = 0, nk = 0;
+      uint32_t q_uses[kQBufs] = {0, 0};
       bool ok = true;
-      for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
-        const Item it = load_item(a, i);
-        if (it.n <= 0) continue;
-        if (!mbar_wait(&tail->q_full, q_phase, abort_flag)) { ok = false; break; }
-        q_phase ^= 1u;
-        for (int j = 0; j < it.n; ++j) {
-          // ---- S = Q K_j^T
-          if (!mbar_wait(&tail->ring_full[slot], ring_phase, abort_flag)) { ok = false; break; }
-          tc_fence_after_sync();
-          {
-            const uint32_t k_addr = smem_u32(smem_ring + slot * kTileBytes);
-#pragma unroll
-            for (int kk = 0; kk < kD / 16; ++kk) {
-              const uint32_t off = static_cast<uint32_t>((kk >> 2) * kHalfBytes + (kk & 3) * 32);
-              umma_ss(tmem_s, make_smem_desc_sw128(q_addr + off, 16, 1024),
-                      make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk != 0 ? 1u : 0u);
-            }
-            umma_commit(&tail->ring_empty[slot]);
-            umma_commit(&tail->s_full);
-            if (j == it.n - 1) umma_commit(&tail->q_empty);
-            if (++slot == kRing) { slot = 0; ring_phase ^= 1u; }
-          }
-          // ---- O (+)= P_j V_j
-          if (!mbar_wait(&tail->p_full, p_phase, abort_flag)) { ok = false; break; }
-          p_phase ^= 1u;
-          if (!mbar_wait(&tail->ring_full[slot], ring_phase, abort_flag)) { ok = false; break; }
-          tc_fence_after_sync();
-          {
-            const uint32_t v_addr = smem_u32(smem_ring + slot * kTileBytes);
-#pragma unroll
-            for (int kk = 0; kk < kBKV / 16; ++kk) {
-              // V is MN-major: 16 kv rows further = 16 * 128 B; the two 64-column halves are 16 KB apart
-              umma_ts(tmem_o, tmem_s + static_cast<uint32_t>(kk * 8),
-                      make_smem_desc_sw128(v_addr + static_cast<uint32_t>(kk * 2048), kHalfBytes, 1024),
-                      idesc_pv, (j | kk) != 0 ? 1u : 0u);
-            }
-            umma_commit(&tail->ring_empty[slot]);
-            if (j == it.n - 1) umma_commit(&tail->o_full);
-            if (++slot == kRing) { slot = 0; ring_phase ^= 1u; }
-          }
+      while (ok && seq.next(a, ignore_empty)) {
+        const uint32_t sb = g & 1u;
+        const int qb_i = seq.item_no & 1;
+        // S[sb] is free once the softmax of block g-2 has handed over its P
+        if (g >= 2u && !mbar_wait(&tail->p_full[sb], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (seq.first()) {
+          if (!mbar_wait(&tail->q_full[qb_i], q_uses[qb_i] & 1u, abort_flag)) { ok = false; break; }
+          ++q_uses[qb_i];
         }
+        const int slot = static_cast<int>(nk % kRingK);
+        if (!mbar_wait(&tail->k_full[slot], (nk / kRingK) & 1u, abort_flag)) { ok = false; break; }
+        ++nk;
+        tc_fence_after_sync();
+        FO_TRACE(0, static_cast<int>(g));  // QK batch start
+        const uint32_t q_lo = q_lo0 + static_cast<uint32_t>((qb_i * kTileBytes) >> 4);
+        const uint32_t k_lo = k_lo0 + static_cast<uint32_t>((slot * kTileBytes) >> 4);
+        uint32_t la[8], lb[8];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // 16 elements further along K: +32 B inside a 64-column half, +16 KB for the second half
+          const uint32_t off = static_cast<uint32_t>(((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4);
+          la[kk] = q_lo + off;
+          lb[kk] = k_lo + off;
+        }
+        umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
+        umma_commit(&tail->s_full[sb]);
+        umma_commit(&tail->k_empty[slot]);
+        if (seq.last()) umma_commit(&tail->q_empty[qb_i]);
+        FO_TRACE(1, static_cast<int>(g));  // QK batch issued
+        ++g;
+      }
+    }
+  } else if (warp == kWarpPV) {
+    // ------------------------------------------------------------------ PV issuer: O (+)= P[g&1] V_g
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = make_idesc_f16(kBQ, kD, kBf16, 0, 1);
+      // V is MN-major: its two 64-column halves are 16 KB apart (leading byte offset)
+      const uint64_t d0 = make_smem_desc_sw128(smem_u32(smem_ring + kRingK * kTileBytes), kHalfBytes, 1024);
+      const uint32_t hi = static_cast<uint32_t>(d0 >> 32), v_lo0 = static_cast<uint32_t>(d0);
+      BlockSeq seq;
+      seq.init(sched_start, sched_stride, n_items);
+      uint32_t g = 0, nv = 0, items_started = 0;
+      bool ok = true;
+      while (ok && seq.next(a, ignore_empty)) {
+        const uint32_t sb = g & 1u;
+        if (!mbar_wait(&tail->p_full[sb], (g >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (seq.first() && items_started > 0) {  // O must have been drained by the previous item's epilogue
+          if (!mbar_wait(&tail->o_free, (items_started - 1u) & 1u, abort_flag)) { ok = false; break; }
+        }
+        const int slot = static_cast<int>(nv % kRingV);
+        if (!mbar_wait(&tail->v_full[slot], (nv / kRingV) & 1u, abort_flag)) { ok = false; break; }
+        ++nv;
+        tc_fence_after_sync();
+        FO_TRACE(2, static_cast<int>(g));  // PV batch start
+        const uint32_t tmem_p = tmem_base + kColP + sb * 64u;
+        const uint32_t v_lo = v_lo0 + static_cast<uint32_t>((slot * kTileBytes) >> 4);
+        uint32_t ta[8], lb[8];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // 16 kv rows further = 16 * 128 B in the V tile, 8 columns further in the 16-bit P tile
+          ta[kk] = tmem_p + static_cast<uint32_t>(kk * 8);
+          lb[kk] = v_lo + static_cast<uint32_t>((kk * 2048) >> 4);
+        }
+        umma_ts_x8(tmem_base + kColO, hi, idesc_pv, seq.first() ? 0u : 1u, ta, lb);
+        umma_commit(&tail->pv_done[sb]);
+        umma_commit(&tail->v_empty[slot]);
+        if (seq.last()) umma_commit(&tail->o_full);
+        FO_TRACE(3, static_cast<int>(g));  // PV batch issued
+        if (seq.first()) ++items_started;
+        ++g;
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax / epilogue warps
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t tmem_s = tmem_base + lane_base + kColS;
-    const uint32_t tmem_o = tmem_base + lane_base + kColO;
-    const int r_in_tile = warp * 32 + lane;
-    uint32_t s_phase = 0, o_phase = 0;
-    bool ok = true;
+    // ------------------------------------------------------------------ softmax / epilogue warps 0..15
+    // Four threads per q row: thread (quadrant = warp & 3, column quarter cq = warp >> 2) owns columns
+    // [32cq, 32cq+32) of S, P and O for row 32*quadrant + lane.
+    const int cq = warp >> 2;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t col0 = static_cast<uint32_t>(32 * cq);
+    const uint32_t tmem_s0 = tmem_base + lane_base + kColS + col0;
+    const uint32_t tmem_p0 = tmem_base + lane_base + kColP + (col0 >> 1);
+    const uint32_t tmem_o = tmem_base + lane_base + kColO + col0;
+    const int r_in_tile = (warp & 3) * 32 + lane;
+    const bool tracer = (threadIdx.x == 0);
+    (void)tracer;
     uint16_t* o16 = reinterpret_cast<uint16_t*>(a.o);
-    for (int i = blockIdx.x; i < n_items && ok; i += gridDim.x) {
-      const Item it = load_item(a, i);
-      const int hq = it.h - a.head_begin;
-      const int q0 = a.qo_indptr[it.b];
-      const int q_len = a.qo_indptr[it.b + 1] - q0;
-      const int kv_len = a.kv_indptr[it.b + 1] - a.kv_indptr[it.b];
-      const int row_in_req = it.qb * kBQ + r_in_tile;
-      const bool row_ok = row_in_req < q_len;
+    bool ok = true;
+    uint32_t xbar_phase = 0;
+    // Barrier among the 16 softmax warps built on an mbarrier, so that it is bounded like every other
+    // wait of the kernel (a warp that gave up elsewhere cannot leave the others parked forever).
+    auto softmax_bar = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->xbar);
+      const bool r = mbar_wait(&tail->xbar, xbar_phase, abort_flag);
+      xbar_phase ^= 1u;
+      return r;
+    };
+
+    struct RowCtx {  // where an item's rows live in global memory
+      uint16_t* orow;
+      float* lse;
+      bool row_ok;
+    };
+    auto row_ctx = [&](int b, int h, int qb) -> RowCtx {
+      RowCtx c;
+      const int hq = h - a.head_begin;
+      const int q0 = a.qo_indptr[b];
+      const int q_len = a.qo_indptr[b + 1] - q0;
+      const int row_in_req = qb * kBQ + r_in_tile;
+      c.row_ok = row_in_req < q_len;
       const int64_t grow = static_cast<int64_t>(q0) + row_in_req;
-      uint16_t* orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h;
-
-      if (it.n <= 0) {
-        if (row_ok) {
-          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      c.orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h + col0;
+      c.lse = (a.lse != nullptr && cq == 0) ? a.lse + grow * a.lse_stride_n + hq : nullptr;
+      return c;
+    };
+    auto on_empty = [&](int b, int h, int qb) {  // active q-block that keeps nothing: zeros, lse = -5e4
+      const RowCtx c = row_ctx(b, h, qb);
+      if (c.row_ok) {
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-          for (int c = 0; c < kD / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = z;
-          if (a.lse != nullptr) a.lse[grow * a.lse_stride_n + hq] = -5e4f;
-        }
-        continue;
+        for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(c.orow)[i] = z;
+        if (c.lse != nullptr) *c.lse = -5e4f;
       }
+    };
 
-      float m_used = -INFINITY;  // running max (scaled, log2 domain) that the exponentials refer to
-      float l = 0.f;
-      for (int j = 0; j < it.n; ++j) {
-        if (!mbar_wait(&tail->s_full, s_phase, abort_flag)) { ok = false; break; }
-        s_phase ^= 1u;
-        tc_fence_after_sync();
-        const int kvb = it.kv[j];
-        const int valid = kv_len - kvb * kBKV;  // columns of this block inside the request (>= 128: all)
-        // ---- pass 1: row max
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < kBKV / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_x32(tmem_s + static_cast<uint32_t>(c * 32), v);
-          tmem_wait_ld();
-          if (valid >= kBKV) {
-#pragma unroll
-            for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(v[t]));
-          } else {
-#pragma unroll
-            for (int t = 0; t < 32; ++t)
-              if (c * 32 + t < valid) mx = fmaxf(mx, __uint_as_float(v[t]));
-          }
-        }
-        const float m_new = fmaxf(m_used, mx * a.sm_scale_log2);
-        // ---- lazy rescale of l and O (warp-uniform decision; TMEM round trip is warp-collective)
-        const bool need = (m_new - m_used) > kRescaleThreshold;  // true on the first block (m_used = -inf)
-        if (j == 0) {
-          m_used = m_new;
-        } else if (__any_sync(0xffffffffu, need)) {
-          const float alpha = need ? ex2_approx(m_used - m_new) : 1.0f;
-          if (need) m_used = m_new;
-          l *= alpha;
-#pragma unroll 1
-          for (int c = 0; c < kD / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_x32(tmem_o + static_cast<uint32_t>(c * 32), v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
-            tmem_st_x32(tmem_o + static_cast<uint32_t>(c * 32), v);
-          }
-        }
-        // ---- pass 2: P = exp2(S*scale - m_used), row sum, write P (16-bit) over the S columns
-        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-#pragma unroll 1
-        for (int c = 0; c < kBKV / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_x32(tmem_s + static_cast<uint32_t>(c * 32), v);
-          tmem_wait_ld();
-          uint32_t pk[16];
-#pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            float p0 = ex2_approx(fmaf(__uint_as_float(v[2 * t]), a.sm_scale_log2, neg_m));
-            float p1 = ex2_approx(fmaf(__uint_as_float(v[2 * t + 1]), a.sm_scale_log2, neg_m));
-            if (valid < kBKV) {
-              if (c * 32 + 2 * t >= valid) p0 = 0.f;
-              if (c * 32 + 2 * t + 1 >= valid) p1 = 0.f;
-            }
-            l += p0 + p1;
-            pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
-          }
-          tmem_st_x16(tmem_s + static_cast<uint32_t>(c * 16), pk);
-        }
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->p_full);
-      }
-      if (!ok) break;
-      // ---- epilogue: O / l -> global
-      if (!mbar_wait(&tail->o_full, o_phase, abort_flag)) { ok = false; break; }
-      o_phase ^= 1u;
+    BlockSeq seq;
+    seq.init(sched_start, sched_stride, n_items);
+    uint32_t g = 0;           // global block index
+    uint32_t s_uses[2] = {0, 0};
+    uint32_t items_done = 0;  // epilogues completed
+    float m_used = -INFINITY, l = 0.f;
+    // an item whose last block has been handed over and whose O is still being accumulated
+    bool pend = false;
+    float pend_l = 0.f, pend_m = 0.f;
+    RowCtx pend_ctx;
+    pend_ctx.orow = nullptr; pend_ctx.lse = nullptr; pend_ctx.row_ok = false;
+
+    auto epilogue = [&]() -> bool {
+      // the four quarters of a row exchange their partial sums
+      float* xs = tail->xsum[0];
+      xs[cq * kBQ + r_in_tile] = pend_l;
+      if (!softmax_bar()) return false;
+      const float lsum = xs[r_in_tile] + xs[kBQ + r_in_tile] + xs[2 * kBQ + r_in_tile] + xs[3 * kBQ + r_in_tile];
+      if (!mbar_wait(&tail->o_full, items_done & 1u, abort_flag)) return false;
       tc_fence_after_sync();
-      const float inv_l = l > 0.f ? __frcp_rn(l) : 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kD / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(tmem_o + static_cast<uint32_t>(c * 32), v);
-        tmem_wait_ld();
-        if (row_ok) {
-          uint4 outv[4];
-          uint32_t* o32 = reinterpret_cast<uint32_t*>(outv);
-#pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            const float x0 = __uint_as_float(v[2 * t]) * inv_l, x1 = __uint_as_float(v[2 * t + 1]) * inv_l;
-            o32[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
-          }
-          uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
-#pragma unroll
-          for (int t = 0; t < 4; ++t) dst[t] = outv[t];
-        }
-      }
-      if (row_ok && a.lse != nullptr) {
-        a.lse[grow * a.lse_stride_n + hq] = (l > 0.f) ? (log2f(l) + m_used) : -5e4f;
-      }
+      const float inv_l = lsum > 0.f ? __frcp_rn(lsum) : 0.f;
+      uint32_t v[32];
+      tmem_ld_x32(tmem_o, v);
+      tmem_wait_ld();
       tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->o_free);  // O may be overwritten by the next item
+      if (pend_ctx.row_ok) {
+        uint4 outv[4];
+        uint32_t* o32 = reinterpret_cast<uint32_t*>(outv);
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+          const float x0 = __uint_as_float(v[2 * t]) * inv_l, x1 = __uint_as_float(v[2 * t + 1]) * inv_l;
+          o32[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(pend_ctx.orow);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) dst[t] = outv[t];
+        if (pend_ctx.lse != nullptr) *pend_ctx.lse = (lsum > 0.f) ? (log2f(lsum) + pend_m) : -5e4f;
+      }
+      ++items_done;
+      pend = false;
+      return softmax_bar();  // xsum is reused by the next epilogue
+    };
+
+    int kv_len = 0;
+    while (ok && seq.next(a, on_empty)) {
+      if (seq.first()) {
+        m_used = -INFINITY;
+        l = 0.f;
+        kv_len = a.kv_indptr[seq.b + 1] - a.kv_indptr[seq.b];
+      }
+      const uint32_t sb = g & 1u;
+      if (!mbar_wait(&tail->s_full[sb], s_uses[sb] & 1u, abort_flag)) { ok = false; break; }
+      ++s_uses[sb];
+      if (tracer) FO_TRACE(4, static_cast<int>(g));  // S ready seen by softmax
+      tc_fence_after_sync();
+      const int valid = kv_len - seq.kvb * kBKV - static_cast<int>(col0);  // valid columns of my quarter
+      uint32_t s[32];
+      tmem_ld_x32(tmem_s0 + sb * 128u, s);
+      tmem_wait_ld();
+      float mx = -INFINITY;
+      if (valid >= 32) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(s[t]));
+      } else {
+#pragma unroll
+        for (int t = 0; t < 32; ++t)
+          if (t < valid) mx = fmaxf(mx, __uint_as_float(s[t]));
+      }
+      float* xm = tail->xmax[sb][0];
+      xm[cq * kBQ + r_in_tile] = mx;
+      if (!softmax_bar()) { ok = false; break; }
+      if (tracer) FO_TRACE(5, static_cast<int>(g));  // max exchanged
+      mx = fmaxf(fmaxf(xm[r_in_tile], xm[kBQ + r_in_tile]), fmaxf(xm[2 * kBQ + r_in_tile], xm[3 * kBQ + r_in_tile]));
+      const float m_new = fmaxf(m_used, mx * a.sm_scale_log2);
+      // ---- lazy rescale of l and O (warp-uniform decision; the TMEM round trip is warp-collective).
+      // O is rescaled only after the PV of the previous block has completed.
+      const bool need = (m_new - m_used) > kRescaleThreshold;  // true on an item's first block
+      if (seq.first()) {
+        m_used = m_new;
+      } else if (__any_sync(0xffffffffu, need)) {
+        // PV of block g-1 is completion number (g-1)/2 on the barrier of its parity
+        if (!mbar_wait(&tail->pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const float alpha = need ? ex2_approx(m_used - m_new) : 1.0f;
+        if (need) m_used = m_new;
+        l *= alpha;
+        uint32_t v[32];
+        tmem_ld_x32(tmem_o, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
+        tmem_st_x32(tmem_o, v);
+      }
+      // ---- P = exp2(S*scale - m_used), row sum, P (16 bit) to its own TMEM buffer
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+      uint32_t pk[16];
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        // every fourth pair takes the polynomial path (FMA pipe), the rest the MUFU path
+        float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * t]), a.sm_scale_log2, neg_m));
+        const float x1 = fmaf(__uint_as_float(s[2 * t + 1]), a.sm_scale_log2, neg_m);
+        float p1 = (t % kPolyEvery == 0) ? ex2_poly(x1) : ex2_approx(x1);
+        if (valid < 32) {
+          if (2 * t >= valid) p0 = 0.f;
+          if (2 * t + 1 >= valid) p1 = 0.f;
+        }
+        l += p0 + p1;
+        pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+      }
+      // P[sb] was last read by the PV of block g-2
+      if (g >= 2u && !mbar_wait(&tail->pv_done[sb], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tmem_st_x16(tmem_p0 + sb * 64u, pk);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->p_full[sb]);
+      if (tracer) FO_TRACE(6, static_cast<int>(g));  // P handed over
+      ++g;
+      // the previous item's epilogue runs one block late, so that its last PV overlaps this softmax
+      if (pend) {
+        if (!epilogue()) { ok = false; break; }
+      }
+      if (seq.last()) {
+        pend = true;
+        pend_l = l;
+        pend_m = m_used;
+        pend_ctx = row_ctx(seq.b, seq.h, seq.qb);
+      }
     }
+    if (ok && pend) epilogue();
   }
 
   // ------------------------------------------------------------------ common exit
@@ -323,13 +504,19 @@ __global__ void __launch_bounds__(kThreads, 2) attention_kernel(const __grid_con
     if (threadIdx.x == 0) atomicExch(a.status, kDevWaitTimeout);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == kWarpMma) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
 }  // namespace
+
+#ifdef FO_ATTN_TRACE
+extern "C" __attribute__((visibility("default"))) int fo_trace_dump(long long* host_dst) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_dst, g_trace, sizeof(g_trace)));
+}
+#endif
 
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream) {
   if (max_ctas <= 0) return cudaSuccess;

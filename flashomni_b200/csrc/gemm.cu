@@ -3,16 +3,23 @@
 //   Y[b, rows(iy), cols(ix)] = init + sum_{k-blocks of the tile} X[b, rows, kblk] * W[cols, kblk]^T
 //
 // GEMM-Q (reference: include/flashomni/gemm/w16a16/gemm.cuh:27-228): the tile list holds only the
-// active (b, iy, ix) output tiles; every tile runs the whole K range; init = bias[cols] or 0; tiles
+// active 128x128 output tiles; every tile runs the whole K range; init = bias[cols] or 0; tiles
 // that are not listed are never touched.
 // GEMM-O (reference: include/flashomni/gemm/w16a16/gemm_reduction.cuh:27-276): every output tile is
 // produced; its K loop visits only the K-slices of the heads selected for its row block (compacted
 // list, ascending); init = cache[b, rows, cols] or bias[cols] or 0.
 //
-// CTA = 192 threads: warps 0-3 epilogue (TMEM -> registers -> global), warp 4 TMA producer,
-// warp 5 MMA issuer. 128x128 output tile, K step 64 (one 128-byte swizzle atom), 6-stage ring of
-// (A 16 KB + B 16 KB), two 128-column TMEM accumulators so the epilogue of tile i overlaps the
-// main loop of tile i+1. Tiles are dealt round-robin to the persistent CTAs.
+// A CTA works on "pair tiles": one 128-row A tile against TWO 128-column blocks of W (any two: for
+// GEMM-Q they are two active heads of the same row block), issued as one UMMA of N = 256 so that
+// the A operand is read from shared memory once per 256 output columns. A leftover single block
+// runs as N = 128.
+//
+// CTA = 192 threads: warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA issuer. K step 64 (one
+// 128-byte swizzle atom), 4-stage ring of (A 16 KB + B 32 KB), two 256-column TMEM accumulators so
+// the epilogue of tile i overlaps the main loop of tile i+1. The epilogue converts 64-column slabs
+// (TMEM -> registers -> +init -> 16-bit) into a swizzled shared-memory slab and hands each slab to a
+// TMA store, so global writes are full 128-byte lines and asynchronous. Tiles are dealt round-robin
+// to the persistent CTAs.
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -20,13 +27,17 @@
 namespace fo {
 namespace {
 
-constexpr int kBM = 128, kBN = 128, kBK = 64;
-constexpr int kStages = 6;
-constexpr int kABytes = kBM * kBK * 2;
-constexpr int kBBytes = kBN * kBK * 2;
-constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kBM = 128, kBNH = 128, kBK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;        // 16 KB
+constexpr int kBHalfBytes = kBNH * kBK * 2;   // 16 KB per 128-column block of W
+constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
+constexpr int kSlabCols = 64;
+constexpr int kSlabBytes = kBM * kSlabCols * 2;  // 16 KB
+constexpr int kSlabBufs = 2;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;
+constexpr int kMaxHeadsSmem = 128;
 
 struct Tail {
   uint64_t full[kStages];
@@ -35,18 +46,21 @@ struct Tail {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int heads[kMaxHeadsSmem];  // GEMM-O: the current tile's head list, staged for the producer
 };
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + static_cast<int>(sizeof(Tail));
+constexpr int kSmemBytes = kStages * kStageBytes + kSlabBufs * kSlabBytes + 1024 + static_cast<int>(sizeof(Tail));
 
 struct TileInfo {
-  int a_row;            // first row of the A tile in [batch*m]
-  int w_row;            // first row of the W tile (= first output column)
-  int nkb;              // number of 64-wide K blocks
-  const int32_t* heads; // GEMM-O: selected heads of the row block (null for GEMM-Q)
+  int a_row;             // first row of the A tile in [batch*m]
+  int w_row0, w_row1;    // first rows of the two W blocks (= first output columns); w_row1 < 0: single
+  int nkb;               // number of 64-wide K blocks
+  const int32_t* heads;  // GEMM-O: selected heads of the row block (null for GEMM-Q)
 };
 
+__device__ __forceinline__ int pairs_per_row(const GemmArgs& a) { return (a.n / kBNH + 1) / 2; }
+
 __device__ __forceinline__ int num_tiles(const GemmArgs& a) {
-  const int cap = a.batch * (a.m / kBM) * (a.n / kBN);
+  const int cap = a.batch * (a.m / kBM) * pairs_per_row(a);
   if (a.mode == kGemmQ && a.tiles != nullptr) {
     const int n = *a.n_tiles_ptr;
     return n < cap ? (n < 0 ? 0 : n) : cap;
@@ -56,25 +70,28 @@ __device__ __forceinline__ int num_tiles(const GemmArgs& a) {
 
 __device__ __forceinline__ TileInfo get_tile(const GemmArgs& a, int t) {
   TileInfo ti;
-  if (a.mode == kGemmQ) {
-    int b, iy, ix;
-    if (a.tiles != nullptr) {
-      b = a.tiles[3 * t + 0]; iy = a.tiles[3 * t + 1]; ix = a.tiles[3 * t + 2];
-    } else {  // dense: t enumerates (b, iy, ix) in row-major order
-      const int nct = a.n / kBN, mt = a.m / kBM;
-      ix = t % nct;
-      iy = (t / nct) % mt;
-      b = t / (nct * mt);
-    }
-    ti.a_row = b * a.m + iy * kBM;
-    ti.w_row = ix * kBN;
+  const int nct = a.n / kBNH;
+  if (a.mode == kGemmQ && a.tiles != nullptr) {
+    const int4 rec = *reinterpret_cast<const int4*>(a.tiles + 4 * t);  // (b, iy, ix0, ix1)
+    ti.a_row = rec.x * a.m + rec.y * kBM;
+    ti.w_row0 = rec.z * kBNH;
+    ti.w_row1 = rec.w >= 0 ? rec.w * kBNH : -1;
+    ti.nkb = a.k / kBK;
+    ti.heads = nullptr;
+    return ti;
+  }
+  const int npr = pairs_per_row(a);
+  const int j = t % npr;
+  const int rr = t / npr;
+  ti.w_row0 = (2 * j) * kBNH;
+  ti.w_row1 = (2 * j + 1 < nct) ? (2 * j + 1) * kBNH : -1;
+  if (a.mode == kGemmQ) {  // dense: row blocks in natural order
+    ti.a_row = rr * kBM;
     ti.nkb = a.k / kBK;
     ti.heads = nullptr;
   } else {
-    const int nct = a.n / kBN;
-    const int r = a.row_order[t / nct];
+    const int r = a.row_order[rr];
     ti.a_row = r * kBM;
-    ti.w_row = (t % nct) * kBN;
     const int h0 = a.row_indptr[r], h1 = a.row_indptr[r + 1];
     ti.heads = a.row_heads + h0;
     ti.nkb = (h1 - h0) * a.kb_per_head;
@@ -88,12 +105,15 @@ __device__ __forceinline__ int kcol_of(const GemmArgs& a, const TileInfo& ti, in
   return (ti.heads[hh] * a.kb_per_head + (j - hh * a.kb_per_head)) * kBK;
 }
 
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
-  Tail* tail = reinterpret_cast<Tail*>(smem + kStages * kStageBytes);
+  uint8_t* smem_slab = smem + kStages * kStageBytes;
+  Tail* tail = reinterpret_cast<Tail*>(smem_slab + kSlabBufs * kSlabBytes);
   volatile int* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -114,6 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&a.tmap_a);
     tma_prefetch_desc(&a.tmap_b);
+    tma_prefetch_desc(&a.tmap_y);
   }
   if (warp == 5) {
     tmem_alloc(&tail->tmem_base, kTmemCols);
@@ -128,49 +149,67 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
   if (warp == 4) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        const TileInfo ti = get_tile(a, t);
+    // All lanes stage the tile's head list in shared memory (one coalesced read instead of one
+    // dependent global load per K block); lane 0 then issues the copies.
+    int stage = 0;
+    uint32_t phase = 0;
+    int ok = 1;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      TileInfo ti = get_tile(a, t);
+      if (ti.heads != nullptr) {
+        const int nh = ti.nkb / a.kb_per_head;
+        if (nh <= kMaxHeadsSmem) {
+          for (int i = lane; i < nh; i += 32) tail->heads[i] = ti.heads[i];
+          ti.heads = tail->heads;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t bytes = ti.w_row1 >= 0 ? kStageBytes : (kABytes + kBHalfBytes);
         for (int j = 0; j < ti.nkb; ++j) {
-          if (!mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag)) { ok = 0; break; }
           const int kcol = kcol_of(a, ti, j);
           uint8_t* sa = smem + stage * kStageBytes;
-          mbar_expect_tx(&tail->full[stage], kStageBytes);
+          mbar_expect_tx(&tail->full[stage], bytes);
           tma_load_2d(sa, &a.tmap_a, &tail->full[stage], kcol, ti.a_row);
-          tma_load_2d(sa + kABytes, &a.tmap_b, &tail->full[stage], kcol, ti.w_row);
+          tma_load_2d(sa + kABytes, &a.tmap_b, &tail->full[stage], kcol, ti.w_row0);
+          if (ti.w_row1 >= 0)
+            tma_load_2d(sa + kABytes + kBHalfBytes, &a.tmap_b, &tail->full[stage], kcol, ti.w_row1);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      stage = __shfl_sync(0xffffffffu, stage, 0);
+      phase = __shfl_sync(0xffffffffu, phase, 0);
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(kBM, kBN, kBf16, 0, 0);
+      constexpr uint32_t idesc256 = make_idesc_f16(kBM, 2 * kBNH, kBf16, 0, 0);
+      constexpr uint32_t idesc128 = make_idesc_f16(kBM, kBNH, kBf16, 0, 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      // every operand tile is K-major with 128-byte swizzle: same descriptor high word, low word = address
+      const uint64_t desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
+      const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32), desc_lo0 = static_cast<uint32_t>(desc0);
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
         const TileInfo ti = get_tile(a, t);
+        const uint32_t idesc = ti.w_row1 >= 0 ? idesc256 : idesc128;
         if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBN);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 2 * kBNH);
         for (int j = 0; j < ti.nkb; ++j) {
           if (!mbar_wait(&tail->full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
-          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(sa + kABytes, 16, 1024);
-#pragma unroll
-          for (int kk = 0; kk < kBK / 16; ++kk) {
-            // advancing 16 elements (32 bytes) along K inside the swizzle atom: +2 in the address field
-            umma_ss(d_tmem, adesc + static_cast<uint64_t>(kk * 2), bdesc + static_cast<uint64_t>(kk * 2), idesc,
-                    (j | kk) != 0 ? 1u : 0u);
-          }
+          // descriptor low words of the 4 K = 16 steps (advancing 32 bytes inside the swizzle atom = +2)
+          const uint32_t a_lo = desc_lo0 + static_cast<uint32_t>((stage * kStageBytes) >> 4);
+          const uint32_t b_lo = a_lo + static_cast<uint32_t>(kABytes >> 4);
+          const uint32_t la[4] = {a_lo, a_lo + 2u, a_lo + 4u, a_lo + 6u};
+          const uint32_t lb[4] = {b_lo, b_lo + 2u, b_lo + 4u, b_lo + 6u};
+          umma_ss_x4(d_tmem, desc_hi, desc_hi, idesc, j != 0 ? 1u : 0u, la, lb);
           umma_commit(&tail->empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -185,41 +224,56 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    uint32_t slab_count = 0;  // slabs handed to TMA stores so far (selects the staging buffer)
     const uint16_t* init16 = reinterpret_cast<const uint16_t*>(a.init);
-    uint16_t* y16 = reinterpret_cast<uint16_t*>(a.y);
+    const int r_in_tile = warp * 32 + lane;
+    const uint32_t swz = static_cast<uint32_t>(r_in_tile & 7);
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       const TileInfo ti = get_tile(a, t);
-      if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
-      const int64_t row = static_cast<int64_t>(ti.a_row) + warp * 32 + lane;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * kBN);
-#pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t v[32];
-        if (ti.nkb > 0) {
-          tmem_ld_x32(taddr + static_cast<uint32_t>(c * 32), v);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0u;
-        }
-        const int col0 = ti.w_row + c * 32;
-        uint4 add[4];
+      const int64_t row = static_cast<int64_t>(ti.a_row) + r_in_tile;
+      const int nslab = ti.w_row1 >= 0 ? 4 : 2;
+      // init values of slab 0 are fetched before the accumulator is waited for
+      uint4 initv[8];
+      auto load_init = [&](int s) {
+        const int col0 = ((s >> 1) == 0 ? ti.w_row0 : ti.w_row1) + (s & 1) * kSlabCols;
         if (a.init_mode == kInitBias1D) {
           const uint4* p = reinterpret_cast<const uint4*>(init16 + col0);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) add[i] = __ldg(p + i);
+          for (int i = 0; i < 8; ++i) initv[i] = __ldg(p + i);
         } else if (a.init_mode == kInitFull) {
           const uint4* p = reinterpret_cast<const uint4*>(init16 + row * a.n + col0);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) add[i] = __ldg(p + i);
+          for (int i = 0; i < 8; ++i) initv[i] = __ldg(p + i);
         }
-        uint4 outv[4];
-        uint32_t* o32 = reinterpret_cast<uint32_t*>(outv);
-        const uint32_t* a32 = reinterpret_cast<const uint32_t*>(add);
+      };
+      load_init(0);
+      if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * 2 * kBNH);
+#pragma unroll 1
+      for (int s = 0; s < nslab; ++s) {
+        const int col0 = ((s >> 1) == 0 ? ti.w_row0 : ti.w_row1) + (s & 1) * kSlabCols;
+        uint32_t v0[32], v1[32];
+        if (ti.nkb > 0) {
+          tmem_ld_x32(taddr + static_cast<uint32_t>(s * kSlabCols), v0);
+          tmem_ld_x32(taddr + static_cast<uint32_t>(s * kSlabCols + 32), v1);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
+          for (int i = 0; i < 32; ++i) { v0[i] = 0u; v1[i] = 0u; }
+        }
+        if (s == nslab - 1) {  // accumulator fully read: hand it back to the MMA warp
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tail->acc_empty[acc]);
+        }
+        uint4 outv[8];
+        uint32_t* o32 = reinterpret_cast<uint32_t*>(outv);
+        const uint32_t* a32 = reinterpret_cast<const uint32_t*>(initv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float lo = __uint_as_float(i < 16 ? v0[2 * i] : v1[2 * i - 32]);
+          float hi = __uint_as_float(i < 16 ? v0[2 * i + 1] : v1[2 * i - 31]);
           if (a.init_mode != kInitNone) {
             if (kBf16) {
               lo += __uint_as_float(a32[i] << 16);
@@ -232,16 +286,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           }
           o32[i] = kBf16 ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
         }
-        uint4* dst = reinterpret_cast<uint4*>(y16 + row * a.n + col0);
+        if (s + 1 < nslab) load_init(s + 1);  // next slab's init loads fly during the store hand-off
+        // staging buffer of this slab must no longer be read by the store issued two slabs ago
+        uint8_t* buf = smem_slab + (slab_count & 1u) * kSlabBytes;
+        if (threadIdx.x == 0) tma_store_wait_read<1>();
+        epi_bar();
+        uint8_t* rowp = buf + r_in_tile * 128;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = outv[i];
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(rowp + ((static_cast<uint32_t>(c) ^ swz) << 4)) = outv[c];
+        fence_proxy_async_smem();
+        epi_bar();
+        if (threadIdx.x == 0) {
+          tma_store_2d(&a.tmap_y, buf, col0, ti.a_row);
+          tma_store_commit();
+        }
+        ++slab_count;
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tail->acc_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (threadIdx.x == 0) tma_store_wait_all<0>();
   }
 
   // ------------------------------------------------------------- common exit
@@ -264,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 }  // namespace
 
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream) {
-  const int cap = a.batch * (a.m / kBM) * (a.n / kBN);
+  const int cap = a.batch * (a.m / kBM) * ((a.n / kBNH + 1) / 2);
   if (cap <= 0) return cudaSuccess;
   const int grid = cap < max_ctas ? cap : max_ctas;
   cudaError_t e;

@@ -43,7 +43,7 @@ struct GemmListArgs {
   int64_t info_bytes;
   int batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens;
   int is_full, is_for_cache;
-  int32_t* tiles;                  // GEMM-Q: [max_tiles, 3] (b, iy, ix)
+  int32_t* tiles;                  // GEMM-Q: [max_tiles, 4] pair records (b, iy, ix0, ix1)
   int max_tiles;
   int32_t* row_indptr;             // GEMM-O: [rows + 1]
   int32_t* row_heads;              // GEMM-O: [rows * local_heads]
@@ -66,6 +66,7 @@ enum GemmInit : int { kInitNone = 0, kInitBias1D = 1, kInitFull = 2 };
 struct GemmArgs {
   CUtensorMap tmap_a;              // X as [batch*m, k], box 64 x 128, 128B swizzle
   CUtensorMap tmap_b;              // W as [n, k],       box 64 x 128, 128B swizzle
+  CUtensorMap tmap_y;              // Y as [batch*m, n], box 64 x 128, 128B swizzle (TMA stores)
   void* y;                         // [batch, m, n]
   const void* init;                // bias [n] or cache [batch, m, n] or null
   int init_mode;
@@ -73,7 +74,7 @@ struct GemmArgs {
   int is_bf16;
   int batch, m, n, k;
   int kb_per_head;                 // GEMM-O: head_dim / 64
-  const int32_t* tiles;            // GEMM-Q work list (b, iy, ix); null = every tile (dense)
+  const int32_t* tiles;            // GEMM-Q pair records (b, iy, ix0, ix1); null = every tile (dense)
   const int32_t* n_tiles_ptr;      // device count of GEMM-Q tiles
   const int32_t* row_indptr;       // GEMM-O lists
   const int32_t* row_heads;

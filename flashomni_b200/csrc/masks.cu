@@ -197,16 +197,20 @@ __global__ void compact_count_kernel(CompactArgs a) {
 }
 
 // Pass 2: single CTA. Exclusive scans of the active flags (item index) and of the kept counts
-// (offset into kv_idx), then the longest-first permutation by a stable counting sort.
-__global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a) {
+// (offset into kv_idx), then the longest-first permutation by a stable counting sort: W warps own
+// contiguous candidate slices, each with its own histogram in shared memory; bucket starts are
+// (items with more kept blocks) + (same bucket, earlier slices); every warp then places its slice in
+// ascending candidate order, 32 at a time.
+__global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int sort_warps) {
+  extern __shared__ int s_whist[];  // [sort_warps][nb]
   __shared__ int s_warp_items[32];
   __shared__ long long s_warp_kept[32];
   __shared__ int s_carry_items;
   __shared__ long long s_carry_kept;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nb = a.max_nkv + 1;
   if (tid == 0) { s_carry_items = 0; s_carry_kept = 0; }
-  // zero the histogram (one bucket per kept count 0..max_nkv)
-  for (int i = tid; i <= a.max_nkv; i += blockDim.x) a.hist[i] = 0;
+  for (int i = tid; i < sort_warps * nb; i += blockDim.x) s_whist[i] = 0;
   __syncthreads();
   for (int64_t base = 0; base < a.n_cand; base += blockDim.x) {
     const int64_t c = base + tid;
@@ -241,7 +245,6 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a) {
     if (c < a.n_cand) {
       a.item_pos[c] = flag ? pre_i : -1;
       a.kv_off[c] = pre_k;
-      if (flag) atomicAdd(&a.hist[kept], 1);
     }
     __syncthreads();
     if (tid == 0) {
@@ -255,17 +258,37 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a) {
   if (tid == 0) {
     a.counters[0] = n_items;
     a.counters[1] = static_cast<int>(total_kept > 0x7fffffffLL ? 0x7fffffff : total_kept);
+    a.counters[2] = (total_kept > a.max_kept || n_items > a.max_items) ? kDevBadIndex : kDevOk;
     a.counters[3] = a.max_nkv;
-    if (total_kept > a.max_kept || n_items > a.max_items) a.counters[2] = kDevBadIndex;
     a.kv_ptr[n_items <= a.max_items ? n_items : 0] = static_cast<int>(total_kept);
   }
-  __threadfence_block();
+  // ---- stable counting sort by descending kept count
+  const int64_t slice = ((a.n_cand + sort_warps - 1) / sort_warps + 31) / 32 * 32;
+  const int64_t my0 = static_cast<int64_t>(warp) * slice;
+  const int64_t my1 = (my0 + slice < a.n_cand) ? my0 + slice : a.n_cand;
+  if (warp < sort_warps) {
+    int* h = s_whist + warp * nb;
+    for (int64_t c = my0 + lane; c < my1; c += 32) {
+      const int v = a.cnt[c];
+      if (v >= 0 && v < nb) atomicAdd(&h[v], 1);
+    }
+  }
   __syncthreads();
-  // Bucket starts for descending kept order: start[k] = number of items with kept > k.
-  // Serial suffix scan by one warp in chunks of 32 (max_nkv is a few hundred at most in practice).
+  // per bucket: exclusive prefix over the slices; the bucket total goes to a.hist (global scratch)
+  for (int k = tid; k < nb; k += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < sort_warps; ++w) {
+      const int t = s_whist[w * nb + k];
+      s_whist[w * nb + k] = run;
+      run += t;
+    }
+    a.hist[k] = run;
+  }
+  __syncthreads();
+  // bucket bases for descending order: base[k] = number of items with kept > k (suffix scan by warp 0)
   if (warp == 0) {
     int carry = 0;
-    for (int hi = a.max_nkv; hi >= 0; hi -= 32) {
+    for (int hi = nb - 1; hi >= 0; hi -= 32) {
       const int k = hi - lane;
       const int v = (k >= 0) ? a.hist[k] : 0;
       int x = v;
@@ -274,22 +297,26 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a) {
         const int y = __shfl_up_sync(0xffffffffu, x, o);
         if (lane >= o) x += y;
       }
-      if (k >= 0) a.hist[k] = carry + x - v;  // exclusive start of bucket k
+      if (k >= 0) a.hist[k] = carry + x - v;
       carry += __shfl_sync(0xffffffffu, x, 31);
     }
-    __syncwarp();
-    // Stable placement: candidates visited in ascending index, 32 at a time.
-    for (int64_t base = 0; base < a.n_cand; base += 32) {
+  }
+  __syncthreads();
+  for (int i = tid; i < sort_warps * nb; i += blockDim.x) s_whist[i] += a.hist[i % nb];
+  __syncthreads();
+  if (warp < sort_warps) {
+    int* h = s_whist + warp * nb;
+    for (int64_t base = my0; base < my1; base += 32) {
       const int64_t c = base + lane;
-      const int v = (c < a.n_cand) ? a.cnt[c] : -1;
-      const bool flag = v >= 0;
+      const int v = (c < my1) ? a.cnt[c] : -1;
+      const bool flag = v >= 0 && v < nb;
       const unsigned grp = __match_any_sync(0xffffffffu, flag ? v : -1 - lane);
       const int rank_in_grp = __popc(grp & ((1u << lane) - 1u));
       const int leader = __ffs(grp) - 1;
       int start = 0;
       if (flag && lane == leader) {
-        start = a.hist[v];
-        a.hist[v] = start + __popc(grp);
+        start = h[v];
+        h[v] = start + __popc(grp);
       }
       start = __shfl_sync(0xffffffffu, start, leader);
       if (flag) {
@@ -363,10 +390,18 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
   const int threads = 256, wpb = threads / 32;
   int64_t blocks = (a.n_cand + wpb - 1) / wpb;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  cudaError_t e = cudaMemsetAsync(a.counters, 0, 4 * sizeof(int), stream);
-  if (e != cudaSuccess) return e;
+  // sort histograms: as many warps as fit in ~160 KB of shared memory
+  const int64_t nb = static_cast<int64_t>(a.max_nkv) + 1;
+  int64_t sort_warps = (160 * 1024) / (nb * 4);
+  if (sort_warps > 32) sort_warps = 32;
+  if (sort_warps < 1) return cudaErrorInvalidValue;  // more than 40960 kv-blocks per request
+  const size_t scan_smem = static_cast<size_t>(sort_warps * nb * 4);
+  if (scan_smem > 40 * 1024) {
+    cudaError_t ea = cudaFuncSetAttribute(compact_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
+    if (ea != cudaSuccess) return ea;
+  }
   compact_count_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(a);
-  compact_scan_kernel<<<1, 1024, 0, stream>>>(a);
+  compact_scan_kernel<<<1, 1024, scan_smem, stream>>>(a, static_cast<int>(sort_warps));
   compact_fill_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(a);
   return cudaGetLastError();
 }
@@ -374,64 +409,84 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
 // ---------------------------------------------------------------------------------------------
 // GEMM work lists (single CTA: the candidate counts are a few thousand at most)
 // ---------------------------------------------------------------------------------------------
-// GEMM-Q: ascending list of active (b, iy, ix) tiles; count in counters[0].
+// GEMM-Q: pair-tile records (b, iy, ix0, ix1). Per row block (b, iy), ascending in (b, iy), the active
+// column blocks are taken two at a time in ascending order; a leftover single block has ix1 = -1.
+// counters[0] = number of records, counters[1] = number of active 128x128 tiles.
 __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
   __shared__ int s_warp[32];
-  __shared__ int s_carry;
+  __shared__ int s_warp_t[32];
+  __shared__ int s_carry, s_carry_t;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) s_carry = 0;
+  if (tid == 0) { s_carry = 0; s_carry_t = 0; }
   __syncthreads();
   const int mt = a.m / 128, nt = a.n / 128;
-  const int64_t n_cand = static_cast<int64_t>(a.batch) * mt * nt;
-  for (int64_t base = 0; base < n_cand; base += blockDim.x) {
-    const int64_t c = base + tid;
-    int flag = 0, b = 0, iy = 0, ix = 0;
-    if (c < n_cand) {
-      b = static_cast<int>(c / (static_cast<int64_t>(mt) * nt));
-      const int rem = static_cast<int>(c % (static_cast<int64_t>(mt) * nt));
-      iy = rem / nt;
-      ix = rem % nt;
+  const int rows = a.batch * mt;
+  for (int base = 0; base < rows; base += blockDim.x) {
+    const int r = base + tid;
+    int cnt = 0;
+    const uint8_t* seg = nullptr;
+    int64_t limit = 0, bit0 = 0;
+    if (r < rows) {
+      const int b = r / mt, iy = r % mt;
       if (a.is_full) {
-        flag = 1;
+        cnt = nt;
       } else {
         const int64_t ioff = a.info_indptr[b];
+        seg = a.sparse_info + ioff;
+        limit = a.info_bytes - ioff;
         const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
-        const int64_t bit = qb * a.num_heads + a.head_begin + (ix * 128) / a.head_dim;
-        flag = get_bit(a.sparse_info + ioff, bit, a.info_bytes - ioff);
+        bit0 = qb * a.num_heads + a.head_begin;
+        for (int ix = 0; ix < nt; ++ix) cnt += get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit);
       }
     }
-    int x = flag;
+    const int recs = (cnt + 1) >> 1;
+    int x = recs, xt = cnt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
+      const int yt = __shfl_up_sync(0xffffffffu, xt, o);
+      if (lane >= o) { x += y; xt += yt; }
     }
-    if (lane == 31) s_warp[warp] = x;
+    if (lane == 31) { s_warp[warp] = x; s_warp_t[warp] = xt; }
     __syncthreads();
     if (warp == 0) {
-      int w = s_warp[lane];
+      int w = s_warp[lane], wt = s_warp_t[lane];
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int y = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += y;
+        const int yt = __shfl_up_sync(0xffffffffu, wt, o);
+        if (lane >= o) { w += y; wt += yt; }
       }
       s_warp[lane] = w;
+      s_warp_t[lane] = wt;
     }
     __syncthreads();
-    const int pos = s_carry + (warp ? s_warp[warp - 1] : 0) + x - flag;
-    if (flag && pos < a.max_tiles) {
-      a.tiles[3 * pos + 0] = b;
-      a.tiles[3 * pos + 1] = iy;
-      a.tiles[3 * pos + 2] = ix;
+    int pos = s_carry + (warp ? s_warp[warp - 1] : 0) + x - recs;
+    if (r < rows && recs > 0) {
+      const int b = r / mt, iy = r % mt;
+      int first = -1;
+      for (int ix = 0; ix < nt; ++ix) {
+        const int on = a.is_full ? 1 : get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit);
+        if (!on) continue;
+        if (first < 0) {
+          first = ix;
+        } else {
+          if (pos < a.max_tiles) *reinterpret_cast<int4*>(a.tiles + 4 * pos) = make_int4(b, iy, first, ix);
+          ++pos;
+          first = -1;
+        }
+      }
+      if (first >= 0 && pos < a.max_tiles) *reinterpret_cast<int4*>(a.tiles + 4 * pos) = make_int4(b, iy, first, -1);
     }
     __syncthreads();
-    if (tid == 0) s_carry += s_warp[31];
+    if (tid == 0) { s_carry += s_warp[31]; s_carry_t += s_warp_t[31]; }
     __syncthreads();
   }
   if (tid == 0) {
     a.counters[0] = s_carry;
-    a.counters[1] = 0;
+    a.counters[1] = s_carry_t;
     a.counters[2] = s_carry > a.max_tiles ? kDevBadIndex : kDevOk;
+    a.counters[4] = kDevOk;  // status word of the GEMM kernel that follows
   }
 }
 
@@ -499,6 +554,7 @@ __global__ void __launch_bounds__(1024) gemm_o_rows_kernel(GemmListArgs a) {
     a.counters[0] = rows;
     a.counters[1] = s_carry;
     a.counters[2] = kDevOk;
+    a.counters[4] = kDevOk;  // status word of the GEMM kernel that follows
     // bucket starts, descending count
     int acc = 0;
     for (int k = local_heads; k >= 0; --k) { const int v = s_hist[k]; s_hist[k] = acc; acc += v; }

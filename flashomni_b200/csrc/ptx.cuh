@@ -222,6 +222,114 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Variants with the accumulate flag fixed at compile time (no predicate set-up on the issuing thread).
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_ss_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  if (kAccumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.eq.b32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc)
+        : "memory");
+  }
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  if (kAccumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.eq.b32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, 0, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        : "memory");
+  }
+}
+// ---------------------------------------------------------------------------------------------
+// Batched issue. A single thread feeds the tensor pipe, so the instruction count between two
+// tcgen05.mma matters: rebuilding 64-bit descriptors and predicates in C++ costs ~100 clocks per MMA,
+// more than a 128x128x16 MMA takes to execute (64). These helpers issue a whole K = 64 / K = 128
+// group from one asm block; the descriptors' high words are constant and only the low words (which
+// hold the 14-bit start address) vary.
+// ---------------------------------------------------------------------------------------------
+#define FO_MMA_SS(LA, LB, P) \
+  "mov.b64 da, {" LA ", %1}; mov.b64 db, {" LB ", %2}; tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, " P ";\n"
+#define FO_MMA_TS(TA, LB, P) \
+  "mov.b64 db, {" LB ", %1}; tcgen05.mma.cta_group::1.kind::f16 [%0], [" TA "], db, %2, " P ";\n"
+
+// 8 x (D[tmem] (+)= A[smem] * B[smem]); the first instruction accumulates iff `acc_first`.
+__device__ __forceinline__ void umma_ss_x8(uint32_t d_tmem, uint32_t a_hi, uint32_t b_hi, uint32_t idesc,
+                                           uint32_t acc_first, const uint32_t (&la)[8], const uint32_t (&lb)[8]) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p0, %4, 0;\n"
+      "setp.eq.b32 p1, 0, 0;\n"
+      FO_MMA_SS("%5", "%13", "p0") FO_MMA_SS("%6", "%14", "p1") FO_MMA_SS("%7", "%15", "p1")
+      FO_MMA_SS("%8", "%16", "p1") FO_MMA_SS("%9", "%17", "p1") FO_MMA_SS("%10", "%18", "p1")
+      FO_MMA_SS("%11", "%19", "p1") FO_MMA_SS("%12", "%20", "p1")
+      "}\n" ::"r"(d_tmem),
+      "r"(a_hi), "r"(b_hi), "r"(idesc), "r"(acc_first), "r"(la[0]), "r"(la[1]), "r"(la[2]), "r"(la[3]), "r"(la[4]),
+      "r"(la[5]), "r"(la[6]), "r"(la[7]), "r"(lb[0]), "r"(lb[1]), "r"(lb[2]), "r"(lb[3]), "r"(lb[4]), "r"(lb[5]),
+      "r"(lb[6]), "r"(lb[7])
+      : "memory");
+}
+// 4 x (D[tmem] (+)= A[smem] * B[smem])
+__device__ __forceinline__ void umma_ss_x4(uint32_t d_tmem, uint32_t a_hi, uint32_t b_hi, uint32_t idesc,
+                                           uint32_t acc_first, const uint32_t (&la)[4], const uint32_t (&lb)[4]) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p0, %4, 0;\n"
+      "setp.eq.b32 p1, 0, 0;\n"
+      FO_MMA_SS("%5", "%9", "p0") FO_MMA_SS("%6", "%10", "p1") FO_MMA_SS("%7", "%11", "p1") FO_MMA_SS("%8", "%12", "p1")
+      "}\n" ::"r"(d_tmem),
+      "r"(a_hi), "r"(b_hi), "r"(idesc), "r"(acc_first), "r"(la[0]), "r"(la[1]), "r"(la[2]), "r"(la[3]), "r"(lb[0]),
+      "r"(lb[1]), "r"(lb[2]), "r"(lb[3])
+      : "memory");
+}
+// 8 x (D[tmem] (+)= A[tmem] * B[smem]); A advances by ta[i] columns.
+__device__ __forceinline__ void umma_ts_x8(uint32_t d_tmem, uint32_t b_hi, uint32_t idesc, uint32_t acc_first,
+                                           const uint32_t (&ta)[8], const uint32_t (&lb)[8]) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p0, %3, 0;\n"
+      "setp.eq.b32 p1, 0, 0;\n"
+      FO_MMA_TS("%4", "%12", "p0") FO_MMA_TS("%5", "%13", "p1") FO_MMA_TS("%6", "%14", "p1") FO_MMA_TS("%7", "%15", "p1")
+      FO_MMA_TS("%8", "%16", "p1") FO_MMA_TS("%9", "%17", "p1") FO_MMA_TS("%10", "%18", "p1") FO_MMA_TS("%11", "%19", "p1")
+      "}\n" ::"r"(d_tmem),
+      "r"(b_hi), "r"(idesc), "r"(acc_first), "r"(ta[0]), "r"(ta[1]), "r"(ta[2]), "r"(ta[3]), "r"(ta[4]), "r"(ta[5]),
+      "r"(ta[6]), "r"(ta[7]), "r"(lb[0]), "r"(lb[1]), "r"(lb[2]), "r"(lb[3]), "r"(lb[4]), "r"(lb[5]), "r"(lb[6]),
+      "r"(lb[7])
+      : "memory");
+}
+
 // Arrive (count 1) on `bar` once every tcgen05 op issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -273,6 +381,20 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// exp2 on the FMA / ALU pipes (no MUFU): round-to-nearest range reduction with the 1.5*2^23 trick, degree-4
+// polynomial for 2^f on [-0.5, 0.5] (relative error < 5e-5), exponent inserted by integer add. Used for a
+// share of the softmax exponentials so that the MUFU unit (16 results / clock / SM) is not the only pipe
+// that limits the softmax.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float xr = x + 12582912.f;
+  const float f = x - (xr - 12582912.f);
+  float p = fmaf(f, 0.0096181291f, 0.0555041087f);
+  p = fmaf(p, f, 0.2402265070f);
+  p = fmaf(p, f, 0.6931471806f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;

@@ -9,7 +9,8 @@
 //
 // Limits and rules:
 //   * the array is kStaticScratchBytes (1 MiB) per GPU that loads the library, held until the process
-//     exits; it fits problems with up to 87 378 output tiles of 128x128 (batch * m/128 * n/128); larger
+//     exits; it fits work lists of up to 65 534 records (a record covers one or two 128x128 output
+//     tiles of one 128-row block, so batch * m/128 * ceil(n/256) must stay below that); larger
 //     problems are rejected with FO_ERR_WORKSPACE and a message that names both sizes;
 //   * the first call on each device resolves the device address of the array (one cudaGetSymbolAddress,
 //     with that device current); make that first call before any stream capture begins;

@@ -133,8 +133,10 @@ FO_API int fo_gemm_o(const void* x, const void* w, void* y, const void* init, in
               void* workspace, size_t workspace_bytes, void* stream);
 
 /* The list builders that fo_gemm_q / fo_gemm_o run first (exposed so that the lists can be checked
- * bit for bit). They fill the same workspace layout: GEMM-Q: words [8 + 3*i ..] = (b, iy, ix) of the
- * i-th active tile, counters[0] = tile count. GEMM-O with R = batch*m/128 row blocks and
+ * bit for bit). They fill the same workspace layout: GEMM-Q: words [8 + 4*i ..] = (b, iy, ix0, ix1), the
+ * i-th pair record: per row block (b, iy), ascending, its active 128-column blocks taken two at a
+ * time (ix1 = -1 for a leftover single block); counters[0] = record count, counters[1] = active
+ * tile count. GEMM-O with R = batch*m/128 row blocks and
  * L = k/head_dim local heads: words [8 .. 8+R] row_indptr, then [8+R+1 ..] row_heads (R*L words
  * reserved), then row_order (R words): row blocks by descending list length (stable). */
 FO_API int fo_gemm_q_worklist(int32_t batch, int32_t m, int32_t n, int32_t num_heads, int32_t head_begin,

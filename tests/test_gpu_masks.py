@@ -121,9 +121,10 @@ def test_gemm_worklists_bit_exact(cuda_device):
                                     _native.ptr(ws), ws.numel(), st)
         _native.check(rc, "fo_gemm_q_worklist")
         w = ws.view(torch.int32).cpu().numpy()
-        ref = om.gemm_q_tiles(m.sparse_info, m.info_indptr, B, m_rows, N, H, 128, ntt)
+        ref = om.gemm_q_tile_pairs(m.sparse_info, m.info_indptr, B, m_rows, N, H, 128, ntt)
         assert w[0] == len(ref) and w[2] == 0
-        assert np.array_equal(w[8:8 + 3 * len(ref)].reshape(-1, 3), ref)
+        assert w[1] == len(om.gemm_q_tiles(m.sparse_info, m.info_indptr, B, m_rows, N, H, 128, ntt))
+        assert np.array_equal(w[8:8 + 4 * len(ref)].reshape(-1, 4), ref)
         for cache in (0, 1):
             rc = lib.fo_gemm_o_worklist(B, m_rows, K, H, 0, 128, 128, ntt, cache, _native.ptr(si), si.numel(),
                                         _native.ptr(ip), _native.ptr(ws), ws.numel(), st)

@@ -54,10 +54,10 @@ def test_static_scratch_entry_matches_workspace_entry(cuda_device):
 def test_static_scratch_entry_rejects_oversized_problems(cuda_device):
     lib = _native.load()
     cap = lib.fo_gemm_q_static_max_bytes()
-    B, M, N, K = 64, 128 * 64, 128 * 32, 64     # 131072 tiles -> 1.5 MiB of list, above the 1 MiB array
+    B, M, N, K = 64, 128 * 64, 128 * 64, 64     # 131072 list records of 16 bytes, above the 1 MiB array
     assert lib.fo_gemm_workspace_bytes(B, M, N, K, 128) > cap
     t = torch.zeros(16, dtype=torch.bfloat16, device=cuda_device)   # never dereferenced: the size check comes first
-    rc = lib.fo_gemm_q_static(_native.ptr(t), _native.ptr(t), _native.ptr(t), None, _native.FO_DTYPE_BF16, B, M, N, K, 32, 0,
+    rc = lib.fo_gemm_q_static(_native.ptr(t), _native.ptr(t), _native.ptr(t), None, _native.FO_DTYPE_BF16, B, M, N, K, 64, 0,
                               128, 128, 0, 1, None, 0, None, torch.cuda.current_stream(cuda_device).cuda_stream)
     assert rc == _native.FO_ERR_WORKSPACE
     msg = lib.fo_gemm_q_static_last_error().decode()
