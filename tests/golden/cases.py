@@ -1,0 +1,69 @@
+"""Definition of the golden cases: small seeded inputs (rebuilt identically wherever they are needed)
+whose outputs were produced by the REFERENCE's own CUDA kernels (see make_golden.py)."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from flashomni_b200 import workloads as wl
+
+
+def attention_case(name):
+    if name == "attn_uniform":
+        H, lens_q, lens_kv, density, seed = 2, [512], [512], 0.6, 101
+    elif name == "attn_ragged":
+        H, lens_q, lens_kv, density, seed = 3, [300, 205], [256, 333], 0.7, 102
+    else:
+        raise KeyError(name)
+    qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(lens_kv)]).astype(np.int32)
+    rng = np.random.default_rng(seed)
+    qa = [(rng.random((-(-a // 128), H)) < density).astype(np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // 128), H, -(-b // 128))) < density).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    for a, b in zip(qa, kk):
+        a[0, 0] = 1
+        b[0, 0, 0] = 1          # at least one non-trivial item
+        b *= a[:, :, None]
+        # the reference writes garbage-free output only if an active q-block keeps something; keep >= 1
+        for qb in range(a.shape[0]):
+            for h in range(H):
+                if a[qb, h] and b[qb, h].sum() == 0:
+                    b[qb, h, 0] = 1
+    m = wl.pack_masks(qa, kk)
+    q = wl.randn_bf16((int(qo[-1]), H, 128), seed + 1)
+    k = wl.randn_bf16((int(kv[-1]), H, 128), seed + 2)
+    v = wl.randn_bf16((int(kv[-1]), H, 128), seed + 3)
+    prior = wl.randn_bf16((int(qo[-1]), H, 128), seed + 4)
+    return {"q": q, "k": k, "v": v, "qo": qo, "kv": kv, "masks": m, "prior": prior, "H": H}
+
+
+def gemm_case(name):
+    if name == "gemm_q":
+        B, nq, H, K, seed = 1, 3, 2, 256, 201
+    elif name == "gemm_o":
+        B, nq, H, K, seed = 2, 2, 2, 256, 202
+    else:
+        raise KeyError(name)
+    m = wl.flux_masks(B, H, nq, nq, 0.5, seed=seed, text_blocks=1)
+    x = wl.randn_bf16((B, nq * 128, K), seed + 1)
+    w = wl.randn_bf16((H * 128, K), seed + 2, std=K ** -0.5)
+    bias = wl.randn_bf16((H * 128,), seed + 3)
+    prior = wl.randn_bf16((B, nq * 128, H * 128), seed + 4)
+    return {"x": x, "w": w, "bias": bias, "prior": prior, "masks": m, "H": H, "B": B}
+
+
+def packbits_case():
+    rng = np.random.default_rng(301)
+    lens = [0, 1, 7, 8, 9, 63, 64, 65, 1000, 2047]
+    indptr = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    x = rng.integers(0, 2, int(indptr[-1])).astype(np.uint8)
+    return x, indptr
+
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).cpu().numpy().copy()
+
+
+def from_bits(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
