@@ -71,3 +71,54 @@ class SparseDiTAttentionBlock:
         flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0, self.cache,
                                  is_for_cache=False, head_begin=hb, head_dim=D, out=self.y)
         return self.y
+
+
+class UlyssesSparseDiTAttentionBlock:
+    """The same block under Ulysses sequence parallelism (long video sequences, batch 1): this rank holds the
+    tokens [tok_begin, tok_end) (whole 128-token blocks) and full weights; the projections run on the local
+    tokens for all heads, an all-to-all regroups Q/K/V to [all tokens, local heads] for the attention, and a
+    second one brings the attention output back to [local tokens, all heads] for GEMM-O. With one rank the
+    exchanges are skipped."""
+
+    def __init__(self, weights: BlockWeights, num_heads: int, head_dim: int, num_tokens: int, rank: int, world: int,
+                 device, dtype=torch.bfloat16, group=None):
+        from . import parallel as par
+        self.par = par
+        self.w, self.H, self.D, self.S = weights, num_heads, head_dim, num_tokens
+        self.rank, self.world, self.group, self.device, self.dtype = rank, world, group, device, dtype
+        self.t0, self.t1 = par.token_range(num_tokens, rank, world)
+        self.s_loc = self.t1 - self.t0
+        if self.s_loc % 128 != 0:
+            raise ValueError("the local token count must be a multiple of 128 (GEMM row tiles)")
+        self.hb, self.hc = par.head_window(num_heads, rank, world)
+        hid_out = weights.wo.shape[0]
+        mk = lambda *s: torch.zeros(*s, dtype=dtype, device=device)
+        n = num_heads * head_dim
+        self.q, self.k, self.v = mk(1, self.s_loc, n), mk(1, self.s_loc, n), mk(1, self.s_loc, n)
+        self.attn = mk(num_tokens, self.hc, head_dim)
+        self.y = mk(1, self.s_loc, hid_out)
+        self.cache = mk(1, self.s_loc, hid_out)
+        self.wrapper = BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=device))
+        indptr = torch.tensor([0, num_tokens], dtype=torch.int32, device=device)
+        self.wrapper.plan(indptr, indptr, self.hc, self.hc, head_dim, q_data_type=dtype, mask_num_heads=num_heads,
+                          mask_head_begin=self.hb)
+
+    def forward(self, x_local, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr):
+        """x_local [1, local tokens, hidden] -> this rank's rows of the block output [1, local tokens, hidden]."""
+        H, D, S = self.H, self.D, self.S
+        # the row offset of the local tokens inside the sequence is what the ops call num_text_tokens
+        flashomni_gemm(x_local, self.w.wq, H, sparse_info, sparse_info_indptr, self.t0, None, out=self.q, head_dim=D)
+        flashomni_gemm(x_local, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
+        flashomni_gemm(x_local, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
+        if self.world > 1:
+            qh = self.par.tokens_to_heads(self.q.view(self.s_loc, H, D), S, self.group)
+            kh = self.par.tokens_to_heads(self.k.view(self.s_loc, H, D), S, self.group)
+            vh = self.par.tokens_to_heads(self.v.view(self.s_loc, H, D), S, self.group)
+        else:
+            qh, kh, vh = (t.view(S, H, D) for t in (self.q, self.k, self.v))
+        self.wrapper.run(qh, kh, vh, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
+                         out=self.attn)
+        o_loc = self.par.heads_to_tokens(self.attn, S, self.group) if self.world > 1 else self.attn
+        flashomni_gemm_reduction(o_loc.view(1, self.s_loc, H * D), self.w.wo, H, sparse_info, sparse_info_indptr,
+                                 self.t0, self.cache, is_for_cache=False, head_dim=D, out=self.y)
+        return self.y
