@@ -44,13 +44,17 @@ constexpr int kWarpMma = kWarpQK;               // owner of the TMEM allocation
 constexpr int kThreads = (kWarpPV + 1) * 32;    // 608
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
+#ifndef FO_TWO_BLOCK_STEPS
+#define FO_TWO_BLOCK_STEPS 0
+#endif
+constexpr bool kTwoBlockSteps = FO_TWO_BLOCK_STEPS != 0;  // softmax handles two blocks of an item per step
 constexpr int kPolyEvery = FO_POLY_EVERY;   // 1 in (2 * kPolyEvery) exponentials is computed by polynomial
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: keep the old max while exp2 stays <= 2^8
 
 struct Tail {
   uint64_t q_full[kQBufs], q_empty[kQBufs];
   uint64_t k_full[kRingK], k_empty[kRingK], v_full[kRingV], v_empty[kRingV];
-  uint64_t s_full[2];
+  uint64_t s_full[2], s_free[2];  // S buffer written by QK / copied to registers by the softmax
   uint64_t p_full[2], pv_done[2];  // indexed by block parity, so that no waiter can fall two phases behind
   uint64_t o_full, o_free;
   uint64_t xbar;          // barrier among the softmax warps (bounded, unlike bar.sync)
@@ -132,6 +136,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     for (int i = 0; i < kRingV; ++i) { mbar_init(&tail->v_full[i], 1); mbar_init(&tail->v_empty[i], 1); }
     mbar_init(&tail->s_full[0], 1);
     mbar_init(&tail->s_full[1], 1);
+    mbar_init(&tail->s_free[0], kSoftmaxWarps);
+    mbar_init(&tail->s_free[1], kSoftmaxWarps);
     for (int i = 0; i < 2; ++i) { mbar_init(&tail->p_full[i], kSoftmaxWarps); mbar_init(&tail->pv_done[i], 1); }
     mbar_init(&tail->o_full, 1);
     mbar_init(&tail->o_free, kSoftmaxWarps);
@@ -238,8 +244,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       while (ok && seq.next(a, ignore_empty)) {
         const uint32_t sb = g & 1u;
         const int qb_i = seq.item_no & 1;
-        // S[sb] is free once the softmax of block g-2 has handed over its P
-        if (g >= 2u && !mbar_wait(&tail->p_full[sb], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        // S[sb] is free once the softmax has copied block g-2 into registers
+        if (g >= 2u && !mbar_wait(&tail->s_free[sb], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
         if (seq.first()) {
           if (!mbar_wait(&tail->q_full[qb_i], q_uses[qb_i] & 1u, abort_flag)) { ok = false; break; }
           ++q_uses[qb_i];
@@ -406,31 +412,63 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     };
 
     int kv_len = 0;
+    uint32_t step_no = 0;
+    // One softmax step handles up to two consecutive blocks of an item (both S buffers): one max
+    // exchange, one rescale decision and one hand-over for 256 kv columns.
     while (ok && seq.next(a, on_empty)) {
       if (seq.first()) {
         m_used = -INFINITY;
         l = 0.f;
         kv_len = a.kv_indptr[seq.b + 1] - a.kv_indptr[seq.b];
       }
-      const uint32_t sb = g & 1u;
-      if (!mbar_wait(&tail->s_full[sb], s_uses[sb] & 1u, abort_flag)) { ok = false; break; }
-      ++s_uses[sb];
+      const bool step_first = seq.first();
+      const int valid0 = kv_len - seq.kvb * kBKV - static_cast<int>(col0);  // valid columns of my quarter
+      const bool two = kTwoBlockSteps && !seq.last();
+      int valid1 = 0;
+      if (two) {
+        seq.next(a, on_empty);  // stays inside the item
+        valid1 = kv_len - seq.kvb * kBKV - static_cast<int>(col0);
+      }
+      const uint32_t b0 = g & 1u, b1 = b0 ^ 1u;
+      if (!mbar_wait(&tail->s_full[b0], s_uses[b0] & 1u, abort_flag)) { ok = false; break; }
+      ++s_uses[b0];
+      if (two) {
+        if (!mbar_wait(&tail->s_full[b1], s_uses[b1] & 1u, abort_flag)) { ok = false; break; }
+        ++s_uses[b1];
+      }
       if (tracer) FO_TRACE(4, static_cast<int>(g));  // S ready seen by softmax
       tc_fence_after_sync();
-      const int valid = kv_len - seq.kvb * kBKV - static_cast<int>(col0);  // valid columns of my quarter
-      uint32_t s[32];
-      tmem_ld_x32(tmem_s0 + sb * 128u, s);
+      uint32_t s0[32], s1[32];
+      tmem_ld_x32(tmem_s0 + b0 * 128u, s0);
+      if (two) tmem_ld_x32(tmem_s0 + b1 * 128u, s1);
       tmem_wait_ld();
+      // both S buffers are in registers: the QK of the blocks after next may overwrite them
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&tail->s_free[b0]);
+        if (two) mbar_arrive(&tail->s_free[b1]);
+      }
       float mx = -INFINITY;
-      if (valid >= 32) {
+      if (valid0 >= 32) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(s[t]));
+        for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(s0[t]));
       } else {
 #pragma unroll
         for (int t = 0; t < 32; ++t)
-          if (t < valid) mx = fmaxf(mx, __uint_as_float(s[t]));
+          if (t < valid0) mx = fmaxf(mx, __uint_as_float(s0[t]));
       }
-      float* xm = tail->xmax[sb][0];
+      if (two) {
+        if (valid1 >= 32) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(s1[t]));
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t)
+            if (t < valid1) mx = fmaxf(mx, __uint_as_float(s1[t]));
+        }
+      }
+      float* xm = tail->xmax[step_no & 1u][0];
       xm[cq * kBQ + r_in_tile] = mx;
       if (!softmax_bar()) { ok = false; break; }
       if (tracer) FO_TRACE(5, static_cast<int>(g));  // max exchanged
@@ -439,7 +477,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       // ---- lazy rescale of l and O (warp-uniform decision; the TMEM round trip is warp-collective).
       // O is rescaled only after the PV of the previous block has completed.
       const bool need = (m_new - m_used) > kRescaleThreshold;  // true on an item's first block
-      if (seq.first()) {
+      if (step_first) {
         m_used = m_new;
       } else if (__any_sync(0xffffffffu, need)) {
         // PV of block g-1 is completion number (g-1)/2 on the barrier of its parity
@@ -455,32 +493,47 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
         tmem_st_x32(tmem_o, v);
       }
-      // ---- P = exp2(S*scale - m_used), row sum, P (16 bit) to its own TMEM buffer
+      // ---- P = exp2(S*scale - m_used), row sum, P (16 bit) to its own TMEM buffers
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      uint32_t pk[16];
+      auto exp_block = [&](const uint32_t (&s)[32], int valid, uint32_t (&pk)[16]) {
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        // every fourth pair takes the polynomial path (FMA pipe), the rest the MUFU path
-        float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * t]), a.sm_scale_log2, neg_m));
-        const float x1 = fmaf(__uint_as_float(s[2 * t + 1]), a.sm_scale_log2, neg_m);
-        float p1 = (t % kPolyEvery == 0) ? ex2_poly(x1) : ex2_approx(x1);
-        if (valid < 32) {
-          if (2 * t >= valid) p0 = 0.f;
-          if (2 * t + 1 >= valid) p1 = 0.f;
+        for (int t = 0; t < 16; ++t) {
+          // one pair in kPolyEvery takes the polynomial path (FMA pipe) for its second element
+          float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * t]), a.sm_scale_log2, neg_m));
+          const float x1 = fmaf(__uint_as_float(s[2 * t + 1]), a.sm_scale_log2, neg_m);
+          float p1 = (t % kPolyEvery == 0) ? ex2_poly(x1) : ex2_approx(x1);
+          if (valid < 32) {
+            if (2 * t >= valid) p0 = 0.f;
+            if (2 * t + 1 >= valid) p1 = 0.f;
+          }
+          l += p0 + p1;
+          pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
-        l += p0 + p1;
-        pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+      };
+      {
+        uint32_t pk[16];
+        exp_block(s0, valid0, pk);
+        // P[b0] was last read by the PV of block g-2
+        if (g >= 2u && !mbar_wait(&tail->pv_done[b0], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        tmem_st_x16(tmem_p0 + b0 * 64u, pk);
       }
-      // P[sb] was last read by the PV of block g-2
-      if (g >= 2u && !mbar_wait(&tail->pv_done[sb], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
-      tmem_st_x16(tmem_p0 + sb * 64u, pk);
+      if (two) {
+        uint32_t pk[16];
+        exp_block(s1, valid1, pk);
+        if (g >= 1u && !mbar_wait(&tail->pv_done[b1], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        tmem_st_x16(tmem_p0 + b1 * 64u, pk);
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tail->p_full[sb]);
+      if (lane == 0) {
+        mbar_arrive(&tail->p_full[b0]);
+        if (two) mbar_arrive(&tail->p_full[b1]);
+      }
       if (tracer) FO_TRACE(6, static_cast<int>(g));  // P handed over
-      ++g;
-      // the previous item's epilogue runs one block late, so that its last PV overlaps this softmax
+      g += two ? 2u : 1u;
+      ++step_no;
+      // the previous item's epilogue runs one step late, so that its last PV overlaps this softmax
       if (pend) {
         if (!epilogue()) { ok = false; break; }
       }

@@ -50,6 +50,17 @@ struct Tail {
 };
 constexpr int kSmemBytes = kStages * kStageBytes + kSlabBufs * kSlabBytes + 1024 + static_cast<int>(sizeof(Tail));
 
+#ifdef FO_GEMM_TRACE
+// Development aid (only with -DFO_GEMM_TRACE): CTA 0 records clock64() at pipeline events.
+__device__ long long g_gtrace[8][256];
+__device__ __forceinline__ void gtrace(int ev, int idx) {
+  if (blockIdx.x == 0 && idx >= 0 && idx < 256) g_gtrace[ev][idx] = clock64();
+}
+#define FO_GTRACE(ev, idx) gtrace(ev, idx)
+#else
+#define FO_GTRACE(ev, idx)
+#endif
+
 struct TileInfo {
   int a_row;             // first row of the A tile in [batch*m]
   int w_row0, w_row1;    // first rows of the two W blocks (= first output columns); w_row1 < 0: single
@@ -193,6 +204,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       uint32_t acc_phase = 0;
       bool ok = true;
       // every operand tile is K-major with 128-byte swizzle: same descriptor high word, low word = address
+      int tile_no = 0;
+      (void)tile_no;
       const uint64_t desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
       const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32), desc_lo0 = static_cast<uint32_t>(desc0);
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
@@ -200,6 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         const uint32_t idesc = ti.w_row1 >= 0 ? idesc256 : idesc128;
         if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
+        FO_GTRACE(0, tile_no);  // MMA: accumulator available, main loop starts
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 2 * kBNH);
         for (int j = 0; j < ti.nkb; ++j) {
           if (!mbar_wait(&tail->full[stage], phase, abort_flag)) { ok = false; break; }
@@ -215,6 +229,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         }
         if (!ok) break;
         umma_commit(&tail->acc_full[acc]);
+        FO_GTRACE(1, tile_no);  // MMA: main loop issued
+        ++tile_no;
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -225,6 +241,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     uint32_t acc_phase = 0;
     bool ok = true;
     uint32_t slab_count = 0;  // slabs handed to TMA stores so far (selects the staging buffer)
+    int epi_no = 0;
+    (void)epi_no;
     const uint16_t* init16 = reinterpret_cast<const uint16_t*>(a.init);
     const int r_in_tile = warp * 32 + lane;
     const uint32_t swz = static_cast<uint32_t>(r_in_tile & 7);
@@ -248,6 +266,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       };
       load_init(0);
       if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (threadIdx.x == 0) FO_GTRACE(2, epi_no);  // epilogue: accumulator full
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * 2 * kBNH);
 #pragma unroll 1
@@ -289,7 +308,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (s + 1 < nslab) load_init(s + 1);  // next slab's init loads fly during the store hand-off
         // staging buffer of this slab must no longer be read by the store issued two slabs ago
         uint8_t* buf = smem_slab + (slab_count & 1u) * kSlabBytes;
+        if (threadIdx.x == 0 && s == 0) FO_GTRACE(3, epi_no);  // slab 0 converted
         if (threadIdx.x == 0) tma_store_wait_read<1>();
+        if (threadIdx.x == 0 && s == 0) FO_GTRACE(4, epi_no);  // staging buffer free
         epi_bar();
         uint8_t* rowp = buf + r_in_tile * 128;
 #pragma unroll
@@ -303,6 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         }
         ++slab_count;
       }
+      if (threadIdx.x == 0) FO_GTRACE(5, epi_no);  // epilogue of the tile done
+      ++epi_no;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -327,6 +350,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 }
 
 }  // namespace
+
+#ifdef FO_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) int fo_gemm_trace_dump(long long* host_dst) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_dst, g_gtrace, sizeof(g_gtrace)));
+}
+#endif
 
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream) {
   const int cap = a.batch * (a.m / kBM) * ((a.n / kBNH + 1) / 2);
