@@ -89,6 +89,9 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         self._max_total_num_rows = None
         self._backend = backend
         self._planned = False
+        self._side_stream = None
+        self._prepared_event = None
+        self._prepared_key = None
 
     @property
     def is_cuda_graph_enabled(self) -> bool:
@@ -325,18 +328,13 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         ws = self._ws
         stream = _native.current_stream(self.device)
         with torch.cuda.device(self.device):
-            rc = lib.fo_mask_compact(
-                _native.ptr(sparse_info), 0 if sparse_info is None else sparse_info.numel(),
-                _native.ptr(sparse_kv_info), 0 if sparse_kv_info is None else sparse_kv_info.numel(),
-                _native.ptr(sparse_info_indptr), _native.ptr(sparse_kv_info_indptr),
-                _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
-                self._batch_size, self._mask_num_heads, self._mask_head_begin, self._num_qo_heads,
-                self._sparse_block_size_for_q, self._sparse_block_size_for_kv, 1 if is_full else 0,
-                self._n_cand, self._max_nkv, max(self._n_cand, 1), max(self._max_kept, 1),
-                _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
-                _native.ptr(ws["order"]), _native.ptr(ws["counters"]), _native.ptr(ws["scratch"]),
-                self._scratch_bytes, stream)
-            _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper.run (mask compaction)")
+            key = self._mask_key(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full)
+            if self._prepared_key is not None and self._prepared_key == key:
+                # the lists were built by prepare_masks() on the side stream: just order after it
+                torch.cuda.current_stream(self.device).wait_event(self._prepared_event)
+            else:
+                self._compact(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full, stream)
+            self._prepared_key = None
             rc = lib.fo_sparse_attn_fwd(
                 _native.ptr(q), _native.ptr(k), _native.ptr(v), _native.ptr(out), _native.ptr(lse),
                 native_dtype(q.dtype), self._total_q, self._total_kv, self._num_qo_heads, self._num_kv_heads,
@@ -352,6 +350,52 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         return (out, lse) if return_lse else out
 
     run_return_lse = functools.partialmethod(run, return_lse=True)
+
+    # ------------------------------------------------------------------------------------------ mask step
+    @staticmethod
+    def _mask_key(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full):
+        if is_full:
+            return ("full",)
+        return tuple((t.data_ptr(), t._version) for t in (sparse_info, sparse_kv_info, sparse_info_indptr,
+                                                          sparse_kv_info_indptr))
+
+    def _compact(self, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full, stream):
+        ws = self._ws
+        rc = _native.load().fo_mask_compact(
+            _native.ptr(sparse_info), 0 if sparse_info is None else sparse_info.numel(),
+            _native.ptr(sparse_kv_info), 0 if sparse_kv_info is None else sparse_kv_info.numel(),
+            _native.ptr(sparse_info_indptr), _native.ptr(sparse_kv_info_indptr),
+            _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
+            self._batch_size, self._mask_num_heads, self._mask_head_begin, self._num_qo_heads,
+            self._sparse_block_size_for_q, self._sparse_block_size_for_kv, 1 if is_full else 0,
+            self._n_cand, self._max_nkv, max(self._n_cand, 1), max(self._max_kept, 1),
+            _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
+            _native.ptr(ws["order"]), _native.ptr(ws["counters"]), _native.ptr(ws["scratch"]),
+            self._scratch_bytes, stream)
+        _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper (mask compaction)")
+
+    def prepare_masks(self, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
+                      is_full: bool = False) -> None:
+        """Optional (extension): builds the work lists for these mask tensors now, on a side stream that is
+        ordered after the current stream, so that the step overlaps whatever the caller enqueues next (the
+        Q/K/V projections). The following `run()` with the same, unmodified mask tensors re-uses the lists;
+        any other `run()` compacts as usual. Masks only depend on the block selection, not on q/k/v."""
+        if not self._planned:
+            raise RuntimeError("plan() must be called before prepare_masks()")
+        if not is_full:
+            if sparse_info_indptr.dtype != torch.int32 or sparse_kv_info_indptr.dtype != torch.int32:
+                return  # run() will convert and compact itself
+        with torch.cuda.device(self.device):
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(self.device)
+                self._prepared_event = torch.cuda.Event()
+            cur = torch.cuda.current_stream(self.device)
+            self._side_stream.wait_stream(cur)
+            self._compact(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full,
+                          self._side_stream.cuda_stream)
+            self._prepared_event.record(self._side_stream)
+        self._prepared_key = self._mask_key(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
+                                            is_full)
 
     # ------------------------------------------------------------------------------------------ extras
     def check_status(self) -> None:

@@ -60,6 +60,8 @@ class SparseDiTAttentionBlock:
     def forward(self, x, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr):
         """One sparse step. x [B, S, hidden]. Returns this rank's (partial) output [B, S, hidden]."""
         H, D, hb = self.H, self.D, self.hb
+        # the work lists only depend on the masks: build them beside the projections
+        self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr)
         flashomni_gemm(x, self.w.wq, H, sparse_info, sparse_info_indptr, 0, None, out=self.q,
                        head_begin=hb, head_dim=D)
         flashomni_gemm(x, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
@@ -106,6 +108,7 @@ class UlyssesSparseDiTAttentionBlock:
     def forward(self, x_local, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr):
         """x_local [1, local tokens, hidden] -> this rank's rows of the block output [1, local tokens, hidden]."""
         H, D, S = self.H, self.D, self.S
+        self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr)
         # the row offset of the local tokens inside the sequence is what the ops call num_text_tokens
         flashomni_gemm(x_local, self.w.wq, H, sparse_info, sparse_info_indptr, self.t0, None, out=self.q, head_dim=D)
         flashomni_gemm(x_local, self.w.wk, H, is_full=True, out=self.k, head_dim=D)

@@ -130,3 +130,23 @@ def test_flux_layer_size_sampled_heads(cuda_device):
         rows = act[h].repeat_interleave(128)
         ref = torch.where(rows[:, None], ref, dev(prior, cuda_device)[:, h].float())
         assert_close_bf16(o[:, h], ref, f"flux layer head {h} (gpu fp32)")
+
+
+def test_prepare_masks_on_side_stream_gives_identical_result(cuda_device):
+    H, S = 4, 1024
+    inp = wl.attention_inputs(1, H, S, 128, 0.5, seed=91)
+    w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, H)
+    si, skv, ip, kp = masks_to_device(inp.masks, cuda_device)
+    q, k, v = (dev(t, cuda_device) for t in (inp.q, inp.k, inp.v))
+    a = w.run(q, k, v, si, skv, ip, kp).clone()
+    w.prepare_masks(si, skv, ip, kp)
+    b = w.run(q, k, v, si, skv, ip, kp).clone()
+    w.check_status()
+    assert torch.equal(a, b)
+    # a mask changed in place after prepare_masks() must not re-use the prepared lists
+    w.prepare_masks(si, skv, ip, kp)
+    si.fill_(255)
+    c = w.run(q, k, v, si, skv, ip, kp).clone()
+    w.check_status()
+    assert w.work_lists()["n_items"] == H * (S // 128)   # every q-block active now: the lists were rebuilt
+    assert torch.equal(c, w.run(q, k, v, si, skv, ip, kp))
