@@ -57,8 +57,10 @@ class SparseDiTAttentionBlock:
                                  is_for_cache=True, head_begin=self.hb, head_dim=self.D, out=self.cache)
         return self.cache
 
-    def forward(self, x, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr):
-        """One sparse step. x [B, S, hidden]. Returns this rank's (partial) output [B, S, hidden]."""
+    def forward(self, x, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, out=None):
+        """One sparse step. x [B, S, hidden]. Returns this rank's (partial) output [B, S, hidden] (written
+        into `out` when given, else into the block's own buffer)."""
+        y = self.y if out is None else out
         H, D, hb = self.H, self.D, self.hb
         # the work lists only depend on the masks: build them beside the projections
         self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr)
@@ -71,8 +73,8 @@ class SparseDiTAttentionBlock:
                          sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                          out=self.attn.view(T, self.hc, D))
         flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0, self.cache,
-                                 is_for_cache=False, head_begin=hb, head_dim=D, out=self.y)
-        return self.y
+                                 is_for_cache=False, head_begin=hb, head_dim=D, out=y)
+        return y
 
 
 class UlyssesSparseDiTAttentionBlock:
