@@ -254,7 +254,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (!mbar_wait(&tail->k_full[slot], (nk / kRingK) & 1u, abort_flag)) { ok = false; break; }
         ++nk;
         tc_fence_after_sync();
-        FO_TRACE(0, static_cast<int>(g));  // QK batch start
         const uint32_t q_lo = q_lo0 + static_cast<uint32_t>((qb_i * kTileBytes) >> 4);
         const uint32_t k_lo = k_lo0 + static_cast<uint32_t>((slot * kTileBytes) >> 4);
         uint32_t la[8], lb[8];
@@ -269,7 +268,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         umma_commit(&tail->s_full[sb]);
         umma_commit(&tail->k_empty[slot]);
         if (seq.last()) umma_commit(&tail->q_empty[qb_i]);
-        FO_TRACE(1, static_cast<int>(g));  // QK batch issued
         ++g;
       }
     }
@@ -294,7 +292,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (!mbar_wait(&tail->v_full[slot], (nv / kRingV) & 1u, abort_flag)) { ok = false; break; }
         ++nv;
         tc_fence_after_sync();
-        FO_TRACE(2, static_cast<int>(g));  // PV batch start
         const uint32_t tmem_p = tmem_base + kColP + sb * 64u;
         const uint32_t v_lo = v_lo0 + static_cast<uint32_t>((slot * kTileBytes) >> 4);
         uint32_t ta[8], lb[8];
@@ -308,7 +305,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         umma_commit(&tail->pv_done[sb]);
         umma_commit(&tail->v_empty[slot]);
         if (seq.last()) umma_commit(&tail->o_full);
-        FO_TRACE(3, static_cast<int>(g));  // PV batch issued
         if (seq.first()) ++items_started;
         ++g;
       }
@@ -371,7 +367,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     uint32_t g = 0;           // global block index
     uint32_t s_uses[2] = {0, 0};
     uint32_t items_done = 0;  // epilogues completed
-    float m_used = -INFINITY, l = 0.f;
+    float m_used = -INFINITY;
+    uint64_t l2 = 0;  // running row sum of this thread's columns, as a packed pair of partial sums
     // an item whose last block has been handed over and whose O is still being accumulated
     bool pend = false;
     float pend_l = 0.f, pend_m = 0.f;
@@ -418,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     while (ok && seq.next(a, on_empty)) {
       if (seq.first()) {
         m_used = -INFINITY;
-        l = 0.f;
+        l2 = 0;
         kv_len = a.kv_indptr[seq.b + 1] - a.kv_indptr[seq.b];
       }
       const bool step_first = seq.first();
@@ -442,6 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       tmem_ld_x32(tmem_s0 + b0 * 128u, s0);
       if (two) tmem_ld_x32(tmem_s0 + b1 * 128u, s1);
       tmem_wait_ld();
+      if (tracer) FO_TRACE(0, static_cast<int>(g));  // S in registers
       // both S buffers are in registers: the QK of the blocks after next may overwrite them
       tc_fence_before_sync();
       __syncwarp();
@@ -452,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       float mx = -INFINITY;
       if (valid0 >= 32) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(s0[t]));
+        for (int t = 0; t < 16; ++t) mx = fmax3(mx, __uint_as_float(s0[2 * t]), __uint_as_float(s0[2 * t + 1]));
       } else {
 #pragma unroll
         for (int t = 0; t < 32; ++t)
@@ -461,13 +459,14 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       if (two) {
         if (valid1 >= 32) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(s1[t]));
+          for (int t = 0; t < 16; ++t) mx = fmax3(mx, __uint_as_float(s1[2 * t]), __uint_as_float(s1[2 * t + 1]));
         } else {
 #pragma unroll
           for (int t = 0; t < 32; ++t)
             if (t < valid1) mx = fmaxf(mx, __uint_as_float(s1[t]));
         }
       }
+      if (tracer) FO_TRACE(1, static_cast<int>(g));  // local max done
       float* xm = tail->xmax[step_no & 1u][0];
       xm[cq * kBQ + r_in_tile] = mx;
       if (!softmax_bar()) { ok = false; break; }
@@ -485,7 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         tc_fence_after_sync();
         const float alpha = need ? ex2_approx(m_used - m_new) : 1.0f;
         if (need) m_used = m_new;
-        l *= alpha;
+        l2 = ffma2(l2, pack_f32x2(alpha, alpha), 0ull);
         uint32_t v[32];
         tmem_ld_x32(tmem_o, v);
         tmem_wait_ld();
@@ -495,26 +494,41 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       }
       // ---- P = exp2(S*scale - m_used), row sum, P (16 bit) to its own TMEM buffers
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+      const uint64_t scale2 = pack_f32x2(a.sm_scale_log2, a.sm_scale_log2);
+      const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
       auto exp_block = [&](const uint32_t (&s)[32], int valid, uint32_t (&pk)[16]) {
+        if (valid >= 32) {
+          // packed path: one FMA and one add per PAIR of columns; one pair in kPolyEvery takes the
+          // polynomial exp2 (FMA pipe) for its second element, the rest use MUFU
 #pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          // one pair in kPolyEvery takes the polynomial path (FMA pipe) for its second element
-          float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * t]), a.sm_scale_log2, neg_m));
-          const float x1 = fmaf(__uint_as_float(s[2 * t + 1]), a.sm_scale_log2, neg_m);
-          float p1 = (t % kPolyEvery == 0) ? ex2_poly(x1) : ex2_approx(x1);
-          if (valid < 32) {
+          for (int t = 0; t < 16; ++t) {
+            const uint64_t x2 = ffma2(pack_f32x2(__uint_as_float(s[2 * t]), __uint_as_float(s[2 * t + 1])), scale2, negm2);
+            float x0, x1;
+            unpack_f32x2(x2, x0, x1);
+            const float p0 = ex2_approx(x0);
+            const float p1 = (t % kPolyEvery == 0) ? ex2_poly(x1) : ex2_approx(x1);
+            l2 = fadd2(l2, pack_f32x2(p0, p1));
+            pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * t]), a.sm_scale_log2, neg_m));
+            float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * t + 1]), a.sm_scale_log2, neg_m));
             if (2 * t >= valid) p0 = 0.f;
             if (2 * t + 1 >= valid) p1 = 0.f;
+            l2 = fadd2(l2, pack_f32x2(p0, p1));
+            pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
           }
-          l += p0 + p1;
-          pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
       };
       {
         uint32_t pk[16];
         exp_block(s0, valid0, pk);
+        if (tracer) FO_TRACE(2, static_cast<int>(g));  // exponentials done
         // P[b0] was last read by the PV of block g-2
         if (g >= 2u && !mbar_wait(&tail->pv_done[b0], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (tracer) FO_TRACE(3, static_cast<int>(g));  // pv_done seen
         tmem_st_x16(tmem_p0 + b0 * 64u, pk);
       }
       if (two) {
@@ -524,6 +538,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         tmem_st_x16(tmem_p0 + b1 * 64u, pk);
       }
       tmem_wait_st();
+      if (tracer) FO_TRACE(7, static_cast<int>(g));  // P stored
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -539,7 +554,11 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       }
       if (seq.last()) {
         pend = true;
-        pend_l = l;
+        {
+          float la, lb;
+          unpack_f32x2(l2, la, lb);
+          pend_l = la + lb;
+        }
         pend_m = m_used;
         pend_ctx = row_ctx(seq.b, seq.h, seq.qb);
       }
