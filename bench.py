@@ -196,6 +196,20 @@ def run_ours(args):
         step()
     torch.cuda.synchronize()
     block.wrapper.check_status()
+    graph = None
+    if args.graph:
+        # one CUDA graph per step (the launches of a step are fixed for fixed shapes and mask buffers)
+        graph = torch.cuda.CUDAGraph()
+        cs = torch.cuda.Stream(device)
+        cs.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(cs):
+            with torch.cuda.graph(graph, stream=cs):
+                step()
+        eager_step = step
+        step = graph.replay  # noqa: F841
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     sampler.start()
     ms = timed(step, args.steps)
@@ -270,7 +284,7 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "flux_block: hidden 3072, H=24, D=128, S=4608, batch 2, block density 0.5 "
                                    "(GEMM-Q sparse, GEMM-K/V dense, block-sparse attention, GEMM-O active heads + cache)",
-                       "parallelism": f"heads/{world}", "seed": SEED,
+                       "parallelism": f"heads/{world}", "seed": SEED, "cuda_graph": bool(args.graph),
                        "l2": "per-step working set (x, 4 weights, q/k/v, attention out, cache, y) is >200 MB per rank, "
                              "larger than the 126 MB L2; no explicit flush",
                        "executed_flops_per_step": fl_total, "active_pairs": fl["active_pairs"],
@@ -440,6 +454,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="flux_block", choices=["flux_block", "video"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="replay the step from a CUDA graph (device-resident leg only)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -46,7 +46,7 @@ struct Tail {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int heads[kMaxHeadsSmem];  // GEMM-O: the current tile's head list, staged for the producer
+  int heads[2][kMaxHeadsSmem];  // GEMM-O: head lists of the current and the next tile, staged for the producer
 };
 constexpr int kSmemBytes = kStages * kStageBytes + kSlabBufs * kSlabBytes + 1024 + static_cast<int>(sizeof(Tail));
 
@@ -162,24 +162,47 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     // ------------------------------------------------------------- TMA producer
     // All lanes stage the tile's head list in shared memory (one coalesced read instead of one
     // dependent global load per K block); lane 0 then issues the copies.
+    // The head list of tile i+1 is fetched into registers while lane 0 feeds tile i, so that the
+    // dependent global loads (row order -> row indptr -> heads) never sit between two tiles.
     int stage = 0;
     uint32_t phase = 0;
     int ok = 1;
-    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-      TileInfo ti = get_tile(a, t);
-      if (ti.heads != nullptr) {
-        const int nh = ti.nkb / a.kb_per_head;
-        if (nh <= kMaxHeadsSmem) {
-          for (int i = lane; i < nh; i += 32) tail->heads[i] = ti.heads[i];
-          ti.heads = tail->heads;
-        }
+    const int t0 = static_cast<int>(blockIdx.x), dt = static_cast<int>(gridDim.x);
+    TileInfo nxt;
+    nxt.a_row = nxt.w_row0 = nxt.nkb = 0; nxt.w_row1 = -1; nxt.heads = nullptr;
+    int hreg[kMaxHeadsSmem / 32];
+    auto fetch_heads = [&](const TileInfo& ti) {
+      if (ti.heads == nullptr) return;
+      const int nh = ti.nkb / a.kb_per_head;
+#pragma unroll
+      for (int i = 0; i < kMaxHeadsSmem / 32; ++i) hreg[i] = (lane + 32 * i < nh && nh <= kMaxHeadsSmem) ? ti.heads[lane + 32 * i] : 0;
+    };
+    auto stash_heads = [&](int par) {
+#pragma unroll
+      for (int i = 0; i < kMaxHeadsSmem / 32; ++i) tail->heads[par][lane + 32 * i] = hreg[i];
+    };
+    if (t0 < n_tiles) {
+      nxt = get_tile(a, t0);
+      fetch_heads(nxt);
+      stash_heads(0);
+    }
+    __syncwarp();
+    int par = 0;
+    for (int t = t0; t < n_tiles && ok; t += dt, par ^= 1) {
+      TileInfo ti = nxt;
+      if (ti.heads != nullptr && ti.nkb / a.kb_per_head <= kMaxHeadsSmem) ti.heads = tail->heads[par];
+      const bool more = t + dt < n_tiles;
+      if (more) {
+        nxt = get_tile(a, t + dt);
+        fetch_heads(nxt);
       }
-      __syncwarp();
       if (lane == 0) {
         const uint32_t bytes = ti.w_row1 >= 0 ? kStageBytes : (kABytes + kBHalfBytes);
+        // K columns are generated without divisions: (head list entry, K block inside the head)
+        int hh = 0, sub = 0;
+        int kcol = (ti.heads != nullptr && ti.nkb > 0) ? ti.heads[0] * a.kb_per_head * kBK : 0;
         for (int j = 0; j < ti.nkb; ++j) {
           if (!mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag)) { ok = 0; break; }
-          const int kcol = kcol_of(a, ti, j);
           uint8_t* sa = smem + stage * kStageBytes;
           mbar_expect_tx(&tail->full[stage], bytes);
           tma_load_2d(sa, &a.tmap_a, &tail->full[stage], kcol, ti.a_row);
@@ -187,8 +210,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           if (ti.w_row1 >= 0)
             tma_load_2d(sa + kABytes + kBHalfBytes, &a.tmap_b, &tail->full[stage], kcol, ti.w_row1);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          // next K block
+          if (ti.heads == nullptr) {
+            kcol += kBK;
+          } else if (++sub < a.kb_per_head) {
+            kcol += kBK;
+          } else {
+            sub = 0;
+            ++hh;
+            if (j + 1 < ti.nkb) kcol = ti.heads[hh] * a.kb_per_head * kBK;
+          }
         }
       }
+      __syncwarp();
+      if (more) stash_heads(par ^ 1);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       stage = __shfl_sync(0xffffffffu, stage, 0);
       phase = __shfl_sync(0xffffffffu, phase, 0);
@@ -208,8 +243,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       (void)tile_no;
       const uint64_t desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
       const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32), desc_lo0 = static_cast<uint32_t>(desc0);
+      TileInfo nxt;
+      nxt.a_row = nxt.w_row0 = nxt.nkb = 0; nxt.w_row1 = -1; nxt.heads = nullptr;
+      if (static_cast<int>(blockIdx.x) < n_tiles) nxt = get_tile(a, blockIdx.x);
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        const TileInfo ti = get_tile(a, t);
+        const TileInfo ti = nxt;  // the next tile's record is fetched while this one runs
+        if (t + static_cast<int>(gridDim.x) < n_tiles) nxt = get_tile(a, t + gridDim.x);
         const uint32_t idesc = ti.w_row1 >= 0 ? idesc256 : idesc128;
         if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
@@ -246,8 +285,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     const uint16_t* init16 = reinterpret_cast<const uint16_t*>(a.init);
     const int r_in_tile = warp * 32 + lane;
     const uint32_t swz = static_cast<uint32_t>(r_in_tile & 7);
+    TileInfo nxt;
+    nxt.a_row = nxt.w_row0 = nxt.nkb = 0; nxt.w_row1 = -1; nxt.heads = nullptr;
+    if (static_cast<int>(blockIdx.x) < n_tiles) nxt = get_tile(a, blockIdx.x);
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-      const TileInfo ti = get_tile(a, t);
+      const TileInfo ti = nxt;
+      if (t + static_cast<int>(gridDim.x) < n_tiles) nxt = get_tile(a, t + gridDim.x);
       const int64_t row = static_cast<int64_t>(ti.a_row) + r_in_tile;
       const int nslab = ti.w_row1 >= 0 ? 4 : 2;
       // init values of slab 0 are fetched before the accumulator is waited for

@@ -113,6 +113,23 @@ __device__ __forceinline__ int get_bit(const uint8_t* seg, int64_t pos, int64_t 
   return (seg[bi] >> (pos & 7)) & 1;
 }
 
+// up to 64 bits of the stream starting at bit `pos` (9 independent byte loads, clamped like load_bits32)
+__device__ __forceinline__ uint64_t load_bits64(const uint8_t* seg, int64_t pos, int64_t limit, int nbits) {
+  const int64_t byte0 = pos >> 3;
+  const int sh = static_cast<int>(pos & 7);
+  uint64_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t bi = byte0 + i;
+    const uint64_t v = (bi < limit) ? seg[bi] : 0u;
+    lo |= v << (8 * i);
+  }
+  if (byte0 + 8 < limit) hi = seg[byte0 + 8];
+  uint64_t r = sh ? ((lo >> sh) | (hi << (64 - sh))) : lo;
+  if (nbits < 64) r &= (1ull << nbits) - 1ull;
+  return r;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Attention mask compaction
 // ---------------------------------------------------------------------------------------------
@@ -426,6 +443,8 @@ __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
     int cnt = 0;
     const uint8_t* seg = nullptr;
     int64_t limit = 0, bit0 = 0;
+    uint64_t rowbits = 0;
+    bool fast = false;
     if (r < rows) {
       const int b = r / mt, iy = r % mt;
       if (a.is_full) {
@@ -436,7 +455,13 @@ __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
         limit = a.info_bytes - ioff;
         const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
         bit0 = qb * a.num_heads + a.head_begin;
-        for (int ix = 0; ix < nt; ++ix) cnt += get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit);
+        if (a.head_dim == 128 && nt <= 64) {  // one bit per column block: fetch the row's bits at once
+          rowbits = load_bits64(seg, bit0, limit, nt);
+          cnt = __popcll(rowbits);
+          fast = true;
+        } else {
+          for (int ix = 0; ix < nt; ++ix) cnt += get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit);
+        }
       }
     }
     const int recs = (cnt + 1) >> 1;
@@ -466,7 +491,8 @@ __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
       const int b = r / mt, iy = r % mt;
       int first = -1;
       for (int ix = 0; ix < nt; ++ix) {
-        const int on = a.is_full ? 1 : get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit);
+        const int on = a.is_full ? 1 : (fast ? static_cast<int>((rowbits >> ix) & 1ull)
+                                               : get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit));
         if (!on) continue;
         if (first < 0) {
           first = ix;
@@ -507,13 +533,20 @@ __global__ void __launch_bounds__(1024) gemm_o_rows_kernel(GemmListArgs a) {
   for (int base = 0; base < rows; base += blockDim.x) {
     const int r = base + tid;
     int cnt = 0;
+    uint64_t rowbits = 0;
     if (r < rows) {
       const int b = r / mt, iy = r % mt;
       const int64_t ioff = a.info_indptr[b];
       const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
       const int64_t bit0 = qb * a.num_heads + a.head_begin;
-      for (int h = 0; h < local_heads; ++h)
-        cnt += get_bit(a.sparse_info + ioff, bit0 + h, a.info_bytes - ioff) == want;
+      if (local_heads <= 64) {  // fetch the row's bits at once
+        rowbits = load_bits64(a.sparse_info + ioff, bit0, a.info_bytes - ioff, local_heads);
+        if (!want) rowbits = ~rowbits & (local_heads < 64 ? ((1ull << local_heads) - 1ull) : ~0ull);
+        cnt = __popcll(rowbits);
+      } else {
+        for (int h = 0; h < local_heads; ++h)
+          cnt += get_bit(a.sparse_info + ioff, bit0 + h, a.info_bytes - ioff) == want;
+      }
     }
     int x = cnt;
 #pragma unroll
@@ -542,8 +575,16 @@ __global__ void __launch_bounds__(1024) gemm_o_rows_kernel(GemmListArgs a) {
       const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
       const int64_t bit0 = qb * a.num_heads + a.head_begin;
       int w = off;
-      for (int h = 0; h < local_heads; ++h)
-        if (get_bit(a.sparse_info + ioff, bit0 + h, a.info_bytes - ioff) == want) a.row_heads[w++] = h;
+      if (local_heads <= 64) {
+        uint64_t bits = rowbits;
+        while (bits) {
+          a.row_heads[w++] = __ffsll(static_cast<long long>(bits)) - 1;
+          bits &= bits - 1;
+        }
+      } else {
+        for (int h = 0; h < local_heads; ++h)
+          if (get_bit(a.sparse_info + ioff, bit0 + h, a.info_bytes - ioff) == want) a.row_heads[w++] = h;
+      }
     }
     __syncthreads();
     if (tid == 0) s_carry += s_warp[31];

@@ -150,3 +150,41 @@ def test_prepare_masks_on_side_stream_gives_identical_result(cuda_device):
     w.check_status()
     assert w.work_lists()["n_items"] == H * (S // 128)   # every q-block active now: the lists were rebuilt
     assert torch.equal(c, w.run(q, k, v, si, skv, ip, kp))
+
+
+def test_block_forward_is_cuda_graph_capturable(cuda_device, monkeypatch):
+    monkeypatch.delenv("FLASHOMNI_B200_CHECK", raising=False)  # the debug checks synchronise: not capturable
+    _block_graph_capture(cuda_device)
+
+
+def _block_graph_capture(cuda_device):
+    """The whole block (projections, side-stream mask compaction, attention, GEMM-O) captured in one CUDA graph
+    and replayed gives the eager result (the reference supports graph capture of run(), attention.py:353-377)."""
+    from flashomni_b200.layer import BlockWeights, SparseDiTAttentionBlock
+    B, H, S, hid = 1, 4, 1024, 512
+    m = wl.flux_masks(B, H, S // 128, S // 128, 0.5, seed=93, text_blocks=1)
+    si, skv, ip, kp = masks_to_device(m, cuda_device)
+    ws = [dev(wl.randn_bf16((hid, hid), 94 + i, std=hid ** -0.5), cuda_device) for i in range(4)]
+    blk = SparseDiTAttentionBlock(BlockWeights(*ws), H, 128, B, S, device=cuda_device)
+    blk.cache.copy_(dev(wl.randn_bf16((B, S, hid), 99), cuda_device))
+    x = dev(wl.randn_bf16((B, S, hid), 98), cuda_device)
+    for _ in range(2):
+        eager = blk.forward(x, si, skv, ip, kp).clone()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            y = blk.forward(x, si, skv, ip, kp)
+    blk.y.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    blk.wrapper.check_status()
+    assert torch.equal(y, eager)
+    # new input, same graph
+    x.copy_(dev(wl.randn_bf16((B, S, hid), 97), cuda_device))
+    g.replay()
+    torch.cuda.synchronize()
+    replayed = y.clone()
+    assert torch.equal(replayed, blk.forward(x, si, skv, ip, kp))
