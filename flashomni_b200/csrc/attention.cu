@@ -7,24 +7,31 @@
 // never written. An item with an empty list writes zeros (lse = -5e4), like the reference.
 //
 // One persistent CTA per SM walks its items (dealt round-robin in longest-first order) as ONE
-// sequence of kv blocks g = 0, 1, 2, ... and software-pipelines it three deep:
+// sequence of kv blocks g = 0, 1, 2, ... and software-pipelines it:
 //
-//   round r:   tensor pipe   S[(r+1)&1] = Q K_{r+1}^T   interleaved with   O += P[(r-1)&1] V_{r-1}
-//              softmax warps block r: S[r&1] -> P[r&1]
+//   tensor pipe     S[g&1] = Q K_g^T   (QK issuer)   and   O (+)= P[g&1] V_g   (PV issuer)
+//   softmax group   g&1:  S[g&1] -> registers -> P[g&1]
 //
-// TMEM (512 columns): S0, S1 (fp32, 128 each), O (fp32, 128), P0, P1 (16 bit, 64 each). Because S is
-// double-buffered and P does not alias S, the QK and PV batches of a round are independent of each
-// other and of the softmax of the block in between; they are issued by two different threads, because
-// a thread that issues a batch is held until the batch has drained.
-// Warps: 0-15 softmax / O-rescale / epilogue (4 threads per q row: TMEM lane = row, 32 columns
-// each), 16 TMA producer (double-buffered Q tile + two-slot FIFOs of 32 KB K and V tiles, K running two
-// blocks ahead of V), 17 QK issuer, 18 PV issuer. Every mbarrier wait is bounded.
+// TMEM (512 columns): S0, S1 (fp32, 128 each), O (fp32, 128), P0, P1 (16 bit, 64 each). S is
+// double-buffered and P does not alias S, so the QK and PV batches are independent of each other and
+// of the softmax in between; they are issued by two different threads, because a thread that issues a
+// batch is held until the batch has drained.
+// The softmax is split into two groups of four warps that take alternate blocks (group = g & 1), one
+// thread per q row with all 128 columns of the block in registers: no exchange inside a group, and
+// while one group is in its exponential phase (MUFU-bound) the other one loads, reduces and hands
+// over, so that the special-function unit and the tensor pipe both stay busy. The running maximum
+// passes from block to block through shared memory (m_pub / m_ready); each group keeps its own
+// partial row sum, and the two are merged, with the output, in the epilogue (each group writes one
+// 64-column half of the row).
+// Warps: 0-3 softmax group 0, 4-7 softmax group 1 (TMEM lane = q row), 8 TMA producer of Q
+// (double-buffered) and K (two-slot FIFO of 32 KB tiles), 9 QK issuer, 10 PV issuer, 11 TMA producer
+// of V (its own two-slot FIFO). Every mbarrier wait is bounded.
 #include <cuda_fp16.h>
 
 #include "internal.h"
 
-#ifndef FO_POLY_EVERY
-#define FO_POLY_EVERY 4
+#ifndef FO_ROT_STEP
+#define FO_ROT_STEP 5
 #endif
 
 namespace fo {
@@ -36,46 +43,110 @@ constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half (one swizzle-a
 constexpr int kRingK = 2, kRingV = 2;  // separate FIFOs of 32 KB tiles for K and V
 constexpr int kRing = kRingK + kRingV;
 constexpr int kQBufs = 2;
-constexpr int kSoftmaxWarps = 16;
+constexpr int kGroupWarps = 8;                  // warps of one softmax group (two threads per q row)
+constexpr int kSoftmaxWarps = 2 * kGroupWarps;
 constexpr int kWarpProducer = kSoftmaxWarps;
 constexpr int kWarpQK = kSoftmaxWarps + 1;      // issues S = Q K^T
 constexpr int kWarpPV = kSoftmaxWarps + 2;      // issues O += P V
+constexpr int kWarpProducerV = kSoftmaxWarps + 3;
 constexpr int kWarpMma = kWarpQK;               // owner of the TMEM allocation
-constexpr int kThreads = (kWarpPV + 1) * 32;    // 608
+constexpr int kThreads = (kSoftmaxWarps + 4) * 32;  // 640: four softmax warpgroups and the producer / issuer warpgroup
+constexpr int kRegsSoftmax = 112, kRegsOther = 32;  // register split between the warpgroups (setmaxnreg)
+// setmaxnreg.inc waits until the registers are free in the pool the CTA was launched with (threads x the
+// per-thread count the compiler settles on for this block size): a split that asks for more never returns.
+constexpr int kRegsAtLaunch = (65536 / kThreads) / 8 * 8;
+static_assert(kSoftmaxWarps * 32 * kRegsSoftmax + (kThreads - kSoftmaxWarps * 32) * kRegsOther <= kThreads * kRegsAtLaunch,
+              "register split exceeds the CTA's register pool");
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
-#ifndef FO_TWO_BLOCK_STEPS
-#define FO_TWO_BLOCK_STEPS 0
-#endif
-constexpr bool kTwoBlockSteps = FO_TWO_BLOCK_STEPS != 0;  // softmax handles two blocks of an item per step
-constexpr int kPolyEvery = FO_POLY_EVERY;   // 1 in (2 * kPolyEvery) exponentials is computed by polynomial
+constexpr int kRotStep = FO_ROT_STEP;       // q-block qb starts its kv list at entry (qb * kRotStep) mod length
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: keep the old max while exp2 stays <= 2^8
 
 struct Tail {
   uint64_t q_full[kQBufs], q_empty[kQBufs];
   uint64_t k_full[kRingK], k_empty[kRingK], v_full[kRingV], v_empty[kRingV];
-  uint64_t s_full[2], s_free[2];  // S buffer written by QK / copied to registers by the softmax
+  uint64_t s_full[2], s_free[2];  // S buffer written by QK / copied to registers by its softmax group
   uint64_t p_full[2], pv_done[2];  // indexed by block parity, so that no waiter can fall two phases behind
+  uint64_t m_ready[2];             // running maximum after a block of this parity has been published
+  uint64_t stats_ready[2];         // indexed by item parity: both groups have published (m, l) of the item
   uint64_t o_full, o_free;
-  uint64_t xbar;          // barrier among the softmax warps (bounded, unlike bar.sync)
   uint32_t tmem_base;
   int abort_flag;
-  float xmax[2][4][128];  // [block parity][column quarter][row]: partial row maxima
-  float xsum[4][128];     // [column quarter][row]: partial row sums
+  uint64_t pair_bar[2][4];   // [group][quadrant]: the two warps that share 32 rows
+  float m_pub[2][128];       // [block parity][row]: running maximum in use after that block
+  float xmax[2][2][2][128];  // [group][parity of the group's block count][column half][row]: half-row maxima
+  float stats_m[2][4][128];  // [item parity][2 * group + half][row]: the maximum the partial sum refers to
+  float stats_l[2][4][128];  // [item parity][2 * group + half][row]: partial row sum
 };
-constexpr int kSmemBytes = (kQBufs + kRing) * kTileBytes + 1024 + static_cast<int>(sizeof(Tail));
 
 #ifdef FO_ATTN_TRACE
-// Development aid (only with -DFO_ATTN_TRACE): CTA 0 records clock64() at pipeline events.
-__device__ long long g_trace[8][512];
-__device__ __forceinline__ void trace(int ev, int idx) {
-  if (blockIdx.x == 0 && idx >= 0 && idx < 512) g_trace[ev][idx] = clock64();
+// Development aid (only with -DFO_ATTN_TRACE): CTA 0 records the low 32 bits of clock64() at pipeline
+// events into shared memory (a global store before an mbarrier arrive would delay the arrive) and
+// copies the table out when it exits.
+constexpr int kTraceEvents = 18, kTraceSlots = 256;
+__device__ uint32_t g_trace[kTraceEvents * kTraceSlots];
+__device__ __forceinline__ void trace(uint32_t* tr, int ev, int idx) {
+  if (blockIdx.x == 0 && idx >= 0 && idx < kTraceSlots) tr[ev * kTraceSlots + idx] = static_cast<uint32_t>(clock64());
 }
-#define FO_TRACE(ev, idx) trace(ev, idx)
+#define FO_TRACE(ev, idx) trace(trace_buf, ev, idx)
+#define FO_TRACE_TIME(ev, idx) do { if (blockIdx.x == 0) trace_buf[(ev) * kTraceSlots + (idx)] = static_cast<uint32_t>(global_timer_ns()); } while (0)
+constexpr int kTraceBytes = kTraceEvents * kTraceSlots * 4;
 #else
+#define FO_TRACE_TIME(ev, idx)
 #define FO_TRACE(ev, idx)
+constexpr int kTraceBytes = 0;
 #endif
 
+
+constexpr int kSmemBytes = (kQBufs + kRing) * kTileBytes + 1024 + static_cast<int>(sizeof(Tail)) + kTraceBytes;
+
+// The kept kv blocks of an item are visited in rotated order (the online softmax does not care):
+// q-block qb starts at entry (qb * kRotStep) mod length of its list.
+__device__ __forceinline__ int rot_of(int qb, int n) {
+  return static_cast<int>(static_cast<unsigned>(qb * kRotStep) % static_cast<unsigned>(n));
+}
+
+// The same walk for the softmax groups, which do not need the kv-block indices: only which step of an
+// item (if any) is the ragged last block of its request. No global load sits between two blocks.
+struct GroupSeq {
+  int pos, stride, n_items;
+  int b, h, qb, n, j;
+  int kv_len;
+  int ragged_j, ragged_valid;  // visiting step of the request's partial last kv block (-1: none) and its columns
+  __device__ __forceinline__ void init(int start, int stride_, int n_items_) {
+    pos = start; stride = stride_; n_items = n_items_; n = 0; j = 0;
+    b = h = qb = 0; kv_len = 0; ragged_j = -1; ragged_valid = 0;
+  }
+  template <class F>
+  __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
+    if (j + 1 < n) { ++j; return true; }
+    while (pos < n_items) {
+      const int it = a.order[pos];
+      pos += stride;
+      const int4 rec = *reinterpret_cast<const int4*>(a.items + 4 * it);
+      if (rec.w <= 0) { on_empty(rec.x, rec.y, rec.z); continue; }
+      b = rec.x; h = rec.y; qb = rec.z; n = rec.w; j = 0;
+      kv_len = a.kv_indptr[b + 1] - a.kv_indptr[b];
+      ragged_j = -1;
+      const int tail_cols = kv_len % kBKV;
+      if (tail_cols != 0) {
+        // lists are ascending: only the last entry can be the partial block
+        const int last_entry = a.kv_idx[a.kv_ptr[it] + n - 1];
+        if (last_entry == kv_len / kBKV) {
+          ragged_j = n - 1 - rot_of(qb, n);
+          if (ragged_j < 0) ragged_j += n;
+          ragged_valid = tail_cols;
+        }
+      }
+      return true;
+    }
+    n = 0; j = 0;
+    return false;
+  }
+  __device__ __forceinline__ bool first() const { return j == 0; }
+  __device__ __forceinline__ bool last() const { return j == n - 1; }
+  __device__ __forceinline__ int valid() const { return j == ragged_j ? ragged_valid : kBKV; }
+};
 
 // Walks the CTA's share of the schedule as a flat sequence of kv blocks.
 struct BlockSeq {
@@ -83,10 +154,11 @@ struct BlockSeq {
   int item_no;   // index among this CTA's non-empty items (selects the Q buffer, o_full / o_free phases)
   int b, h, qb, n, j;
   int kvb, kvb_next;  // kv-block index of the current block; the next one is fetched a block early
+  int rot;            // rotation of the visiting order inside the item's kv list
   const int32_t* kv;
   __device__ __forceinline__ void init(int start, int stride_, int n_items_) {
     pos = start; stride = stride_; n_items = n_items_; item_no = -1; n = 0; j = 0; kv = nullptr;
-    b = h = qb = 0; kvb = kvb_next = 0;
+    b = h = qb = 0; kvb = kvb_next = 0; rot = 0;
   }
   // Advances to the next block; `on_empty(b, h, qb)` is called for every item without kv blocks that
   // is passed on the way. Returns false at the end of the sequence.
@@ -95,7 +167,7 @@ struct BlockSeq {
     if (j + 1 < n) {
       ++j;
       kvb = kvb_next;
-      if (j + 1 < n) kvb_next = kv[j + 1];
+      if (j + 1 < n) kvb_next = kv[at(j + 1)];
       return true;
     }
     while (pos < n_items) {
@@ -105,13 +177,18 @@ struct BlockSeq {
       if (rec.w <= 0) { on_empty(rec.x, rec.y, rec.z); continue; }
       b = rec.x; h = rec.y; qb = rec.z; n = rec.w; j = 0;
       kv = a.kv_idx + a.kv_ptr[it];
-      kvb = kv[0];
-      if (n > 1) kvb_next = kv[1];
+      rot = rot_of(qb, n);
+      kvb = kv[at(0)];
+      if (n > 1) kvb_next = kv[at(1)];
       ++item_no;
       return true;
     }
     n = 0; j = 0;
     return false;
+  }
+  __device__ __forceinline__ int at(int jj) const {
+    const int t = jj + rot;
+    return t >= n ? t - n : t;
   }
   __device__ __forceinline__ bool first() const { return j == 0; }
   __device__ __forceinline__ bool last() const { return j == n - 1; }
@@ -126,6 +203,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   uint8_t* smem_ring = smem + kQBufs * kTileBytes;  // kRing tiles
   Tail* tail = reinterpret_cast<Tail*>(smem + (kQBufs + kRing) * kTileBytes);
   volatile int* abort_flag = &tail->abort_flag;
+#ifdef FO_ATTN_TRACE
+  uint32_t* trace_buf = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(tail) + ((sizeof(Tail) + 15) & ~size_t(15)));
+#endif
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -136,12 +216,17 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     for (int i = 0; i < kRingV; ++i) { mbar_init(&tail->v_full[i], 1); mbar_init(&tail->v_empty[i], 1); }
     mbar_init(&tail->s_full[0], 1);
     mbar_init(&tail->s_full[1], 1);
-    mbar_init(&tail->s_free[0], kSoftmaxWarps);
-    mbar_init(&tail->s_free[1], kSoftmaxWarps);
-    for (int i = 0; i < 2; ++i) { mbar_init(&tail->p_full[i], kSoftmaxWarps); mbar_init(&tail->pv_done[i], 1); }
+    mbar_init(&tail->s_free[0], kGroupWarps);
+    mbar_init(&tail->s_free[1], kGroupWarps);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tail->p_full[i], kGroupWarps);
+      mbar_init(&tail->pv_done[i], 1);
+      mbar_init(&tail->m_ready[i], kGroupWarps);
+      mbar_init(&tail->stats_ready[i], kSoftmaxWarps);
+    }
     mbar_init(&tail->o_full, 1);
     mbar_init(&tail->o_free, kSoftmaxWarps);
-    mbar_init(&tail->xbar, kSoftmaxWarps);
+    for (int i = 0; i < 8; ++i) mbar_init(&tail->pair_bar[i >> 2][i & 3], 2);
     tail->abort_flag = 0;
     fence_barrier_init();
   }
@@ -159,70 +244,72 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = tail->tmem_base;
 
+  if (threadIdx.x == 0) { FO_TRACE(11, 0); FO_TRACE_TIME(11, 1); }
   int n_items = a.counters[0];
   if (n_items < 0) n_items = 0;
   const int sched_start = static_cast<int>(blockIdx.x), sched_stride = static_cast<int>(gridDim.x);
   auto ignore_empty = [](int, int, int) {};
 
+  // The softmax threads hold a whole 128-column row of S in registers: the two softmax warpgroups take
+  // the registers that the producer / issuer warpgroup does not need.
+  if (warp >= kSoftmaxWarps) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
   if (warp == kWarpProducer) {
-    // ------------------------------------------------------------------ TMA producer
-    // Push order: K_0, K_1, then (K_t, V_{t-2}) for t = 2, 3, ... and the last two V (K runs two blocks ahead).
+    // ------------------------------------------------------------------ TMA producer of Q and K tiles
+    // K and V have their own producer threads: a K tile is requested as soon as its slot has been
+    // read by the QK two blocks earlier, whatever the state of the V FIFO (and the other way round).
     if (lane == 0) {
       BlockSeq seq;
       seq.init(sched_start, sched_stride, n_items);
-      uint32_t nk = 0, nv = 0;           // K / V tiles pushed so far
+      uint32_t nk = 0;                   // K tiles pushed so far
       uint32_t q_uses[kQBufs] = {0, 0};  // loads issued per Q buffer
-      int hist_row[3] = {0, 0, 0}, hist_head[3] = {0, 0, 0};  // kv row / kv head of blocks t, t-1, t-2
-      int pending_v = 0;                 // number of blocks whose V has not been pushed yet (0..2)
       int kv_row0 = 0;                   // first kv row of the current item's request
       bool ok = true;
-      auto push = [&](bool is_v, int head, int row) -> bool {
-        const uint32_t n = is_v ? nv : nk;
-        const int slot = static_cast<int>(n % (is_v ? kRingV : kRingK));
-        const uint32_t phase = (n / (is_v ? kRingV : kRingK)) & 1u;
-        uint64_t* empty = is_v ? &tail->v_empty[slot] : &tail->k_empty[slot];
-        uint64_t* full = is_v ? &tail->v_full[slot] : &tail->k_full[slot];
-        if (!mbar_wait(empty, phase ^ 1u, abort_flag)) return false;
-        uint8_t* dst = smem_ring + (is_v ? kRingK + slot : slot) * kTileBytes;
-        const CUtensorMap* tm = is_v ? &a.tmap_v : &a.tmap_k;
-        mbar_expect_tx(full, kTileBytes);
-        tma_load_3d(dst, tm, full, 0, head, row);
-        tma_load_3d(dst + kHalfBytes, tm, full, 64, head, row);
-        if (is_v) ++nv; else ++nk;
-        return true;
-      };
-      while (ok) {
-        const bool have = seq.next(a, ignore_empty);
-        if (have) {
-          const int hq = seq.h - a.head_begin;
-          const int hk = hq / a.group_size;
-          if (seq.first()) kv_row0 = a.kv_indptr[seq.b];
-          if (seq.first()) {  // new item: its Q tile goes to buffer item_no & 1
-            const int qb_i = seq.item_no & 1;
-            if (!mbar_wait(&tail->q_empty[qb_i], (q_uses[qb_i] & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-            ++q_uses[qb_i];
-            const int q_row = a.qo_indptr[seq.b] + seq.qb * kBQ;
-            uint8_t* dst = smem_q + qb_i * kTileBytes;
-            mbar_expect_tx(&tail->q_full[qb_i], kTileBytes);
-            tma_load_3d(dst, &a.tmap_q, &tail->q_full[qb_i], 0, hq, q_row);
-            tma_load_3d(dst + kHalfBytes, &a.tmap_q, &tail->q_full[qb_i], 64, hq, q_row);
-          }
-          hist_row[2] = hist_row[1]; hist_row[1] = hist_row[0];
-          hist_head[2] = hist_head[1]; hist_head[1] = hist_head[0];
-          hist_row[0] = kv_row0 + seq.kvb * kBKV;
-          hist_head[0] = hk;
-          if (!push(false, hist_head[0], hist_row[0])) { ok = false; break; }
-          if (pending_v == 2) {
-            if (!push(true, hist_head[2], hist_row[2])) { ok = false; break; }
-          } else {
-            ++pending_v;
-          }
-        } else {
-          // drain: V of the last (up to two) blocks, oldest first
-          if (pending_v == 2) ok = push(true, hist_head[1], hist_row[1]);
-          if (ok && pending_v >= 1) ok = push(true, hist_head[0], hist_row[0]);
-          break;
+      while (ok && seq.next(a, ignore_empty)) {
+        const int hq = seq.h - a.head_begin;
+        const int hk = hq / a.group_size;
+        if (seq.first()) {  // new item: its Q tile goes to buffer item_no & 1
+          kv_row0 = a.kv_indptr[seq.b];
+          const int qb_i = seq.item_no & 1;
+          if (!mbar_wait(&tail->q_empty[qb_i], (q_uses[qb_i] & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          ++q_uses[qb_i];
+          const int q_row = a.qo_indptr[seq.b] + seq.qb * kBQ;
+          uint8_t* dst = smem_q + qb_i * kTileBytes;
+          mbar_expect_tx(&tail->q_full[qb_i], kTileBytes);
+          tma_load_3d(dst, &a.tmap_q, &tail->q_full[qb_i], 0, hq, q_row);
+          tma_load_3d(dst + kHalfBytes, &a.tmap_q, &tail->q_full[qb_i], 64, hq, q_row);
         }
+        const int slot = static_cast<int>(nk % kRingK);
+        if (!mbar_wait(&tail->k_empty[slot], ((nk / kRingK) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        FO_TRACE(12, static_cast<int>(nk));  // K slot free, load issued
+        ++nk;
+        uint8_t* dst = smem_ring + slot * kTileBytes;
+        const int row = kv_row0 + seq.kvb * kBKV;
+        mbar_expect_tx(&tail->k_full[slot], kTileBytes);
+        tma_load_3d(dst, &a.tmap_k, &tail->k_full[slot], 0, hk, row);
+        tma_load_3d(dst + kHalfBytes, &a.tmap_k, &tail->k_full[slot], 64, hk, row);
+      }
+    }
+  } else if (warp == kWarpProducerV) {
+    // ------------------------------------------------------------------ TMA producer of V tiles
+    if (lane == 0) {
+      BlockSeq seq;
+      seq.init(sched_start, sched_stride, n_items);
+      uint32_t nv = 0;
+      int kv_row0 = 0;
+      bool ok = true;
+      while (ok && seq.next(a, ignore_empty)) {
+        const int hk = (seq.h - a.head_begin) / a.group_size;
+        if (seq.first()) kv_row0 = a.kv_indptr[seq.b];
+        const int slot = static_cast<int>(nv % kRingV);
+        if (!mbar_wait(&tail->v_empty[slot], ((nv / kRingV) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        FO_TRACE(13, static_cast<int>(nv));  // V slot free, load issued
+        ++nv;
+        uint8_t* dst = smem_ring + (kRingK + slot) * kTileBytes;
+        const int row = kv_row0 + seq.kvb * kBKV;
+        mbar_expect_tx(&tail->v_full[slot], kTileBytes);
+        tma_load_3d(dst, &a.tmap_v, &tail->v_full[slot], 0, hk, row);
+        tma_load_3d(dst + kHalfBytes, &a.tmap_v, &tail->v_full[slot], 64, hk, row);
       }
     }
   } else if (warp == kWarpQK) {
@@ -242,6 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       uint32_t q_uses[kQBufs] = {0, 0};
       bool ok = true;
       while (ok && seq.next(a, ignore_empty)) {
+        FO_TRACE(17, static_cast<int>(g));  // QK: next block fetched
         const uint32_t sb = g & 1u;
         const int qb_i = seq.item_no & 1;
         // S[sb] is free once the softmax has copied block g-2 into registers
@@ -250,6 +338,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           if (!mbar_wait(&tail->q_full[qb_i], q_uses[qb_i] & 1u, abort_flag)) { ok = false; break; }
           ++q_uses[qb_i];
         }
+        FO_TRACE(15, static_cast<int>(g));  // QK: S buffer free seen
         const int slot = static_cast<int>(nk % kRingK);
         if (!mbar_wait(&tail->k_full[slot], (nk / kRingK) & 1u, abort_flag)) { ok = false; break; }
         ++nk;
@@ -264,10 +353,13 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           la[kk] = q_lo + off;
           lb[kk] = k_lo + off;
         }
+        FO_TRACE(8, static_cast<int>(g));  // QK: operands and S buffer ready
         umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
+        FO_TRACE(7, static_cast<int>(g));  // QK issued
         umma_commit(&tail->s_full[sb]);
         umma_commit(&tail->k_empty[slot]);
         if (seq.last()) umma_commit(&tail->q_empty[qb_i]);
+        FO_TRACE(16, static_cast<int>(g));  // QK: commits issued
         ++g;
       }
     }
@@ -288,6 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (seq.first() && items_started > 0) {  // O must have been drained by the previous item's epilogue
           if (!mbar_wait(&tail->o_free, (items_started - 1u) & 1u, abort_flag)) { ok = false; break; }
         }
+        FO_TRACE(14, static_cast<int>(g));  // PV: P seen
         const int slot = static_cast<int>(nv % kRingV);
         if (!mbar_wait(&tail->v_full[slot], (nv / kRingV) & 1u, abort_flag)) { ok = false; break; }
         ++nv;
@@ -301,7 +394,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           ta[kk] = tmem_p + static_cast<uint32_t>(kk * 8);
           lb[kk] = v_lo + static_cast<uint32_t>((kk * 2048) >> 4);
         }
+        FO_TRACE(9, static_cast<int>(g));  // PV: P and V ready
         umma_ts_x8(tmem_base + kColO, hi, idesc_pv, seq.first() ? 0u : 1u, ta, lb);
+        FO_TRACE(10, static_cast<int>(g));  // PV issued
         umma_commit(&tail->pv_done[sb]);
         umma_commit(&tail->v_empty[slot]);
         if (seq.last()) umma_commit(&tail->o_full);
@@ -309,33 +404,31 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         ++g;
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     // ------------------------------------------------------------------ softmax / epilogue warps 0..15
-    // Four threads per q row: thread (quadrant = warp & 3, column quarter cq = warp >> 2) owns columns
-    // [32cq, 32cq+32) of S, P and O for row 32*quadrant + lane.
-    const int cq = warp >> 2;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t col0 = static_cast<uint32_t>(32 * cq);
-    const uint32_t tmem_s0 = tmem_base + lane_base + kColS + col0;
-    const uint32_t tmem_p0 = tmem_base + lane_base + kColP + (col0 >> 1);
-    const uint32_t tmem_o = tmem_base + lane_base + kColO + col0;
-    const int r_in_tile = (warp & 3) * 32 + lane;
-    const bool tracer = (threadIdx.x == 0);
+    // Group X = warp / 8 takes the blocks with g & 1 == X. Two threads per q row: thread
+    // (quadrant = warp & 3, half ch = (warp >> 2) & 1, lane) owns row 32 * quadrant + lane (its TMEM lane)
+    // and the columns [64 ch, 64 ch + 64) of S[X], P[X] and (in a rescale) O; in the epilogue the 16 warps
+    // cover O in 32-column quarters.
+    const uint32_t X = static_cast<uint32_t>(warp >> 3), Y = X ^ 1u;
+    const uint32_t ch = static_cast<uint32_t>((warp >> 2) & 1);
+    const int quad = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_base + kColS + X * 128u + ch * 64u;
+    const uint32_t tmem_p = tmem_base + lane_base + kColP + X * 64u + ch * 32u;
+    const uint32_t tmem_o = tmem_base + lane_base + kColO;
+    const uint32_t ocol = 64u * X + 32u * ch;  // this thread's quarter of O in the epilogue
+    const int row = quad * 32 + lane;
+    uint64_t* pair_bar = &tail->pair_bar[X][quad];
+    uint32_t pair_phase = 0;
+    const bool tracer = (quad == 0 && ch == 0 && lane == 0);
     (void)tracer;
     uint16_t* o16 = reinterpret_cast<uint16_t*>(a.o);
     bool ok = true;
-    uint32_t xbar_phase = 0;
-    // Barrier among the 16 softmax warps built on an mbarrier, so that it is bounded like every other
-    // wait of the kernel (a warp that gave up elsewhere cannot leave the others parked forever).
-    auto softmax_bar = [&]() -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tail->xbar);
-      const bool r = mbar_wait(&tail->xbar, xbar_phase, abort_flag);
-      xbar_phase ^= 1u;
-      return r;
-    };
 
-    struct RowCtx {  // where an item's rows live in global memory
+    struct RowCtx {  // where an item's row lives in global memory (this thread's 32-column quarter)
       uint16_t* orow;
       float* lse;
       bool row_ok;
@@ -345,11 +438,11 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       const int hq = h - a.head_begin;
       const int q0 = a.qo_indptr[b];
       const int q_len = a.qo_indptr[b + 1] - q0;
-      const int row_in_req = qb * kBQ + r_in_tile;
+      const int row_in_req = qb * kBQ + row;
       c.row_ok = row_in_req < q_len;
       const int64_t grow = static_cast<int64_t>(q0) + row_in_req;
-      c.orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h + col0;
-      c.lse = (a.lse != nullptr && cq == 0) ? a.lse + grow * a.lse_stride_n + hq : nullptr;
+      c.orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h + ocol;
+      c.lse = (a.lse != nullptr && ocol == 0u) ? a.lse + grow * a.lse_stride_n + hq : nullptr;
       return c;
     };
     auto on_empty = [&](int b, int h, int qb) {  // active q-block that keeps nothing: zeros, lse = -5e4
@@ -362,206 +455,203 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       }
     };
 
-    BlockSeq seq;
+    GroupSeq seq;
     seq.init(sched_start, sched_stride, n_items);
-    uint32_t g = 0;           // global block index
-    uint32_t s_uses[2] = {0, 0};
-    uint32_t items_done = 0;  // epilogues completed
-    float m_used = -INFINITY;
-    uint64_t l2 = 0;  // running row sum of this thread's columns, as a packed pair of partial sums
-    // an item whose last block has been handed over and whose O is still being accumulated
+    uint32_t g = 0;          // global block index (both parities)
+    uint32_t my_blocks = 0;  // blocks this group has processed
+    uint32_t items_seen = 0; // items whose last block has been passed
+    float m_ref = -INFINITY; // the maximum this thread's partial sum refers to
+    uint64_t l2a = 0, l2b = 0;  // partial row sum over this thread's columns of the group's blocks
+    // an item whose statistics have been published and whose O is still being accumulated
     bool pend = false;
-    float pend_l = 0.f, pend_m = 0.f;
-    RowCtx pend_ctx;
-    pend_ctx.orow = nullptr; pend_ctx.lse = nullptr; pend_ctx.row_ok = false;
+    uint32_t pend_item = 0;
+    int pend_b = 0, pend_h = 0, pend_qb = 0;
 
     auto epilogue = [&]() -> bool {
-      // the four quarters of a row exchange their partial sums
-      float* xs = tail->xsum[0];
-      xs[cq * kBQ + r_in_tile] = pend_l;
-      if (!softmax_bar()) return false;
-      const float lsum = xs[r_in_tile] + xs[kBQ + r_in_tile] + xs[2 * kBQ + r_in_tile] + xs[3 * kBQ + r_in_tile];
-      if (!mbar_wait(&tail->o_full, items_done & 1u, abort_flag)) return false;
+      const uint32_t ip = pend_item & 1u;
+      if (!mbar_wait(&tail->stats_ready[ip], (pend_item >> 1) & 1u, abort_flag)) return false;
+      float lsum = 0.f, m_fin = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) m_fin = fmaxf(m_fin, tail->stats_m[ip][i][row]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float mi = tail->stats_m[ip][i][row];
+        const float ci = (mi == m_fin) ? 1.f : ex2_approx(mi - m_fin);
+        lsum = fmaf(tail->stats_l[ip][i][row], ci, lsum);
+      }
+      if (!mbar_wait(&tail->o_full, pend_item & 1u, abort_flag)) return false;
       tc_fence_after_sync();
       const float inv_l = lsum > 0.f ? __frcp_rn(lsum) : 0.f;
       uint32_t v[32];
-      tmem_ld_x32(tmem_o, v);
+      tmem_ld_x32(tmem_o + ocol, v);
       tmem_wait_ld();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->o_free);  // O may be overwritten by the next item
+      const RowCtx pend_ctx = row_ctx(pend_b, pend_h, pend_qb);
       if (pend_ctx.row_ok) {
-        uint4 outv[4];
-        uint32_t* o32 = reinterpret_cast<uint32_t*>(outv);
-#pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          const float x0 = __uint_as_float(v[2 * t]) * inv_l, x1 = __uint_as_float(v[2 * t + 1]) * inv_l;
-          o32[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
-        }
         uint4* dst = reinterpret_cast<uint4*>(pend_ctx.orow);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) dst[t] = outv[t];
-        if (pend_ctx.lse != nullptr) *pend_ctx.lse = (lsum > 0.f) ? (log2f(lsum) + pend_m) : -5e4f;
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float x0 = __uint_as_float(v[8 * q + 2 * t]) * inv_l;
+            const float x1 = __uint_as_float(v[8 * q + 2 * t + 1]) * inv_l;
+            w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+          }
+          dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (pend_ctx.lse != nullptr) *pend_ctx.lse = (lsum > 0.f) ? (log2f(lsum) + m_fin) : -5e4f;
       }
-      ++items_done;
       pend = false;
-      return softmax_bar();  // xsum is reused by the next epilogue
+      return true;
     };
 
-    int kv_len = 0;
-    uint32_t step_no = 0;
-    // One softmax step handles up to two consecutive blocks of an item (both S buffers): one max
-    // exchange, one rescale decision and one hand-over for 256 kv columns.
     while (ok && seq.next(a, on_empty)) {
       if (seq.first()) {
-        m_used = -INFINITY;
-        l2 = 0;
-        kv_len = a.kv_indptr[seq.b + 1] - a.kv_indptr[seq.b];
+        m_ref = -INFINITY;
+        l2a = 0;
+        l2b = 0;
       }
-      const bool step_first = seq.first();
-      const int valid0 = kv_len - seq.kvb * kBKV - static_cast<int>(col0);  // valid columns of my quarter
-      const bool two = kTwoBlockSteps && !seq.last();
-      int valid1 = 0;
-      if (two) {
-        seq.next(a, on_empty);  // stays inside the item
-        valid1 = kv_len - seq.kvb * kBKV - static_cast<int>(col0);
-      }
-      const uint32_t b0 = g & 1u, b1 = b0 ^ 1u;
-      if (!mbar_wait(&tail->s_full[b0], s_uses[b0] & 1u, abort_flag)) { ok = false; break; }
-      ++s_uses[b0];
-      if (two) {
-        if (!mbar_wait(&tail->s_full[b1], s_uses[b1] & 1u, abort_flag)) { ok = false; break; }
-        ++s_uses[b1];
-      }
-      if (tracer) FO_TRACE(4, static_cast<int>(g));  // S ready seen by softmax
-      tc_fence_after_sync();
-      uint32_t s0[32], s1[32];
-      tmem_ld_x32(tmem_s0 + b0 * 128u, s0);
-      if (two) tmem_ld_x32(tmem_s0 + b1 * 128u, s1);
-      tmem_wait_ld();
-      if (tracer) FO_TRACE(0, static_cast<int>(g));  // S in registers
-      // both S buffers are in registers: the QK of the blocks after next may overwrite them
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&tail->s_free[b0]);
-        if (two) mbar_arrive(&tail->s_free[b1]);
-      }
-      float mx = -INFINITY;
-      if (valid0 >= 32) {
-#pragma unroll
-        for (int t = 0; t < 16; ++t) mx = fmax3(mx, __uint_as_float(s0[2 * t]), __uint_as_float(s0[2 * t + 1]));
-      } else {
-#pragma unroll
-        for (int t = 0; t < 32; ++t)
-          if (t < valid0) mx = fmaxf(mx, __uint_as_float(s0[t]));
-      }
-      if (two) {
-        if (valid1 >= 32) {
-#pragma unroll
-          for (int t = 0; t < 16; ++t) mx = fmax3(mx, __uint_as_float(s1[2 * t]), __uint_as_float(s1[2 * t + 1]));
-        } else {
-#pragma unroll
-          for (int t = 0; t < 32; ++t)
-            if (t < valid1) mx = fmaxf(mx, __uint_as_float(s1[t]));
-        }
-      }
-      if (tracer) FO_TRACE(1, static_cast<int>(g));  // local max done
-      float* xm = tail->xmax[step_no & 1u][0];
-      xm[cq * kBQ + r_in_tile] = mx;
-      if (!softmax_bar()) { ok = false; break; }
-      if (tracer) FO_TRACE(5, static_cast<int>(g));  // max exchanged
-      mx = fmaxf(fmaxf(xm[r_in_tile], xm[kBQ + r_in_tile]), fmaxf(xm[2 * kBQ + r_in_tile], xm[3 * kBQ + r_in_tile]));
-      const float m_new = fmaxf(m_used, mx * a.sm_scale_log2);
-      // ---- lazy rescale of l and O (warp-uniform decision; the TMEM round trip is warp-collective).
-      // O is rescaled only after the PV of the previous block has completed.
-      const bool need = (m_new - m_used) > kRescaleThreshold;  // true on an item's first block
-      if (step_first) {
-        m_used = m_new;
-      } else if (__any_sync(0xffffffffu, need)) {
-        // PV of block g-1 is completion number (g-1)/2 on the barrier of its parity
-        if (!mbar_wait(&tail->pv_done[(g - 1u) & 1u], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+      if ((g & 1u) == X) {
+        // ---- pass 1: the maximum of this thread's half row of S[X], 32 columns at a time (the values are
+        // read again for the exponentials: holding them across the exchanges below would cost registers)
+        if (!mbar_wait(&tail->s_full[X], my_blocks & 1u, abort_flag)) { ok = false; break; }
+        if (tracer) FO_TRACE(4, static_cast<int>(g));  // S ready seen by the group
         tc_fence_after_sync();
-        const float alpha = need ? ex2_approx(m_used - m_new) : 1.0f;
-        if (need) m_used = m_new;
-        l2 = ffma2(l2, pack_f32x2(alpha, alpha), 0ull);
-        uint32_t v[32];
-        tmem_ld_x32(tmem_o, v);
-        tmem_wait_ld();
+        const int valid = seq.valid() - static_cast<int>(64u * ch);  // of my columns, how many exist
+        float mx;
+        {
+          float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
-        tmem_st_x32(tmem_o, v);
-      }
-      // ---- P = exp2(S*scale - m_used), row sum, P (16 bit) to its own TMEM buffers
-      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      const uint64_t scale2 = pack_f32x2(a.sm_scale_log2, a.sm_scale_log2);
-      const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
-      auto exp_block = [&](const uint32_t (&s)[32], int valid, uint32_t (&pk)[16]) {
-        if (valid >= 32) {
-          // packed path: one FMA and one add per PAIR of columns; one pair in kPolyEvery takes the
-          // polynomial exp2 (FMA pipe) for its second element, the rest use MUFU
+          for (int c = 0; c < 2; ++c) {
+            uint32_t s[32];
+            tmem_ld_x32(tmem_s + 32u * c, s);
+            tmem_wait_ld();
+            if (valid < 32 * c + 32) {
+#pragma unroll
+              for (int t = 0; t < 32; ++t)
+                if (32 * c + t >= valid) s[t] = 0xff800000u;  // -inf
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                mxs[i] = fmax3(mxs[i], __uint_as_float(s[8 * t + 2 * i]), __uint_as_float(s[8 * t + 2 * i + 1]));
+            }
+          }
+          mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+        }
+        if (tracer) FO_TRACE(0, static_cast<int>(g));  // half-row maximum known
+        // ---- the two halves of a row exchange their maxima (the warps `warp` and `warp ^ 4`)
+        tail->xmax[X][my_blocks & 1u][ch][row] = mx;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pair_bar);
+        if (!mbar_wait(pair_bar, pair_phase, abort_flag)) { ok = false; break; }
+        pair_phase ^= 1u;
+        mx = fmaxf(mx, tail->xmax[X][my_blocks & 1u][ch ^ 1u][row]);
+        // ---- the running maximum after block g-1 comes from the other group (every block waits, so
+        // that the two groups stay within one phase of each other)
+        if (g >= 1u && !mbar_wait(&tail->m_ready[Y], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        const float m_prev = seq.first() ? -INFINITY : tail->m_pub[Y][row];
+        const float m_new = fmaxf(m_prev, mx * a.sm_scale_log2);
+        // lazy rescale (the decision is the same in both warps of a row: same rows, same values)
+        const bool need = (m_new - m_prev) > kRescaleThreshold;
+        const bool rescale = !seq.first() && __any_sync(0xffffffffu, need);
+        const float m_used = (seq.first() || (rescale && need)) ? m_new : m_prev;
+        if (ch == 0u) tail->m_pub[X][row] = m_used;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->m_ready[X]);
+        if (tracer) FO_TRACE(5, static_cast<int>(g));  // maximum published
+        if (rescale) {
+          // O is rescaled only after the PV of block g-1 has completed; that PV may be the first of
+          // its item and wait for the previous item's epilogue, so this thread's share of it goes first
+          if (pend && !epilogue()) { ok = false; break; }
+          if (!mbar_wait(&tail->pv_done[Y], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const float alpha = need ? ex2_approx(m_prev - m_new) : 1.0f;
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32];
+            tmem_ld_x32(tmem_o + 64u * ch + 32u * c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
+            tmem_st_x32(tmem_o + 64u * ch + 32u * c, v);
+          }
+        }
+        // this thread's partial sum follows the maximum in use
+        if (m_ref != m_used) {
+          const float beta = ex2_approx(m_ref - m_used);
+          const uint64_t beta2 = pack_f32x2(beta, beta);
+          l2a = ffma2(l2a, beta2, 0ull);
+          l2b = ffma2(l2b, beta2, 0ull);
+          m_ref = m_used;
+        }
+        // P[X] was last read by the PV of this group's previous block
+        if (my_blocks >= 1u && !mbar_wait(&tail->pv_done[X], (my_blocks - 1u) & 1u, abort_flag)) { ok = false; break; }
+        if (tracer) FO_TRACE(3, static_cast<int>(g));  // pv_done seen
+        // ---- pass 2: P = exp2(S * scale - m_used), row sum, P (16 bit) to TMEM: one FMA and one add per
+        // PAIR of columns
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        const uint64_t scale2 = pack_f32x2(a.sm_scale_log2, a.sm_scale_log2);
+        const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
+        uint32_t s[64];
+        tmem_ld_x32(tmem_s, s);
+        tmem_ld_x32(tmem_s + 32u, s + 32);
+        tmem_wait_ld();
+        // the QK of this group's next block may overwrite S[X]
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->s_free[X]);
+        if (valid < 64) {
+#pragma unroll
+          for (int t = 0; t < 64; ++t)
+            if (t >= valid) s[t] = 0xff800000u;  // -inf: exp2 gives 0
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[16];
 #pragma unroll
           for (int t = 0; t < 16; ++t) {
-            const uint64_t x2 = ffma2(pack_f32x2(__uint_as_float(s[2 * t]), __uint_as_float(s[2 * t + 1])), scale2, negm2);
+            const int e = 32 * c + 2 * t;
+            const uint64_t x2 = ffma2(pack_f32x2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
             float x0, x1;
             unpack_f32x2(x2, x0, x1);
-            const float p0 = ex2_approx(x0);
-            const float p1 = (t % kPolyEvery == 0) ? ex2_poly(x1) : ex2_approx(x1);
-            l2 = fadd2(l2, pack_f32x2(p0, p1));
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            if (t & 1) l2b = fadd2(l2b, pack_f32x2(p0, p1)); else l2a = fadd2(l2a, pack_f32x2(p0, p1));
             pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
           }
-        } else {
-#pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * t]), a.sm_scale_log2, neg_m));
-            float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * t + 1]), a.sm_scale_log2, neg_m));
-            if (2 * t >= valid) p0 = 0.f;
-            if (2 * t + 1 >= valid) p1 = 0.f;
-            l2 = fadd2(l2, pack_f32x2(p0, p1));
-            pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
-          }
+          tmem_st_x16(tmem_p + 16u * c, pk);
         }
-      };
-      {
-        uint32_t pk[16];
-        exp_block(s0, valid0, pk);
         if (tracer) FO_TRACE(2, static_cast<int>(g));  // exponentials done
-        // P[b0] was last read by the PV of block g-2
-        if (g >= 2u && !mbar_wait(&tail->pv_done[b0], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
-        if (tracer) FO_TRACE(3, static_cast<int>(g));  // pv_done seen
-        tmem_st_x16(tmem_p0 + b0 * 64u, pk);
-      }
-      if (two) {
-        uint32_t pk[16];
-        exp_block(s1, valid1, pk);
-        if (g >= 1u && !mbar_wait(&tail->pv_done[b1], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
-        tmem_st_x16(tmem_p0 + b1 * 64u, pk);
-      }
-      tmem_wait_st();
-      if (tracer) FO_TRACE(7, static_cast<int>(g));  // P stored
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&tail->p_full[b0]);
-        if (two) mbar_arrive(&tail->p_full[b1]);
-      }
-      if (tracer) FO_TRACE(6, static_cast<int>(g));  // P handed over
-      g += two ? 2u : 1u;
-      ++step_no;
-      // the previous item's epilogue runs one step late, so that its last PV overlaps this softmax
-      if (pend) {
-        if (!epilogue()) { ok = false; break; }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->p_full[X]);
+        if (tracer) FO_TRACE(6, static_cast<int>(g));  // P handed over
+        ++my_blocks;
+        // the previous item's epilogue runs after this group's first block of the next item, so that
+        // the item's last PV overlaps a softmax step
+        if (pend && !epilogue()) { ok = false; break; }
       }
       if (seq.last()) {
+        if (pend && !epilogue()) { ok = false; break; }
+        const uint32_t ip = items_seen & 1u;
+        float la, lb, lc, ld;
+        unpack_f32x2(l2a, la, lb);
+        unpack_f32x2(l2b, lc, ld);
+        tail->stats_m[ip][2u * X + ch][row] = m_ref;
+        tail->stats_l[ip][2u * X + ch][row] = (la + lb) + (lc + ld);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->stats_ready[ip]);
         pend = true;
-        {
-          float la, lb;
-          unpack_f32x2(l2, la, lb);
-          pend_l = la + lb;
-        }
-        pend_m = m_used;
-        pend_ctx = row_ctx(seq.b, seq.h, seq.qb);
+        pend_item = items_seen;
+        pend_b = seq.b; pend_h = seq.h; pend_qb = seq.qb;
+        ++items_seen;
       }
+      ++g;
     }
     if (ok && pend) epilogue();
   }
@@ -570,6 +660,12 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) { FO_TRACE(11, 2); FO_TRACE_TIME(11, 3); }
+#ifdef FO_ATTN_TRACE
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < kTraceEvents * kTraceSlots; i += kThreads) g_trace[i] = trace_buf[i];
+#endif
   if (*abort_flag != 0) {
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
