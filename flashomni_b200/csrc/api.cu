@@ -396,7 +396,7 @@ int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t d
     g.tiles = la.tiles;
     g.n_tiles_ptr = la.counters;
   } else {
-    e = cudaMemsetAsync(wsw + 4, 0, sizeof(int32_t), st);  // the list kernel does this on the sparse path
+    e = cudaMemsetAsync(wsw + 4, 0, 2 * sizeof(int32_t), st);  // status word and tile cursor (the list kernel does this on the sparse path)
     if (e != cudaSuccess) return fail_cuda("fo_gemm_q (status reset)", e);
   }
   g.y = y;
@@ -410,6 +410,7 @@ int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t d
   g.k = k;
   g.kb_per_head = 1;
   g.status = wsw + 4;
+  g.cursor = is_full ? nullptr : wsw + 5;  // equal tiles keep a fixed share
   e = launch_gemm(g, sm_count(), st);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_q", e);
 }
@@ -452,6 +453,7 @@ int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t i
   g.row_heads = la.row_heads;
   g.row_order = la.row_order;
   g.status = wsw + 4;
+  g.cursor = wsw + 5;
   e = launch_gemm(g, sm_count(), st);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_o", e);
 }

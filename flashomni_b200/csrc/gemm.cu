@@ -38,12 +38,16 @@ constexpr int kSlabBufs = 2;
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kMaxHeadsSmem = 128;
+constexpr int kTileQ = 8;   // entries of the tile queue (the producer runs at most a few tiles ahead of the epilogue)
 
 struct Tail {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t tq_full[kTileQ];   // tile queue: the producer warp draws tile numbers and hands them to the other roles
+  uint64_t tq_empty[kTileQ];
+  int tile_q[kTileQ];
   uint32_t tmem_base;
   int abort_flag;
   int heads[2][kMaxHeadsSmem];  // GEMM-O: head lists of the current and the next tile, staged for the producer
@@ -110,12 +114,6 @@ __device__ __forceinline__ TileInfo get_tile(const GemmArgs& a, int t) {
   return ti;
 }
 
-__device__ __forceinline__ int kcol_of(const GemmArgs& a, const TileInfo& ti, int j) {
-  if (ti.heads == nullptr) return j * kBK;
-  const int hh = j / a.kb_per_head;
-  return (ti.heads[hh] * a.kb_per_head + (j - hh * a.kb_per_head)) * kBK;
-}
-
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <bool kBf16>
@@ -139,6 +137,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       mbar_init(&tail->acc_full[i], 1);
       mbar_init(&tail->acc_empty[i], 4);
     }
+    for (int i = 0; i < kTileQ; ++i) {
+      mbar_init(&tail->tq_full[i], 1);
+      mbar_init(&tail->tq_empty[i], 5);  // the MMA thread and the four epilogue warps
+    }
     tail->abort_flag = 0;
     fence_barrier_init();
   }
@@ -157,6 +159,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   const uint32_t tmem_base = tail->tmem_base;
 
   const int n_tiles = num_tiles(a);
+  // Tiles are handed out in list order through a device-wide cursor (longest first where the lists are
+  // sorted), so that a CTA that finishes early takes the next tile instead of idling at the end of a
+  // fixed share. Tile i < gridDim.x goes to CTA i; the cursor counts the tiles after those.
+  // Entry k of a CTA's sequence travels through slot k % kTileQ; -1 ends the sequence.
+  auto read_slot = [&](int k) -> int {  // one thread of a consumer role; -2 when the wait gave up
+    const int slot = k % kTileQ;
+    if (!mbar_wait(&tail->tq_full[slot], static_cast<uint32_t>(k / kTileQ) & 1u, abort_flag)) return -2;
+    const int t = tail->tile_q[slot];
+    mbar_arrive(&tail->tq_empty[slot]);
+    return t;
+  };
 
   if (warp == 4) {
     // ------------------------------------------------------------- TMA producer
@@ -167,7 +180,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     int stage = 0;
     uint32_t phase = 0;
     int ok = 1;
-    const int t0 = static_cast<int>(blockIdx.x), dt = static_cast<int>(gridDim.x);
     TileInfo nxt;
     nxt.a_row = nxt.w_row0 = nxt.nkb = 0; nxt.w_row1 = -1; nxt.heads = nullptr;
     int hreg[kMaxHeadsSmem / 32];
@@ -181,19 +193,51 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 #pragma unroll
       for (int i = 0; i < kMaxHeadsSmem / 32; ++i) tail->heads[par][lane + 32 * i] = hreg[i];
     };
-    if (t0 < n_tiles) {
-      nxt = get_tile(a, t0);
+    int n_pub = 0;  // entries published so far (lane 0)
+    auto publish = [&](int t) -> bool {  // lane 0
+      const int slot = n_pub % kTileQ;
+      if (!mbar_wait(&tail->tq_empty[slot], (static_cast<uint32_t>(n_pub / kTileQ) & 1u) ^ 1u, abort_flag)) return false;
+      tail->tile_q[slot] = t;
+      mbar_arrive(&tail->tq_full[slot]);
+      ++n_pub;
+      return true;
+    };
+    int n_drawn = 0;
+    auto draw = [&]() -> int {  // lane 0: the next tile of the device-wide sequence
+      // equal tiles (dense: no cursor) keep the fixed round-robin share and skip the atomic
+      ++n_drawn;
+      const int t = a.cursor != nullptr ? atomicAdd(a.cursor, 1) + static_cast<int>(gridDim.x)
+                                        : static_cast<int>(blockIdx.x) + n_drawn * static_cast<int>(gridDim.x);
+      return t < n_tiles ? t : -1;
+    };
+    // t_cur is being loaded, t_n1 is known and published, t_n2 is drawn while t_cur runs (two tiles of
+    // lead, so that the atomic's round trip never sits between two tiles)
+    int t_cur = static_cast<int>(blockIdx.x) < n_tiles ? static_cast<int>(blockIdx.x) : -1;
+    int t_n1 = -1;
+    if (lane == 0) {
+      ok = publish(t_cur) ? 1 : 0;
+      if (ok && t_cur >= 0) {
+        t_n1 = draw();
+        ok = publish(t_n1) ? 1 : 0;
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    t_n1 = __shfl_sync(0xffffffffu, t_n1, 0);
+    if (t_cur >= 0) {
+      nxt = get_tile(a, t_cur);
       fetch_heads(nxt);
       stash_heads(0);
     }
     __syncwarp();
     int par = 0;
-    for (int t = t0; t < n_tiles && ok; t += dt, par ^= 1) {
+    while (t_cur >= 0 && ok) {
+      int t_n2 = -1;
+      if (lane == 0 && t_n1 >= 0) t_n2 = draw();
       TileInfo ti = nxt;
       if (ti.heads != nullptr && ti.nkb / a.kb_per_head <= kMaxHeadsSmem) ti.heads = tail->heads[par];
-      const bool more = t + dt < n_tiles;
+      const bool more = t_n1 >= 0;
       if (more) {
-        nxt = get_tile(a, t + dt);
+        nxt = get_tile(a, t_n1);
         fetch_heads(nxt);
       }
       if (lane == 0) {
@@ -221,12 +265,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             if (j + 1 < ti.nkb) kcol = ti.heads[hh] * a.kb_per_head * kBK;
           }
         }
+        if (ok && more && !publish(t_n2)) ok = 0;
       }
       __syncwarp();
       if (more) stash_heads(par ^ 1);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       stage = __shfl_sync(0xffffffffu, stage, 0);
       phase = __shfl_sync(0xffffffffu, phase, 0);
+      t_n2 = __shfl_sync(0xffffffffu, t_n2, 0);
+      t_cur = t_n1;
+      t_n1 = t_n2;
+      par ^= 1;
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------- MMA issuer
@@ -245,10 +294,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32), desc_lo0 = static_cast<uint32_t>(desc0);
       TileInfo nxt;
       nxt.a_row = nxt.w_row0 = nxt.nkb = 0; nxt.w_row1 = -1; nxt.heads = nullptr;
-      if (static_cast<int>(blockIdx.x) < n_tiles) nxt = get_tile(a, blockIdx.x);
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      int k_seq = 0;
+      int t_cur = read_slot(0);
+      if (t_cur >= 0) nxt = get_tile(a, t_cur);
+      for (; t_cur >= 0 && ok; ++k_seq) {
         const TileInfo ti = nxt;  // the next tile's record is fetched while this one runs
-        if (t + static_cast<int>(gridDim.x) < n_tiles) nxt = get_tile(a, t + gridDim.x);
+        const int t_nxt = read_slot(k_seq + 1);
+        if (t_nxt >= 0) nxt = get_tile(a, t_nxt);
+        if (t_nxt == -2) ok = false;
+        t_cur = t_nxt;
         const uint32_t idesc = ti.w_row1 >= 0 ? idesc256 : idesc128;
         if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
@@ -287,10 +341,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     const uint32_t swz = static_cast<uint32_t>(r_in_tile & 7);
     TileInfo nxt;
     nxt.a_row = nxt.w_row0 = nxt.nkb = 0; nxt.w_row1 = -1; nxt.heads = nullptr;
-    if (static_cast<int>(blockIdx.x) < n_tiles) nxt = get_tile(a, blockIdx.x);
-    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+    auto read_slot_warp = [&](int k) -> int {  // lane 0 reads, the warp shares the value
+      int t = 0;
+      if (lane == 0) t = read_slot(k);
+      return __shfl_sync(0xffffffffu, t, 0);
+    };
+    int k_seq = 0;
+    int t_cur = read_slot_warp(0);
+    if (t_cur >= 0) nxt = get_tile(a, t_cur);
+    for (; t_cur >= 0 && ok; ++k_seq) {
       const TileInfo ti = nxt;
-      if (t + static_cast<int>(gridDim.x) < n_tiles) nxt = get_tile(a, t + gridDim.x);
+      const int t_nxt = read_slot_warp(k_seq + 1);
+      if (t_nxt >= 0) nxt = get_tile(a, t_nxt);
+      if (t_nxt == -2) ok = false;
+      t_cur = t_nxt;
       const int64_t row = static_cast<int64_t>(ti.a_row) + r_in_tile;
       const int nslab = ti.w_row1 >= 0 ? 4 : 2;
       // init values of slab 0 are fetched before the accumulator is waited for

@@ -80,6 +80,7 @@ struct GemmArgs {
   const int32_t* row_heads;
   const int32_t* row_order;
   int32_t* status;                 // device status word (DevStatus)
+  int32_t* cursor;                 // device-wide tile cursor, zero when the kernel starts
 };
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream);
 

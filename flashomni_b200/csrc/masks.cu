@@ -426,93 +426,106 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
 // ---------------------------------------------------------------------------------------------
 // GEMM work lists (single CTA: the candidate counts are a few thousand at most)
 // ---------------------------------------------------------------------------------------------
-// GEMM-Q: pair-tile records (b, iy, ix0, ix1). Per row block (b, iy), ascending in (b, iy), the active
-// column blocks are taken two at a time in ascending order; a leftover single block has ix1 = -1.
-// counters[0] = number of records, counters[1] = number of active 128x128 tiles.
+// GEMM-Q: tile records (b, iy, ix0, ix1). Per row block (b, iy) the active column blocks are taken two
+// at a time in ascending order; a leftover single block has ix1 = -1. All two-block records come first,
+// the single-block records after them, each part in ascending (b, iy) order: the GEMM hands tiles to its
+// CTAs in list order, and the half-size tiles at the end fill the last wave.
+// counters[0] = number of records, counters[1] = number of active 128x128 tiles, counters[3] = number
+// of two-block records. The kernel walks the row blocks twice: totals first, then the records.
 __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
   __shared__ int s_warp[32];
   __shared__ int s_warp_t[32];
-  __shared__ int s_carry, s_carry_t;
+  __shared__ int s_carry, s_carry_t, s_pairs_total;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) { s_carry = 0; s_carry_t = 0; }
-  __syncthreads();
   const int mt = a.m / 128, nt = a.n / 128;
   const int rows = a.batch * mt;
-  for (int base = 0; base < rows; base += blockDim.x) {
-    const int r = base + tid;
-    int cnt = 0;
-    const uint8_t* seg = nullptr;
-    int64_t limit = 0, bit0 = 0;
-    uint64_t rowbits = 0;
-    bool fast = false;
-    if (r < rows) {
-      const int b = r / mt, iy = r % mt;
-      if (a.is_full) {
-        cnt = nt;
-      } else {
-        const int64_t ioff = a.info_indptr[b];
-        seg = a.sparse_info + ioff;
-        limit = a.info_bytes - ioff;
-        const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
-        bit0 = qb * a.num_heads + a.head_begin;
-        if (a.head_dim == 128 && nt <= 64) {  // one bit per column block: fetch the row's bits at once
-          rowbits = load_bits64(seg, bit0, limit, nt);
-          cnt = __popcll(rowbits);
-          fast = true;
+  for (int pass = 0; pass < 2; ++pass) {
+    if (tid == 0) { s_carry = 0; s_carry_t = 0; }
+    __syncthreads();
+    const int pairs_total = pass == 0 ? 0 : s_pairs_total;
+    for (int base = 0; base < rows; base += blockDim.x) {
+      const int r = base + tid;
+      int cnt = 0;
+      const uint8_t* seg = nullptr;
+      int64_t limit = 0, bit0 = 0;
+      uint64_t rowbits = 0;
+      bool fast = false;
+      if (r < rows) {
+        const int b = r / mt, iy = r % mt;
+        if (a.is_full) {
+          cnt = nt;
         } else {
-          for (int ix = 0; ix < nt; ++ix) cnt += get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit);
+          const int64_t ioff = a.info_indptr[b];
+          seg = a.sparse_info + ioff;
+          limit = a.info_bytes - ioff;
+          const int64_t qb = (static_cast<int64_t>(a.num_text_tokens) + static_cast<int64_t>(iy) * 128) / a.sparse_q_size;
+          bit0 = qb * a.num_heads + a.head_begin;
+          if (a.head_dim == 128 && nt <= 64) {  // one bit per column block: fetch the row's bits at once
+            rowbits = load_bits64(seg, bit0, limit, nt);
+            cnt = __popcll(rowbits);
+            fast = true;
+          } else {
+            for (int ix = 0; ix < nt; ++ix) cnt += get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit);
+          }
         }
       }
-    }
-    const int recs = (cnt + 1) >> 1;
-    int x = recs, xt = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int y = __shfl_up_sync(0xffffffffu, x, o);
-      const int yt = __shfl_up_sync(0xffffffffu, xt, o);
-      if (lane >= o) { x += y; xt += yt; }
-    }
-    if (lane == 31) { s_warp[warp] = x; s_warp_t[warp] = xt; }
-    __syncthreads();
-    if (warp == 0) {
-      int w = s_warp[lane], wt = s_warp_t[lane];
+      // x: two-block records, xt: single-block records (inclusive scans over the CTA)
+      const int npair = cnt >> 1, nsingle = cnt & 1;
+      int x = npair, xt = nsingle;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        const int y = __shfl_up_sync(0xffffffffu, w, o);
-        const int yt = __shfl_up_sync(0xffffffffu, wt, o);
-        if (lane >= o) { w += y; wt += yt; }
+        const int y = __shfl_up_sync(0xffffffffu, x, o);
+        const int yt = __shfl_up_sync(0xffffffffu, xt, o);
+        if (lane >= o) { x += y; xt += yt; }
       }
-      s_warp[lane] = w;
-      s_warp_t[lane] = wt;
-    }
-    __syncthreads();
-    int pos = s_carry + (warp ? s_warp[warp - 1] : 0) + x - recs;
-    if (r < rows && recs > 0) {
-      const int b = r / mt, iy = r % mt;
-      int first = -1;
-      for (int ix = 0; ix < nt; ++ix) {
-        const int on = a.is_full ? 1 : (fast ? static_cast<int>((rowbits >> ix) & 1ull)
-                                               : get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit));
-        if (!on) continue;
-        if (first < 0) {
-          first = ix;
-        } else {
-          if (pos < a.max_tiles) *reinterpret_cast<int4*>(a.tiles + 4 * pos) = make_int4(b, iy, first, ix);
-          ++pos;
-          first = -1;
+      if (lane == 31) { s_warp[warp] = x; s_warp_t[warp] = xt; }
+      __syncthreads();
+      if (warp == 0) {
+        int w = s_warp[lane], wt = s_warp_t[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, w, o);
+          const int yt = __shfl_up_sync(0xffffffffu, wt, o);
+          if (lane >= o) { w += y; wt += yt; }
         }
+        s_warp[lane] = w;
+        s_warp_t[lane] = wt;
       }
-      if (first >= 0 && pos < a.max_tiles) *reinterpret_cast<int4*>(a.tiles + 4 * pos) = make_int4(b, iy, first, -1);
+      __syncthreads();
+      if (pass == 1 && r < rows && cnt > 0) {
+        int pos = s_carry + (warp ? s_warp[warp - 1] : 0) + x - npair;
+        const int spos = pairs_total + s_carry_t + (warp ? s_warp_t[warp - 1] : 0) + xt - nsingle;
+        const int b = r / mt, iy = r % mt;
+        int first = -1;
+        for (int ix = 0; ix < nt; ++ix) {
+          const int on = a.is_full ? 1 : (fast ? static_cast<int>((rowbits >> ix) & 1ull)
+                                                 : get_bit(seg, bit0 + (ix * 128) / a.head_dim, limit));
+          if (!on) continue;
+          if (first < 0) {
+            first = ix;
+          } else {
+            if (pos < a.max_tiles) *reinterpret_cast<int4*>(a.tiles + 4 * pos) = make_int4(b, iy, first, ix);
+            ++pos;
+            first = -1;
+          }
+        }
+        if (first >= 0 && spos < a.max_tiles) *reinterpret_cast<int4*>(a.tiles + 4 * spos) = make_int4(b, iy, first, -1);
+      }
+      __syncthreads();
+      if (tid == 0) { s_carry += s_warp[31]; s_carry_t += s_warp_t[31]; }
+      __syncthreads();
     }
-    __syncthreads();
-    if (tid == 0) { s_carry += s_warp[31]; s_carry_t += s_warp_t[31]; }
+    if (pass == 0 && tid == 0) s_pairs_total = s_carry;
     __syncthreads();
   }
   if (tid == 0) {
-    a.counters[0] = s_carry;
-    a.counters[1] = s_carry_t;
-    a.counters[2] = s_carry > a.max_tiles ? kDevBadIndex : kDevOk;
+    const int n_rec = s_carry + s_carry_t;
+    a.counters[0] = n_rec;
+    a.counters[1] = 2 * s_carry + s_carry_t;
+    a.counters[2] = n_rec > a.max_tiles ? kDevBadIndex : kDevOk;
+    a.counters[3] = s_carry;
     a.counters[4] = kDevOk;  // status word of the GEMM kernel that follows
+    a.counters[5] = 0;       // its tile cursor
   }
 }
 
@@ -596,6 +609,7 @@ __global__ void __launch_bounds__(1024) gemm_o_rows_kernel(GemmListArgs a) {
     a.counters[1] = s_carry;
     a.counters[2] = kDevOk;
     a.counters[4] = kDevOk;  // status word of the GEMM kernel that follows
+    a.counters[5] = 0;       // its tile cursor
     // bucket starts, descending count
     int acc = 0;
     for (int k = local_heads; k >= 0; --k) { const int v = s_hist[k]; s_hist[k] = acc; acc += v; }

@@ -166,21 +166,23 @@ def gemm_q_tile_pairs(sparse_info, info_indptr, batch: int, m: int, n: int, num_
                       sparse_q_size: int = 128, num_text_tokens: int = 0, is_full: bool = False,
                       head_begin: int = 0, head_dim: int | None = None) -> np.ndarray:
     """The work list GEMM-Q runs over: int32 [n_records, 4] = (b, iy, ix0, ix1). Per row block (b, iy),
-    ascending, the active column blocks of `gemm_q_tiles` taken two at a time in ascending order; a
-    leftover single block has ix1 = -1."""
+    ascending, the active column blocks of `gemm_q_tiles` are taken two at a time in ascending order; a
+    leftover single block has ix1 = -1. The list holds all two-block records first and the single-block
+    records after them (both in ascending (b, iy) order): the GEMM hands tiles to its CTAs in list order,
+    and the half-size tiles at the end fill the last wave."""
     tiles = gemm_q_tiles(sparse_info, info_indptr, batch, m, n, num_heads, sparse_q_size, num_text_tokens,
                          is_full, head_begin, head_dim)
-    recs = []
+    pairs, singles = [], []
     i = 0
     while i < len(tiles):
         b, iy, ix = (int(v) for v in tiles[i])
         if i + 1 < len(tiles) and int(tiles[i + 1][0]) == b and int(tiles[i + 1][1]) == iy:
-            recs.append((b, iy, ix, int(tiles[i + 1][2])))
+            pairs.append((b, iy, ix, int(tiles[i + 1][2])))
             i += 2
         else:
-            recs.append((b, iy, ix, -1))
+            singles.append((b, iy, ix, -1))
             i += 1
-    return np.asarray(recs, dtype=np.int32).reshape(-1, 4)
+    return np.asarray(pairs + singles, dtype=np.int32).reshape(-1, 4)
 
 
 def gemm_o_rows(sparse_info, info_indptr, batch: int, m: int, k: int, num_heads: int,

@@ -87,8 +87,13 @@ def test_gemm_lists():
     assert tiles.tolist() == [list(t) for t in exp]
     pairs = om.gemm_q_tile_pairs(m.sparse_info, m.info_indptr, 2, 6 * 128, 4 * 128, 4)
     flat = [(b, iy, ix) for b, iy, i0, i1 in pairs.tolist() for ix in (i0, i1) if ix >= 0]
-    assert flat == [tuple(t) for t in tiles.tolist()]
+    assert sorted(flat) == [tuple(t) for t in tiles.tolist()]
     assert all(i1 == -1 or i1 > i0 for _, _, i0, i1 in pairs.tolist())
+    # two-block records first, single-block records last, each part in ascending (b, iy) order
+    kinds = [i1 < 0 for _, _, _, i1 in pairs.tolist()]
+    assert kinds == sorted(kinds)
+    for part in ([r for r in pairs.tolist() if r[3] >= 0], [r for r in pairs.tolist() if r[3] < 0]):
+        assert part == sorted(part)
     # a row offset (num_text_tokens) shifts the q-block a row tile maps to
     tiles2 = om.gemm_q_tiles(m.sparse_info, m.info_indptr, 2, 4 * 128, 4 * 128, 4, num_text_tokens=256)
     exp2 = [(b, iy, ix) for b in range(2) for iy in range(4) for ix in range(4) if m.q_active[b][iy + 2, ix]]
