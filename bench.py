@@ -46,16 +46,54 @@ def block_flops(masks, hb, hc, batch=B, seq=S):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs: NVML from a
+    thread every few milliseconds (the timed region of the default run is only tens of milliseconds long),
+    nvidia-smi at 100 ms when the NVML module is missing. Read-only queries."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
-        self.idx, self.p = gpu_index, None
+        self.idx, self.p, self.thread = gpu_index, None, None
+        self.sm, self.reasons, self.mx, self.stop_flag = [], set(), None, False
+
+    def _nvml_loop(self, nv, handle):
+        bits = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                r = int(get_reasons(handle))
+                for name, bit in bits.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML numbers the GPUs of the machine; CUDA_VISIBLE_DEVICES may renumber them for this process
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = self.idx
+            if vis:
+                ent = vis.split(",")[self.idx].strip()
+                phys = int(ent) if ent.isdigit() else None
+            handle = nv.nvmlDeviceGetHandleByIndex(phys) if phys is not None else nv.nvmlDeviceGetHandleByUUID(ent)
+            self.mx = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.p = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}",
                                        "--format=csv,noheader,nounits", "-lms", "100"],
@@ -64,6 +102,11 @@ class ClockSampler:
             self.p = None
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.mx,
+                    "reasons": sorted(self.reasons), "samples": len(self.sm), "source": "nvml"}
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -86,7 +129,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 def make_inputs(rank, world):
@@ -351,6 +394,14 @@ def run_video(args):
     torch.cuda.synchronize()
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1) / args.steps
+    # phase breakdown of two more steps (outside the timed region), rank 0's view
+    phases = {}
+    for _ in range(2):
+        marks = []
+        blk.forward(x, *m_dev, marks=marks)
+        torch.cuda.synchronize()
+        names = ("proj_and_exchange", "attention", "exchange_back", "gemm_o")
+        phases = {n: round(marks[i].elapsed_time(marks[i + 1]), 4) for i, n in enumerate(names)}
     tiles = wl.executed_attention_tiles(masks, blk.hb, blk.hc)
     rows_blocks = blk.s_loc // 128
     fl_rank = tiles * FL_ATTN_TILE + 4 * (2 * blk.s_loc * hid * hid)
@@ -371,7 +422,8 @@ def run_video(args):
             "config": {"workload": "video_layer: hidden 5120, H=40, D=128, S=77312 (20 frames x 3840 + 512 text), batch 1, "
                                    "spatiotemporal-local block mask (+-1 frame + 10% random + text), Ulysses all-to-all",
                        "parallelism": f"ulysses/{world}", "seed": SEED, "executed_flops_per_step": fl_total,
-                       "attention_tiles_rank0": tiles, "l2": "working set of several GB, far above the 126 MB L2"},
+                       "attention_tiles_rank0": tiles, "l2": "working set of several GB, far above the 126 MB L2",
+                       "phase_ms_rank0": phases},
             "gpu_launches": int(args.steps * 10), "clocks": clocks}), flush=True)
     if dist is not None:
         dist.barrier()

@@ -6,7 +6,7 @@
 // base-2 online softmax, output rounded to the input dtype. q-blocks that are not in the list are
 // never written. An item with an empty list writes zeros (lse = -5e4), like the reference.
 //
-// One persistent CTA per SM walks its items (dealt round-robin in longest-first order) as ONE
+// One persistent CTA per SM walks its items (dealt round-robin in the order of the work list) as ONE
 // sequence of kv blocks g = 0, 1, 2, ... and software-pipelines it:
 //
 //   tensor pipe     S[g&1] = Q K_g^T   (QK issuer)   and   O (+)= P[g&1] V_g   (PV issuer)

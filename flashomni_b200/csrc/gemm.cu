@@ -159,9 +159,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
   const uint32_t tmem_base = tail->tmem_base;
 
   const int n_tiles = num_tiles(a);
-  // Tiles are handed out in list order through a device-wide cursor (longest first where the lists are
-  // sorted), so that a CTA that finishes early takes the next tile instead of idling at the end of a
-  // fixed share. Tile i < gridDim.x goes to CTA i; the cursor counts the tiles after those.
+  // Tiles are handed out in list order through a device-wide cursor (the GEMM-O rows are sorted
+  // longest first, the GEMM-Q list ends with its half-size tiles), so that a CTA that finishes early
+  // takes the next tile instead of idling at the end of a fixed share. Tile i < gridDim.x goes to CTA i; the cursor counts the tiles after those.
   // Entry k of a CTA's sequence travels through slot k % kTileQ; -1 ends the sequence.
   auto read_slot = [&](int k) -> int {  // one thread of a consumer role; -2 when the wait gave up
     const int slot = k % kTileQ;

@@ -214,20 +214,19 @@ __global__ void compact_count_kernel(CompactArgs a) {
 }
 
 // Pass 2: single CTA. Exclusive scans of the active flags (item index) and of the kept counts
-// (offset into kv_idx), then the longest-first permutation by a stable counting sort: W warps own
-// contiguous candidate slices, each with its own histogram in shared memory; bucket starts are
-// (items with more kept blocks) + (same bucket, earlier slices); every warp then places its slice in
-// ascending candidate order, 32 at a time.
+// (offset into kv_idx), then the processing order: items grouped by (request, head), q-blocks ascending
+// inside a group, by a stable counting sort: W warps own contiguous candidate slices, each with its own
+// histogram in shared memory; bucket starts are (items of smaller keys) + (same bucket, earlier
+// slices); every warp then places its slice in ascending candidate order, 32 at a time.
 __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int sort_warps) {
-  extern __shared__ int s_whist[];  // [sort_warps][nb]
+  extern __shared__ int s_whist[];  // [sort_warps + 1][batch * head_count]
   __shared__ int s_warp_items[32];
   __shared__ long long s_warp_kept[32];
   __shared__ int s_carry_items;
   __shared__ long long s_carry_kept;
+  __shared__ int64_t s_prefix[kMaxBatchSmem + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int nb = a.max_nkv + 1;
   if (tid == 0) { s_carry_items = 0; s_carry_kept = 0; }
-  for (int i = tid; i < sort_warps * nb; i += blockDim.x) s_whist[i] = 0;
   __syncthreads();
   for (int64_t base = 0; base < a.n_cand; base += blockDim.x) {
     const int64_t c = base + tid;
@@ -279,19 +278,35 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
     a.counters[3] = a.max_nkv;
     a.kv_ptr[n_items <= a.max_items ? n_items : 0] = static_cast<int>(total_kept);
   }
-  // ---- stable counting sort by descending kept count
+  // ---- processing order: stable counting sort by (request, head), so that the CTAs that run at the same
+  // time work on neighbouring q-blocks of the same few heads and share their K / V tiles in L2
+  const int nb = a.batch * a.head_count;
+  if (sort_warps <= 0) {  // too many (request, head) groups for the shared-memory histograms: canonical order
+    for (int i = tid; i < n_items && i < a.max_items; i += blockDim.x) a.order[i] = i;
+    return;
+  }
+  int* s_total = s_whist + sort_warps * nb;  // [nb] bucket totals, then bucket starts
+  for (int i = tid; i < (sort_warps + 1) * nb; i += blockDim.x) s_whist[i] = 0;
+  build_cand_prefix(a, s_prefix);
+  auto key_of = [&](int64_t c) -> int {
+    int lo = 0, hi = a.batch;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_prefix[mid] <= c) lo = mid; else hi = mid;
+    }
+    return lo * a.head_count + static_cast<int>((c - s_prefix[lo]) % a.head_count);
+  };
   const int64_t slice = ((a.n_cand + sort_warps - 1) / sort_warps + 31) / 32 * 32;
   const int64_t my0 = static_cast<int64_t>(warp) * slice;
   const int64_t my1 = (my0 + slice < a.n_cand) ? my0 + slice : a.n_cand;
   if (warp < sort_warps) {
     int* h = s_whist + warp * nb;
     for (int64_t c = my0 + lane; c < my1; c += 32) {
-      const int v = a.cnt[c];
-      if (v >= 0 && v < nb) atomicAdd(&h[v], 1);
+      if (a.cnt[c] >= 0) atomicAdd(&h[key_of(c)], 1);
     }
   }
   __syncthreads();
-  // per bucket: exclusive prefix over the slices; the bucket total goes to a.hist (global scratch)
+  // per bucket: exclusive prefix over the slices; the bucket total goes to s_total
   for (int k = tid; k < nb; k += blockDim.x) {
     int run = 0;
     for (int w = 0; w < sort_warps; ++w) {
@@ -299,35 +314,35 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
       s_whist[w * nb + k] = run;
       run += t;
     }
-    a.hist[k] = run;
+    s_total[k] = run;
   }
   __syncthreads();
-  // bucket bases for descending order: base[k] = number of items with kept > k (suffix scan by warp 0)
+  // bucket starts in ascending key order (exclusive scan by warp 0)
   if (warp == 0) {
     int carry = 0;
-    for (int hi = nb - 1; hi >= 0; hi -= 32) {
-      const int k = hi - lane;
-      const int v = (k >= 0) ? a.hist[k] : 0;
+    for (int k0 = 0; k0 < nb; k0 += 32) {
+      const int k = k0 + lane;
+      const int v = (k < nb) ? s_total[k] : 0;
       int x = v;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int y = __shfl_up_sync(0xffffffffu, x, o);
         if (lane >= o) x += y;
       }
-      if (k >= 0) a.hist[k] = carry + x - v;
+      if (k < nb) s_total[k] = carry + x - v;
       carry += __shfl_sync(0xffffffffu, x, 31);
     }
   }
   __syncthreads();
-  for (int i = tid; i < sort_warps * nb; i += blockDim.x) s_whist[i] += a.hist[i % nb];
+  for (int i = tid; i < sort_warps * nb; i += blockDim.x) s_whist[i] += s_total[i % nb];
   __syncthreads();
   if (warp < sort_warps) {
     int* h = s_whist + warp * nb;
     for (int64_t base = my0; base < my1; base += 32) {
       const int64_t c = base + lane;
-      const int v = (c < my1) ? a.cnt[c] : -1;
-      const bool flag = v >= 0 && v < nb;
-      const unsigned grp = __match_any_sync(0xffffffffu, flag ? v : -1 - lane);
+      const bool flag = (c < my1) && a.cnt[c] >= 0;
+      const int v = flag ? key_of(c) : -1 - lane;
+      const unsigned grp = __match_any_sync(0xffffffffu, v);
       const int rank_in_grp = __popc(grp & ((1u << lane) - 1u));
       const int leader = __ffs(grp) - 1;
       int start = 0;
@@ -407,13 +422,14 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
   const int threads = 256, wpb = threads / 32;
   int64_t blocks = (a.n_cand + wpb - 1) / wpb;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  // sort histograms: as many warps as fit in ~160 KB of shared memory
-  const int64_t nb = static_cast<int64_t>(a.max_nkv) + 1;
-  int64_t sort_warps = (160 * 1024) / (nb * 4);
+  // sort histograms: as many warps as fit in ~160 KB of shared memory, plus one row of bucket totals;
+  // with more (request, head) groups than fit, the kernel leaves the items in canonical order
+  const int64_t nb = static_cast<int64_t>(a.batch) * a.head_count;
+  int64_t sort_warps = nb > 0 ? (160 * 1024) / (nb * 4) - 1 : 0;
   if (sort_warps > 32) sort_warps = 32;
-  if (sort_warps < 1) return cudaErrorInvalidValue;  // more than 40960 kv-blocks per request
-  const size_t scan_smem = static_cast<size_t>(sort_warps * nb * 4);
-  if (scan_smem > 40 * 1024) {
+  if (sort_warps < 1) sort_warps = 0;
+  const size_t scan_smem = static_cast<size_t>((sort_warps + 1) * nb * 4) * (sort_warps > 0 ? 1 : 0);
+  if (scan_smem > 32 * 1024) {
     cudaError_t ea = cudaFuncSetAttribute(compact_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
     if (ea != cudaSuccess) return ea;
   }

@@ -100,6 +100,14 @@ class UlyssesSparseDiTAttentionBlock:
         n = num_heads * head_dim
         self.q, self.k, self.v = mk(1, self.s_loc, n), mk(1, self.s_loc, n), mk(1, self.s_loc, n)
         self.attn = mk(num_tokens, self.hc, head_dim)
+        if world > 1:
+            # the exchange of Q (K) runs on a side stream beside the projection of K (V)
+            self.heads_in = [mk(num_tokens, self.hc, head_dim) for _ in range(3)]
+            self.send_buf = [mk(world * self.s_loc, self.hc, head_dim) for _ in range(3)]
+            self.on_gpu = torch.device(device).type == "cuda"
+            if self.on_gpu:
+                self.comm_stream = torch.cuda.Stream(device=device)
+                self.ev = [torch.cuda.Event() for _ in range(4)]
         self.y = mk(1, self.s_loc, hid_out)
         self.cache = mk(1, self.s_loc, hid_out)
         self.wrapper = BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=device))
@@ -107,23 +115,53 @@ class UlyssesSparseDiTAttentionBlock:
         self.wrapper.plan(indptr, indptr, self.hc, self.hc, head_dim, q_data_type=dtype, mask_num_heads=num_heads,
                           mask_head_begin=self.hb)
 
-    def forward(self, x_local, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr):
-        """x_local [1, local tokens, hidden] -> this rank's rows of the block output [1, local tokens, hidden]."""
+    def forward(self, x_local, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, marks=None):
+        """x_local [1, local tokens, hidden] -> this rank's rows of the block output [1, local tokens, hidden].
+        `marks` (a list) receives CUDA events at the phase boundaries: start, projections + exchange done,
+        attention done, exchange back done, end."""
         H, D, S = self.H, self.D, self.S
+
+        def mark():
+            if marks is not None:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append(e)
+
+        mark()
         self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr)
         # the row offset of the local tokens inside the sequence is what the ops call num_text_tokens
-        flashomni_gemm(x_local, self.w.wq, H, sparse_info, sparse_info_indptr, self.t0, None, out=self.q, head_dim=D)
-        flashomni_gemm(x_local, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
-        flashomni_gemm(x_local, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
-        if self.world > 1:
-            qh = self.par.tokens_to_heads(self.q.view(self.s_loc, H, D), S, self.group)
-            kh = self.par.tokens_to_heads(self.k.view(self.s_loc, H, D), S, self.group)
-            vh = self.par.tokens_to_heads(self.v.view(self.s_loc, H, D), S, self.group)
+        if self.world > 1 and self.on_gpu:
+            main = torch.cuda.current_stream()
+            proj = ((self.q, self.w.wq, False), (self.k, self.w.wk, True), (self.v, self.w.wv, True))
+            for i, (dst, w, dense) in enumerate(proj):
+                if dense:
+                    flashomni_gemm(x_local, w, H, is_full=True, out=dst, head_dim=D)
+                else:
+                    flashomni_gemm(x_local, w, H, sparse_info, sparse_info_indptr, self.t0, None, out=dst, head_dim=D)
+                self.ev[i].record(main)
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(self.ev[i])
+                    self.par.tokens_to_heads(dst.view(self.s_loc, H, D), S, self.group, out=self.heads_in[i],
+                                             send_buf=self.send_buf[i])
+            self.ev[3].record(self.comm_stream)
+            main.wait_event(self.ev[3])
+            qh, kh, vh = self.heads_in
         else:
-            qh, kh, vh = (t.view(S, H, D) for t in (self.q, self.k, self.v))
+            flashomni_gemm(x_local, self.w.wq, H, sparse_info, sparse_info_indptr, self.t0, None, out=self.q, head_dim=D)
+            flashomni_gemm(x_local, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
+            flashomni_gemm(x_local, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
+            if self.world > 1:
+                qh, kh, vh = (self.par.tokens_to_heads(t.view(self.s_loc, H, D), S, self.group, out=o, send_buf=sb)
+                              for t, o, sb in zip((self.q, self.k, self.v), self.heads_in, self.send_buf))
+            else:
+                qh, kh, vh = (t.view(S, H, D) for t in (self.q, self.k, self.v))
+        mark()
         self.wrapper.run(qh, kh, vh, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                          out=self.attn)
+        mark()
         o_loc = self.par.heads_to_tokens(self.attn, S, self.group) if self.world > 1 else self.attn
+        mark()
         flashomni_gemm_reduction(o_loc.view(1, self.s_loc, H * D), self.w.wo, H, sparse_info, sparse_info_indptr,
                                  self.t0, self.cache, is_for_cache=False, head_dim=D, out=self.y)
+        mark()
         return self.y

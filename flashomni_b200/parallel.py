@@ -45,8 +45,10 @@ def token_range(num_tokens: int, rank: int, world: int) -> Tuple[int, int]:
     return b0, b1
 
 
-def tokens_to_heads(x: torch.Tensor, num_tokens: int, group=None) -> torch.Tensor:
-    """[local tokens, H, D] (all heads of my token range) -> [all tokens, H/P, D] (my heads of all tokens)."""
+def tokens_to_heads(x: torch.Tensor, num_tokens: int, group=None, out: torch.Tensor | None = None,
+                    send_buf: torch.Tensor | None = None) -> torch.Tensor:
+    """[local tokens, H, D] (all heads of my token range) -> [all tokens, H/P, D] (my heads of all tokens).
+    `out` ([num_tokens, H/P, D]) and `send_buf` ([P * local tokens, H/P, D]) let a caller reuse its buffers."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     s_loc, H, D = x.shape
@@ -54,8 +56,13 @@ def tokens_to_heads(x: torch.Tensor, num_tokens: int, group=None) -> torch.Tenso
     counts = [token_range(num_tokens, r, world) for r in range(world)]
     counts = [b - a for a, b in counts]
     assert counts[rank] == s_loc, "local token count does not match the block sharding"
-    send = x.view(s_loc, world, hc, D).permute(1, 0, 2, 3).contiguous().view(world * s_loc, hc, D)
-    recv = torch.empty((num_tokens, hc, D), dtype=x.dtype, device=x.device)
+    src = x.view(s_loc, world, hc, D).permute(1, 0, 2, 3)
+    if send_buf is None:
+        send = src.contiguous().view(world * s_loc, hc, D)
+    else:
+        send_buf.view(world, s_loc, hc, D).copy_(src)
+        send = send_buf
+    recv = out if out is not None else torch.empty((num_tokens, hc, D), dtype=x.dtype, device=x.device)
     dist.all_to_all_single(recv, send, output_split_sizes=counts, input_split_sizes=[s_loc] * world, group=group)
     return recv
 

@@ -68,7 +68,8 @@ FO_API int fo_segment_packbits(const uint8_t* x, const int32_t* indptr, const in
  *   items   int32 [max_items,4]  (b, h, qb, n_kept) of every active q-block, ascending (b, qb, h)
  *   kv_ptr  int32 [max_items+1]  offsets into kv_idx
  *   kv_idx  int32 [max_kept]     ascending kept kv-block indices per item
- *   order   int32 [max_items]    item indices by descending n_kept (stable): the schedule
+ *   order   int32 [max_items]    the processing order: item indices grouped by (b, h), q-blocks ascending
+ *                                (the identity when batch * head_count > 20480)
  *   counters int32 [4]           n_items, total_kept, status (FO_DEV_*), max_nkv
  * n_cand = sum over requests of ceil(qo_len/sbq)*head_count and max_nkv = max ceil(kv_len/sbkv) are
  * host-known (plan time). is_full != 0 ignores the masks (they may be null). scratch must hold
