@@ -421,7 +421,7 @@ def run_video(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "video_layer: hidden 5120, H=40, D=128, S=77312 (20 frames x 3840 + 512 text), batch 1, "
                                    "spatiotemporal-local block mask (+-1 frame + 10% random + text), Ulysses all-to-all",
-                       "parallelism": f"ulysses/{world}", "seed": SEED, "executed_flops_per_step": fl_total,
+                       "parallelism": f"ulysses/{world}", "exchange": blk.exchange, "seed": SEED, "executed_flops_per_step": fl_total,
                        "attention_tiles_rank0": tiles, "l2": "working set of several GB, far above the 126 MB L2",
                        "phase_ms_rank0": phases},
             "gpu_launches": int(args.steps * 10), "clocks": clocks}), flush=True)

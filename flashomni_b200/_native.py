@@ -22,6 +22,7 @@ FO_DEV_OK, FO_DEV_WAIT_TIMEOUT, FO_DEV_BAD_INDEX = 0, 1, 2
 _P = c_void_p
 SIGNATURES = {
     "fo_last_error": (c_char_p, []),
+    "fo_strided_gather": (c_int32, [c_int32, _P, _P, _P, _P, _P, c_int64, _P]),
     "fo_abi_version": (c_int32, []),
     "fo_packbits": (c_int32, [_P, c_int64, c_int32, _P, _P]),
     "fo_segment_packbits": (c_int32, [_P, _P, _P, c_int32, c_int64, c_int32, _P, _P]),

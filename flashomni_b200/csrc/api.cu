@@ -458,4 +458,35 @@ int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t i
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_o", e);
 }
 
+int32_t fo_strided_gather(int32_t n_src, const void* const* src, const int64_t* src_row_stride_bytes,
+                          const int64_t* n_rows, void* const* dst, const int64_t* dst_row_stride_bytes,
+                          int64_t row_bytes, void* stream) {
+  if (n_src < 0 || n_src > kMaxGatherSources)
+    return fail(FO_ERR_INVALID_ARG, "fo_strided_gather: between 0 and 16 sources");
+  if (n_src == 0) return FO_OK;
+  if (src == nullptr || dst == nullptr || src_row_stride_bytes == nullptr || dst_row_stride_bytes == nullptr ||
+      n_rows == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_strided_gather: null array");
+  if (row_bytes <= 0 || row_bytes % 16 != 0)
+    return fail(FO_ERR_INVALID_ARG, "fo_strided_gather: row_bytes must be a positive multiple of 16");
+  GatherArgs a;
+  memset(&a, 0, sizeof(a));
+  a.n_src = n_src;
+  a.row_vecs = row_bytes / 16;
+  for (int i = 0; i < n_src; ++i) {
+    if (n_rows[i] < 0) return fail(FO_ERR_INVALID_ARG, "fo_strided_gather: negative row count");
+    if (n_rows[i] > 0 && (src[i] == nullptr || dst[i] == nullptr || !aligned16(src[i]) || !aligned16(dst[i]) ||
+                          src_row_stride_bytes[i] % 16 != 0 || dst_row_stride_bytes[i] % 16 != 0 ||
+                          src_row_stride_bytes[i] < row_bytes || dst_row_stride_bytes[i] < row_bytes))
+      return fail(FO_ERR_INVALID_ARG, "fo_strided_gather: pointers and strides must be 16-byte aligned, strides >= row_bytes");
+    a.src[i] = static_cast<const uint8_t*>(src[i]);
+    a.dst[i] = static_cast<uint8_t*>(dst[i]);
+    a.src_stride[i] = src_row_stride_bytes[i];
+    a.dst_stride[i] = dst_row_stride_bytes[i];
+    a.vec_prefix[i + 1] = a.vec_prefix[i] + n_rows[i] * a.row_vecs;
+  }
+  const cudaError_t e = launch_strided_gather(a, sm_count(), static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_strided_gather", e);
+}
+
 }  // extern "C"

@@ -84,6 +84,19 @@ struct GemmArgs {
 };
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream);
 
+// ------------------------------------------------------------------ strided gather (exchange)
+constexpr int kMaxGatherSources = 16;
+struct GatherArgs {
+  const uint8_t* src[kMaxGatherSources];
+  uint8_t* dst[kMaxGatherSources];
+  int64_t src_stride[kMaxGatherSources];   // bytes between rows
+  int64_t dst_stride[kMaxGatherSources];
+  int64_t vec_prefix[kMaxGatherSources + 1];  // exclusive prefix of rows * row_vecs
+  int64_t row_vecs;                         // 16-byte vectors per row
+  int n_src;
+};
+cudaError_t launch_strided_gather(const GatherArgs& a, int sm_count, cudaStream_t stream);
+
 // ------------------------------------------------------------------ attention
 struct AttnArgs {
   CUtensorMap tmap_q;              // [D, H, Tq]   box 64 x 1 x 128

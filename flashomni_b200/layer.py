@@ -85,7 +85,7 @@ class UlyssesSparseDiTAttentionBlock:
     exchanges are skipped."""
 
     def __init__(self, weights: BlockWeights, num_heads: int, head_dim: int, num_tokens: int, rank: int, world: int,
-                 device, dtype=torch.bfloat16, group=None):
+                 device, dtype=torch.bfloat16, group=None, exchange: str = "p2p"):
         from . import parallel as par
         self.par = par
         self.w, self.H, self.D, self.S = weights, num_heads, head_dim, num_tokens
@@ -98,9 +98,23 @@ class UlyssesSparseDiTAttentionBlock:
         hid_out = weights.wo.shape[0]
         mk = lambda *s: torch.zeros(*s, dtype=dtype, device=device)
         n = num_heads * head_dim
-        self.q, self.k, self.v = mk(1, self.s_loc, n), mk(1, self.s_loc, n), mk(1, self.s_loc, n)
-        self.attn = mk(num_tokens, self.hc, head_dim)
-        if world > 1:
+        self.px = par.PeerExchange(group, device) if (world > 1 and exchange == "p2p") else None
+        if self.px is not None and self.px.available:
+            # buffers that other ranks read: symmetric memory, the same (largest) shape on every rank
+            rows_max = max(par.shard_blocks((num_tokens + 127) // 128, world)) * 128
+            self.q_full, self.q_ptrs, _ = self.px.alloc((1, rows_max, n), dtype)
+            self.k_full, self.k_ptrs, _ = self.px.alloc((1, rows_max, n), dtype)
+            self.v_full, self.v_ptrs, _ = self.px.alloc((1, rows_max, n), dtype)
+            self.q, self.k, self.v = (t[:, :self.s_loc] for t in (self.q_full, self.k_full, self.v_full))
+            self.attn, self.attn_ptrs, _ = self.px.alloc((num_tokens, self.hc, head_dim), dtype)
+            self.heads_in = [mk(num_tokens, self.hc, head_dim) for _ in range(3)]
+            self.o_loc = mk(self.s_loc, num_heads, head_dim)
+            self.exchange = "p2p"
+        else:
+            self.q, self.k, self.v = mk(1, self.s_loc, n), mk(1, self.s_loc, n), mk(1, self.s_loc, n)
+            self.attn = mk(num_tokens, self.hc, head_dim)
+            self.exchange = "nccl" if world > 1 else "none"
+        if self.exchange == "nccl":
             # the exchange of Q (K) runs on a side stream beside the projection of K (V)
             self.heads_in = [mk(num_tokens, self.hc, head_dim) for _ in range(3)]
             self.send_buf = [mk(world * self.s_loc, self.hc, head_dim) for _ in range(3)]
@@ -130,7 +144,16 @@ class UlyssesSparseDiTAttentionBlock:
         mark()
         self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr)
         # the row offset of the local tokens inside the sequence is what the ops call num_text_tokens
-        if self.world > 1 and self.on_gpu:
+        if self.exchange == "p2p":
+            flashomni_gemm(x_local, self.w.wq, H, sparse_info, sparse_info_indptr, self.t0, None, out=self.q, head_dim=D)
+            flashomni_gemm(x_local, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
+            flashomni_gemm(x_local, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
+            self.px.barrier(0)  # every rank's projections are complete (and its previous pull of attn is over)
+            isz = self.q.element_size()
+            for ptrs, dst in zip((self.q_ptrs, self.k_ptrs, self.v_ptrs), self.heads_in):
+                self.px.pull_heads(ptrs, S, H, D, isz, dst)
+            qh, kh, vh = self.heads_in
+        elif self.world > 1 and self.on_gpu:
             main = torch.cuda.current_stream()
             proj = ((self.q, self.w.wq, False), (self.k, self.w.wk, True), (self.v, self.w.wv, True))
             for i, (dst, w, dense) in enumerate(proj):
@@ -159,7 +182,12 @@ class UlyssesSparseDiTAttentionBlock:
         self.wrapper.run(qh, kh, vh, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                          out=self.attn)
         mark()
-        o_loc = self.par.heads_to_tokens(self.attn, S, self.group) if self.world > 1 else self.attn
+        if self.exchange == "p2p":
+            self.px.barrier(1)  # every rank's attention is complete (and its pulls of q / k / v are over)
+            self.px.pull_tokens(self.attn_ptrs, S, H, D, self.attn.element_size(), self.o_loc)
+            o_loc = self.o_loc
+        else:
+            o_loc = self.par.heads_to_tokens(self.attn, S, self.group) if self.world > 1 else self.attn
         mark()
         flashomni_gemm_reduction(o_loc.view(1, self.s_loc, H * D), self.w.wo, H, sparse_info, sparse_info_indptr,
                                  self.t0, self.cache, is_for_cache=False, head_dim=D, out=self.y)

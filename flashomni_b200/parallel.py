@@ -78,3 +78,86 @@ def heads_to_tokens(x: torch.Tensor, num_tokens: int, group=None) -> torch.Tenso
     recv = torch.empty((world * s_loc, hc, D), dtype=x.dtype, device=x.device)
     dist.all_to_all_single(recv, x.contiguous(), output_split_sizes=[s_loc] * world, input_split_sizes=counts, group=group)
     return recv.view(world, s_loc, hc, D).permute(1, 0, 2, 3).contiguous().view(s_loc, world * hc, D)
+
+
+class PeerExchange:
+    """The Ulysses exchange over peer memory instead of a library all-to-all: the buffers that other ranks
+    read live in symmetric memory (every rank maps every rank's copy), and each rank pulls the slices it needs
+    with one strided-gather kernel (C ABI `fo_strided_gather`: plain loads over NVLink, written in their final
+    layout). Steps are ordered by the symmetric-memory barrier (a device-side signal exchange of a few
+    microseconds on the current stream).
+
+    `available` is False when symmetric memory cannot be set up (CPU tensors, a torch build without it, a
+    failed rendezvous); callers then keep the `all_to_all_single` path."""
+
+    def __init__(self, group, device, timeout_ms: int = 10000):
+        self.group = group if group is not None else dist.group.WORLD
+        self.device = torch.device(device)
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.timeout_ms = timeout_ms
+        self.available = False
+        self._sm = None
+        self._bar = None
+        if self.device.type != "cuda":
+            return
+        try:
+            import torch.distributed._symmetric_memory as sm
+            self._sm = sm
+            pad = sm.empty((256,), dtype=torch.int32, device=self.device)
+            self._bar = sm.rendezvous(pad, self.group)
+            self._pad = pad
+            self.available = True
+        except Exception as e:  # noqa: BLE001 - any failure means "not available here"
+            self.reason = f"{type(e).__name__}: {e}"
+
+    def alloc(self, shape, dtype):
+        """A zero-filled tensor in symmetric memory (same shape on every rank) and the device pointers of all
+        ranks' copies as mapped into this process."""
+        t = self._sm.empty(tuple(shape), dtype=dtype, device=self.device)
+        t.zero_()
+        hdl = self._sm.rendezvous(t, self.group)
+        return t, [int(p) for p in hdl.buffer_ptrs], hdl
+
+    def barrier(self, channel: int = 0):
+        """All ranks' work queued before this point on their current streams is complete when the current
+        stream passes it."""
+        self._bar.barrier(channel=channel, timeout_ms=self.timeout_ms)
+
+    @staticmethod
+    def gather(srcs, src_strides, n_rows, dsts, dst_strides, row_bytes: int):
+        """One launch of the strided row gather on the current stream (lists of equal length, byte units)."""
+        import ctypes
+        from . import _native
+        n = len(srcs)
+        lib = _native.load()
+        P = ctypes.c_void_p * n
+        L = ctypes.c_int64 * n
+        rc = lib.fo_strided_gather(n, P(*srcs), L(*src_strides), L(*n_rows), P(*dsts), L(*dst_strides), row_bytes,
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        _native.check(rc, "fo_strided_gather")
+
+    def pull_heads(self, peer_ptrs, num_tokens: int, num_heads: int, head_dim: int, itemsize: int, out: torch.Tensor):
+        """tokens -> heads: `peer_ptrs[r]` is rank r's [local tokens of r, H, D] buffer; fills `out`
+        [num_tokens, H/P, D] with this rank's heads of every rank's tokens."""
+        hc = num_heads // self.world
+        row = hc * head_dim * itemsize
+        srcs, sst, rows, dsts, dst_ = [], [], [], [], []
+        for r in range(self.world):
+            a, b = token_range(num_tokens, r, self.world)
+            srcs.append(peer_ptrs[r] + self.rank * row)
+            sst.append(num_heads * head_dim * itemsize)
+            rows.append(b - a)
+            dsts.append(out.data_ptr() + a * row)
+            dst_.append(row)
+        self.gather(srcs, sst, rows, dsts, dst_, row)
+
+    def pull_tokens(self, peer_ptrs, num_tokens: int, num_heads: int, head_dim: int, itemsize: int, out: torch.Tensor):
+        """heads -> tokens: `peer_ptrs[r]` is rank r's [num_tokens, H/P, D] buffer (its heads); fills `out`
+        [local tokens, H, D] with all heads of this rank's tokens."""
+        hc = num_heads // self.world
+        row = hc * head_dim * itemsize
+        a, b = token_range(num_tokens, self.rank, self.world)
+        n = self.world
+        self.gather([peer_ptrs[r] + a * row for r in range(n)], [row] * n, [b - a] * n,
+                    [out.data_ptr() + r * row for r in range(n)], [num_heads * head_dim * itemsize] * n, row)

@@ -151,6 +151,19 @@ FO_API int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_h
                        const int32_t* sparse_info_indptr, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* ---- strided row gather (sequence-parallel exchange) -----------------------------------------------
+ * No counterpart in the reference (it has no multi-GPU code). For source i < n_src (at most 16), copies
+ * n_rows[i] rows of row_bytes bytes from src[i] (rows src_row_stride_bytes[i] apart) to dst[i] (rows
+ * dst_row_stride_bytes[i] apart), all in one launch. A source may be another GPU's buffer mapped into this
+ * process (a peer pointer): the kernel reads it with plain loads over NVLink and writes into local memory,
+ * which turns the all-to-all of a sequence-parallel attention block plus its two layout changes into one
+ * pull per rank. Pointers, strides and row_bytes must be multiples of 16. The arrays are host arrays and
+ * are read before the call returns. Ordering against the producers of the sources (on other GPUs) is the
+ * caller's business. */
+FO_API int32_t fo_strided_gather(int32_t n_src, const void* const* src, const int64_t* src_row_stride_bytes,
+                                 const int64_t* n_rows, void* const* dst, const int64_t* dst_row_stride_bytes,
+                                 int64_t row_bytes, void* stream);
+
 /* ---- GEMM-Q without a caller workspace ------------------------------------------------------------
  * No counterpart in the reference. Same arguments and result as fo_gemm_q minus the workspace: the
  * tile list, counters and status word live in a 1 MiB array that is part of the library image (one

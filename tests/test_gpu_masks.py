@@ -137,3 +137,25 @@ def test_gemm_worklists_bit_exact(cuda_device):
             assert np.array_equal(w[8 + R + 1:8 + R + 1 + len(rheads)], rheads)
             o0 = 8 + R + 1 + R * H
             assert np.array_equal(w[o0:o0 + R], rorder)
+
+
+def test_strided_gather_matches_torch(cuda_device):
+    """fo_strided_gather on local buffers: the two layouts of the sequence-parallel exchange."""
+    from flashomni_b200.parallel import PeerExchange
+    g = torch.Generator().manual_seed(5)
+    H, D, hc = 8, 128, 2
+    srcs = [torch.randn(n, H, D, generator=g).to(torch.bfloat16).to(cuda_device) for n in (256, 128, 384)]
+    out = torch.zeros(sum(t.shape[0] for t in srcs), hc, D, dtype=torch.bfloat16, device=cuda_device)
+    row = hc * D * 2
+    offs = [0, 256, 384]
+    PeerExchange.gather([t.data_ptr() + 3 * row for t in srcs], [H * D * 2] * 3, [t.shape[0] for t in srcs],
+                        [out.data_ptr() + o * row for o in offs], [row] * 3, row)
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.cat([t[:, 6:8] for t in srcs]))
+    # the way back: contiguous source rows into a column block of a wider destination
+    back = torch.zeros(128, H, D, dtype=torch.bfloat16, device=cuda_device)
+    PeerExchange.gather([out.data_ptr() + 256 * row], [row], [128], [back.data_ptr() + 3 * row], [H * D * 2], row)
+    torch.cuda.synchronize()
+    assert torch.equal(back[:, 6:8], srcs[1][:, 6:8]) and int(back[:, :6].abs().sum()) == 0
+    with pytest.raises(ValueError):
+        PeerExchange.gather([out.data_ptr() + 2], [row], [1], [back.data_ptr()], [row], row)   # misaligned

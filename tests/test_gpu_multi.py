@@ -31,7 +31,7 @@ def _case():
     return H, S, hid, m, ws, x, cache
 
 
-def _worker(rank, world, port, out_dict):
+def _worker(rank, world, port, out_dict, exchange):
     import torch.distributed as dist
     from flashomni_b200.layer import BlockWeights, UlyssesSparseDiTAttentionBlock
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -42,7 +42,9 @@ def _worker(rank, world, port, out_dict):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
         H, S, hid, m, ws, x, cache = _case()
-        blk = UlyssesSparseDiTAttentionBlock(BlockWeights(*(w.to(device) for w in ws)), H, 128, S, rank, world, device)
+        blk = UlyssesSparseDiTAttentionBlock(BlockWeights(*(w.to(device) for w in ws)), H, 128, S, rank, world, device,
+                                             exchange=exchange)
+        assert blk.exchange == exchange, getattr(blk.px, "reason", "")
         blk.cache.copy_(cache[:, blk.t0:blk.t1].to(device))
         masks = [torch.from_numpy(a).to(device) for a in (m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr)]
         xl = x[:, blk.t0:blk.t1].contiguous().to(device)
@@ -56,7 +58,9 @@ def _worker(rank, world, port, out_dict):
         dist.destroy_process_group()
 
 
-def test_ulysses_block_matches_single_gpu():
+@pytest.mark.parametrize("exchange", ["p2p", "nccl"])
+def test_ulysses_block_matches_single_gpu(exchange):
+    """p2p: pulls over peer memory (fo_strided_gather); nccl: all_to_all_single on a side stream."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -64,7 +68,7 @@ def test_ulysses_block_matches_single_gpu():
     world = 2
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), out, exchange), nprocs=world, join=True)
     H, S, hid, m, ws, x, cache = _case()
     device = torch.device("cuda", 0)
     blk = SparseDiTAttentionBlock(BlockWeights(*(w.to(device) for w in ws)), H, 128, 1, S, device=device)
