@@ -14,3 +14,4 @@ from .gemm import flashomni_gemm as flashomni_gemm  # noqa: F401
 from .gemm import flashomni_gemm_reduction as flashomni_gemm_reduction  # noqa: F401
 from .quantization import packbits as packbits  # noqa: F401
 from .quantization import segment_packbits as segment_packbits  # noqa: F401
+from .selection import select_blocks as select_blocks  # noqa: F401

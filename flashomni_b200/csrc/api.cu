@@ -458,6 +458,55 @@ int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t i
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_o", e);
 }
 
+size_t fo_select_blocks_scratch_bytes(int32_t batch, int32_t num_blocks) {
+  if (batch < 0 || num_blocks < 0) return 0;
+  const size_t n = static_cast<size_t>(batch) * static_cast<size_t>(num_blocks);
+  return ((n * 4 + 15) & ~static_cast<size_t>(15)) + ((n + 15) & ~static_cast<size_t>(15)) + 16;
+}
+
+int32_t fo_select_blocks(const float* pooled_score, int32_t batch, int32_t num_heads, int32_t num_blocks,
+                         int32_t num_text_blocks, const float* q_threshold, const float* kv_threshold,
+                         int32_t zero_inactive, uint8_t* sparse_info, int64_t sparse_info_bytes,
+                         uint8_t* sparse_kv_info, int64_t sparse_kv_info_bytes, int32_t* info_indptr,
+                         int32_t* kv_info_indptr, void* scratch, size_t scratch_bytes, void* stream) {
+  if (batch <= 0 || num_heads <= 0 || num_blocks <= 0 || num_text_blocks < 0 || num_text_blocks > num_blocks)
+    return fail(FO_ERR_INVALID_ARG, "fo_select_blocks: bad sizes");
+  if (num_blocks > 2048) return fail(FO_ERR_UNSUPPORTED, "fo_select_blocks: at most 2048 blocks per request");
+  if (pooled_score == nullptr || q_threshold == nullptr || kv_threshold == nullptr || sparse_info == nullptr ||
+      sparse_kv_info == nullptr || info_indptr == nullptr || kv_info_indptr == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_select_blocks: null pointer");
+  SelectArgs a;
+  memset(&a, 0, sizeof(a));
+  a.info_seg_bytes = (static_cast<int64_t>(num_blocks) * num_heads + 7) / 8;
+  a.kv_seg_bytes = (static_cast<int64_t>(num_blocks) * num_heads * num_blocks + 7) / 8;
+  a.kv_words = (static_cast<int64_t>(batch) * a.kv_seg_bytes + 3) / 4;
+  if (a.kv_seg_bytes * batch > 0x7fffffffLL)
+    return fail(FO_ERR_UNSUPPORTED, "fo_select_blocks: packed kv mask above 2 GiB (int32 byte indptr)");
+  if (sparse_info_bytes < a.info_seg_bytes * batch || sparse_kv_info_bytes < a.kv_words * 4)
+    return fail(FO_ERR_INVALID_ARG, "fo_select_blocks: output buffers too small (the kv stream is written in 4-byte words)");
+  if ((reinterpret_cast<uintptr_t>(sparse_kv_info) & 3u) != 0)
+    return fail(FO_ERR_INVALID_ARG, "fo_select_blocks: sparse_kv_info must be 4-byte aligned");
+  if (scratch == nullptr || scratch_bytes < fo_select_blocks_scratch_bytes(batch, num_blocks) || !aligned16(scratch))
+    return fail(FO_ERR_WORKSPACE, "fo_select_blocks: scratch too small or misaligned");
+  a.score = pooled_score;
+  a.q_thr = q_threshold;
+  a.kv_thr = kv_threshold;
+  a.batch = batch;
+  a.heads = num_heads;
+  a.n = num_blocks;
+  a.t2t = num_text_blocks;
+  a.zero_inactive = zero_inactive;
+  a.sparse_info = sparse_info;
+  a.sparse_kv_info = sparse_kv_info;
+  a.info_indptr = info_indptr;
+  a.kv_info_indptr = kv_info_indptr;
+  const size_t n = static_cast<size_t>(batch) * static_cast<size_t>(num_blocks);
+  a.t2i = static_cast<float*>(scratch);
+  a.q_keep = static_cast<uint8_t*>(scratch) + ((n * 4 + 15) & ~static_cast<size_t>(15));
+  const cudaError_t e = launch_select_blocks(a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_select_blocks", e);
+}
+
 int32_t fo_strided_gather(int32_t n_src, const void* const* src, const int64_t* src_row_stride_bytes,
                           const int64_t* n_rows, void* const* dst, const int64_t* dst_row_stride_bytes,
                           int64_t row_bytes, void* stream) {

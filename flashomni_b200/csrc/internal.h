@@ -84,6 +84,24 @@ struct GemmArgs {
 };
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream);
 
+// ------------------------------------------------------------------ block selection
+struct SelectArgs {
+  const float* score;        // [batch, heads, n, n]
+  const float* q_thr;        // [batch]
+  const float* kv_thr;       // [heads]
+  int batch, heads, n, t2t, zero_inactive;
+  int64_t info_seg_bytes;    // ceil(n * heads / 8)
+  int64_t kv_seg_bytes;      // ceil(n * heads * n / 8)
+  int64_t kv_words;          // 32-bit words of sparse_kv_info that are zeroed first
+  uint8_t* sparse_info;
+  uint8_t* sparse_kv_info;
+  int32_t* info_indptr;      // [batch + 1]
+  int32_t* kv_info_indptr;   // [batch + 1]
+  float* t2i;                // scratch [batch, n]
+  uint8_t* q_keep;           // scratch [batch, n]
+};
+cudaError_t launch_select_blocks(const SelectArgs& a, cudaStream_t stream);
+
 // ------------------------------------------------------------------ strided gather (exchange)
 constexpr int kMaxGatherSources = 16;
 struct GatherArgs {

@@ -151,6 +151,27 @@ FO_API int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_h
                        const int32_t* sparse_info_indptr, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* ---- block selection: pooled scores -> packed masks ------------------------------------------------
+ * Replaces the mask generation of benchmark/test_attn_score.py:93-133 (torch sum / softmax / sort / cumsum /
+ * searchsorted + Triton fill kernels on an unpacked [B, H, nq, nkv] layout) and the transpose + bit-pack its
+ * callers add (benchmark/utils.py:83-84). pooled_score is fp32 [batch, heads, n, n] (n q-blocks = n kv-blocks,
+ * the first num_text_blocks are text). q_threshold [batch] and kv_threshold [heads] are device arrays.
+ *   q-blocks: text-to-image scores summed over heads and text rows, softmax over the image blocks; the blocks
+ *     taken in ascending (mass, index) order while the cumulative mass stays <= threshold are switched off for
+ *     every head. Nothing is switched off when there are no text blocks.
+ *   kv-blocks: per (b, h, image q-block) the row softmax over all kv-blocks, same rule with the head's
+ *     threshold; text q rows keep everything. With zero_inactive the rows of switched-off q-blocks are zero.
+ * Outputs: sparse_info (bit qb*H + h) and sparse_kv_info (bit (qb*H + h)*n + kvb), little-endian, one segment of
+ * ceil(bits / 8) bytes per request, plus the two byte indptrs [batch + 1]: exactly what fo_mask_compact and the
+ * GEMM entry points read. sparse_kv_info must be 4-byte aligned and hold the total rounded up to 4 bytes.
+ * The arithmetic is fixed (see oracle/select.py): results are bit-identical to that statement. */
+FO_API size_t fo_select_blocks_scratch_bytes(int32_t batch, int32_t num_blocks);
+FO_API int32_t fo_select_blocks(const float* pooled_score, int32_t batch, int32_t num_heads, int32_t num_blocks,
+                                int32_t num_text_blocks, const float* q_threshold, const float* kv_threshold,
+                                int32_t zero_inactive, uint8_t* sparse_info, int64_t sparse_info_bytes,
+                                uint8_t* sparse_kv_info, int64_t sparse_kv_info_bytes, int32_t* info_indptr,
+                                int32_t* kv_info_indptr, void* scratch, size_t scratch_bytes, void* stream);
+
 /* ---- strided row gather (sequence-parallel exchange) -----------------------------------------------
  * No counterpart in the reference (it has no multi-GPU code). For source i < n_src (at most 16), copies
  * n_rows[i] rows of row_bytes bytes from src[i] (rows src_row_stride_bytes[i] apart) to dst[i] (rows

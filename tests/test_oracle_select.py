@@ -1,0 +1,57 @@
+"""Block selection: the integer / fixed-arithmetic statement against the float statement in the reference's
+operation order, and its properties."""
+
+import numpy as np
+import pytest
+
+from oracle import select as osel
+from oracle.masks import unpack_segment
+
+
+def _scores(seed, B, H, n, scale=2.0):
+    return (np.random.default_rng(seed).standard_normal((B, H, n, n)) * scale).astype(np.float32)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_matches_float_statement(seed):
+    s = _scores(seed, 2, 3, 24)
+    got = osel.select_blocks(s, 2, [0.2, 0.35], [0.1, 0.3, 0.5])
+    ref = osel.select_blocks_float(s, 2, [0.2, 0.35], [0.1, 0.3, 0.5])
+    assert np.array_equal(got[0], ref[0]) and np.array_equal(got[1], ref[1])
+
+
+def test_exponential_accuracy_and_exactness():
+    x = (np.random.default_rng(1).standard_normal((16, 600)) * 3).astype(np.float32)
+    m = osel.det_exp2_mass(x).astype(np.float64) / 2 ** 31
+    ref = np.exp((x - x.max(-1, keepdims=True)).astype(np.float64))
+    assert np.max(np.abs(m - ref)) < 2e-6
+    assert np.all(osel.det_exp2_mass(x).max(-1) == 2 ** 31)          # the row maximum is exactly 1
+    assert osel.det_exp2_mass(np.array([0.0, -100.0], np.float32)).tolist() == [2 ** 31, 0]
+
+
+def test_thresholds_and_text_rows():
+    s = _scores(3, 1, 2, 12, scale=1.0)
+    qa, kk = osel.select_blocks(s, 3, 0.0, 0.0)
+    assert qa.all() and kk.all()                                     # nothing has cumulative mass <= 0
+    qa, kk = osel.select_blocks(s, 3, 1.0, 1.0, zero_inactive=False)
+    assert qa[0, :3].all() and not qa[0, 3:].any()                   # every image q-block switched off
+    assert kk[0, :3].all() and not kk[0, 3:].any()                   # text rows keep all, image rows nothing
+    qa, kk = osel.select_blocks(s, 0, 0.5, 0.3)
+    assert qa.all()                                                  # no text rows: no q-block selection
+    # the switched-off kv-blocks of a row are exactly its lowest scores
+    qa, kk = osel.select_blocks(s, 3, 0.0, 0.4)
+    for h in range(2):
+        for q in range(3, 12):
+            off = kk[0, q, h] == 0
+            if off.any() and (~off).any():
+                assert s[0, h, q][off].max() <= s[0, h, q][~off].min()
+
+
+def test_packing_layout():
+    s = _scores(4, 2, 3, 10)
+    qa, kk = osel.select_blocks(s, 2, 0.3, 0.3)
+    info, kv, ip, kp = osel.pack_selection(qa, kk)
+    assert ip.tolist() == [0, 4, 8] and kp.tolist() == [0, 38, 76]   # ceil(30/8), ceil(300/8)
+    for b in range(2):
+        assert np.array_equal(unpack_segment(info, int(ip[b]), 30), qa[b].reshape(-1))
+        assert np.array_equal(unpack_segment(kv, int(kp[b]), 300), kk[b].reshape(-1))
