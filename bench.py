@@ -31,8 +31,8 @@ HID, H, D, S, B, DENSITY, SEED = 3072, 24, 128, 4608, 2, 0.5, 2024
 FL_ATTN_TILE = 4 * 128 * 128 * 128
 FL_GEMM_TILE = 2 * 128 * 128 * HID
 # dram__bytes_read.sum + dram__bytes_write.sum per launch (ncu captures summarised in profiles/)
-GEMM_TRAFFIC_BYTES = 109.4e6   # average of one step's GEMM-Q, K, V, O launches
-ATTN_TRAFFIC_BYTES = 567.0e6
+GEMM_TRAFFIC_BYTES = 112.6e6   # average of one step's GEMM-Q, K, V, O launches
+ATTN_TRAFFIC_BYTES = 165.7e6
 
 
 def block_flops(masks, hb, hc, batch=B, seq=S):
