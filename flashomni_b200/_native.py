@@ -23,6 +23,9 @@ _P = c_void_p
 SIGNATURES = {
     "fo_last_error": (c_char_p, []),
     "fo_strided_gather": (c_int32, [c_int32, _P, _P, _P, _P, _P, c_int64, _P]),
+    "fo_gemm_q_prepared": (c_int32, [_P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, _P, c_size_t, _P]),
+    "fo_gemm_o_prepared": (c_int32, [_P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                     _P, c_size_t, _P]),
     "fo_select_blocks_scratch_bytes": (c_size_t, [c_int32, c_int32]),
     "fo_select_blocks": (c_int32, [_P, c_int32, c_int32, c_int32, c_int32, _P, _P, c_int32, _P, c_int64, _P, c_int64,
                                    _P, _P, _P, c_size_t, _P]),

@@ -366,15 +366,18 @@ int encode_gemm_maps(const char* who, GemmArgs& g, const void* x, const void* w,
 
 }  // namespace
 
-int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch, int32_t m,
-              int32_t n, int32_t k, int32_t num_heads, int32_t head_begin, int32_t head_dim,
-              int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full, const uint8_t* sparse_info,
-              int64_t sparse_info_bytes, const int32_t* sparse_info_indptr, void* workspace,
-              size_t workspace_bytes, void* stream) {
+namespace {
+// `prepared`: the work list is already in the workspace (built by fo_gemm_q_worklist on any stream ordered
+// before this call); only the status word and the tile cursor are reset here.
+int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch, int32_t m,
+                int32_t n, int32_t k, int32_t num_heads, int32_t head_begin, int32_t head_dim,
+                int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full, const uint8_t* sparse_info,
+                int64_t sparse_info_bytes, const int32_t* sparse_info_indptr, void* workspace,
+                size_t workspace_bytes, void* stream, bool prepared) {
   if (x == nullptr || w == nullptr || y == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_gemm_q: null x/w/y");
   if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_gemm_q: bad dtype");
   const GemmShape s = {batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens};
-  int rc = check_lists_common("fo_gemm_q", s, !is_full, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
+  int rc = check_lists_common("fo_gemm_q", s, !is_full && !prepared, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
   if (rc != FO_OK) return rc;
   if (k % 64 != 0) return fail(FO_ERR_UNSUPPORTED, "fo_gemm_q: k must be a multiple of 64");
   if (128 % head_dim != 0 && head_dim % 128 != 0)
@@ -391,7 +394,7 @@ int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t d
   if (!is_full) {
     GemmListArgs la = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
     la.is_full = 0;
-    e = launch_gemm_q_tiles(la, st);
+    e = prepared ? cudaMemsetAsync(wsw + 4, 0, 2 * sizeof(int32_t), st) : launch_gemm_q_tiles(la, st);
     if (e != cudaSuccess) return fail_cuda("fo_gemm_q (work list)", e);
     g.tiles = la.tiles;
     g.n_tiles_ptr = la.counters;
@@ -414,16 +417,35 @@ int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t d
   e = launch_gemm(g, sm_count(), st);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_q", e);
 }
+}  // namespace
 
-int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t init_is_full, int32_t dtype,
-              int32_t batch, int32_t m, int32_t n, int32_t k, int32_t num_heads, int32_t head_begin,
-              int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_for_cache,
-              const uint8_t* sparse_info, int64_t sparse_info_bytes, const int32_t* sparse_info_indptr,
-              void* workspace, size_t workspace_bytes, void* stream) {
+int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch, int32_t m,
+              int32_t n, int32_t k, int32_t num_heads, int32_t head_begin, int32_t head_dim,
+              int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full, const uint8_t* sparse_info,
+              int64_t sparse_info_bytes, const int32_t* sparse_info_indptr, void* workspace,
+              size_t workspace_bytes, void* stream) {
+  return gemm_q_impl(x, w, y, bias, dtype, batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size,
+                     num_text_tokens, is_full, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace,
+                     workspace_bytes, stream, false);
+}
+
+int fo_gemm_q_prepared(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch,
+                       int32_t m, int32_t n, int32_t k, int32_t head_dim, void* workspace, size_t workspace_bytes,
+                       void* stream) {
+  return gemm_q_impl(x, w, y, bias, dtype, batch, m, n, k, 1, 0, head_dim, 128, 0, 0, nullptr, 0, nullptr, workspace,
+                     workspace_bytes, stream, true);
+}
+
+namespace {
+int gemm_o_impl(const void* x, const void* w, void* y, const void* init, int32_t init_is_full, int32_t dtype,
+                int32_t batch, int32_t m, int32_t n, int32_t k, int32_t num_heads, int32_t head_begin,
+                int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_for_cache,
+                const uint8_t* sparse_info, int64_t sparse_info_bytes, const int32_t* sparse_info_indptr,
+                void* workspace, size_t workspace_bytes, void* stream, bool prepared) {
   if (x == nullptr || w == nullptr || y == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_gemm_o: null x/w/y");
   if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_gemm_o: bad dtype");
   const GemmShape s = {batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens};
-  int rc = check_lists_common("fo_gemm_o", s, true, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
+  int rc = check_lists_common("fo_gemm_o", s, !prepared, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
   if (rc != FO_OK) return rc;
   if (head_dim % 64 != 0) return fail(FO_ERR_UNSUPPORTED, "fo_gemm_o: head_dim must be a multiple of 64");
   if (k % head_dim != 0) return fail(FO_ERR_INVALID_ARG, "fo_gemm_o: k must be a multiple of head_dim");
@@ -437,7 +459,7 @@ int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t i
   if (rc != FO_OK) return rc;
   GemmListArgs la = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
   la.is_for_cache = is_for_cache;
-  cudaError_t e = launch_gemm_o_rows(la, st);
+  cudaError_t e = prepared ? cudaMemsetAsync(wsw + 4, 0, 2 * sizeof(int32_t), st) : launch_gemm_o_rows(la, st);
   if (e != cudaSuccess) return fail_cuda("fo_gemm_o (work list)", e);
   g.y = y;
   g.init = init;
@@ -456,6 +478,24 @@ int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t i
   g.cursor = wsw + 5;
   e = launch_gemm(g, sm_count(), st);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_o", e);
+}
+}  // namespace
+
+int fo_gemm_o(const void* x, const void* w, void* y, const void* init, int32_t init_is_full, int32_t dtype,
+              int32_t batch, int32_t m, int32_t n, int32_t k, int32_t num_heads, int32_t head_begin,
+              int32_t head_dim, int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_for_cache,
+              const uint8_t* sparse_info, int64_t sparse_info_bytes, const int32_t* sparse_info_indptr,
+              void* workspace, size_t workspace_bytes, void* stream) {
+  return gemm_o_impl(x, w, y, init, init_is_full, dtype, batch, m, n, k, num_heads, head_begin, head_dim,
+                     sparse_q_size, num_text_tokens, is_for_cache, sparse_info, sparse_info_bytes,
+                     sparse_info_indptr, workspace, workspace_bytes, stream, false);
+}
+
+int fo_gemm_o_prepared(const void* x, const void* w, void* y, const void* init, int32_t init_is_full, int32_t dtype,
+                       int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+  return gemm_o_impl(x, w, y, init, init_is_full, dtype, batch, m, n, k, 1, 0, head_dim, 128, 0, 0, nullptr, 0,
+                     nullptr, workspace, workspace_bytes, stream, true);
 }
 
 size_t fo_select_blocks_scratch_bytes(int32_t batch, int32_t num_blocks) {

@@ -61,11 +61,14 @@ def flashomni_gemm(
     *,
     head_begin: int = 0,
     head_dim: Optional[int] = None,
+    worklist: Optional["GemmWorklist"] = None,
 ) -> torch.Tensor:
     """GEMM-Q: out[b, rows, cols] = bias + A[b, rows, :] @ B[cols, :]^T for the 128x128 tiles whose
     (q-block, head) bit is set; other tiles of `out` keep their contents (reference:
     flashomni/gemm.py:156-186, kernel gemm.cuh:27-228). `head_begin` / `head_dim` (extensions, default =
-    reference behaviour) let B hold the rows of a head window when heads are split over GPUs."""
+    reference behaviour) let B hold the rows of a head window when heads are split over GPUs. `worklist`
+    (extension): a list from `prepare_gemm_q_list` for the same mask and shape, built earlier (e.g. on a side
+    stream); the mask arguments are then not read."""
     _gemm_common(A, B, "flashomni_gemm")
     batch, M, K = A.shape
     N = B.shape[0]
@@ -73,11 +76,22 @@ def flashomni_gemm(
         out = torch.empty((batch, M, N), device=A.device, dtype=A.dtype)
     elif tuple(out.shape) != (batch, M, N) or out.dtype != A.dtype or not out.is_contiguous():
         raise ValueError("flashomni_gemm: out must be a contiguous [batch, M, N] tensor of A's dtype")
-    if not is_full and (sparse_info is None or sparse_info_indptr is None):
-        raise ValueError("flashomni_gemm: sparse_info and sparse_info_indptr are required unless is_full=True")
     if head_dim is None:
         head_dim = N // num_qo_heads
     lib = _native.load()
+    if worklist is not None and not is_full:
+        worklist.check("q", batch, M, N, head_dim, A.device)
+        with torch.cuda.device(A.device):
+            worklist.wait(A.device)
+            rc = lib.fo_gemm_q_prepared(_native.ptr(A), _native.ptr(B), _native.ptr(out), _native.ptr(bias),
+                                        native_dtype(A.dtype), batch, M, N, K, head_dim, _native.ptr(worklist.ws),
+                                        worklist.ws.numel(), _native.current_stream(A.device))
+        _native.check(rc, "flashomni_gemm")
+        if _native.debug_checks():
+            _check_status(worklist.ws, "flashomni_gemm")
+        return out
+    if not is_full and (sparse_info is None or sparse_info_indptr is None):
+        raise ValueError("flashomni_gemm: sparse_info and sparse_info_indptr are required unless is_full=True")
     nbytes = lib.fo_gemm_workspace_bytes(batch, M, N, K, head_dim)
     ws = _workspace(A.device, nbytes)
     if sparse_info_indptr is not None and sparse_info_indptr.dtype != torch.int32:
@@ -108,13 +122,14 @@ def flashomni_gemm_reduction(
     head_begin: int = 0,
     head_dim: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    worklist: Optional["GemmWorklist"] = None,
 ) -> torch.Tensor:
     """GEMM-O: out = init + sum over the selected heads of A[..., hD:(h+1)D] @ B[:, hD:(h+1)D]^T, selected =
     active heads (is_for_cache=False, init = the cached [batch, M, N] tensor passed as `bias`) or inactive
     heads (is_for_cache=True, init = 1-D bias) (reference: flashomni/gemm.py:188-216, kernel
     gemm_reduction.cuh:27-276). `head_begin` / `head_dim` / `out` are extensions with reference defaults."""
     _gemm_common(A, B, "flashomni_gemm_reduction")
-    if sparse_info is None or sparse_info_indptr is None:
+    if worklist is None and (sparse_info is None or sparse_info_indptr is None):
         raise ValueError("flashomni_gemm_reduction: sparse_info and sparse_info_indptr are required")
     batch, M, K = A.shape
     N = B.shape[0]
@@ -135,6 +150,17 @@ def flashomni_gemm_reduction(
                                  "[batch, M, N] tensor")
             init_is_full = 1
     lib = _native.load()
+    if worklist is not None:
+        worklist.check("o", batch, M, K, head_dim, A.device, is_for_cache)
+        with torch.cuda.device(A.device):
+            worklist.wait(A.device)
+            rc = lib.fo_gemm_o_prepared(_native.ptr(A), _native.ptr(B), _native.ptr(out), _native.ptr(bias), init_is_full,
+                                        native_dtype(A.dtype), batch, M, N, K, head_dim, _native.ptr(worklist.ws),
+                                        worklist.ws.numel(), _native.current_stream(A.device))
+        _native.check(rc, "flashomni_gemm_reduction")
+        if _native.debug_checks():
+            _check_status(worklist.ws, "flashomni_gemm_reduction")
+        return out
     nbytes = lib.fo_gemm_workspace_bytes(batch, M, N, K, head_dim)
     ws = _workspace(A.device, nbytes)
     if sparse_info_indptr.dtype != torch.int32:
@@ -149,3 +175,76 @@ def flashomni_gemm_reduction(
     if _native.debug_checks():
         _check_status(ws, "flashomni_gemm_reduction")
     return out
+
+
+class GemmWorklist:
+    """A GEMM work list kept in its own workspace (extension): built from the mask by `prepare_gemm_q_list` /
+    `prepare_gemm_o_list`, possibly on a side stream, and consumed by `flashomni_gemm(..., worklist=)` /
+    `flashomni_gemm_reduction(..., worklist=)` on the caller's stream, which waits for the build first.
+    The list depends on the mask and the shape only, not on the operands."""
+
+    def __init__(self, kind: str, key: tuple, ws: torch.Tensor):
+        self.kind, self.key, self.ws = kind, key, ws
+        self.event: Optional[torch.cuda.Event] = None
+
+    def check(self, kind: str, batch: int, M: int, n_or_k: int, head_dim: int, device, is_for_cache: bool = False):
+        if (kind, (batch, M, n_or_k, head_dim, bool(is_for_cache)), device) != (self.kind, self.key, self.ws.device):
+            raise ValueError("worklist was prepared for a different op, shape or device")
+
+    def wait(self, device) -> None:
+        if self.event is not None:
+            torch.cuda.current_stream(device).wait_event(self.event)
+
+
+def _prepare(kind: str, batch: int, M: int, N: int, K: int, num_qo_heads: int, head_dim: int, sparse_info, indptr,
+             num_text_tokens: int, sparse_q_size: int, head_begin: int, is_for_cache: bool, into, stream):
+    _native.require_cuda(sparse_info, indptr)
+    dev = sparse_info.device
+    lib = _native.load()
+    # the consuming call checks the size for its full shape, which this list does not depend on (K for GEMM-Q,
+    # N for GEMM-O): size for up to 256 heads / 16 384 output columns
+    nbytes = lib.fo_gemm_workspace_bytes(batch, M, N if kind == "q" else 128 * 128, K if kind == "o" else 256 * head_dim,
+                                         head_dim)
+    key = (batch, M, N if kind == "q" else K, head_dim, bool(is_for_cache))
+    if into is not None and into.kind == kind and into.key == key and into.ws.device == dev and into.ws.numel() >= nbytes:
+        wl = into
+    else:
+        wl = GemmWorklist(kind, key, torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=dev))
+    if indptr.dtype != torch.int32:
+        indptr = indptr.to(torch.int32)
+    st = torch.cuda.current_stream(dev) if stream is None else stream
+    with torch.cuda.device(dev):
+        if kind == "q":
+            rc = lib.fo_gemm_q_worklist(batch, M, N, num_qo_heads, head_begin, head_dim, sparse_q_size, num_text_tokens,
+                                        0, _native.ptr(sparse_info), sparse_info.numel(), _native.ptr(indptr),
+                                        _native.ptr(wl.ws), wl.ws.numel(), st.cuda_stream)
+        else:
+            rc = lib.fo_gemm_o_worklist(batch, M, K, num_qo_heads, head_begin, head_dim, sparse_q_size, num_text_tokens,
+                                        1 if is_for_cache else 0, _native.ptr(sparse_info), sparse_info.numel(),
+                                        _native.ptr(indptr), _native.ptr(wl.ws), wl.ws.numel(), st.cuda_stream)
+        _native.check(rc, "prepare_gemm_list")
+        if wl.event is None:
+            wl.event = torch.cuda.Event()
+        wl.event.record(st)
+    return wl
+
+
+def prepare_gemm_q_list(batch: int, M: int, N: int, num_qo_heads: int, sparse_info, sparse_info_indptr,
+                        num_text_tokens: int = 512, sparse_q_size: int = 128, *, head_begin: int = 0,
+                        head_dim: Optional[int] = None, into: Optional[GemmWorklist] = None,
+                        stream: Optional[torch.cuda.Stream] = None) -> GemmWorklist:
+    """Builds the GEMM-Q work list for a [batch, M, *] x [N, *] product from the mask, on `stream` (default: the
+    current stream). `into` re-uses the workspace of an earlier list of the same shape."""
+    hd = N // num_qo_heads if head_dim is None else head_dim
+    return _prepare("q", batch, M, N, hd, num_qo_heads, hd, sparse_info, sparse_info_indptr, num_text_tokens,
+                    sparse_q_size, head_begin, False, into, stream)
+
+
+def prepare_gemm_o_list(batch: int, M: int, K: int, num_qo_heads: int, sparse_info, sparse_info_indptr,
+                        num_text_tokens: int, is_for_cache: bool = False, sparse_q_size: int = 128, *,
+                        head_begin: int = 0, head_dim: Optional[int] = None, into: Optional[GemmWorklist] = None,
+                        stream: Optional[torch.cuda.Stream] = None) -> GemmWorklist:
+    """Builds the GEMM-O row / head lists for a [batch, M, K] input from the mask (see prepare_gemm_q_list)."""
+    hd = K // num_qo_heads if head_dim is None else head_dim
+    return _prepare("o", batch, M, 128, K, num_qo_heads, hd, sparse_info, sparse_info_indptr, num_text_tokens,
+                    sparse_q_size, head_begin, is_for_cache, into, stream)

@@ -62,7 +62,11 @@ class SparseDiTAttentionBlock:
         into `out` when given, else into the block's own buffer)."""
         y = self.y if out is None else out
         H, D, hb = self.H, self.D, self.hb
-        # the work lists only depend on the masks: build them beside the projections
+        # The attention work lists only depend on the masks: they are built on a side stream beside the
+        # projections. The projection kernels fill every SM (shared memory), so that work runs in their tails;
+        # GEMM-Q goes first because its tiles are handed out dynamically and tolerate an SM that starts late.
+        # (Building the GEMM lists on a side stream as well -- prepare_gemm_q_list / prepare_gemm_o_list --
+        # measured no gain here for the same reason.)
         self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr)
         flashomni_gemm(x, self.w.wq, H, sparse_info, sparse_info_indptr, 0, None, out=self.q,
                        head_begin=hb, head_dim=D)

@@ -151,6 +151,18 @@ FO_API int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_h
                        const int32_t* sparse_info_indptr, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* ---- GEMM-Q / GEMM-O over a work list built earlier -------------------------------------------------
+ * No counterpart in the reference. Same computation as fo_gemm_q (sparse) / fo_gemm_o, but the work list is
+ * taken from `workspace` as fo_gemm_q_worklist / fo_gemm_o_worklist left it (same batch, m, n / k, head_dim),
+ * built on any stream that is ordered before this call -- e.g. a side stream, beside the dense projections,
+ * since the list depends on the mask only. Only the kernel status word and the tile cursor are reset here. */
+FO_API int32_t fo_gemm_q_prepared(const void* x, const void* w, void* y, const void* bias, int32_t dtype,
+                                  int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+FO_API int32_t fo_gemm_o_prepared(const void* x, const void* w, void* y, const void* init, int32_t init_is_full,
+                                  int32_t dtype, int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- block selection: pooled scores -> packed masks ------------------------------------------------
  * Replaces the mask generation of benchmark/test_attn_score.py:93-133 (torch sum / softmax / sort / cumsum /
  * searchsorted + Triton fill kernels on an unpacked [B, H, nq, nkv] layout) and the transpose + bit-pack its

@@ -123,3 +123,30 @@ def test_gemm_full_size_config(cuda_device):
     ref_active = xs.view(1, 4608, 3072) @ w.float().T
     y_act = fo.flashomni_gemm_reduction(x, w, H, si, ip, 0, None, is_for_cache=False)
     assert_close_bf16(y_act, ref_active, "gemm_o active heads 4608", allow_ulp=1.0)
+
+
+def test_prepared_worklists_give_the_same_result(cuda_device):
+    """flashomni_gemm / flashomni_gemm_reduction over lists built earlier on a side stream (extension)."""
+    from flashomni_b200.gemm import prepare_gemm_o_list, prepare_gemm_q_list
+    B, H, S, hid = 2, 6, 1024, 768
+    m = wl.flux_masks(B, H, S // 128, S // 128, 0.5, seed=61, text_blocks=1)
+    si, _, ip, _ = masks_to_device(m, cuda_device)
+    x = dev(wl.randn_bf16((B, S, hid), 62), cuda_device)
+    w = dev(wl.randn_bf16((hid, hid), 63, std=hid ** -0.5), cuda_device)
+    cache = dev(wl.randn_bf16((B, S, hid), 64), cuda_device)
+    prior = dev(wl.randn_bf16((B, S, hid), 65), cuda_device)
+    side = torch.cuda.Stream(cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    ql = prepare_gemm_q_list(B, S, hid, H, si, ip, 0, stream=side)
+    ol = prepare_gemm_o_list(B, S, hid, H, si, ip, 0, stream=side)
+    for _ in range(2):  # the second round re-uses the lists
+        a = fo.flashomni_gemm(x, w, H, si, ip, 0, out=prior.clone())
+        b = fo.flashomni_gemm(x, w, H, None, None, 0, out=prior.clone(), worklist=ql)
+        assert torch.equal(a, b)
+        c = fo.flashomni_gemm_reduction(x, w, H, si, ip, 0, cache)
+        d = fo.flashomni_gemm_reduction(x, w, H, None, None, 0, cache, worklist=ol)
+        assert torch.equal(c, d)
+    ql2 = prepare_gemm_q_list(B, S, hid, H, si, ip, 0, into=ql)
+    assert ql2 is ql
+    with pytest.raises(ValueError):
+        fo.flashomni_gemm_reduction(x, w, H, None, None, 0, cache, worklist=ql)
