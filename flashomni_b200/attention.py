@@ -254,6 +254,7 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             buf = torch.zeros(need, dtype=torch.uint8, device=self.device)
             self._int_workspace_buffer = buf
         words = buf.view(torch.uint8)[: need].view(torch.int32)
+        words[offs["counters"]: offs["counters"] + 8].zero_()  # counters and status / cursor words start from zero
         self._ws = {k: words[v:] for k, v in offs.items()}
         self._ws_words = words
         self._ws_offs = offs

@@ -60,6 +60,8 @@ static_assert(kSoftmaxWarps * 32 * kRegsSoftmax + (kThreads - kSoftmaxWarps * 32
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 constexpr int kRotStep = FO_ROT_STEP;       // q-block qb starts its kv list at entry (qb * kRotStep) mod length
+constexpr int kItemQ = 8;                   // entries of the item queue
+constexpr int kItemReaders = kSoftmaxWarps + 3;  // softmax warps, V producer, the two MMA issuers
 constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: keep the old max while exp2 stays <= 2^8
 
 struct Tail {
@@ -70,6 +72,8 @@ struct Tail {
   uint64_t m_ready[2];             // running maximum after a block of this parity has been published
   uint64_t stats_ready[2];         // indexed by item parity: both groups have published (m, l) of the item
   uint64_t o_full, o_free;
+  uint64_t iq_full[kItemQ], iq_empty[kItemQ];  // item queue: the K producer draws work-list positions for the CTA
+  int item_q[kItemQ];
   uint32_t tmem_base;
   int abort_flag;
   uint64_t pair_bar[2][4];   // [group][quadrant]: the two warps that share 32 rows
@@ -106,23 +110,92 @@ __device__ __forceinline__ int rot_of(int qb, int n) {
   return static_cast<int>(static_cast<unsigned>(qb * kRotStep) % static_cast<unsigned>(n));
 }
 
+// Work-list positions are handed out dynamically: position i < gridDim.x goes to CTA i, the following ones are
+// drawn from a device-wide cursor by the CTA's K producer, which passes them to the other roles through a small
+// shared-memory queue (entry k in slot k % kItemQ, -1 ends the sequence). A CTA that got short items draws more.
+struct ItemDraw {  // the drawing role (one thread)
+  Tail* tail;
+  int32_t* cursor;
+  volatile int* abort_flag;
+  int n_items, n_pub;
+  int p0, p1, p2;  // current, published next, drawn (still in flight) after next: the atomic never sits between two items
+  bool started, ended;
+  __device__ __forceinline__ int draw() {
+    const int p = atomicAdd(cursor, 1) + static_cast<int>(gridDim.x);
+    return p < n_items ? p : -1;
+  }
+  __device__ __forceinline__ bool publish(int v) {
+    if (ended) return true;
+    const int slot = n_pub % kItemQ;
+    if (!mbar_wait(&tail->iq_empty[slot], (static_cast<uint32_t>(n_pub / kItemQ) & 1u) ^ 1u, abort_flag)) return false;
+    tail->item_q[slot] = v;
+    mbar_arrive(&tail->iq_full[slot]);
+    ++n_pub;
+    if (v < 0) ended = true;
+    return true;
+  }
+  __device__ __forceinline__ void init(Tail* t, int32_t* cur, volatile int* ab, int n) {
+    tail = t; cursor = cur; abort_flag = ab; n_items = n; n_pub = 0; started = false; ended = false;
+    p0 = static_cast<int>(blockIdx.x) < n ? static_cast<int>(blockIdx.x) : -1;
+    p1 = p2 = -1;
+    bool ok = publish(p0);
+    if (ok && p0 >= 0) {
+      p1 = draw();
+      ok = publish(p1);
+      if (ok && p1 >= 0) p2 = draw();
+    }
+    if (!ok) p0 = -1;
+  }
+  __device__ __forceinline__ int next() {
+    if (!started) { started = true; return p0; }
+    p0 = p1;
+    if (p0 < 0) return -1;
+    p1 = p2;
+    if (!publish(p1)) return -1;
+    p2 = p1 >= 0 ? draw() : -1;
+    return p0;
+  }
+};
+
+template <bool kWholeWarp>
+struct ItemRead {  // the reading roles: one thread, or all lanes of a softmax warp
+  Tail* tail;
+  volatile int* abort_flag;
+  int k;
+  __device__ __forceinline__ void init(Tail* t, volatile int* ab) { tail = t; abort_flag = ab; k = 0; }
+  __device__ __forceinline__ int next() {
+    const int slot = k % kItemQ;
+    if (!mbar_wait(&tail->iq_full[slot], static_cast<uint32_t>(k / kItemQ) & 1u, abort_flag)) return -1;
+    const int v = tail->item_q[slot];
+    if (kWholeWarp) {
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(&tail->iq_empty[slot]);
+    } else {
+      mbar_arrive(&tail->iq_empty[slot]);
+    }
+    ++k;
+    return v;
+  }
+};
+
 // The same walk for the softmax groups, which do not need the kv-block indices: only which step of an
 // item (if any) is the ragged last block of its request. No global load sits between two blocks.
 struct GroupSeq {
-  int pos, stride, n_items;
+  ItemRead<true> src;
   int b, h, qb, n, j;
   int kv_len;
   int ragged_j, ragged_valid;  // visiting step of the request's partial last kv block (-1: none) and its columns
-  __device__ __forceinline__ void init(int start, int stride_, int n_items_) {
-    pos = start; stride = stride_; n_items = n_items_; n = 0; j = 0;
+  __device__ __forceinline__ void init(Tail* tail, volatile int* abort_flag) {
+    src.init(tail, abort_flag); n = 0; j = 0;
     b = h = qb = 0; kv_len = 0; ragged_j = -1; ragged_valid = 0;
   }
   template <class F>
   __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
     if (j + 1 < n) { ++j; return true; }
-    while (pos < n_items) {
+    while (true) {
+      const int pos = src.next();
+      if (pos < 0) break;
       const int it = a.order[pos];
-      pos += stride;
       const int4 rec = *reinterpret_cast<const int4*>(a.items + 4 * it);
       if (rec.w <= 0) { on_empty(rec.x, rec.y, rec.z); continue; }
       b = rec.x; h = rec.y; qb = rec.z; n = rec.w; j = 0;
@@ -149,15 +222,16 @@ struct GroupSeq {
 };
 
 // Walks the CTA's share of the schedule as a flat sequence of kv blocks.
+template <class Src>
 struct BlockSeq {
-  int pos, stride, n_items;
+  Src src;
   int item_no;   // index among this CTA's non-empty items (selects the Q buffer, o_full / o_free phases)
   int b, h, qb, n, j;
   int kvb, kvb_next;  // kv-block index of the current block; the next one is fetched a block early
   int rot;            // rotation of the visiting order inside the item's kv list
   const int32_t* kv;
-  __device__ __forceinline__ void init(int start, int stride_, int n_items_) {
-    pos = start; stride = stride_; n_items = n_items_; item_no = -1; n = 0; j = 0; kv = nullptr;
+  __device__ __forceinline__ void init() {
+    item_no = -1; n = 0; j = 0; kv = nullptr;
     b = h = qb = 0; kvb = kvb_next = 0; rot = 0;
   }
   // Advances to the next block; `on_empty(b, h, qb)` is called for every item without kv blocks that
@@ -170,9 +244,10 @@ struct BlockSeq {
       if (j + 1 < n) kvb_next = kv[at(j + 1)];
       return true;
     }
-    while (pos < n_items) {
+    while (true) {
+      const int pos = src.next();
+      if (pos < 0) break;
       const int it = a.order[pos];
-      pos += stride;
       const int4 rec = *reinterpret_cast<const int4*>(a.items + 4 * it);
       if (rec.w <= 0) { on_empty(rec.x, rec.y, rec.z); continue; }
       b = rec.x; h = rec.y; qb = rec.z; n = rec.w; j = 0;
@@ -226,6 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     }
     mbar_init(&tail->o_full, 1);
     mbar_init(&tail->o_free, kSoftmaxWarps);
+    for (int i = 0; i < kItemQ; ++i) { mbar_init(&tail->iq_full[i], 1); mbar_init(&tail->iq_empty[i], kItemReaders); }
     for (int i = 0; i < 8; ++i) mbar_init(&tail->pair_bar[i >> 2][i & 3], 2);
     tail->abort_flag = 0;
     fence_barrier_init();
@@ -247,7 +323,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   if (threadIdx.x == 0) { FO_TRACE(11, 0); FO_TRACE_TIME(11, 1); }
   int n_items = a.counters[0];
   if (n_items < 0) n_items = 0;
-  const int sched_start = static_cast<int>(blockIdx.x), sched_stride = static_cast<int>(gridDim.x);
   auto ignore_empty = [](int, int, int) {};
 
   // The softmax threads hold a whole 128-column row of S in registers: the two softmax warpgroups take
@@ -259,8 +334,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     // K and V have their own producer threads: a K tile is requested as soon as its slot has been
     // read by the QK two blocks earlier, whatever the state of the V FIFO (and the other way round).
     if (lane == 0) {
-      BlockSeq seq;
-      seq.init(sched_start, sched_stride, n_items);
+      BlockSeq<ItemDraw> seq;
+      seq.init();
+      seq.src.init(tail, a.status + 1, abort_flag, n_items);
       uint32_t nk = 0;                   // K tiles pushed so far
       uint32_t q_uses[kQBufs] = {0, 0};  // loads issued per Q buffer
       int kv_row0 = 0;                   // first kv row of the current item's request
@@ -293,8 +369,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   } else if (warp == kWarpProducerV) {
     // ------------------------------------------------------------------ TMA producer of V tiles
     if (lane == 0) {
-      BlockSeq seq;
-      seq.init(sched_start, sched_stride, n_items);
+      BlockSeq<ItemRead<false>> seq;
+      seq.init();
+      seq.src.init(tail, abort_flag);
       uint32_t nv = 0;
       int kv_row0 = 0;
       bool ok = true;
@@ -323,8 +400,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       const uint32_t hi = static_cast<uint32_t>(d0 >> 32);
       const uint32_t q_lo0 = static_cast<uint32_t>(d0);
       const uint32_t k_lo0 = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(smem_ring), 16, 1024));
-      BlockSeq seq;
-      seq.init(sched_start, sched_stride, n_items);
+      BlockSeq<ItemRead<false>> seq;
+      seq.init();
+      seq.src.init(tail, abort_flag);
       uint32_t g = 0, nk = 0;
       uint32_t q_uses[kQBufs] = {0, 0};
       bool ok = true;
@@ -370,8 +448,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       // V is MN-major: its two 64-column halves are 16 KB apart (leading byte offset)
       const uint64_t d0 = make_smem_desc_sw128(smem_u32(smem_ring + kRingK * kTileBytes), kHalfBytes, 1024);
       const uint32_t hi = static_cast<uint32_t>(d0 >> 32), v_lo0 = static_cast<uint32_t>(d0);
-      BlockSeq seq;
-      seq.init(sched_start, sched_stride, n_items);
+      BlockSeq<ItemRead<false>> seq;
+      seq.init();
+      seq.src.init(tail, abort_flag);
       uint32_t g = 0, nv = 0, items_started = 0;
       bool ok = true;
       while (ok && seq.next(a, ignore_empty)) {
@@ -456,7 +535,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     };
 
     GroupSeq seq;
-    seq.init(sched_start, sched_stride, n_items);
+    seq.init(tail, abort_flag);
     uint32_t g = 0;          // global block index (both parities)
     uint32_t my_blocks = 0;  // blocks this group has processed
     uint32_t items_seen = 0; // items whose last block has been passed
@@ -675,6 +754,14 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   if (warp == kWarpMma) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+  // the last CTA to get here puts the cursor and the arrival count back to zero for the next launch
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.status + 2, 1) == static_cast<int>(gridDim.x) - 1) {
+      atomicExch(a.status + 1, 0);
+      atomicExch(a.status + 2, 0);
+    }
   }
 }
 

@@ -90,7 +90,10 @@ FO_API int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes
  * with element strides (row, head); the innermost dimension is contiguous. lse (optional, may be
  * null): float32 [total_q, Hq], base 2. Hq here is the number of heads IN THE TENSORS; item head
  * indices are mask heads and map to tensor head (h - head_begin). q-blocks that are not listed are
- * not written. status: int32 device word, set to FO_DEV_WAIT_TIMEOUT if a bounded wait ran out.
+ * not written. status: FOUR int32 device words that the caller zeroes once: [0] is set to
+ * FO_DEV_WAIT_TIMEOUT if a bounded wait ran out; [1] (work-list cursor: items are handed to the CTAs
+ * dynamically) and [2] (count of finished CTAs) are used by the kernel and are zero again when it ends, so
+ * launches that share the words must not overlap; [3] is reserved.
  * This build implements D = 128 with 128-row q and kv blocks. */
 FO_API int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
                        int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,

@@ -188,3 +188,32 @@ def _block_graph_capture(cuda_device):
     torch.cuda.synchronize()
     replayed = y.clone()
     assert torch.equal(replayed, blk.forward(x, si, skv, ip, kp))
+
+
+def test_video_layer_size_sampled_rows(cuda_device):
+    """Config-5 size (77 312 tokens = 604 blocks, spatiotemporal-local mask at density ~0.25), four heads. The
+    whole attention runs on the GPU; sampled (head, q-block) rows are compared with an fp32 blockwise computation
+    on the GPU over the row's kept kv-blocks (a CPU oracle of this size would take minutes)."""
+    H, frames, bpf = 4, 20, 30
+    nblk = 4 + frames * bpf
+    S = nblk * 128
+    m = wl.video_masks(H, frames, bpf, seed=77)
+    q, k, v = (dev(wl.randn_bf16((S, H, 128), 80 + i), cuda_device) for i in range(3))
+    si, skv, ip, kp = masks_to_device(m, cuda_device)
+    indptr = torch.tensor([0, S], dtype=torch.int32, device=cuda_device)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
+    w.plan(indptr, indptr, H, H, 128, q_data_type=torch.bfloat16)
+    o = w.run(q, k, v, si, skv, ip, kp)
+    w.check_status()
+    lists = w.work_lists()
+    assert lists["n_items"] == H * nblk and lists["total_kept"] == wl.executed_attention_tiles(m)
+    rng = np.random.default_rng(5)
+    rows = [(0, 0), (1, 3), (2, 4), (3, nblk - 1), (0, 33), (1, 34)] + [(int(rng.integers(H)), int(rng.integers(nblk)))
+                                                                          for _ in range(10)]
+    for h, qb in rows:
+        kept = np.nonzero(m.kv_kept[0][qb, h])[0]
+        cols = torch.from_numpy(np.concatenate([np.arange(b * 128, b * 128 + 128) for b in kept])).to(cuda_device)
+        qf = q[qb * 128:(qb + 1) * 128, h].float()
+        s = (qf @ k[cols, h].float().T) / math.sqrt(128)
+        ref = torch.softmax(s, -1) @ v[cols, h].float()
+        assert_close_bf16(o[qb * 128:(qb + 1) * 128, h].cpu(), ref.cpu(), f"video layer head {h} q-block {qb}")
