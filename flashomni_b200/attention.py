@@ -158,8 +158,8 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         if q_data_type != kv_data_type:
             raise NotImplementedError("flashomni_b200: q and kv must share a dtype")
         native_dtype(q_data_type)
-        if num_qo_heads != num_kv_heads:
-            raise NotImplementedError("flashomni_b200: grouped-query attention is not implemented")
+        if num_kv_heads <= 0 or num_qo_heads % num_kv_heads != 0:
+            raise ValueError("num_qo_heads must be a multiple of num_kv_heads")
         if head_dim_qk != 128 or head_dim_vo != 128:
             raise NotImplementedError("flashomni_b200: only head_dim 128 is implemented")
         if sparse_block_size_for_q != 128 or sparse_block_size_for_kv != 128:

@@ -217,3 +217,21 @@ def test_video_layer_size_sampled_rows(cuda_device):
         s = (qf @ k[cols, h].float().T) / math.sqrt(128)
         ref = torch.softmax(s, -1) @ v[cols, h].float()
         assert_close_bf16(o[qb * 128:(qb + 1) * 128, h].cpu(), ref.cpu(), f"video layer head {h} q-block {qb}")
+
+
+def test_grouped_query_attention(cuda_device):
+    """kv head = qo head // group (reference: prefill.cuh:1283-1287); the masks are indexed by qo head."""
+    H, Hkv, S = 8, 2, 640
+    rng = np.random.default_rng(3)
+    m = wl.flux_masks(1, H, S // 128, S // 128, 0.6, seed=31, text_blocks=1)
+    q = wl.randn_bf16((S, H, 128), 32)
+    k = wl.randn_bf16((S, Hkv, 128), 33)
+    v = wl.randn_bf16((S, Hkv, 128), 34)
+    si, skv, ip, kp = masks_to_device(m, cuda_device)
+    indptr = torch.tensor([0, S], dtype=torch.int32, device=cuda_device)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
+    w.plan(indptr, indptr, H, Hkv, 128, q_data_type=torch.bfloat16)
+    o = w.run(dev(q, cuda_device), dev(k, cuda_device), dev(v, cuda_device), si, skv, ip, kp)
+    w.check_status()
+    ref = oa.sparse_attention(q, k, v, [0, S], [0, S], m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr)
+    assert_close_bf16(o.cpu(), ref, "gqa")
