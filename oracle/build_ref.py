@@ -3,7 +3,7 @@ around the reference's own CUDA kernels, compiled from the reference headers whe
 
     python oracle/build_ref.py [--force]
 
-Needs the reference checkout (default /root/reference, override with FLASHOMNI_REFERENCE_DIR) and the
+Needs the reference checkout (its directory is taken from FLASHOMNI_REFERENCE_DIR, with a built-in default) and the
 CUTLASS / CuTe headers the reference's GEMMs include (taken from the installed flashinfer wheel; the
 reference's own 3rdparty/cutlass submodule is empty). Nothing is copied from the reference; the only
 output is the shared library under oracle/_ref/, which is git-ignored. Does nothing (exit 0) when the
