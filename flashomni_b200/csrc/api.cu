@@ -414,7 +414,7 @@ int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t
   g.kb_per_head = 1;
   g.status = wsw + 4;
   g.cursor = is_full ? nullptr : wsw + 5;  // equal tiles keep a fixed share
-  e = launch_gemm(g, sm_count(), st);
+  e = gemm_tall_applies(g) ? launch_gemm_tall(g, sm_count(), st) : launch_gemm(g, sm_count(), st);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_q", e);
 }
 }  // namespace

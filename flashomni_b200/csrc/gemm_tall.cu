@@ -1,0 +1,280 @@
+// Dense projection GEMM with 256x256 output tiles: Y[rows, n] = X[rows, k] W[n, k]^T (+ bias).
+//
+// Why a second GEMM kernel: the path from L2 to the SMs is what limits the 128x256 tiles of gemm.cu (48 KB
+// of operands per 512 tensor clocks = 94 B/clk per SM against about 84 B/clk that all SMs can pull from L2 at
+// once). A 256x256 tile needs 64 KB per 1024 tensor clocks (62.5 B/clk): two 128-row halves of X share one
+// 256-column block of W in shared memory. Only the dense mode uses it (a sparse GEMM-Q would need two row
+// blocks with the same active heads); shapes that do not divide fall back to gemm.cu.
+//
+// One persistent CTA per SM, 384 threads. Warp 8: TMA producer, 3 stages of 64 KB (X top, X bottom, W, W).
+// Warps 9 and 10: MMA issuers, per K block of 64 four 128x256x16 MMAs into the top accumulator (TMEM columns
+// 0-255) by the one and four into the bottom one (256-511) by the other. Both accumulators belong to the same tile, so the epilogue of a
+// tile only overlaps the next tile's operand loads, not its MMAs; to keep that gap short the epilogue has
+// one warpgroup per half (warps 0-3 top, 4-7 bottom: TMEM lane quadrant = warp % 4), reads the whole
+// accumulator into registers first and stores it through a small per-warp staging area while the next tile's
+// MMAs already run. Every mbarrier wait is bounded.
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace fo {
+namespace {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64;
+constexpr int kStages = 3;
+constexpr int kHalfBytes = kBM * kBK * 2;          // 16 KB: a 128-row K block of X or W
+constexpr int kStageBytes = 4 * kHalfBytes;        // X top | X bottom | W rows 0-127 | W rows 128-255
+constexpr int kEpiWarps = 8;
+constexpr int kWarpProducer = kEpiWarps, kWarpMma = kEpiWarps + 1;  // warps 9 and 10 issue the MMAs of one half each
+constexpr int kThreads = (kEpiWarps + 4) * 32;     // 384: three warpgroups (warp 11 only takes part in the set-up)
+constexpr int kRegsEpilogue = 208, kRegsOther = 40;  // setmaxnreg split: the epilogue holds a 256-column row in registers
+static_assert(kEpiWarps * 32 * kRegsEpilogue + 4 * 32 * kRegsOther <= kThreads * ((65536 / kThreads) / 8 * 8),
+              "register split exceeds the CTA's register pool");
+constexpr int kTmemCols = 512;
+
+struct Tail {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[2];    // [half]
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int kStageWarpBytes = 16 * 128;          // store staging per epilogue warp
+constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kStageWarpBytes + 1024 + static_cast<int>(sizeof(Tail));
+
+#ifdef FO_GEMM_TRACE
+__device__ long long g_ttrace[8][64];
+#define FO_TTRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 64) g_ttrace[ev][idx] = clock64(); } while (0)
+#else
+#define FO_TTRACE(ev, idx)
+#endif
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_constant__ GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint8_t* smem_stage = smem + kStages * kStageBytes;
+  Tail* tail = reinterpret_cast<Tail*>(smem_stage + kEpiWarps * kStageWarpBytes);
+  volatile int* abort_flag = &tail->abort_flag;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 2);  // both issuers have read the stage
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tail->acc_full[i], 1);
+      mbar_init(&tail->acc_empty[i], 4);
+    }
+    tail->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == kWarpProducer && lane == 0) {
+    tma_prefetch_desc(&a.tmap_a);
+    tma_prefetch_desc(&a.tmap_b);
+  }
+  if (warp == kWarpMma) {
+    tmem_alloc(&tail->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  const int col_tiles = a.n / kBN;
+  const int n_tiles = (a.batch * a.m / (2 * kBM)) * col_tiles;
+  const int nkb = a.k / kBK;
+  // tile t: row pair t / col_tiles, column block t % col_tiles (CTAs that run together share X rows and W columns)
+
+  if (warp >= kEpiWarps) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+  if (warp == kWarpProducer) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const int a_row = (t / col_tiles) * 2 * kBM;
+        const int w_row = (t % col_tiles) * kBN;
+        for (int j = 0; j < nkb; ++j) {
+          if (!mbar_wait(&tail->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* s = smem + stage * kStageBytes;
+          mbar_expect_tx(&tail->full[stage], kStageBytes);
+          tma_load_2d(s, &a.tmap_a, &tail->full[stage], j * kBK, a_row);
+          tma_load_2d(s + kHalfBytes, &a.tmap_a, &tail->full[stage], j * kBK, a_row + kBM);
+          tma_load_2d(s + 2 * kHalfBytes, &a.tmap_b, &tail->full[stage], j * kBK, w_row);
+          tma_load_2d(s + 3 * kHalfBytes, &a.tmap_b, &tail->full[stage], j * kBK, w_row + kBM);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == kWarpMma || warp == kWarpMma + 1) {
+    // Two issuing threads, one per half of the tile: a thread that issues a batch of MMAs is held until the
+    // batch has drained, so a single issuer would leave the tensor pipe idle during its own bookkeeping
+    // (barrier wait, descriptors, commit) between two K blocks.
+    if (lane == 0) {
+      const int half = warp - kWarpMma;
+      constexpr uint32_t idesc = make_idesc_f16(kBM, kBN, kBf16, 0, 0);
+      const uint64_t desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
+      const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32), desc_lo0 = static_cast<uint32_t>(desc0);
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(half * kBN);
+      int stage = 0;
+      uint32_t phase = 0, tile_phase = 0;
+      bool ok = true;
+      int tno = -1;
+      (void)tno;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        ++tno;
+        for (int j = 0; j < nkb; ++j) {
+          if (!mbar_wait(&tail->full[stage], phase, abort_flag)) { ok = false; break; }
+          if (j == 0) {  // the previous tile's half must have been read out of TMEM
+            if (!mbar_wait(&tail->acc_empty[half], tile_phase ^ 1u, abort_flag)) { ok = false; break; }
+          }
+          tc_fence_after_sync();
+          const uint32_t lo = desc_lo0 + static_cast<uint32_t>((stage * kStageBytes) >> 4);
+          const uint32_t x = lo + static_cast<uint32_t>((half * kHalfBytes) >> 4), b = lo + (2 * kHalfBytes >> 4);
+          const uint32_t la[4] = {x, x + 2u, x + 4u, x + 6u};
+          const uint32_t lb[4] = {b, b + 2u, b + 4u, b + 6u};
+          if (j == 0) FO_TTRACE(half * 4 + 0, tno);
+          umma_ss_x4(d_tmem, desc_hi, desc_hi, idesc, j != 0 ? 1u : 0u, la, lb);
+          if (j == 7) FO_TTRACE(half * 4 + 1, tno);
+          if (j == 39) FO_TTRACE(half * 4 + 2, tno);
+          if (j == nkb - 1) FO_TTRACE(half * 4 + 3, tno);
+          umma_commit(&tail->empty[stage]);
+          if (j == nkb - 1) umma_commit(&tail->acc_full[half]);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        tile_phase ^= 1u;
+      }
+    }
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
+    // ------------------------------------------------------------- epilogue: warpgroup `half` drains its accumulator
+    const int half = warp >> 2;
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(half * kBN);
+    const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(a.init);
+    uint16_t* y16 = reinterpret_cast<uint16_t*>(a.y);
+    uint32_t tile_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      const int w_row = (t % col_tiles) * kBN;
+      if (!mbar_wait(&tail->acc_full[half], tile_phase, abort_flag)) { ok = false; break; }
+      tile_phase ^= 1u;
+      tc_fence_after_sync();
+      // The accumulator is read out and rounded to 16 bits completely (128 registers per thread) before anything
+      // is stored: the next tile's MMAs may start as soon as the last TMEM load has returned, and the row-wise
+      // stores (each thread writes its own 512-byte row segment: slow) run beside them.
+      uint32_t pk[kBN / 64][32];
+#pragma unroll
+      for (int q = 0; q < kBN / 64; ++q) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_x32(taddr + static_cast<uint32_t>(q * 64), v0);
+        tmem_ld_x32(taddr + static_cast<uint32_t>(q * 64 + 32), v1);
+        tmem_wait_ld();
+        if (q == kBN / 64 - 1) {  // accumulator fully read: the next tile may overwrite it
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tail->acc_empty[half]);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float lo = __uint_as_float(i < 16 ? v0[2 * i] : v1[2 * i - 32]);
+          float hi = __uint_as_float(i < 16 ? v0[2 * i + 1] : v1[2 * i - 31]);
+          if (a.init_mode == kInitBias1D) {
+            const uint32_t bb = *reinterpret_cast<const uint32_t*>(bias16 + w_row + q * 64 + 2 * i);
+            if (kBf16) {
+              lo += __uint_as_float(bb << 16);
+              hi += __uint_as_float(bb & 0xFFFF0000u);
+            } else {
+              const __half2 h2 = *reinterpret_cast<const __half2*>(&bb);
+              lo += __low2float(h2);
+              hi += __high2float(h2);
+            }
+          }
+          pk[q][i] = kBf16 ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+        }
+      }
+      // Stores: through a 2 KB staging area per warp (16 rows x 128 bytes, 16-byte chunks XOR-swizzled by the
+      // row), so that every store instruction writes four full 128-byte lines instead of 32 scattered 16-byte
+      // pieces (scattered stores of one tile took as long as a quarter of its MMAs and held up the operand
+      // loads of the next tile).
+      uint8_t* stg = smem_stage + warp * kStageWarpBytes;
+      uint16_t* ytile = y16 + (static_cast<int64_t>(t / col_tiles) * 2 * kBM + half * kBM + (warp & 3) * 32) * a.n + w_row;
+#pragma unroll
+      for (int s = 0; s < kBN / 64; ++s) {
+#pragma unroll
+        for (int ph = 0; ph < 2; ++ph) {
+          if ((lane >> 4) == ph) {
+            const int r = lane & 15;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4)) =
+                  make_uint4(pk[s][4 * c], pk[s][4 * c + 1], pk[s][4 * c + 2], pk[s][4 * c + 3]);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int r = it * 4 + (lane >> 3), c = lane & 7;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4));
+            *reinterpret_cast<uint4*>(ytile + static_cast<int64_t>(ph * 16 + r) * a.n + s * 64 + c * 8) = v;
+          }
+          __syncwarp();
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------- common exit
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // give copies that may still be in flight time to land before the CTA's smem is released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    if (threadIdx.x == 0) atomicExch(a.status, kDevWaitTimeout);
+    __syncthreads();
+  }
+  if (warp == kWarpMma) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+#ifdef FO_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) int fo_gemm_tall_trace_dump(long long* host_dst) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_dst, g_ttrace, sizeof(g_ttrace)));
+}
+#endif
+
+bool gemm_tall_applies(const GemmArgs& a) {
+  return a.mode == kGemmQ && a.tiles == nullptr && (a.init_mode == kInitNone || a.init_mode == kInitBias1D) &&
+         (static_cast<int64_t>(a.batch) * a.m) % (2 * kBM) == 0 && a.n % kBN == 0 && a.k % kBK == 0 && a.k > 0;
+}
+
+cudaError_t launch_gemm_tall(const GemmArgs& a, int max_ctas, cudaStream_t stream) {
+  const int64_t tiles = (static_cast<int64_t>(a.batch) * a.m / (2 * kBM)) * (a.n / kBN);
+  if (tiles <= 0) return cudaSuccess;
+  const int grid = tiles < max_ctas ? static_cast<int>(tiles) : max_ctas;
+  cudaError_t e;
+  if (a.is_bf16) {
+    e = cudaFuncSetAttribute(gemm_tall_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    gemm_tall_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(a);
+  } else {
+    e = cudaFuncSetAttribute(gemm_tall_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    gemm_tall_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace fo

@@ -83,6 +83,9 @@ struct GemmArgs {
   int32_t* cursor;                 // device-wide tile cursor, zero when the kernel starts
 };
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream);
+// dense projections whose shape divides into 256x256 tiles take the tall-tile kernel (gemm_tall.cu)
+bool gemm_tall_applies(const GemmArgs& a);
+cudaError_t launch_gemm_tall(const GemmArgs& a, int max_ctas, cudaStream_t stream);
 
 // ------------------------------------------------------------------ block selection
 struct SelectArgs {
