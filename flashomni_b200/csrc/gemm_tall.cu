@@ -87,7 +87,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
   const uint32_t tmem_base = tail->tmem_base;
 
   const int col_tiles = a.n / kBN;
-  const int n_tiles = (a.batch * a.m / (2 * kBM)) * col_tiles;
+  const int total_rows = a.batch * a.m;  // a multiple of 128; an odd last row block leaves the bottom half of its
+                                         // tile empty (the loads past the end return zeros, nothing is stored)
+  const int n_tiles = ((total_rows + 2 * kBM - 1) / (2 * kBM)) * col_tiles;
   const int nkb = a.k / kBK;
   // tile t: row pair t / col_tiles, column block t % col_tiles (CTAs that run together share X rows and W columns)
 
@@ -200,6 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
           pk[q][i] = kBf16 ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
         }
       }
+      if ((t / col_tiles) * 2 * kBM + half * kBM >= total_rows) continue;  // empty half of the last row pair
       // Stores: through a 2 KB staging area per warp (16 rows x 128 bytes, 16-byte chunks XOR-swizzled by the
       // row), so that every store instruction writes four full 128-byte lines instead of 32 scattered 16-byte
       // pieces (scattered stores of one tile took as long as a quarter of its MMAs and held up the operand
@@ -257,11 +260,12 @@ extern "C" __attribute__((visibility("default"))) int fo_gemm_tall_trace_dump(lo
 
 bool gemm_tall_applies(const GemmArgs& a) {
   return a.mode == kGemmQ && a.tiles == nullptr && (a.init_mode == kInitNone || a.init_mode == kInitBias1D) &&
-         (static_cast<int64_t>(a.batch) * a.m) % (2 * kBM) == 0 && a.n % kBN == 0 && a.k % kBK == 0 && a.k > 0;
+         (static_cast<int64_t>(a.batch) * a.m) % kBM == 0 && static_cast<int64_t>(a.batch) * a.m >= 2 * kBM &&
+         a.n % kBN == 0 && a.k % kBK == 0 && a.k > 0;
 }
 
 cudaError_t launch_gemm_tall(const GemmArgs& a, int max_ctas, cudaStream_t stream) {
-  const int64_t tiles = (static_cast<int64_t>(a.batch) * a.m / (2 * kBM)) * (a.n / kBN);
+  const int64_t tiles = ((static_cast<int64_t>(a.batch) * a.m + 2 * kBM - 1) / (2 * kBM)) * (a.n / kBN);
   if (tiles <= 0) return cudaSuccess;
   const int grid = tiles < max_ctas ? static_cast<int>(tiles) : max_ctas;
   cudaError_t e;
