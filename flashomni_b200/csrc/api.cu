@@ -414,7 +414,17 @@ int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t
   g.kb_per_head = 1;
   g.status = wsw + 4;
   g.cursor = is_full ? nullptr : wsw + 5;  // equal tiles keep a fixed share
-  e = gemm_tall_applies(g) ? launch_gemm_tall(g, sm_count(), st) : launch_gemm(g, sm_count(), st);
+  if (gemm_tall_applies(g)) {
+    // the tall-tile kernel stores 16-row x 64-column boxes (one per-warp staging area at a time)
+    const uint32_t ybox[2] = {64, 16};
+    const uint64_t yd[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(batch) * m};
+    const uint64_t yst[2] = {0, static_cast<uint64_t>(n) * 2};
+    if (encode_tmap_16bit(&g.tmap_y, y, 2, yd, yst, ybox) != 0)
+      return fail(FO_ERR_CUDA, "fo_gemm_q: cuTensorMapEncodeTiled failed (output boxes)");
+    e = launch_gemm_tall(g, sm_count(), st);
+  } else {
+    e = launch_gemm(g, sm_count(), st);
+  }
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_q", e);
 }
 }  // namespace

@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
   if (warp == kWarpProducer && lane == 0) {
     tma_prefetch_desc(&a.tmap_a);
     tma_prefetch_desc(&a.tmap_b);
+    tma_prefetch_desc(&a.tmap_y);
   }
   if (warp == kWarpMma) {
     tmem_alloc(&tail->tmem_base, kTmemCols);
@@ -161,7 +162,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
     const int half = warp >> 2;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(half * kBN);
     const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(a.init);
-    uint16_t* y16 = reinterpret_cast<uint16_t*>(a.y);
     uint32_t tile_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
@@ -203,16 +203,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
         }
       }
       if ((t / col_tiles) * 2 * kBM + half * kBM >= total_rows) continue;  // empty half of the last row pair
-      // Stores: through a 2 KB staging area per warp (16 rows x 128 bytes, 16-byte chunks XOR-swizzled by the
-      // row), so that every store instruction writes four full 128-byte lines instead of 32 scattered 16-byte
-      // pieces (scattered stores of one tile took as long as a quarter of its MMAs and held up the operand
-      // loads of the next tile).
+      // Stores: through a 2 KB staging area per warp (16 rows x 128 bytes in the 128-byte swizzle pattern) handed
+      // to a TMA store of one 16 x 64 box, instead of 32 scattered 16-byte pieces per store instruction
+      // (scattered stores of one tile took as long as a quarter of its MMAs and held up the operand loads of
+      // the next tile).
       uint8_t* stg = smem_stage + warp * kStageWarpBytes;
-      uint16_t* ytile = y16 + (static_cast<int64_t>(t / col_tiles) * 2 * kBM + half * kBM + (warp & 3) * 32) * a.n + w_row;
+      const int row0 = (t / col_tiles) * 2 * kBM + half * kBM + (warp & 3) * 32;  // first row of this warp
 #pragma unroll
       for (int s = 0; s < kBN / 64; ++s) {
 #pragma unroll
         for (int ph = 0; ph < 2; ++ph) {
+          // the staging area is free once the store issued from it has read it
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
           if ((lane >> 4) == ph) {
             const int r = lane & 15;
 #pragma unroll
@@ -220,19 +223,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
               *reinterpret_cast<uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4)) =
                   make_uint4(pk[s][4 * c], pk[s][4 * c + 1], pk[s][4 * c + 2], pk[s][4 * c + 3]);
           }
+          fence_proxy_async_smem();
           __syncwarp();
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int r = it * 4 + (lane >> 3), c = lane & 7;
-            const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4));
-            *reinterpret_cast<uint4*>(ytile + static_cast<int64_t>(ph * 16 + r) * a.n + s * 64 + c * 8) = v;
+          if (lane == 0) {
+            tma_store_2d(&a.tmap_y, stg, w_row + s * 64, row0 + ph * 16);
+            tma_store_commit();
           }
-          __syncwarp();
         }
       }
     }
   }
 
+  if (warp < kEpiWarps && lane == 0) tma_store_wait_all<0>();
   // ------------------------------------------------------------- common exit
   __syncwarp();
   tc_fence_before_sync();
