@@ -59,7 +59,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 }  // namespace
 
 int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box) {
+                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
   cuuint64_t gdim[5];
@@ -73,7 +73,8 @@ int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64
     if (i > 0) gstr[i - 1] = strides_bytes[i];
   }
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
-                        gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
@@ -222,6 +223,9 @@ int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
     int r = encode_tmap_16bit(&a.tmap_q, q, 3, qd, qs, box);
     if (r == 0) r = encode_tmap_16bit(&a.tmap_k, k, 3, kd, ks, box);
     if (r == 0) r = encode_tmap_16bit(&a.tmap_v, v, 3, kd, vs, box);
+    const uint32_t obox[3] = {32, 1, 16};
+    const uint64_t os[3] = {0, static_cast<uint64_t>(o_stride_h) * 2, static_cast<uint64_t>(o_stride_n) * 2};
+    if (r == 0) r = encode_tmap_16bit(&a.tmap_o, o, 3, qd, os, obox, false);
     if (r != 0) {
       char buf[96];
       snprintf(buf, sizeof(buf), "fo_sparse_attn_fwd: cuTensorMapEncodeTiled failed (%d)", r);

@@ -102,7 +102,9 @@ constexpr int kTraceBytes = 0;
 #endif
 
 
-constexpr int kSmemBytes = (kQBufs + kRing) * kTileBytes + 1024 + static_cast<int>(sizeof(Tail)) + kTraceBytes;
+constexpr int kOutStageBytes = 16 * 64;  // per softmax warp: 16 rows x 32 output columns
+constexpr int kSmemBytes = (kQBufs + kRing) * kTileBytes + kSoftmaxWarps * kOutStageBytes + 1024 +
+                           static_cast<int>(sizeof(Tail)) + kTraceBytes;
 
 // The kept kv blocks of an item are visited in rotated order (the online softmax does not care):
 // q-block qb starts at entry (qb * kRotStep) mod length of its list.
@@ -276,7 +278,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   uint8_t* smem_q = smem;                           // kQBufs tiles
   uint8_t* smem_ring = smem + kQBufs * kTileBytes;  // kRing tiles
-  Tail* tail = reinterpret_cast<Tail*>(smem + (kQBufs + kRing) * kTileBytes);
+  uint8_t* smem_ostage = smem + (kQBufs + kRing) * kTileBytes;  // output staging of the softmax warps
+  Tail* tail = reinterpret_cast<Tail*>(smem_ostage + kSoftmaxWarps * kOutStageBytes);
   volatile int* abort_flag = &tail->abort_flag;
 #ifdef FO_ATTN_TRACE
   uint32_t* trace_buf = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(tail) + ((sizeof(Tail) + 15) & ~size_t(15)));
@@ -310,6 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     tma_prefetch_desc(&a.tmap_q);
     tma_prefetch_desc(&a.tmap_k);
     tma_prefetch_desc(&a.tmap_v);
+    tma_prefetch_desc(&a.tmap_o);
   }
   if (warp == kWarpMma) {
     tmem_alloc(&tail->tmem_base, kTmemCols);
@@ -568,21 +572,47 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->o_free);  // O may be overwritten by the next item
       const RowCtx pend_ctx = row_ctx(pend_b, pend_h, pend_qb);
-      if (pend_ctx.row_ok) {
+      uint4 outv[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float x0 = __uint_as_float(v[8 * q + 2 * t]) * inv_l;
+          const float x1 = __uint_as_float(v[8 * q + 2 * t + 1]) * inv_l;
+          w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+        }
+        outv[q] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      const int q0 = a.qo_indptr[pend_b];
+      const bool whole = (pend_qb + 1) * kBQ <= a.qo_indptr[pend_b + 1] - q0;  // no row of the q-block is past the request
+      if (whole) {
+        // Through a 1 KB staging area per warp (16 rows x 64 bytes, plain row-major) and a TMA store of one
+        // 16-row x 32-column box: a store instruction of a warp would otherwise write 32 scattered 16-byte pieces.
+        uint8_t* stg = smem_ostage + warp * kOutStageBytes;
+        const int grow0 = q0 + pend_qb * kBQ + quad * 32;
+#pragma unroll
+        for (int ph = 0; ph < 2; ++ph) {
+          if (lane == 0) tma_store_wait_read<0>();  // the staging area is free once its last store has read it
+          __syncwarp();
+          if ((lane >> 4) == ph) {
+            const int r = lane & 15;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(stg + r * 64 + c * 16) = outv[c];
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&a.tmap_o, stg, static_cast<int>(ocol), pend_h - a.head_begin, grow0 + ph * 16);
+            tma_store_commit();
+          }
+        }
+      } else if (pend_ctx.row_ok) {
         uint4* dst = reinterpret_cast<uint4*>(pend_ctx.orow);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t w[4];
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const float x0 = __uint_as_float(v[8 * q + 2 * t]) * inv_l;
-            const float x1 = __uint_as_float(v[8 * q + 2 * t + 1]) * inv_l;
-            w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
-          }
-          dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-        if (pend_ctx.lse != nullptr) *pend_ctx.lse = (lsum > 0.f) ? (log2f(lsum) + m_fin) : -5e4f;
+        for (int q = 0; q < 4; ++q) dst[q] = outv[q];
       }
+      if (pend_ctx.row_ok && pend_ctx.lse != nullptr) *pend_ctx.lse = (lsum > 0.f) ? (log2f(lsum) + m_fin) : -5e4f;
       pend = false;
       return true;
     };
@@ -733,6 +763,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       ++g;
     }
     if (ok && pend) epilogue();
+    if (lane == 0) tma_store_wait_all<0>();
   }
 
   // ------------------------------------------------------------------ common exit

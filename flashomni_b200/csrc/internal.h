@@ -123,6 +123,7 @@ struct AttnArgs {
   CUtensorMap tmap_q;              // [D, H, Tq]   box 64 x 1 x 128
   CUtensorMap tmap_k;              // [D, Hkv, Tkv]
   CUtensorMap tmap_v;
+  CUtensorMap tmap_o;              // [D, Hq, Tq]   box 32 x 1 x 16, no swizzle (stores of whole q-blocks)
   void* o;                         // [Tq, H, D] (strides below, in elements)
   float* lse;                      // [Tq, H] or null
   int64_t o_stride_n, o_stride_h;
@@ -143,9 +144,9 @@ struct AttnArgs {
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream);
 
 // ------------------------------------------------------------------ host helpers
-// Encodes a tiled tensor map (bf16/f16 elements, 128-byte swizzle). dims/strides innermost first;
+// Encodes a tiled tensor map (bf16/f16 elements, 128-byte swizzle or none). dims/strides innermost first;
 // strides in bytes for dims 1..rank-1. Returns 0 on success.
 int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box);
+                      const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128 = true);
 
 }  // namespace fo
