@@ -400,8 +400,17 @@ def run_video(args):
         marks = []
         blk.forward(x, *m_dev, marks=marks)
         torch.cuda.synchronize()
-        names = ("proj_and_exchange", "attention", "exchange_back", "gemm_o")
+        if len(marks) == 8:  # peer-memory exchange: the two barriers are marked separately
+            names = ("projections", "barrier", "pull_qkv", "attention", "barrier_back", "pull_o", "gemm_o")
+        else:
+            names = ("proj_and_exchange", "attention", "exchange_back", "gemm_o")
         phases = {n: round(marks[i].elapsed_time(marks[i + 1]), 4) for i, n in enumerate(names)}
+    if dist is not None:  # slowest rank per phase
+        pt = torch.tensor([phases[n] for n in phases], device=device, dtype=torch.float64)
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        phases_max = {n: round(float(v), 4) for n, v in zip(phases, pt.tolist())}
+    else:
+        phases_max = phases
     tiles = wl.executed_attention_tiles(masks, blk.hb, blk.hc)
     rows_blocks = blk.s_loc // 128
     fl_rank = tiles * FL_ATTN_TILE + 4 * (2 * blk.s_loc * hid * hid)
@@ -423,7 +432,7 @@ def run_video(args):
                                    "spatiotemporal-local block mask (+-1 frame + 10% random + text), Ulysses all-to-all",
                        "parallelism": f"ulysses/{world}", "exchange": blk.exchange, "seed": SEED, "executed_flops_per_step": fl_total,
                        "attention_tiles_rank0": tiles, "l2": "working set of several GB, far above the 126 MB L2",
-                       "phase_ms_rank0": phases},
+                       "phase_ms_rank0": phases, "phase_ms_slowest_rank": phases_max},
             "gpu_launches": int(args.steps * 10), "clocks": clocks}), flush=True)
     if dist is not None:
         dist.barrier()

@@ -136,7 +136,8 @@ class UlyssesSparseDiTAttentionBlock:
     def forward(self, x_local, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, marks=None):
         """x_local [1, local tokens, hidden] -> this rank's rows of the block output [1, local tokens, hidden].
         `marks` (a list) receives CUDA events at the phase boundaries: start, projections + exchange done,
-        attention done, exchange back done, end."""
+        attention done, exchange back done, end (with the peer-memory exchange also before and after each of the
+        two barriers)."""
         H, D, S = self.H, self.D, self.S
 
         def mark():
@@ -152,7 +153,9 @@ class UlyssesSparseDiTAttentionBlock:
             flashomni_gemm(x_local, self.w.wq, H, sparse_info, sparse_info_indptr, self.t0, None, out=self.q, head_dim=D)
             flashomni_gemm(x_local, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
             flashomni_gemm(x_local, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
+            mark()
             self.px.barrier(0)  # every rank's projections are complete (and its previous pull of attn is over)
+            mark()
             isz = self.q.element_size()
             for ptrs, dst in zip((self.q_ptrs, self.k_ptrs, self.v_ptrs), self.heads_in):
                 self.px.pull_heads(ptrs, S, H, D, isz, dst)
@@ -188,6 +191,7 @@ class UlyssesSparseDiTAttentionBlock:
         mark()
         if self.exchange == "p2p":
             self.px.barrier(1)  # every rank's attention is complete (and its pulls of q / k / v are over)
+            mark()
             self.px.pull_tokens(self.attn_ptrs, S, H, D, self.attn.element_size(), self.o_loc)
             o_loc = self.o_loc
         else:
