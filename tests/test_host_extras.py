@@ -1,0 +1,43 @@
+"""Host-side checks of the extensions (no GPU): argument validation, CPU refusal, list bookkeeping."""
+
+import numpy as np
+import pytest
+import torch
+
+import flashomni_b200 as fo
+from flashomni_b200 import parallel as par
+from flashomni_b200.gemm import GemmWorklist
+
+
+def test_select_blocks_rejects_cpu_and_bad_shapes():
+    s = torch.zeros(1, 2, 4, 4)
+    with pytest.raises(RuntimeError):
+        fo.select_blocks(s, 1, 0.2, 0.2)                      # no CPU path
+    with pytest.raises(ValueError):
+        fo.select_blocks(torch.zeros(1, 2, 4, 5), 1, 0.2, 0.2)  # nq != nkv
+    with pytest.raises(ValueError):
+        fo.select_blocks(s.double(), 1, 0.2, 0.2)
+
+
+def test_exchange_row_counts_of_the_video_layer():
+    """The pulls of the sequence-parallel exchange are built from these per-rank token ranges."""
+    sizes = [par.token_range(77312, r, 8)[1] - par.token_range(77312, r, 8)[0] for r in range(8)]
+    assert sizes == [9728] * 4 + [9600] * 4 and sum(sizes) == 77312
+
+
+def test_worklist_key_check():
+    wl = GemmWorklist("q", (2, 256, 512, 128, False), torch.zeros(256, dtype=torch.uint8))
+    wl.check("q", 2, 256, 512, 128, torch.device("cpu"))
+    with pytest.raises(ValueError):
+        wl.check("o", 2, 256, 512, 128, torch.device("cpu"))
+    with pytest.raises(ValueError):
+        wl.check("q", 2, 256, 1024, 128, torch.device("cpu"))
+
+
+def test_selection_statement_is_deterministic_across_layouts():
+    from oracle import select as osel
+    rng = np.random.default_rng(0)
+    s = rng.standard_normal((1, 2, 9, 9)).astype(np.float32)
+    a = osel.select_blocks(s, 2, 0.3, 0.3)
+    b = osel.select_blocks(np.ascontiguousarray(s.transpose(0, 1, 3, 2)).transpose(0, 1, 3, 2), 2, 0.3, 0.3)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
