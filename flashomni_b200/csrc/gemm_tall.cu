@@ -4,15 +4,16 @@
 // of operands per 512 tensor clocks = 94 B/clk per SM against about 84 B/clk that all SMs can pull from L2 at
 // once). A 256x256 tile needs 64 KB per 1024 tensor clocks (62.5 B/clk): two 128-row halves of X share one
 // 256-column block of W in shared memory. Only the dense mode uses it (a sparse GEMM-Q would need two row
-// blocks with the same active heads); shapes that do not divide fall back to gemm.cu.
+// blocks with the same active heads); shapes whose N is not a multiple of 256 fall back to gemm.cu.
 //
 // One persistent CTA per SM, 384 threads. Warp 8: TMA producer, 3 stages of 64 KB (X top, X bottom, W, W).
 // Warps 9 and 10: MMA issuers, per K block of 64 four 128x256x16 MMAs into the top accumulator (TMEM columns
-// 0-255) by the one and four into the bottom one (256-511) by the other. Both accumulators belong to the same tile, so the epilogue of a
-// tile only overlaps the next tile's operand loads, not its MMAs; to keep that gap short the epilogue has
+// 0-255) by the one and four into the bottom one (256-511) by the other. Both accumulators belong to the same
+// tile, so the read-out of a tile cannot overlap the next tile's MMAs; to keep that gap short the epilogue has
 // one warpgroup per half (warps 0-3 top, 4-7 bottom: TMEM lane quadrant = warp % 4), reads the whole
-// accumulator into registers first and stores it through a small per-warp staging area while the next tile's
-// MMAs already run. Every mbarrier wait is bounded.
+// accumulator into registers first and stores it through a small per-warp staging area (TMA stores of 16 x 64
+// boxes) while the next tile's MMAs already run. A shape whose row count is an odd multiple of 128 leaves the
+// bottom half of its last row pair empty. Every mbarrier wait is bounded.
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -170,8 +171,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
       tile_phase ^= 1u;
       tc_fence_after_sync();
       // The accumulator is read out and rounded to 16 bits completely (128 registers per thread) before anything
-      // is stored: the next tile's MMAs may start as soon as the last TMEM load has returned, and the row-wise
-      // stores (each thread writes its own 512-byte row segment: slow) run beside them.
+      // is stored: the next tile's MMAs may start as soon as the last TMEM load has returned, and the stores
+      // run beside them.
       uint32_t pk[kBN / 64][32];
 #pragma unroll
       for (int q = 0; q < kBN / 64; ++q) {
