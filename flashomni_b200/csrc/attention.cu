@@ -6,26 +6,30 @@
 // base-2 online softmax, output rounded to the input dtype. q-blocks that are not in the list are
 // never written. An item with an empty list writes zeros (lse = -5e4), like the reference.
 //
-// One persistent CTA per SM walks its items (dealt round-robin in the order of the work list) as ONE
-// sequence of kv blocks g = 0, 1, 2, ... and software-pipelines it:
+// One persistent CTA per SM walks its items as ONE sequence of kv blocks g = 0, 1, 2, ... and
+// software-pipelines it:
 //
 //   tensor pipe     S[g&1] = Q K_g^T   (QK issuer)   and   O (+)= P[g&1] V_g   (PV issuer)
 //   softmax group   g&1:  S[g&1] -> registers -> P[g&1]
 //
+// Items are positions of the work list's processing order, handed out dynamically: position i < grid
+// size goes to CTA i, the rest are drawn from a device-wide cursor by the K producer and passed to the
+// other roles through a small shared-memory queue.
 // TMEM (512 columns): S0, S1 (fp32, 128 each), O (fp32, 128), P0, P1 (16 bit, 64 each). S is
 // double-buffered and P does not alias S, so the QK and PV batches are independent of each other and
 // of the softmax in between; they are issued by two different threads, because a thread that issues a
 // batch is held until the batch has drained.
-// The softmax is split into two groups of four warps that take alternate blocks (group = g & 1), one
-// thread per q row with all 128 columns of the block in registers: no exchange inside a group, and
-// while one group is in its exponential phase (MUFU-bound) the other one loads, reduces and hands
-// over, so that the special-function unit and the tensor pipe both stay busy. The running maximum
-// passes from block to block through shared memory (m_pub / m_ready); each group keeps its own
-// partial row sum, and the two are merged, with the output, in the epilogue (each group writes one
-// 64-column half of the row).
-// Warps: 0-3 softmax group 0, 4-7 softmax group 1 (TMEM lane = q row), 8 TMA producer of Q
-// (double-buffered) and K (two-slot FIFO of 32 KB tiles), 9 QK issuer, 10 PV issuer, 11 TMA producer
-// of V (its own two-slot FIFO). Every mbarrier wait is bounded.
+// The softmax is split into two groups of eight warps that take alternate blocks (group = g & 1), two
+// threads per q row with 64 columns each: while one group is in its exponentials the other one loads,
+// reduces and hands over. S is read twice (row maximum, then exponentials) instead of being held in
+// registers across the exchanges; the two halves of a row meet through shared memory; the running
+// maximum passes from block to block through shared memory (m_pub / m_ready); each thread keeps its
+// own partial row sum, and the four of a row are merged, with the output, in the epilogue (whole
+// q-blocks leave through a per-warp staging area and TMA box stores).
+// Warps: 0-7 softmax group 0, 8-15 softmax group 1 (TMEM lane = q row; `setmaxnreg` gives them 112
+// registers), 16 TMA producer of Q (double-buffered) and K (two-slot FIFO of 32 KB tiles) and drawer of
+// work-list positions, 17 QK issuer, 18 PV issuer, 19 TMA producer of V (its own two-slot FIFO).
+// Every mbarrier wait is bounded.
 #include <cuda_fp16.h>
 
 #include "internal.h"
