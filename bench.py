@@ -164,7 +164,7 @@ def run_ours(args):
     sl = slice(hb * D, (hb + hc) * D)
     weights = BlockWeights(w["wq"][sl].contiguous().to(device), w["wk"][sl].contiguous().to(device),
                            w["wv"][sl].contiguous().to(device), w["wo"][:, sl].contiguous().to(device))
-    block = SparseDiTAttentionBlock(weights, H, D, B, S, hb, hc, device=device)
+    block = SparseDiTAttentionBlock(weights, H, D, B, S, hb, hc, device=device, schedule=args.schedule)
     block.cache.copy_(cache_host.to(device))
     x = x_host.to(device)
     m_host = [torch.from_numpy(a).pin_memory() for a in (masks.sparse_info, masks.sparse_kv_info, masks.info_indptr,
@@ -289,6 +289,39 @@ def run_ours(args):
             ops[k].append(ev[i].elapsed_time(ev[i + 1]))
     op_ms = {k: statistics.mean(v) for k, v in ops.items()}
 
+    # Spread of the whole step (events around every single step), the same with L2 flushed before every step
+    # (a 256 MB buffer is rewritten: larger than the 126 MB L2), and the mask compaction alone.
+    def each_step(flush):
+        ts = []
+        for _ in range(args.steps):
+            if flush is not None:
+                flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return {"median": round(statistics.median(ts), 4), "min": round(min(ts), 4)}
+
+    warm_ms = each_step(None)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    cold_ms = each_step(flush_buf)
+    del flush_buf
+    compact_ts = []
+    for _ in range(args.steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        block.wrapper.build_work_lists(m_dev[0], m_dev[1], m_dev[2], m_dev[3])
+        e1.record()
+        torch.cuda.synchronize()
+        compact_ts.append(e0.elapsed_time(e1))
+    block.wrapper.check_status()
+    timing_detail = {"step_ms": warm_ms, "step_ms_l2_flushed": cold_ms,
+                     "mask_compaction_ms": {"median": round(statistics.median(compact_ts), 4),
+                                            "min": round(min(compact_ts), 4)},
+                     "plan_host_ms": round(block.plan_host_ms, 3)}
+
     fl = block_flops(masks, hb, hc)
     fl_rank = fl["gemm_q"] + fl["gemm_kv"] + fl["attention"] + fl["gemm_o"]
     if dist is not None:
@@ -328,6 +361,7 @@ def run_ours(args):
             "config": {"workload": "flux_block: hidden 3072, H=24, D=128, S=4608, batch 2, block density 0.5 "
                                    "(GEMM-Q sparse, GEMM-K/V dense, block-sparse attention, GEMM-O active heads + cache)",
                        "parallelism": f"heads/{world}", "seed": SEED, "cuda_graph": bool(args.graph),
+                       "schedule": args.schedule,
                        "l2": "per-step working set (x, 4 weights, q/k/v, attention out, cache, y) is >200 MB per rank, "
                              "larger than the 126 MB L2; no explicit flush",
                        "executed_flops_per_step": fl_total, "active_pairs": fl["active_pairs"],
@@ -336,7 +370,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": int(x_pinned.numel() * 2 + sum(t.numel() * t.element_size() for t in m_host)),
                     "d2h_bytes_per_step": int(y_pinned.numel() * 2)},
             "gpu_launches": int(args.steps * 10),
-            "clocks": clocks, "roofline": roofline,
+            "clocks": clocks, "roofline": roofline, "timing_detail": timing_detail,
         }
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(masks, w, x_host, cache_host, steps=40)
@@ -515,6 +549,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="flux_block", choices=["flux_block", "video"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--schedule", default="q_first", choices=["q_first", "kv_first"],
+                    help="flux_block: order of the projections and where the list kernels run")
     ap.add_argument("--graph", dest="graph", action="store_true", default=True,
                     help="replay the step from a CUDA graph (device-resident leg; the default: at 8 GPUs a step is "
                          "about 100 us of kernels and eager launches are host-bound)")

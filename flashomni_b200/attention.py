@@ -375,26 +375,47 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             self._scratch_bytes, stream)
         _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper (mask compaction)")
 
+    def build_work_lists(self, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
+                         is_full: bool = False) -> None:
+        """Extension: the mask compaction alone, on the current stream (what `run()` does first when the lists
+        were not prepared). For callers that time or inspect the step; see `work_lists()`."""
+        if not self._planned:
+            raise RuntimeError("plan() must be called before build_work_lists()")
+        with torch.cuda.device(self.device):
+            self._compact(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full,
+                          _native.current_stream(self.device))
+        self._prepared_key = None
+
     def prepare_masks(self, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
-                      is_full: bool = False) -> None:
+                      is_full: bool = False, *, stream: Optional[torch.cuda.Stream] = None,
+                      after: Optional[torch.cuda.Event] = None) -> None:
         """Optional (extension): builds the work lists for these mask tensors now, on a side stream that is
         ordered after the current stream, so that the step overlaps whatever the caller enqueues next (the
         Q/K/V projections). The following `run()` with the same, unmodified mask tensors re-uses the lists;
-        any other `run()` compacts as usual. Masks only depend on the block selection, not on q/k/v."""
+        any other `run()` compacts as usual. Masks only depend on the block selection, not on q/k/v.
+        `stream` replaces the wrapper's own side stream; with `after` the side stream is ordered after that
+        event instead of after everything enqueued on the current stream so far (the caller guarantees that
+        the previous `run()` of this wrapper precedes the event)."""
         if not self._planned:
             raise RuntimeError("plan() must be called before prepare_masks()")
         if not is_full:
             if sparse_info_indptr.dtype != torch.int32 or sparse_kv_info_indptr.dtype != torch.int32:
                 return  # run() will convert and compact itself
         with torch.cuda.device(self.device):
-            if self._side_stream is None:
-                self._side_stream = torch.cuda.Stream(self.device)
+            if self._prepared_event is None:
                 self._prepared_event = torch.cuda.Event()
-            cur = torch.cuda.current_stream(self.device)
-            self._side_stream.wait_stream(cur)
+            side = stream
+            if side is None:
+                if self._side_stream is None:
+                    self._side_stream = torch.cuda.Stream(self.device)
+                side = self._side_stream
+            if after is not None:
+                side.wait_event(after)
+            else:
+                side.wait_stream(torch.cuda.current_stream(self.device))
             self._compact(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full,
-                          self._side_stream.cuda_stream)
-            self._prepared_event.record(self._side_stream)
+                          side.cuda_stream)
+            self._prepared_event.record(side)
         self._prepared_key = self._mask_key(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                                             is_full)
 

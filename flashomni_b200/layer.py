@@ -9,13 +9,14 @@ cache). Nothing inside the block crosses GPUs; the sum of the partials is left t
 
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass
 from typing import Optional
 
 import torch
 
 from .attention import BatchFlashOmniFAWithRaggedKVWrapper
-from .gemm import flashomni_gemm, flashomni_gemm_reduction
+from .gemm import flashomni_gemm, flashomni_gemm_reduction, prepare_gemm_o_list, prepare_gemm_q_list
 
 
 @dataclass
@@ -28,7 +29,13 @@ class BlockWeights:
 
 class SparseDiTAttentionBlock:
     def __init__(self, weights: BlockWeights, num_heads: int, head_dim: int, batch: int, seq: int,
-                 head_begin: int = 0, head_count: Optional[int] = None, device=None, dtype=torch.bfloat16):
+                 head_begin: int = 0, head_count: Optional[int] = None, device=None, dtype=torch.bfloat16,
+                 schedule: str = "q_first"):
+        if schedule not in ("q_first", "kv_first"):
+            raise ValueError("schedule must be 'q_first' or 'kv_first'")
+        self.schedule = schedule
+        self._side = None
+        self._q_list = self._o_list = None
         self.w = weights
         self.H, self.D, self.B, self.S = num_heads, head_dim, batch, seq
         self.hb = head_begin
@@ -47,8 +54,10 @@ class SparseDiTAttentionBlock:
         self.cache = mk(batch, seq, weights.wo.shape[0])
         self.wrapper = BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=self.device))
         indptr = torch.arange(batch + 1, dtype=torch.int32, device=self.device) * seq
+        t0 = time.perf_counter()
         self.wrapper.plan(indptr, indptr, self.hc, self.hc, head_dim, q_data_type=dtype,
                           mask_num_heads=num_heads, mask_head_begin=head_begin)
+        self.plan_host_ms = (time.perf_counter() - t0) * 1e3   # host time of plan(): once per shape, not per step
 
     def refresh_cache(self, x, sparse_info, sparse_info_indptr):
         """The full step of the two-call protocol: cache = contribution of the heads that the sparse steps
@@ -67,17 +76,51 @@ class SparseDiTAttentionBlock:
         # GEMM-Q goes first because its tiles are handed out dynamically and tolerate an SM that starts late.
         # (Building the GEMM lists on a side stream as well -- prepare_gemm_q_list / prepare_gemm_o_list --
         # measured no gain here for the same reason.)
+        T = self.B * self.S
+        if self.schedule == "kv_first":
+            return self._forward_kv_first(x, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, y)
         self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr)
         flashomni_gemm(x, self.w.wq, H, sparse_info, sparse_info_indptr, 0, None, out=self.q,
                        head_begin=hb, head_dim=D)
         flashomni_gemm(x, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
         flashomni_gemm(x, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
-        T = self.B * self.S
         self.wrapper.run(self.q.view(T, self.hc, D), self.k.view(T, self.hc, D), self.v.view(T, self.hc, D),
                          sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                          out=self.attn.view(T, self.hc, D))
         flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0, self.cache,
                                  is_for_cache=False, head_begin=hb, head_dim=D, out=y)
+        return y
+
+    def _forward_kv_first(self, x, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, y):
+        """The same step with every mask-only kernel (GEMM-Q tile list, attention work lists, GEMM-O row lists)
+        on a side stream beside the dense K and V projections, which go first: the dense kernel deals its tiles
+        statically, some SMs finish a tile early, and the list kernels run there. K is enqueued before the side
+        work so that its CTAs are placed first."""
+        H, D, hb = self.H, self.D, self.hb
+        T = self.B * self.S
+        dev = self.device
+        cur = torch.cuda.current_stream(dev)
+        if self._side is None:
+            self._side = torch.cuda.Stream(dev)
+            self._start = torch.cuda.Event()
+        self._start.record(cur)            # everything of the previous step precedes this event
+        flashomni_gemm(x, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
+        self._side.wait_event(self._start)
+        n_local = self.hc * D
+        self._q_list = prepare_gemm_q_list(self.B, self.S, n_local, H, sparse_info, sparse_info_indptr, 0,
+                                           head_begin=hb, head_dim=D, into=self._q_list, stream=self._side)
+        self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
+                                   stream=self._side, after=self._start)
+        self._o_list = prepare_gemm_o_list(self.B, self.S, n_local, H, sparse_info, sparse_info_indptr, 0,
+                                           head_begin=hb, head_dim=D, into=self._o_list, stream=self._side)
+        flashomni_gemm(x, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
+        flashomni_gemm(x, self.w.wq, H, sparse_info, sparse_info_indptr, 0, None, out=self.q,
+                       head_begin=hb, head_dim=D, worklist=self._q_list)
+        self.wrapper.run(self.q.view(T, self.hc, D), self.k.view(T, self.hc, D), self.v.view(T, self.hc, D),
+                         sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
+                         out=self.attn.view(T, self.hc, D))
+        flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0, self.cache,
+                                 is_for_cache=False, head_begin=hb, head_dim=D, out=y, worklist=self._o_list)
         return y
 
 
