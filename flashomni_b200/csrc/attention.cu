@@ -91,7 +91,7 @@ struct Tail {
 // Development aid (only with -DFO_ATTN_TRACE): CTA 0 records the low 32 bits of clock64() at pipeline
 // events into shared memory (a global store before an mbarrier arrive would delay the arrive) and
 // copies the table out when it exits.
-constexpr int kTraceEvents = 18, kTraceSlots = 256;
+constexpr int kTraceEvents = 18, kTraceSlots = 48;
 __device__ uint32_t g_trace[kTraceEvents * kTraceSlots];
 __device__ __forceinline__ void trace(uint32_t* tr, int ev, int idx) {
   if (blockIdx.x == 0 && idx >= 0 && idx < kTraceSlots) tr[ev * kTraceSlots + idx] = static_cast<uint32_t>(clock64());
@@ -109,6 +109,7 @@ constexpr int kTraceBytes = 0;
 constexpr int kOutStageBytes = 16 * 64;  // per softmax warp: 16 rows x 32 output columns
 constexpr int kSmemBytes = (kQBufs + kRing) * kTileBytes + kSoftmaxWarps * kOutStageBytes + 1024 +
                            static_cast<int>(sizeof(Tail)) + kTraceBytes;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 
 // The kept kv blocks of an item are visited in rotated order (the online softmax does not care):
 // q-block qb starts at entry (qb * kRotStep) mod length of its list.
@@ -333,8 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   if (n_items < 0) n_items = 0;
   auto ignore_empty = [](int, int, int) {};
 
-  // The softmax threads hold a whole 128-column row of S in registers: the two softmax warpgroups take
-  // the registers that the producer / issuer warpgroup does not need.
+  // The softmax warps take the registers that the producer / issuer warpgroup does not need.
   if (warp >= kSoftmaxWarps) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
   if (warp == kWarpProducer) {
@@ -746,7 +746,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (tracer) FO_TRACE(6, static_cast<int>(g));  // P handed over
         ++my_blocks;
         // the previous item's epilogue runs after this group's first block of the next item, so that
-        // the item's last PV overlaps a softmax step
+        // the item's last PV overlaps a softmax step (running it before the block, in the wait for S,
+        // frees O earlier for the next item's first PV but measured 9 % slower: it delays the group's
+        // own chain, which is the longer one)
         if (pend && !epilogue()) { ok = false; break; }
       }
       if (seq.last()) {
