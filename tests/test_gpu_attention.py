@@ -150,6 +150,14 @@ def test_prepare_masks_on_side_stream_gives_identical_result(cuda_device):
     w.check_status()
     assert w.work_lists()["n_items"] == H * (S // 128)   # every q-block active now: the lists were rebuilt
     assert torch.equal(c, w.run(q, k, v, si, skv, ip, kp))
+    # the compaction alone, on the caller's stream or on a stream of the caller's choice after an event
+    w.build_work_lists(si, skv, ip, kp)
+    assert w.work_lists()["n_items"] == H * (S // 128)
+    side, ev = torch.cuda.Stream(cuda_device), torch.cuda.Event()
+    ev.record()
+    w.prepare_masks(si, skv, ip, kp, stream=side, after=ev)
+    assert torch.equal(c, w.run(q, k, v, si, skv, ip, kp))
+    w.check_status()
 
 
 def test_block_forward_is_cuda_graph_capturable(cuda_device, monkeypatch):

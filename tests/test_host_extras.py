@@ -41,3 +41,9 @@ def test_selection_statement_is_deterministic_across_layouts():
     a = osel.select_blocks(s, 2, 0.3, 0.3)
     b = osel.select_blocks(np.ascontiguousarray(s.transpose(0, 1, 3, 2)).transpose(0, 1, 3, 2), 2, 0.3, 0.3)
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
+def test_block_schedule_name_is_checked_before_anything_else():
+    from flashomni_b200.layer import SparseDiTAttentionBlock
+    with pytest.raises(ValueError):
+        SparseDiTAttentionBlock(None, 4, 128, 1, 256, schedule="o_first")
