@@ -418,7 +418,7 @@ int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t
   g.kb_per_head = 1;
   g.status = wsw + 4;
   g.cursor = is_full ? nullptr : wsw + 5;  // equal tiles keep a fixed share
-  if (gemm_tall_applies(g)) {
+  if (gemm_tall_applies(g, sm_count())) {
     // the tall-tile kernel stores 16-row x 64-column boxes (one per-warp staging area at a time)
     const uint32_t ybox[2] = {64, 16};
     const uint64_t yd[2] = {static_cast<uint64_t>(n), static_cast<uint64_t>(batch) * m};

@@ -261,10 +261,19 @@ extern "C" __attribute__((visibility("default"))) int fo_gemm_tall_trace_dump(lo
 }
 #endif
 
-bool gemm_tall_applies(const GemmArgs& a) {
-  return a.mode == kGemmQ && a.tiles == nullptr && (a.init_mode == kInitNone || a.init_mode == kInitBias1D) &&
-         (static_cast<int64_t>(a.batch) * a.m) % kBM == 0 && static_cast<int64_t>(a.batch) * a.m >= 2 * kBM &&
-         a.n % kBN == 0 && a.k % kBK == 0 && a.k > 0;
+bool gemm_tall_applies(const GemmArgs& a, int sm_count) {
+  const bool fits = a.mode == kGemmQ && a.tiles == nullptr && (a.init_mode == kInitNone || a.init_mode == kInitBias1D) &&
+                    (static_cast<int64_t>(a.batch) * a.m) % kBM == 0 && static_cast<int64_t>(a.batch) * a.m >= 2 * kBM &&
+                    a.n % kBN == 0 && a.k % kBK == 0 && a.k > 0;
+  if (!fits || sm_count <= 0) return fits;
+  // Both kernels deal equal tiles in fixed shares, so a launch lasts as long as its fullest SM: compare how well
+  // the 256x256 tiles and the 128x256 tiles of the other kernel fill whole waves (that kernel's tiles run at about
+  // 0.93 of this one's rate), and leave the launch to the other kernel only when it is clearly ahead.
+  const int64_t rows = static_cast<int64_t>(a.batch) * a.m;
+  const int64_t t_tall = ((rows + 2 * kBM - 1) / (2 * kBM)) * (a.n / kBN);
+  const int64_t t_wide = (rows / kBM) * (a.n / kBN);
+  auto fill = [&](int64_t t) { return static_cast<double>(t) / static_cast<double>(((t + sm_count - 1) / sm_count) * sm_count); };
+  return !(fill(t_wide) * 0.93 > fill(t_tall) * 1.05);
 }
 
 cudaError_t launch_gemm_tall(const GemmArgs& a, int max_ctas, cudaStream_t stream) {

@@ -84,7 +84,7 @@ struct GemmArgs {
 };
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream);
 // dense projections whose shape divides into 256x256 tiles take the tall-tile kernel (gemm_tall.cu)
-bool gemm_tall_applies(const GemmArgs& a);
+bool gemm_tall_applies(const GemmArgs& a, int sm_count);
 cudaError_t launch_gemm_tall(const GemmArgs& a, int max_ctas, cudaStream_t stream);
 
 // ------------------------------------------------------------------ block selection
