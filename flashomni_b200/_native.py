@@ -42,6 +42,11 @@ SIGNATURES = {
                                      c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                      _P, _P, c_int32, c_int32, _P, _P, _P, _P, _P,
                                      c_int64, c_int32, c_float, _P, _P]),
+    "fo_sparse_attn_fwd_softcap": (c_int32, [_P, _P, _P, _P, _P, c_int32,
+                                             c_int64, c_int64, c_int32, c_int32, c_int32,
+                                             c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                             _P, _P, c_int32, c_int32, _P, _P, _P, _P, _P,
+                                             c_int64, c_int32, c_float, c_float, _P, _P]),
     "fo_gemm_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "fo_gemm_q": (c_int32, [_P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32,
                             c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,

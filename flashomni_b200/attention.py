@@ -153,8 +153,8 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             raise NotImplementedError("flashomni_b200: causal masking is not implemented (DiT path is non-causal)")
         if PosEncodingMode[pos_encoding_mode] != PosEncodingMode.NONE:
             raise NotImplementedError("flashomni_b200: in-kernel positional encoding is not implemented")
-        if logits_soft_cap > 0:
-            raise NotImplementedError("flashomni_b200: logits soft cap is not implemented")
+        if logits_soft_cap < 0:
+            raise ValueError("logits_soft_cap must be >= 0 (0 disables it)")
         if q_data_type != kv_data_type:
             raise NotImplementedError("flashomni_b200: q and kv must share a dtype")
         native_dtype(q_data_type)
@@ -336,15 +336,19 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             else:
                 self._compact(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full, stream)
             self._prepared_key = None
-            rc = lib.fo_sparse_attn_fwd(
-                _native.ptr(q), _native.ptr(k), _native.ptr(v), _native.ptr(out), _native.ptr(lse),
-                native_dtype(q.dtype), self._total_q, self._total_kv, self._num_qo_heads, self._num_kv_heads,
-                self._head_dim, q.stride(0), q.stride(1), kn, kh, vn, vh, out.stride(0), out.stride(1),
-                _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
-                self._sparse_block_size_for_q, self._sparse_block_size_for_kv,
-                _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
-                _native.ptr(ws["order"]), _native.ptr(ws["counters"]), max(self._n_cand, 1),
-                self._mask_head_begin, float(sm_scale), _native.ptr(ws["status"]), stream)
+            head = (_native.ptr(q), _native.ptr(k), _native.ptr(v), _native.ptr(out), _native.ptr(lse),
+                    native_dtype(q.dtype), self._total_q, self._total_kv, self._num_qo_heads, self._num_kv_heads,
+                    self._head_dim, q.stride(0), q.stride(1), kn, kh, vn, vh, out.stride(0), out.stride(1),
+                    _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
+                    self._sparse_block_size_for_q, self._sparse_block_size_for_kv,
+                    _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
+                    _native.ptr(ws["order"]), _native.ptr(ws["counters"]), max(self._n_cand, 1),
+                    self._mask_head_begin, float(sm_scale))
+            cap = float(self._logits_soft_cap or 0.0)
+            if cap > 0:  # logits = cap * tanh(q.k * sm_scale / cap), as the reference's variant does
+                rc = lib.fo_sparse_attn_fwd_softcap(*head, cap, _native.ptr(ws["status"]), stream)
+            else:
+                rc = lib.fo_sparse_attn_fwd(*head, _native.ptr(ws["status"]), stream)
             _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper.run")
         if _native.debug_checks():
             self.check_status()
@@ -445,9 +449,10 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
                 logits_soft_cap: Optional[float] = None, sm_scale: Optional[float] = None,
                 rope_scale: Optional[float] = None, rope_theta: Optional[float] = None) -> torch.Tensor:
         """Deprecated alias kept for source compatibility (reference: flashomni/attention.py:647-673)."""
-        if causal or pos_encoding_mode != "NONE" or (logits_soft_cap or 0) > 0:
-            raise NotImplementedError("flashomni_b200: causal / pos-encoding / soft-cap are not implemented")
+        if causal or pos_encoding_mode != "NONE":
+            raise NotImplementedError("flashomni_b200: causal / pos-encoding are not implemented")
         self._sm_scale = sm_scale
+        self._logits_soft_cap = logits_soft_cap or 0.0
         return self.run(q, k, v, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, is_full)
 
     def forward_return_lse(self, q, k, v, sparse_info=None, sparse_kv_info=None, sparse_info_indptr=None,
@@ -456,9 +461,10 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
                            logits_soft_cap: Optional[float] = None, sm_scale: Optional[float] = None,
                            rope_scale: Optional[float] = None, rope_theta: Optional[float] = None):
         """Deprecated alias (reference: flashomni/attention.py:839-865)."""
-        if causal or pos_encoding_mode != "NONE" or (logits_soft_cap or 0) > 0:
-            raise NotImplementedError("flashomni_b200: causal / pos-encoding / soft-cap are not implemented")
+        if causal or pos_encoding_mode != "NONE":
+            raise NotImplementedError("flashomni_b200: causal / pos-encoding are not implemented")
         self._sm_scale = sm_scale
+        self._logits_soft_cap = logits_soft_cap or 0.0
         return self.run_return_lse(q, k, v, sparse_info, sparse_kv_info, sparse_info_indptr,
                                    sparse_kv_info_indptr, is_full)
 

@@ -184,14 +184,17 @@ int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes, const
 }
 
 // ------------------------------------------------------------------------------------------ attention
-int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
-                       int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
-                       int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
-                       int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
-                       int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t sbq,
-                       int32_t sbkv, const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx,
-                       const int32_t* order, const int32_t* counters, int64_t max_items, int32_t head_begin,
-                       float sm_scale, int32_t* status, void* stream) {
+namespace {
+int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                     int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                     int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                     int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                     int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t sbq,
+                     int32_t sbkv, const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx,
+                     const int32_t* order, const int32_t* counters, int64_t max_items, int32_t head_begin,
+                     float sm_scale, float logits_soft_cap, int32_t* status, void* stream) {
+  if (!(logits_soft_cap >= 0.f) || !(sm_scale > 0.f))
+    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: sm_scale must be positive and logits_soft_cap >= 0");
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr)
     return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: null q/k/v/o");
   if (qo_indptr == nullptr || kv_indptr == nullptr || items == nullptr || kv_ptr == nullptr ||
@@ -247,12 +250,47 @@ int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   a.head_begin = head_begin;
   a.group_size = num_qo_heads / num_kv_heads;
   a.is_bf16 = dtype == FO_DTYPE_BF16;
-  a.sm_scale_log2 = sm_scale * 1.4426950408889634f;
+  if (logits_soft_cap > 0.f) {
+    a.soft_cap_pre = sm_scale / logits_soft_cap;
+    a.sm_scale_log2 = logits_soft_cap * 1.4426950408889634f;
+  } else {
+    a.soft_cap_pre = 0.f;
+    a.sm_scale_log2 = sm_scale * 1.4426950408889634f;
+  }
   a.status = status;
   int64_t ctas = static_cast<int64_t>(sm_count());  // one persistent CTA per SM
   if (ctas > max_items) ctas = max_items;
   const cudaError_t e = launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_sparse_attn_fwd", e);
+}
+}  // namespace
+
+int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                       int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                       int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                       int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t sbq,
+                       int32_t sbkv, const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx,
+                       const int32_t* order, const int32_t* counters, int64_t max_items, int32_t head_begin,
+                       float sm_scale, int32_t* status, void* stream) {
+  return sparse_attn_impl(q, k, v, o, lse, dtype, total_q, total_kv, num_qo_heads, num_kv_heads, head_dim, q_stride_n,
+                          q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, qo_indptr,
+                          kv_indptr, sbq, sbkv, items, kv_ptr, kv_idx, order, counters, max_items, head_begin, sm_scale,
+                          0.f, status, stream);
+}
+
+int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                               int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                               int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                               int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                               int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t sbq,
+                               int32_t sbkv, const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx,
+                               const int32_t* order, const int32_t* counters, int64_t max_items, int32_t head_begin,
+                               float sm_scale, float logits_soft_cap, int32_t* status, void* stream) {
+  return sparse_attn_impl(q, k, v, o, lse, dtype, total_q, total_kv, num_qo_heads, num_kv_heads, head_dim, q_stride_n,
+                          q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, qo_indptr,
+                          kv_indptr, sbq, sbkv, items, kv_ptr, kv_idx, order, counters, max_items, head_begin, sm_scale,
+                          logits_soft_cap, status, stream);
 }
 
 // ------------------------------------------------------------------------------------------ GEMMs

@@ -276,7 +276,7 @@ struct BlockSeq {
   __device__ __forceinline__ bool last() const { return j == n - 1; }
 };
 
-template <bool kBf16>
+template <bool kBf16, bool kSoftCap>
 __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -668,6 +668,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         // that the two groups stay within one phase of each other)
         if (g >= 1u && !mbar_wait(&tail->m_ready[Y], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
         const float m_prev = seq.first() ? -INFINITY : tail->m_pub[Y][row];
+        // with a soft cap the logit is cap * tanh(s * sm_scale / cap): monotonic, so the maximum is transformed once
+        if constexpr (kSoftCap) mx = (mx == -INFINITY) ? mx : tanh_approx(mx * a.soft_cap_pre);
         const float m_new = fmaxf(m_prev, mx * a.sm_scale_log2);
         // lazy rescale (the decision is the same in both warps of a row: same rows, same values)
         const bool need = (m_new - m_prev) > kRescaleThreshold;
@@ -718,6 +720,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->s_free[X]);
+        if constexpr (kSoftCap) {
+#pragma unroll
+          for (int t = 0; t < 64; ++t) s[t] = __float_as_uint(tanh_approx(__uint_as_float(s[t]) * a.soft_cap_pre));
+        }
         if (valid < 64) {
 #pragma unroll
           for (int t = 0; t < 64; ++t)
@@ -810,19 +816,22 @@ extern "C" __attribute__((visibility("default"))) int fo_trace_dump(long long* h
 }
 #endif
 
+namespace {
+template <bool kBf16, bool kSoftCap>
+cudaError_t launch_one(const AttnArgs& a, int ctas, cudaStream_t stream) {
+  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes);
+  if (e != cudaSuccess) return e;
+  attention_kernel<kBf16, kSoftCap><<<ctas, kThreads, kSmemBytes, stream>>>(a);
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream) {
   if (max_ctas <= 0) return cudaSuccess;
-  cudaError_t e;
-  if (a.is_bf16) {
-    e = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attention_kernel<true><<<max_ctas, kThreads, kSmemBytes, stream>>>(a);
-  } else {
-    e = cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attention_kernel<false><<<max_ctas, kThreads, kSmemBytes, stream>>>(a);
-  }
-  return cudaGetLastError();
+  const bool cap = a.soft_cap_pre > 0.f;
+  if (a.is_bf16) return cap ? launch_one<true, true>(a, max_ctas, stream) : launch_one<true, false>(a, max_ctas, stream);
+  return cap ? launch_one<false, true>(a, max_ctas, stream) : launch_one<false, false>(a, max_ctas, stream);
 }
 
 }  // namespace fo

@@ -138,7 +138,8 @@ struct AttnArgs {
   int head_begin;                  // tensor head = item head - head_begin
   int group_size;                  // H / Hkv
   int is_bf16;
-  float sm_scale_log2;             // sm_scale * log2(e)
+  float sm_scale_log2;             // sm_scale * log2(e); with a soft cap: cap * log2(e)
+  float soft_cap_pre;              // 0: no soft cap; else sm_scale / cap (logits = cap * tanh(q.k * sm_scale / cap))
   int32_t* status;
 };
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream);

@@ -105,6 +105,19 @@ FO_API int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void*
                        int64_t max_items, int32_t head_begin, float sm_scale, int32_t* status,
                        void* stream);
 
+/* The same with the reference's logits soft cap (include/flashomni/attention/variants.cuh:47-50,72-74: the
+ * logit of a (q, k) pair is cap * tanh(q.k * sm_scale / cap) before the softmax). logits_soft_cap = 0 is
+ * fo_sparse_attn_fwd. */
+FO_API int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                       int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                       int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                       int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr,
+                       int32_t sbq, int32_t sbkv, const int32_t* items, const int32_t* kv_ptr,
+                       const int32_t* kv_idx, const int32_t* order, const int32_t* counters,
+                       int64_t max_items, int32_t head_begin, float sm_scale, float logits_soft_cap,
+                       int32_t* status, void* stream);
+
 /* ---- GEMM-Q / GEMM-O ---------------------------------------------------------------------------
  * Workspace (device, caller-owned, 16-byte aligned) of fo_gemm_workspace_bytes(...) bytes, laid out
  * as int32 words: [0..3] counters (count, aux, list status, 0), [4] kernel status (FO_DEV_*),

@@ -31,9 +31,10 @@ def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info=None, sparse_kv_
                      info_indptr=None, kv_info_indptr=None, sbq: int = 128, sbkv: int = 128,
                      is_full: bool = False, sm_scale: float | None = None, out_prior=None,
                      lse_prior=None, return_lse: bool = False, head_begin: int = 0, num_mask_heads=None,
-                     dtype=torch.float32):
+                     dtype=torch.float32, logits_soft_cap: float = 0.0):
     """q [Tq, H, D], k/v [Tkv, Hkv, D] (any float dtype, computed in `dtype`). Returns fp32 `out`
-    (and base-2 `lse`). `out_prior` supplies the rows of skipped q-blocks (zeros if None, as
+    (and base-2 `lse`). With `logits_soft_cap` > 0 the logits are cap * tanh(q.k * sm_scale / cap)
+    (include/flashomni/attention/variants.cuh:47-50,72-74). `out_prior` supplies the rows of skipped q-blocks (zeros if None, as
     flashomni/attention.py:778-781 allocates). Heads of q map to mask heads `head_begin + h`."""
     Tq, H, D = q.shape
     Hkv = k.shape[1]
@@ -77,6 +78,8 @@ def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info=None, sparse_kv_
                 cols = np.concatenate([np.arange(k0 + j * sbkv, min(k0 + (j + 1) * sbkv, k1)) for j in kept])
                 cols_t = torch.from_numpy(cols)
                 s = (qf[r0:r1, h] @ kf[cols_t, hk].T) * sm_scale
+                if logits_soft_cap > 0:
+                    s = torch.tanh(s / logits_soft_cap) * logits_soft_cap
                 p = torch.softmax(s, dim=-1)
                 out[r0:r1, h] = p @ vf[cols_t, hk]
                 if return_lse:

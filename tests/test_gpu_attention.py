@@ -48,6 +48,33 @@ def test_small_uniform(cuda_device, dtype, seq, H, density):
                 assert torch.equal(oc[qb * 128:(qb + 1) * 128, h], prior[qb * 128:(qb + 1) * 128, h])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_logits_soft_cap(cuda_device, dtype):
+    """logits = cap * tanh(q.k * sm_scale / cap) (reference: variants.cuh:47-50,72-74); the cap is small enough
+    for the tanh to bend most logits (q.k * sm_scale ~ N(0, 1) here). Ragged kv tail included."""
+    H, cap = 2, 1.5
+    lens_q, lens_kv = [384, 200], [640, 300]
+    qo = np.concatenate([[0], np.cumsum(lens_q)]); kv = np.concatenate([[0], np.cumsum(lens_kv)])
+    rng = np.random.default_rng(15)
+    qa = [np.ones((-(-a // 128), H), np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // 128), H, -(-b // 128))) < 0.7).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    for x in kk:
+        x[:, :, -1] = 1   # the ragged last kv-block is kept everywhere
+    m = wl.pack_masks(qa, kk)
+    q = wl.randn_bf16((int(qo[-1]), H, 128), 11, dtype=dtype)
+    k = wl.randn_bf16((int(kv[-1]), H, 128), 12, dtype=dtype)
+    v = wl.randn_bf16((int(kv[-1]), H, 128), 13, dtype=dtype)
+    w = _wrapper(cuda_device, qo, kv, H, dtype, logits_soft_cap=cap)
+    o, lse = _run(cuda_device, w, q, k, v, m, return_lse=True)
+    ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                                       return_lse=True, logits_soft_cap=cap)
+    assert_close_bf16(o, ref, f"soft-capped attention {dtype}")
+    assert torch.allclose(lse.cpu(), ref_lse, atol=2e-2, rtol=1e-4)
+    # and it differs from the uncapped result (the cap is really applied)
+    plain = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr)
+    assert (plain - ref).abs().max() > 5e-2
+
+
 def test_ragged_batch_with_empty_rows_and_lse(cuda_device):
     H = 3
     lens_q, lens_kv = [300, 128, 1000, 77], [256, 700, 1300, 129]

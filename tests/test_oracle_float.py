@@ -55,6 +55,20 @@ def test_is_full_equals_plain_softmax_and_lse_is_base2():
     assert torch.allclose(lse, (torch.logsumexp(s, -1) / math.log(2)).T, atol=1e-9)
 
 
+def test_soft_cap_matches_the_formula_and_zero_disables_it():
+    """logits = cap * tanh(q.k * sm_scale / cap) before the softmax (reference: variants.cuh:47-50,72-74)."""
+    q, k, v, qo, kv, _ = _inputs([130], [300], 2, 8, seed=5)
+    cap = 0.8
+    o, lse = oa.sparse_attention(q, k, v, qo, kv, is_full=True, return_lse=True, dtype=torch.float64, logits_soft_cap=cap)
+    s = torch.einsum("qhd,khd->hqk", q.double(), k.double()) / math.sqrt(8)
+    s = cap * torch.tanh(s / cap)
+    ref = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v.double())
+    assert torch.allclose(o, ref, atol=1e-10)
+    assert torch.allclose(lse, (torch.logsumexp(s, -1) / math.log(2)).T, atol=1e-9)
+    o0 = oa.sparse_attention(q, k, v, qo, kv, is_full=True, dtype=torch.float64, logits_soft_cap=0.0)
+    assert torch.equal(o0, oa.sparse_attention(q, k, v, qo, kv, is_full=True, dtype=torch.float64))
+
+
 def test_gemm_q_inactive_tiles_keep_prior():
     m = wl.flux_masks(1, 2, 3, 3, 0.5, seed=4, text_blocks=1)
     g = torch.Generator().manual_seed(0)
