@@ -18,8 +18,9 @@
 // 128-byte swizzle atom), 4-stage ring of (A 16 KB + B 32 KB), two 256-column TMEM accumulators so
 // the epilogue of tile i overlaps the main loop of tile i+1. The epilogue converts 64-column slabs
 // (TMEM -> registers -> +init -> 16-bit) into a swizzled shared-memory slab and hands each slab to a
-// TMA store, so global writes are full 128-byte lines and asynchronous. Tiles are dealt round-robin
-// to the persistent CTAs.
+// TMA store, so global writes are full 128-byte lines and asynchronous. The tiles of the sparse modes
+// (unequal lengths) are handed to the persistent CTAs through a device-wide cursor, in list order; the
+// equal tiles of a dense launch keep fixed round-robin shares.
 #include <cuda_fp16.h>
 
 #include "internal.h"
