@@ -294,6 +294,19 @@ int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* v, void
 }
 
 // ------------------------------------------------------------------------------------------ GEMMs
+int fo_gemm_dense_tile_rows(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t has_full_init, int32_t sm_count) {
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.mode = kGemmQ;
+  g.init_mode = has_full_init ? kInitFull : kInitNone;
+  g.batch = batch;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  return gemm_tall_applies(g, sm_count) ? 256 : 128;
+}
+
 size_t fo_gemm_workspace_bytes(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim) {
   if (batch <= 0 || m <= 0 || n <= 0 || k <= 0 || head_dim <= 0) return 64;
   const size_t mt = static_cast<size_t>(m) / 128, nt = static_cast<size_t>(n) / 128;

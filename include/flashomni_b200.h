@@ -124,6 +124,13 @@ FO_API int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* 
  * [8...] the work list built from the mask. */
 FO_API size_t fo_gemm_workspace_bytes(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim);
 
+/* Host-only query (no device call): the row count of the output tiles, 256 or 128, that a dense launch
+ * (is_full) of fo_gemm_q uses for this shape on a device with sm_count SMs; 0 for an empty shape. Both
+ * dense kernels deal equal tiles in fixed shares, so the choice goes to the shape that fills whole waves
+ * of SMs better. has_full_init: the launch adds a [batch, m, n] tensor (not reachable through fo_gemm_q). */
+FO_API int fo_gemm_dense_tile_rows(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t has_full_init,
+                                   int32_t sm_count);
+
 /* Replaces torch.ops.flashomni_kernels.flashomni_gemm (csrc/gemm.cu:24-59 ->
  * include/flashomni/gemm/w16a16/gemm.cuh:27-357). x [batch, m, k], w [n, k], y [batch, m, n], all
  * contiguous; bias [n] or null. Output tile (iy, ix) of batch b is computed iff is_full or bit

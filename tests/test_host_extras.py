@@ -47,3 +47,21 @@ def test_block_schedule_name_is_checked_before_anything_else():
     from flashomni_b200.layer import SparseDiTAttentionBlock
     with pytest.raises(ValueError):
         SparseDiTAttentionBlock(None, 4, 128, 1, 256, schedule="o_first")
+
+
+def test_dense_gemm_tile_choice_fills_whole_waves():
+    """Host-only query of the dense dispatch on a 148-SM device: 256-row tiles unless the 128-row tiles of the
+    other kernel fill whole waves clearly better (the heads of the flux block split over two GPUs: 216 tiles of
+    256x256 are 1.46 waves, 432 tiles of 128x256 are 2.92)."""
+    from flashomni_b200 import _native
+    lib = _native.load()
+    q = lambda b, m, n, k, full=0, sms=148: lib.fo_gemm_dense_tile_rows(b, m, n, k, full, sms)
+    assert q(2, 4608, 3072, 3072) == 256          # flux block, one GPU: 432 tall tiles, 2.92 waves
+    assert q(2, 4608, 1536, 3072) == 128          # heads over two GPUs
+    assert q(2, 4608, 768, 3072) == 256           # over four: one wave either way
+    assert q(2, 4608, 384, 3072) == 128           # over eight: 384 columns do not divide into 256-column tiles
+    assert q(1, 77312, 5120, 5120) == 256         # video layer
+    assert q(1, 9728, 5120, 5120) == 256          # its token shard on eight GPUs
+    assert q(1, 128, 256, 64) == 128              # a single row block
+    assert q(2, 4608, 3072, 3072, full=1) == 128  # a full-tensor init is the other kernel's
+    assert q(0, 4608, 3072, 3072) == 0
