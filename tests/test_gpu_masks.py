@@ -107,6 +107,25 @@ def test_attention_compaction_bit_exact(cuda_device, case):
     _assert_lists_equal(got, ref)
 
 
+def test_attention_compaction_random_ragged_cases(cuda_device):
+    """Forty seeded cases: ragged request lengths, densities from empty to full, head windows."""
+    rng = np.random.default_rng(2025)
+    for _ in range(40):
+        B, H = int(rng.integers(1, 5)), int(rng.integers(1, 7))
+        lens_q = [int(rng.integers(1, 1500)) for _ in range(B)]
+        lens_kv = [int(rng.integers(1, 6000)) for _ in range(B)]
+        dq, dk = float(rng.choice([0.0, 0.3, 0.8, 1.0])), float(rng.choice([0.0, 0.05, 0.5, 1.0]))
+        qa = [(rng.random((-(-a // 128), H)) < dq).astype(np.uint8) for a in lens_q]
+        kk = [(rng.random((-(-a // 128), H, -(-b // 128))) < dk).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+        hb = int(rng.integers(0, H))
+        hc = int(rng.integers(1, H - hb + 1))
+        qo = np.concatenate([[0], np.cumsum(lens_q)]); kv = np.concatenate([[0], np.cumsum(lens_kv)])
+        m = wl.pack_masks(qa, kk)
+        got = _compact_gpu(cuda_device, m, qo, kv, H, head_begin=hb, head_count=hc)
+        ref = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, kv, H, 128, 128, hb, hc)
+        _assert_lists_equal(got, ref)
+
+
 def test_gemm_worklists_bit_exact(cuda_device):
     lib = _native.load()
     B, H, nq = 2, 24, 36
