@@ -34,6 +34,31 @@ def test_signatures_keep_reference_parameter_order():
                      "is_for_cache", "sparse_q_size"]
 
 
+def test_signatures_match_the_reference_source_parameter_by_parameter():
+    """Names, order and defaults of every positional parameter of the reference's public entry points (read from
+    its source by tests/golden/make_reference_signatures.py); this package only adds optional keyword-only extensions."""
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_signatures.json")) as f:
+        ref = json.load(f)
+    assert len(ref) == 11
+    for name, desc in ref.items():
+        obj = fo
+        for part in name.split("."):
+            obj = getattr(obj, part)
+        ours = [p for p in inspect.signature(obj).parameters.values() if p.kind == p.POSITIONAL_OR_KEYWORD]
+        assert [p.name for p in ours] == [n for n, _ in desc["positional"]], name
+        for p, (_, default) in zip(ours, desc["positional"]):
+            if default is None:
+                assert p.default is inspect.Parameter.empty, (name, p.name)
+            else:
+                assert repr(p.default) == default.replace('"', "'"), (name, p.name)
+        kw = {p.name: p for p in inspect.signature(obj).parameters.values() if p.kind == p.KEYWORD_ONLY}
+        for n, default in desc["keyword_only"]:   # e.g. run(..., *args, out=None, lse=None, return_lse=False)
+            assert n in kw and repr(kw[n].default) == default.replace('"', "'"), (name, n)
+        assert all(p.default is not inspect.Parameter.empty for p in kw.values()), name   # extensions are optional
+
+
 def test_cpu_tensors_are_rejected_not_silently_computed():
     x = torch.zeros(16, dtype=torch.bool)
     with pytest.raises(RuntimeError, match="CUDA"):
