@@ -30,6 +30,9 @@ SIGNATURES = {
     "fo_select_blocks": (c_int32, [_P, c_int32, c_int32, c_int32, c_int32, _P, _P, c_int32, _P, c_int64, _P, c_int64,
                                    _P, _P, _P, c_size_t, _P]),
     "fo_abi_version": (c_int32, []),
+    "fo_launch_count": (ctypes.c_longlong, []),
+    "fo_reduce_rows": (c_int32, [c_int32, _P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int64, c_int32, _P]),
+    "fo_peer_barrier": (c_int32, [c_int32, c_int32, _P, c_int32, c_int32, _P, _P, c_int64, _P]),
     "fo_packbits": (c_int32, [_P, c_int64, c_int32, _P, _P]),
     "fo_segment_packbits": (c_int32, [_P, _P, _P, c_int32, c_int64, c_int32, _P, _P]),
     "fo_mask_compact_scratch_bytes": (c_size_t, [c_int64, c_int32]),

@@ -3,6 +3,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <string>
 
 #include "../../include/flashomni_b200.h"
@@ -12,6 +13,8 @@ namespace fo {
 namespace {
 
 thread_local std::string g_last_error;
+std::atomic<long long> g_kernel_launches{0};  // kernels this library has launched (or recorded into a capture)
+inline void count_launches(int n) { g_kernel_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int fail(int code, const std::string& msg) {
   g_last_error = msg;
@@ -87,6 +90,7 @@ extern "C" {
 
 const char* fo_last_error(void) { return g_last_error.c_str(); }
 int fo_abi_version(void) { return FO_ABI_VERSION; }
+long long fo_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 // ------------------------------------------------------------------------------------------ packbits
 int fo_packbits(const uint8_t* x, int64_t n, int little, uint8_t* y, void* stream) {
@@ -94,6 +98,7 @@ int fo_packbits(const uint8_t* x, int64_t n, int little, uint8_t* y, void* strea
   if (n == 0) return FO_OK;
   if (x == nullptr || y == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_packbits: null pointer");
   const cudaError_t e = launch_packbits(x, n, little, y, static_cast<cudaStream_t>(stream));
+  count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_packbits", e);
 }
 
@@ -105,6 +110,7 @@ int fo_segment_packbits(const uint8_t* x, const int32_t* indptr, const int32_t* 
     return fail(FO_ERR_INVALID_ARG, "fo_segment_packbits: null pointer");
   const cudaError_t e = launch_segment_packbits(x, indptr, new_indptr, num_segments, out_bytes, little, y,
                                                 static_cast<cudaStream_t>(stream));
+  count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_segment_packbits", e);
 }
 
@@ -180,6 +186,7 @@ int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes, const
   p += (n * 8 + 15) & ~static_cast<size_t>(15);
   a.hist = reinterpret_cast<int32_t*>(p);
   const cudaError_t e = launch_attn_compact(a, static_cast<cudaStream_t>(stream));
+  count_launches(a.n_cand > 0 ? 3 : 0);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_mask_compact", e);
 }
 
@@ -247,6 +254,7 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   a.kv_idx = kv_idx;
   a.order = order;
   a.counters = counters;
+  a.max_items = static_cast<int>(max_items > 0x7fffffffLL ? 0x7fffffffLL : max_items);
   a.head_begin = head_begin;
   a.group_size = num_qo_heads / num_kv_heads;
   a.is_bf16 = dtype == FO_DTYPE_BF16;
@@ -261,6 +269,7 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   int64_t ctas = static_cast<int64_t>(sm_count());  // one persistent CTA per SM
   if (ctas > max_items) ctas = max_items;
   const cudaError_t e = launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
+  count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_sparse_attn_fwd", e);
 }
 }  // namespace
@@ -381,6 +390,7 @@ int fo_gemm_q_worklist(int32_t batch, int32_t m, int32_t n, int32_t num_heads, i
   GemmListArgs a = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
   a.is_full = is_full;
   const cudaError_t e = launch_gemm_q_tiles(a, static_cast<cudaStream_t>(stream));
+  count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_q_worklist", e);
 }
 
@@ -395,6 +405,7 @@ int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_heads, i
   GemmListArgs a = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
   a.is_for_cache = is_for_cache;
   const cudaError_t e = launch_gemm_o_rows(a, static_cast<cudaStream_t>(stream));
+  count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_o_worklist", e);
 }
 
@@ -434,7 +445,7 @@ int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t
   const GemmShape s = {batch, m, n, k, num_heads, head_begin, head_dim, sparse_q_size, num_text_tokens};
   int rc = check_lists_common("fo_gemm_q", s, !is_full && !prepared, sparse_info, sparse_info_indptr, workspace, workspace_bytes);
   if (rc != FO_OK) return rc;
-  if (k % 64 != 0) return fail(FO_ERR_UNSUPPORTED, "fo_gemm_q: k must be a multiple of 64");
+  if (k % 32 != 0) return fail(FO_ERR_INVALID_ARG, "fo_gemm_q: k must be a multiple of 32");
   if (128 % head_dim != 0 && head_dim % 128 != 0)
     return fail(FO_ERR_UNSUPPORTED, "fo_gemm_q: head_dim must divide or be a multiple of 128");
   if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (bias != nullptr && !aligned16(bias)))
@@ -451,6 +462,7 @@ int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t
     la.is_full = 0;
     e = prepared ? cudaMemsetAsync(wsw + 4, 0, 2 * sizeof(int32_t), st) : launch_gemm_q_tiles(la, st);
     if (e != cudaSuccess) return fail_cuda("fo_gemm_q (work list)", e);
+    count_launches(prepared ? 0 : 1);
     g.tiles = la.tiles;
     g.n_tiles_ptr = la.counters;
   } else {
@@ -480,6 +492,7 @@ int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t
   } else {
     e = launch_gemm(g, sm_count(), st);
   }
+  count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_gemm_q", e);
 }
 }  // namespace
@@ -526,6 +539,7 @@ int gemm_o_impl(const void* x, const void* w, void* y, const void* init, int32_t
   la.is_for_cache = is_for_cache;
   cudaError_t e = prepared ? cudaMemsetAsync(wsw + 4, 0, 2 * sizeof(int32_t), st) : launch_gemm_o_rows(la, st);
   if (e != cudaSuccess) return fail_cuda("fo_gemm_o (work list)", e);
+  count_launches(prepared ? 1 : 2);
   g.y = y;
   g.init = init;
   g.init_mode = init == nullptr ? kInitNone : (init_is_full ? kInitFull : kInitBias1D);
@@ -609,6 +623,7 @@ int32_t fo_select_blocks(const float* pooled_score, int32_t batch, int32_t num_h
   a.t2i = static_cast<float*>(scratch);
   a.q_keep = static_cast<uint8_t*>(scratch) + ((n * 4 + 15) & ~static_cast<size_t>(15));
   const cudaError_t e = launch_select_blocks(a, static_cast<cudaStream_t>(stream));
+  count_launches(3);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_select_blocks", e);
 }
 
@@ -640,7 +655,64 @@ int32_t fo_strided_gather(int32_t n_src, const void* const* src, const int64_t* 
     a.vec_prefix[i + 1] = a.vec_prefix[i] + n_rows[i] * a.row_vecs;
   }
   const cudaError_t e = launch_strided_gather(a, sm_count(), static_cast<cudaStream_t>(stream));
+  count_launches(a.vec_prefix[a.n_src] > 0 ? 1 : 0);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_strided_gather", e);
+}
+
+int32_t fo_reduce_rows(int32_t n_src, const void* const* src, int64_t src_row_stride_bytes, const void* init,
+                       int64_t init_row_stride_bytes, void* dst, int64_t dst_row_stride_bytes, int64_t n_rows,
+                       int64_t row_bytes, int32_t dtype, void* stream) {
+  if (n_src <= 0 || n_src > kMaxGatherSources) return fail(FO_ERR_INVALID_ARG, "fo_reduce_rows: between 1 and 16 sources");
+  if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_reduce_rows: bad dtype");
+  if (n_rows < 0 || row_bytes <= 0 || row_bytes % 16 != 0)
+    return fail(FO_ERR_INVALID_ARG, "fo_reduce_rows: row_bytes must be a positive multiple of 16");
+  if (n_rows == 0) return FO_OK;
+  if (src == nullptr || dst == nullptr || !aligned16(dst) || dst_row_stride_bytes % 16 != 0 ||
+      src_row_stride_bytes % 16 != 0 || dst_row_stride_bytes < row_bytes || src_row_stride_bytes < row_bytes ||
+      (init != nullptr && (!aligned16(init) || init_row_stride_bytes % 16 != 0 || init_row_stride_bytes < row_bytes)))
+    return fail(FO_ERR_INVALID_ARG, "fo_reduce_rows: pointers and strides must be 16-byte aligned, strides >= row_bytes");
+  ReduceArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int i = 0; i < n_src; ++i) {
+    if (src[i] == nullptr || !aligned16(src[i])) return fail(FO_ERR_INVALID_ARG, "fo_reduce_rows: null or misaligned source");
+    a.src[i] = static_cast<const uint8_t*>(src[i]);
+  }
+  a.init = static_cast<const uint8_t*>(init);
+  a.dst = static_cast<uint8_t*>(dst);
+  a.src_stride = src_row_stride_bytes;
+  a.init_stride = init_row_stride_bytes;
+  a.dst_stride = dst_row_stride_bytes;
+  a.rows = n_rows;
+  a.row_vecs = row_bytes / 16;
+  a.n_src = n_src;
+  const cudaError_t e = launch_reduce_rows(a, dtype == FO_DTYPE_BF16, sm_count(), static_cast<cudaStream_t>(stream));
+  count_launches(1);
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_reduce_rows", e);
+}
+
+int32_t fo_peer_barrier(int32_t world, int32_t rank, int32_t* const* pads, int32_t channel, int32_t num_channels,
+                        int32_t* epoch, int32_t* status, int64_t timeout_ms, void* stream) {
+  if (world <= 0 || world > kMaxBarrierRanks || rank < 0 || rank >= world)
+    return fail(FO_ERR_INVALID_ARG, "fo_peer_barrier: world must be 1..64 and rank inside it");
+  if (channel < 0 || channel >= num_channels) return fail(FO_ERR_INVALID_ARG, "fo_peer_barrier: channel out of range");
+  if (pads == nullptr || epoch == nullptr || status == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_peer_barrier: null pads / epoch / status");
+  if (timeout_ms <= 0 || timeout_ms > 60000) return fail(FO_ERR_INVALID_ARG, "fo_peer_barrier: timeout_ms must be 1..60000");
+  BarrierArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int i = 0; i < world; ++i) {
+    if (pads[i] == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_peer_barrier: null pad pointer");
+    a.pads[i] = pads[i];
+  }
+  a.epoch = epoch;
+  a.status = status;
+  a.rank = rank;
+  a.world = world;
+  a.channel = channel;
+  a.timeout_ns = static_cast<uint64_t>(timeout_ms) * 1000000ull;
+  const cudaError_t e = launch_peer_barrier(a, static_cast<cudaStream_t>(stream));
+  count_launches(1);
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_peer_barrier", e);
 }
 
 }  // extern "C"

@@ -87,28 +87,11 @@ struct Tail {
   float stats_l[2][4][128];  // [item parity][2 * group + half][row]: partial row sum
 };
 
-#ifdef FO_ATTN_TRACE
-// Development aid (only with -DFO_ATTN_TRACE): CTA 0 records the low 32 bits of clock64() at pipeline
-// events into shared memory (a global store before an mbarrier arrive would delay the arrive) and
-// copies the table out when it exits.
-constexpr int kTraceEvents = 18, kTraceSlots = 48;
-__device__ uint32_t g_trace[kTraceEvents * kTraceSlots];
-__device__ __forceinline__ void trace(uint32_t* tr, int ev, int idx) {
-  if (blockIdx.x == 0 && idx >= 0 && idx < kTraceSlots) tr[ev * kTraceSlots + idx] = static_cast<uint32_t>(clock64());
-}
-#define FO_TRACE(ev, idx) trace(trace_buf, ev, idx)
-#define FO_TRACE_TIME(ev, idx) do { if (blockIdx.x == 0) trace_buf[(ev) * kTraceSlots + (idx)] = static_cast<uint32_t>(global_timer_ns()); } while (0)
-constexpr int kTraceBytes = kTraceEvents * kTraceSlots * 4;
-#else
-#define FO_TRACE_TIME(ev, idx)
-#define FO_TRACE(ev, idx)
-constexpr int kTraceBytes = 0;
-#endif
 
 
 constexpr int kOutStageBytes = 16 * 64;  // per softmax warp: 16 rows x 32 output columns
 constexpr int kSmemBytes = (kQBufs + kRing) * kTileBytes + kSoftmaxWarps * kOutStageBytes + 1024 +
-                           static_cast<int>(sizeof(Tail)) + kTraceBytes;
+                           static_cast<int>(sizeof(Tail));
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 
 // The kept kv blocks of an item are visited in rotated order (the online softmax does not care):
@@ -286,9 +269,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   uint8_t* smem_ostage = smem + (kQBufs + kRing) * kTileBytes;  // output staging of the softmax warps
   Tail* tail = reinterpret_cast<Tail*>(smem_ostage + kSoftmaxWarps * kOutStageBytes);
   volatile int* abort_flag = &tail->abort_flag;
-#ifdef FO_ATTN_TRACE
-  uint32_t* trace_buf = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(tail) + ((sizeof(Tail) + 15) & ~size_t(15)));
-#endif
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -329,9 +309,12 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = tail->tmem_base;
 
-  if (threadIdx.x == 0) { FO_TRACE(11, 0); FO_TRACE_TIME(11, 1); }
+  // The list may be shorter than counters[0] says: a compaction that ran out of room records it in counters[2]
+  // and leaves records unwritten. Nothing of such a list is dereferenced; the launch only reports it.
+  const bool list_bad = a.counters[2] != kDevOk;
   int n_items = a.counters[0];
-  if (n_items < 0) n_items = 0;
+  if (list_bad || n_items < 0) n_items = 0;
+  if (n_items > a.max_items) n_items = a.max_items;
   auto ignore_empty = [](int, int, int) {};
 
   // The softmax warps take the registers that the producer / issuer warpgroup does not need.
@@ -365,7 +348,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         }
         const int slot = static_cast<int>(nk % kRingK);
         if (!mbar_wait(&tail->k_empty[slot], ((nk / kRingK) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-        FO_TRACE(12, static_cast<int>(nk));  // K slot free, load issued
         ++nk;
         uint8_t* dst = smem_ring + slot * kTileBytes;
         const int row = kv_row0 + seq.kvb * kBKV;
@@ -388,7 +370,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (seq.first()) kv_row0 = a.kv_indptr[seq.b];
         const int slot = static_cast<int>(nv % kRingV);
         if (!mbar_wait(&tail->v_empty[slot], ((nv / kRingV) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-        FO_TRACE(13, static_cast<int>(nv));  // V slot free, load issued
         ++nv;
         uint8_t* dst = smem_ring + (kRingK + slot) * kTileBytes;
         const int row = kv_row0 + seq.kvb * kBKV;
@@ -415,7 +396,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       uint32_t q_uses[kQBufs] = {0, 0};
       bool ok = true;
       while (ok && seq.next(a, ignore_empty)) {
-        FO_TRACE(17, static_cast<int>(g));  // QK: next block fetched
         const uint32_t sb = g & 1u;
         const int qb_i = seq.item_no & 1;
         // S[sb] is free once the softmax has copied block g-2 into registers
@@ -424,7 +404,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           if (!mbar_wait(&tail->q_full[qb_i], q_uses[qb_i] & 1u, abort_flag)) { ok = false; break; }
           ++q_uses[qb_i];
         }
-        FO_TRACE(15, static_cast<int>(g));  // QK: S buffer free seen
         const int slot = static_cast<int>(nk % kRingK);
         if (!mbar_wait(&tail->k_full[slot], (nk / kRingK) & 1u, abort_flag)) { ok = false; break; }
         ++nk;
@@ -439,13 +418,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           la[kk] = q_lo + off;
           lb[kk] = k_lo + off;
         }
-        FO_TRACE(8, static_cast<int>(g));  // QK: operands and S buffer ready
         umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
-        FO_TRACE(7, static_cast<int>(g));  // QK issued
         umma_commit(&tail->s_full[sb]);
         umma_commit(&tail->k_empty[slot]);
         if (seq.last()) umma_commit(&tail->q_empty[qb_i]);
-        FO_TRACE(16, static_cast<int>(g));  // QK: commits issued
         ++g;
       }
     }
@@ -467,7 +443,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (seq.first() && items_started > 0) {  // O must have been drained by the previous item's epilogue
           if (!mbar_wait(&tail->o_free, (items_started - 1u) & 1u, abort_flag)) { ok = false; break; }
         }
-        FO_TRACE(14, static_cast<int>(g));  // PV: P seen
         const int slot = static_cast<int>(nv % kRingV);
         if (!mbar_wait(&tail->v_full[slot], (nv / kRingV) & 1u, abort_flag)) { ok = false; break; }
         ++nv;
@@ -481,9 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           ta[kk] = tmem_p + static_cast<uint32_t>(kk * 8);
           lb[kk] = v_lo + static_cast<uint32_t>((kk * 2048) >> 4);
         }
-        FO_TRACE(9, static_cast<int>(g));  // PV: P and V ready
         umma_ts_x8(tmem_base + kColO, hi, idesc_pv, seq.first() ? 0u : 1u, ta, lb);
-        FO_TRACE(10, static_cast<int>(g));  // PV issued
         umma_commit(&tail->pv_done[sb]);
         umma_commit(&tail->v_empty[slot]);
         if (seq.last()) umma_commit(&tail->o_full);
@@ -510,8 +483,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     const int row = quad * 32 + lane;
     uint64_t* pair_bar = &tail->pair_bar[X][quad];
     uint32_t pair_phase = 0;
-    const bool tracer = (quad == 0 && ch == 0 && lane == 0);
-    (void)tracer;
     uint16_t* o16 = reinterpret_cast<uint16_t*>(a.o);
     bool ok = true;
 
@@ -631,7 +602,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         // ---- pass 1: the maximum of this thread's half row of S[X], 32 columns at a time (the values are
         // read again for the exponentials: holding them across the exchanges below would cost registers)
         if (!mbar_wait(&tail->s_full[X], my_blocks & 1u, abort_flag)) { ok = false; break; }
-        if (tracer) FO_TRACE(4, static_cast<int>(g));  // S ready seen by the group
         tc_fence_after_sync();
         const int valid = seq.valid() - static_cast<int>(64u * ch);  // of my columns, how many exist
         float mx;
@@ -656,7 +626,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           }
           mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
         }
-        if (tracer) FO_TRACE(0, static_cast<int>(g));  // half-row maximum known
         // ---- the two halves of a row exchange their maxima (the warps `warp` and `warp ^ 4`)
         tail->xmax[X][my_blocks & 1u][ch][row] = mx;
         __syncwarp();
@@ -678,7 +647,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (ch == 0u) tail->m_pub[X][row] = m_used;
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->m_ready[X]);
-        if (tracer) FO_TRACE(5, static_cast<int>(g));  // maximum published
         if (rescale) {
           // O is rescaled only after the PV of block g-1 has completed; that PV may be the first of
           // its item and wait for the previous item's epilogue, so this thread's share of it goes first
@@ -706,7 +674,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         }
         // P[X] was last read by the PV of this group's previous block
         if (my_blocks >= 1u && !mbar_wait(&tail->pv_done[X], (my_blocks - 1u) & 1u, abort_flag)) { ok = false; break; }
-        if (tracer) FO_TRACE(3, static_cast<int>(g));  // pv_done seen
         // ---- pass 2: P = exp2(S * scale - m_used), row sum, P (16 bit) to TMEM: one FMA and one add per
         // PAIR of columns
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
@@ -744,12 +711,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           }
           tmem_st_x16(tmem_p + 16u * c, pk);
         }
-        if (tracer) FO_TRACE(2, static_cast<int>(g));  // exponentials done
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->p_full[X]);
-        if (tracer) FO_TRACE(6, static_cast<int>(g));  // P handed over
         ++my_blocks;
         // the previous item's epilogue runs after this group's first block of the next item, so that
         // the item's last PV overlaps a softmax step (running it before the block, in the wait for S,
@@ -782,18 +747,13 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) { FO_TRACE(11, 2); FO_TRACE_TIME(11, 3); }
-#ifdef FO_ATTN_TRACE
-  __syncthreads();
-  if (blockIdx.x == 0)
-    for (int i = threadIdx.x; i < kTraceEvents * kTraceSlots; i += kThreads) g_trace[i] = trace_buf[i];
-#endif
   if (*abort_flag != 0) {
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     if (threadIdx.x == 0) atomicExch(a.status, kDevWaitTimeout);
     __syncthreads();
   }
+  if (list_bad && blockIdx.x == 0 && threadIdx.x == 0) atomicCAS(a.status, kDevOk, kDevBadIndex);
   if (warp == kWarpMma) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -810,11 +770,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 
 }  // namespace
 
-#ifdef FO_ATTN_TRACE
-extern "C" __attribute__((visibility("default"))) int fo_trace_dump(long long* host_dst) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host_dst, g_trace, sizeof(g_trace)));
-}
-#endif
 
 namespace {
 template <bool kBf16, bool kSoftCap>

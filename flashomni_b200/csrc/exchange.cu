@@ -4,6 +4,8 @@
 // into its own memory -- one kernel instead of a permute copy, a library all-to-all and a second permute.
 // Only loads cross the link; nothing here waits on another GPU (the callers order the steps with their
 // own barriers).
+#include <cuda_fp16.h>
+
 #include "internal.h"
 
 namespace fo {
@@ -34,7 +36,102 @@ __global__ void __launch_bounds__(256) strided_gather_kernel(const __grid_consta
   }
 }
 
+// out[r, :] = init[r, :] + sum over the sources of src_s[r, :] for the rows of one slice, 16-bit elements, fp32
+// accumulation, one rounding at the end. The sources are the partial results of several GPUs (peer pointers, read
+// with plain loads over NVLink); each GPU reduces the row slice it owns, so every partial crosses the link once.
+template <bool kBf16>
+__global__ void __launch_bounds__(256) reduce_rows_kernel(const __grid_constant__ ReduceArgs a) {
+  const int64_t total = a.rows * a.row_vecs;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / a.row_vecs, v = i % a.row_vecs;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    uint4 x[kMaxGatherSources];
+#pragma unroll
+    for (int s = 0; s < kMaxGatherSources; ++s)
+      if (s < a.n_src) x[s] = *reinterpret_cast<const uint4*>(a.src[s] + r * a.src_stride + v * 16);
+    uint4 in = make_uint4(0u, 0u, 0u, 0u);
+    if (a.init != nullptr) in = *reinterpret_cast<const uint4*>(a.init + r * a.init_stride + v * 16);
+    auto add = [&](const uint4& q) {
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (kBf16) {
+          acc[2 * j] += __uint_as_float(w[j] << 16);
+          acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+        } else {
+          const __half2 h2 = *reinterpret_cast<const __half2*>(&w[j]);
+          acc[2 * j] += __low2float(h2);
+          acc[2 * j + 1] += __high2float(h2);
+        }
+      }
+    };
+    if (a.init != nullptr) add(in);
+#pragma unroll
+    for (int s = 0; s < kMaxGatherSources; ++s)
+      if (s < a.n_src) add(x[s]);
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ow[j] = kBf16 ? pack_bf16x2(acc[2 * j], acc[2 * j + 1]) : pack_f16x2(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(a.dst + r * a.dst_stride + v * 16) = o;
+  }
+}
+
+// Barrier between the GPUs of a job, one launch per GPU (each on its own device): thread t tells rank t that
+// this rank has arrived (a release store of the new epoch into rank t's flag pad, over NVLink) and then waits
+// until rank t's arrival shows up in this rank's own pad. The epoch lives in this GPU's memory and advances by
+// one per launch, so a launch replayed from a CUDA graph still uses a fresh value. The wait is bounded: when it
+// runs out the launch records FO_DEV_WAIT_TIMEOUT in the status word and returns; nothing traps.
+__global__ void __launch_bounds__(64) peer_barrier_kernel(const __grid_constant__ BarrierArgs a) {
+  __shared__ int s_epoch;
+  const int t = threadIdx.x;
+  if (t == 0) {
+    s_epoch = a.epoch[a.channel] + 1;
+    a.epoch[a.channel] = s_epoch;
+  }
+  __syncthreads();
+  const int epoch = s_epoch;
+  if (t >= a.world) return;
+  __threadfence_system();
+  if (t != a.rank) {
+    int* remote = a.pads[t] + a.channel * a.world + a.rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const int* mine = a.pads[a.rank] + a.channel * a.world + t;
+    const uint64_t t0 = global_timer_ns();
+    while (true) {
+      int seen;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (seen - epoch >= 0) break;
+      if (global_timer_ns() - t0 > a.timeout_ns) {
+        atomicExch(a.status, kDevWaitTimeout);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __threadfence_system();
+}
+
 }  // namespace
+
+cudaError_t launch_reduce_rows(const ReduceArgs& a, int is_bf16, int sm_count, cudaStream_t stream) {
+  const int64_t total = a.rows * a.row_vecs;
+  if (total <= 0) return cudaSuccess;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count) * 8;
+  if (blocks > cap) blocks = cap;
+  if (is_bf16) reduce_rows_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(a);
+  else reduce_rows_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_barrier(const BarrierArgs& a, cudaStream_t stream) {
+  peer_barrier_kernel<<<1, 64, 0, stream>>>(a);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_strided_gather(const GatherArgs& a, int sm_count, cudaStream_t stream) {
   const int64_t total = a.vec_prefix[a.n_src];

@@ -51,20 +51,11 @@ struct Tail {
   int tile_q[kTileQ];
   uint32_t tmem_base;
   int abort_flag;
+  int epi_go;                   // outcome of the epilogue warps' vote of the current round
   int heads[2][kMaxHeadsSmem];  // GEMM-O: head lists of the current and the next tile, staged for the producer
 };
 constexpr int kSmemBytes = kStages * kStageBytes + kSlabBufs * kSlabBytes + 1024 + static_cast<int>(sizeof(Tail));
 
-#ifdef FO_GEMM_TRACE
-// Development aid (only with -DFO_GEMM_TRACE): CTA 0 records clock64() at pipeline events.
-__device__ long long g_gtrace[8][256];
-__device__ __forceinline__ void gtrace(int ev, int idx) {
-  if (blockIdx.x == 0 && idx >= 0 && idx < 256) g_gtrace[ev][idx] = clock64();
-}
-#define FO_GTRACE(ev, idx) gtrace(ev, idx)
-#else
-#define FO_GTRACE(ev, idx)
-#endif
 
 struct TileInfo {
   int a_row;             // first row of the A tile in [batch*m]
@@ -92,7 +83,7 @@ __device__ __forceinline__ TileInfo get_tile(const GemmArgs& a, int t) {
     ti.a_row = rec.x * a.m + rec.y * kBM;
     ti.w_row0 = rec.z * kBNH;
     ti.w_row1 = rec.w >= 0 ? rec.w * kBNH : -1;
-    ti.nkb = a.k / kBK;
+    ti.nkb = (a.k + kBK - 1) / kBK;  // a last partial K block reads zeros past k (TMA fill)
     ti.heads = nullptr;
     return ti;
   }
@@ -103,7 +94,7 @@ __device__ __forceinline__ TileInfo get_tile(const GemmArgs& a, int t) {
   ti.w_row1 = (2 * j + 1 < nct) ? (2 * j + 1) * kBNH : -1;
   if (a.mode == kGemmQ) {  // dense: row blocks in natural order
     ti.a_row = rr * kBM;
-    ti.nkb = a.k / kBK;
+    ti.nkb = (a.k + kBK - 1) / kBK;  // a last partial K block reads zeros past k (TMA fill)
     ti.heads = nullptr;
   } else {
     const int r = a.row_order[rr];
@@ -289,8 +280,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
       uint32_t acc_phase = 0;
       bool ok = true;
       // every operand tile is K-major with 128-byte swizzle: same descriptor high word, low word = address
-      int tile_no = 0;
-      (void)tile_no;
       const uint64_t desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
       const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32), desc_lo0 = static_cast<uint32_t>(desc0);
       TileInfo nxt;
@@ -307,7 +296,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         const uint32_t idesc = ti.w_row1 >= 0 ? idesc256 : idesc128;
         if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        FO_GTRACE(0, tile_no);  // MMA: accumulator available, main loop starts
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 2 * kBNH);
         for (int j = 0; j < ti.nkb; ++j) {
           if (!mbar_wait(&tail->full[stage], phase, abort_flag)) { ok = false; break; }
@@ -323,8 +311,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         }
         if (!ok) break;
         umma_commit(&tail->acc_full[acc]);
-        FO_GTRACE(1, tile_no);  // MMA: main loop issued
-        ++tile_no;
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -333,10 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     // ------------------------------------------------------------- epilogue warps 0..3
     int acc = 0;
     uint32_t acc_phase = 0;
-    bool ok = true;
     uint32_t slab_count = 0;  // slabs handed to TMA stores so far (selects the staging buffer)
-    int epi_no = 0;
-    (void)epi_no;
     const uint16_t* init16 = reinterpret_cast<const uint16_t*>(a.init);
     const int r_in_tile = warp * 32 + lane;
     const uint32_t swz = static_cast<uint32_t>(r_in_tile & 7);
@@ -350,12 +333,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     int k_seq = 0;
     int t_cur = read_slot_warp(0);
     if (t_cur >= 0) nxt = get_tile(a, t_cur);
-    for (; t_cur >= 0 && ok; ++k_seq) {
+    // The four warps leave this loop together: every round ends in a vote (two CTA-local barriers around one
+    // shared word), so a wait that ran out in one warp can never leave the others behind at `epi_bar`.
+    for (;; ++k_seq) {
       const TileInfo ti = nxt;
-      const int t_nxt = read_slot_warp(k_seq + 1);
-      if (t_nxt >= 0) nxt = get_tile(a, t_nxt);
-      if (t_nxt == -2) ok = false;
-      t_cur = t_nxt;
+      const int t_this = t_cur;
+      bool fail = t_this == -2;
+      if (t_this >= 0) {
+        const int t_nxt = read_slot_warp(k_seq + 1);
+        if (t_nxt >= 0) nxt = get_tile(a, t_nxt);
+        t_cur = t_nxt;
+      }
       const int64_t row = static_cast<int64_t>(ti.a_row) + r_in_tile;
       const int nslab = ti.w_row1 >= 0 ? 4 : 2;
       // init values of slab 0 are fetched before the accumulator is waited for
@@ -372,9 +360,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
           for (int i = 0; i < 8; ++i) initv[i] = __ldg(p + i);
         }
       };
-      load_init(0);
-      if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
-      if (threadIdx.x == 0) FO_GTRACE(2, epi_no);  // epilogue: accumulator full
+      if (t_this >= 0) {
+        load_init(0);
+        if (!mbar_wait_warp(&tail->acc_full[acc], acc_phase, abort_flag)) fail = true;
+      }
+      if (fail && lane == 0) *abort_flag = 1;
+      epi_bar();
+      if (threadIdx.x == 0) tail->epi_go = (*abort_flag == 0) ? 1 : 0;
+      epi_bar();
+      if (tail->epi_go == 0 || t_this < 0) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * 2 * kBNH);
 #pragma unroll 1
@@ -416,9 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         if (s + 1 < nslab) load_init(s + 1);  // next slab's init loads fly during the store hand-off
         // staging buffer of this slab must no longer be read by the store issued two slabs ago
         uint8_t* buf = smem_slab + (slab_count & 1u) * kSlabBytes;
-        if (threadIdx.x == 0 && s == 0) FO_GTRACE(3, epi_no);  // slab 0 converted
         if (threadIdx.x == 0) tma_store_wait_read<1>();
-        if (threadIdx.x == 0 && s == 0) FO_GTRACE(4, epi_no);  // staging buffer free
         epi_bar();
         uint8_t* rowp = buf + r_in_tile * 128;
 #pragma unroll
@@ -432,8 +424,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         }
         ++slab_count;
       }
-      if (threadIdx.x == 0) FO_GTRACE(5, epi_no);  // epilogue of the tile done
-      ++epi_no;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -459,11 +449,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
 }  // namespace
 
-#ifdef FO_GEMM_TRACE
-extern "C" __attribute__((visibility("default"))) int fo_gemm_trace_dump(long long* host_dst) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host_dst, g_gtrace, sizeof(g_gtrace)));
-}
-#endif
 
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream) {
   const int cap = a.batch * (a.m / kBM) * ((a.n / kBNH + 1) / 2);

@@ -44,12 +44,6 @@ struct Tail {
 constexpr int kStageWarpBytes = 16 * 128;          // store staging per epilogue warp
 constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kStageWarpBytes + 1024 + static_cast<int>(sizeof(Tail));
 
-#ifdef FO_GEMM_TRACE
-__device__ long long g_ttrace[8][64];
-#define FO_TTRACE(ev, idx) do { if (blockIdx.x == 0 && (idx) < 64) g_ttrace[ev][idx] = clock64(); } while (0)
-#else
-#define FO_TTRACE(ev, idx)
-#endif
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_constant__ GemmArgs a) {
@@ -130,10 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
       int stage = 0;
       uint32_t phase = 0, tile_phase = 0;
       bool ok = true;
-      int tno = -1;
-      (void)tno;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        ++tno;
         for (int j = 0; j < nkb; ++j) {
           if (!mbar_wait(&tail->full[stage], phase, abort_flag)) { ok = false; break; }
           if (j == 0) {  // the previous tile's half must have been read out of TMEM
@@ -144,11 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
           const uint32_t x = lo + static_cast<uint32_t>((half * kHalfBytes) >> 4), b = lo + (2 * kHalfBytes >> 4);
           const uint32_t la[4] = {x, x + 2u, x + 4u, x + 6u};
           const uint32_t lb[4] = {b, b + 2u, b + 4u, b + 6u};
-          if (j == 0) FO_TTRACE(half * 4 + 0, tno);
           umma_ss_x4(d_tmem, desc_hi, desc_hi, idesc, j != 0 ? 1u : 0u, la, lb);
-          if (j == 7) FO_TTRACE(half * 4 + 1, tno);
-          if (j == 39) FO_TTRACE(half * 4 + 2, tno);
-          if (j == nkb - 1) FO_TTRACE(half * 4 + 3, tno);
           umma_commit(&tail->empty[stage]);
           if (j == nkb - 1) umma_commit(&tail->acc_full[half]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -167,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       const int w_row = (t % col_tiles) * kBN;
-      if (!mbar_wait(&tail->acc_full[half], tile_phase, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&tail->acc_full[half], tile_phase, abort_flag)) { ok = false; break; }
       tile_phase ^= 1u;
       tc_fence_after_sync();
       // The accumulator is read out and rounded to 16 bits completely (128 registers per thread) before anything
@@ -255,11 +242,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
 
 }  // namespace
 
-#ifdef FO_GEMM_TRACE
-extern "C" __attribute__((visibility("default"))) int fo_gemm_tall_trace_dump(long long* host_dst) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host_dst, g_ttrace, sizeof(g_ttrace)));
-}
-#endif
 
 bool gemm_tall_applies(const GemmArgs& a, int sm_count) {
   const bool fits = a.mode == kGemmQ && a.tiles == nullptr && (a.init_mode == kInitNone || a.init_mode == kInitBias1D) &&

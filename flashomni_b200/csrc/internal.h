@@ -118,6 +118,26 @@ struct GatherArgs {
 };
 cudaError_t launch_strided_gather(const GatherArgs& a, int sm_count, cudaStream_t stream);
 
+struct ReduceArgs {
+  const uint8_t* src[kMaxGatherSources];   // partial results (peer pointers allowed), rows src_stride bytes apart
+  const uint8_t* init;                      // optional addend (local), rows init_stride bytes apart
+  uint8_t* dst;
+  int64_t src_stride, init_stride, dst_stride;
+  int64_t rows, row_vecs;                   // 16-byte vectors per row
+  int n_src;
+};
+cudaError_t launch_reduce_rows(const ReduceArgs& a, int is_bf16, int sm_count, cudaStream_t stream);
+
+constexpr int kMaxBarrierRanks = 64;
+struct BarrierArgs {
+  int* pads[kMaxBarrierRanks];   // every rank's flag pad as mapped into this process: int32 [channels][world]
+  int* epoch;                    // this GPU's own epoch counters: int32 [channels]
+  int* status;                   // device status word
+  int rank, world, channel;
+  uint64_t timeout_ns;
+};
+cudaError_t launch_peer_barrier(const BarrierArgs& a, cudaStream_t stream);
+
 // ------------------------------------------------------------------ attention
 struct AttnArgs {
   CUtensorMap tmap_q;              // [D, H, Tq]   box 64 x 1 x 128
@@ -134,7 +154,8 @@ struct AttnArgs {
   const int32_t* kv_ptr;
   const int32_t* kv_idx;
   const int32_t* order;
-  const int32_t* counters;         // counters[0] = n_items
+  const int32_t* counters;         // counters[0] = n_items, counters[2] = status of the compaction
+  int max_items;                   // capacity of items / kv_ptr / order as given to the compaction
   int head_begin;                  // tensor head = item head - head_begin
   int group_size;                  // H / Hkv
   int is_bf16;

@@ -141,6 +141,7 @@ struct Cand {
 };
 
 constexpr int kMaxBatchSmem = 1024;
+constexpr int64_t kCompactFineBuckets = 8192;  // groups * (max_nkv + 1) up to which items are ordered by length inside a group
 
 // Fills smem prefix of candidates per request. Thread 0 computes (B is small), all read after sync.
 __device__ __forceinline__ void build_cand_prefix(const CompactArgs& a, int64_t* s_prefix) {
@@ -218,7 +219,7 @@ __global__ void compact_count_kernel(CompactArgs a) {
 // inside a group, by a stable counting sort: W warps own contiguous candidate slices, each with its own
 // histogram in shared memory; bucket starts are (items of smaller keys) + (same bucket, earlier
 // slices); every warp then places its slice in ascending candidate order, 32 at a time.
-__global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int sort_warps) {
+__global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int sort_warps, int by_length) {
   extern __shared__ int s_whist[];  // [sort_warps + 1][batch * head_count]
   __shared__ int s_warp_items[32];
   __shared__ long long s_warp_kept[32];
@@ -280,7 +281,10 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
   }
   // ---- processing order: stable counting sort by (request, head), so that the CTAs that run at the same
   // time work on neighbouring q-blocks of the same few heads and share their K / V tiles in L2
-  const int nb = a.batch * a.head_count;
+  // With `by_length` the items of a group are ordered by descending list length (ties: q-blocks ascending):
+  // the items drawn last are then the short ones of each group and the launch ends without a long straggler.
+  const int per_group = by_length ? a.max_nkv + 1 : 1;
+  const int nb = a.batch * a.head_count * per_group;
   if (sort_warps <= 0) {  // too many (request, head) groups for the shared-memory histograms: canonical order
     for (int i = tid; i < n_items && i < a.max_items; i += blockDim.x) a.order[i] = i;
     return;
@@ -294,7 +298,11 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
       const int mid = (lo + hi) >> 1;
       if (s_prefix[mid] <= c) lo = mid; else hi = mid;
     }
-    return lo * a.head_count + static_cast<int>((c - s_prefix[lo]) % a.head_count);
+    const int grp = lo * a.head_count + static_cast<int>((c - s_prefix[lo]) % a.head_count);
+    if (!by_length) return grp;
+    int len = a.cnt[c];
+    len = len < 0 ? 0 : (len > a.max_nkv ? a.max_nkv : len);
+    return grp * per_group + (a.max_nkv - len);
   };
   const int64_t slice = ((a.n_cand + sort_warps - 1) / sort_warps + 31) / 32 * 32;
   const int64_t my0 = static_cast<int64_t>(warp) * slice;
@@ -424,7 +432,11 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
   if (blocks > 148 * 8) blocks = 148 * 8;
   // sort histograms: as many warps as fit in ~160 KB of shared memory, plus one row of bucket totals;
   // with more (request, head) groups than fit, the kernel leaves the items in canonical order
-  const int64_t nb = static_cast<int64_t>(a.batch) * a.head_count;
+  // order inside a (request, head) group: by descending list length while the finer histograms still leave
+  // room for at least four sorting warps (kCompactFineBuckets buckets), q-blocks ascending otherwise
+  const int64_t groups = static_cast<int64_t>(a.batch) * a.head_count;
+  const int by_length = groups * (a.max_nkv + 1) <= kCompactFineBuckets ? 1 : 0;
+  const int64_t nb = by_length ? groups * (a.max_nkv + 1) : groups;
   int64_t sort_warps = nb > 0 ? (160 * 1024) / (nb * 4) - 1 : 0;
   if (sort_warps > 32) sort_warps = 32;
   if (sort_warps < 1) sort_warps = 0;
@@ -434,7 +446,7 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
     if (ea != cudaSuccess) return ea;
   }
   compact_count_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(a);
-  compact_scan_kernel<<<1, 1024, scan_smem, stream>>>(a, static_cast<int>(sort_warps));
+  compact_scan_kernel<<<1, 1024, scan_smem, stream>>>(a, static_cast<int>(sort_warps), by_length);
   compact_fill_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(a);
   return cudaGetLastError();
 }

@@ -113,6 +113,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// The same for a whole warp that goes on to warp-collective instructions (tcgen05.ld, __syncwarp): lane 0
+// waits and the outcome is broadcast, so that a wait that runs out never leaves the lanes of a warp on
+// different sides of it. All 32 lanes must call it.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA tiled loads (no multicast anywhere in this library)
 // ---------------------------------------------------------------------------------------------

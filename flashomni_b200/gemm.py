@@ -18,7 +18,10 @@ _workspaces = {}
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    """The work-list / status / tile-cursor words of a call: one tensor per (device, current stream), so that calls
+    enqueued on different streams never share a cursor. Calls on one stream run in order and re-use it."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (device.type, index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
@@ -42,6 +45,7 @@ def _gemm_common(A: torch.Tensor, B: torch.Tensor, what: str):
     if not A.is_contiguous() or not B.is_contiguous():
         raise ValueError(f"{what}: A and B must be contiguous")
     # shape rule of the reference binding (csrc/gemm.cu:36): M % 128 == N % 128 == K % 32 == 0
+    # (GEMM-O further needs head_dim % 64 == 0, which every head size the reference builds satisfies)
     if A.shape[1] % 128 != 0 or B.shape[0] % 128 != 0 or A.shape[2] % 32 != 0:
         raise ValueError(f"{what}: M and N must be multiples of 128 and K of 32")
     _native.require_cuda(A, B)

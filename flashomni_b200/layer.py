@@ -30,10 +30,16 @@ class BlockWeights:
 class SparseDiTAttentionBlock:
     def __init__(self, weights: BlockWeights, num_heads: int, head_dim: int, batch: int, seq: int,
                  head_begin: int = 0, head_count: Optional[int] = None, device=None, dtype=torch.bfloat16,
-                 schedule: str = "q_first"):
+                 schedule: str = "q_first", add_cache: bool = True, fuse_kv: bool = True):
+        """`add_cache=False`: GEMM-O adds nothing to the active heads' sum (a rank of a head partition whose
+        partial is summed with the others' later; only one rank, or the sum itself, adds the cache).
+        `fuse_kv`: the dense K and V projections run as one GEMM over the stacked weights [W_k; W_v], writing
+        one [B, S, 2 * local heads * D] buffer that the attention reads through strided views."""
         if schedule not in ("q_first", "kv_first"):
             raise ValueError("schedule must be 'q_first' or 'kv_first'")
         self.schedule = schedule
+        self.add_cache = add_cache
+        self.fuse_kv = fuse_kv and schedule == "q_first"
         self._side = None
         self._q_list = self._o_list = None
         self.w = weights
@@ -47,8 +53,13 @@ class SparseDiTAttentionBlock:
         self.hidden = hidden
         mk = lambda *s: torch.zeros(*s, dtype=dtype, device=self.device)
         self.q = mk(batch, seq, n_local)      # doubles as the cached Q of earlier steps for inactive tiles
-        self.k = mk(batch, seq, n_local)
-        self.v = mk(batch, seq, n_local)
+        if self.fuse_kv:
+            self.wkv = torch.cat([weights.wk, weights.wv], dim=0).contiguous()
+            self.kv = mk(batch, seq, 2 * n_local)
+            self.k, self.v = self.kv[..., :n_local], self.kv[..., n_local:]
+        else:
+            self.k = mk(batch, seq, n_local)
+            self.v = mk(batch, seq, n_local)
         self.attn = mk(batch, seq, n_local)   # skipped q-blocks keep their previous contents
         self.y = mk(batch, seq, weights.wo.shape[0])
         self.cache = mk(batch, seq, weights.wo.shape[0])
@@ -82,12 +93,19 @@ class SparseDiTAttentionBlock:
         self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr)
         flashomni_gemm(x, self.w.wq, H, sparse_info, sparse_info_indptr, 0, None, out=self.q,
                        head_begin=hb, head_dim=D)
-        flashomni_gemm(x, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
-        flashomni_gemm(x, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
-        self.wrapper.run(self.q.view(T, self.hc, D), self.k.view(T, self.hc, D), self.v.view(T, self.hc, D),
+        if self.fuse_kv:
+            flashomni_gemm(x, self.wkv, H, is_full=True, out=self.kv, head_dim=D)
+            kv = self.kv.view(T, 2 * self.hc, D)
+            k, v = kv[:, :self.hc], kv[:, self.hc:]
+        else:
+            flashomni_gemm(x, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
+            flashomni_gemm(x, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
+            k, v = self.k.view(T, self.hc, D), self.v.view(T, self.hc, D)
+        self.wrapper.run(self.q.view(T, self.hc, D), k, v,
                          sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                          out=self.attn.view(T, self.hc, D))
-        flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0, self.cache,
+        flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0,
+                                 self.cache if self.add_cache else None,
                                  is_for_cache=False, head_begin=hb, head_dim=D, out=y)
         return y
 
@@ -119,7 +137,8 @@ class SparseDiTAttentionBlock:
         self.wrapper.run(self.q.view(T, self.hc, D), self.k.view(T, self.hc, D), self.v.view(T, self.hc, D),
                          sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                          out=self.attn.view(T, self.hc, D))
-        flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0, self.cache,
+        flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0,
+                                 self.cache if self.add_cache else None,
                                  is_for_cache=False, head_begin=hb, head_dim=D, out=y, worklist=self._o_list)
         return y
 
@@ -175,6 +194,13 @@ class UlyssesSparseDiTAttentionBlock:
         indptr = torch.tensor([0, num_tokens], dtype=torch.int32, device=device)
         self.wrapper.plan(indptr, indptr, self.hc, self.hc, head_dim, q_data_type=dtype, mask_num_heads=num_heads,
                           mask_head_begin=self.hb)
+
+    def check_status(self) -> None:
+        """Synchronises and raises if a kernel of the last steps recorded a device-side problem or a barrier gave up
+        waiting for a peer."""
+        self.wrapper.check_status()
+        if self.px is not None and self.px.available:
+            self.px.check_status()
 
     def forward(self, x_local, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr, marks=None):
         """x_local [1, local tokens, hidden] -> this rank's rows of the block output [1, local tokens, hidden].

@@ -3,12 +3,17 @@
 Two schemes, both new with respect to the reference (which has no distributed code at all):
 
 * head partition (`head_window`): rank r owns heads [r*H/P, (r+1)*H/P); nothing crosses GPUs inside the
-  block (flashomni_b200.layer.SparseDiTAttentionBlock takes the window).
+  block (flashomni_b200.layer.SparseDiTAttentionBlock takes the window). The ranks' partial outputs are
+  summed after the block by `PeerExchange.reduce_rows` (each rank sums the row slice it owns, reading the
+  peers' partials over NVLink), or by a library reduce-scatter where peer memory is not available.
 * Ulysses sequence parallelism for long sequences: tokens are sharded by whole 128-token blocks; the
-  projections run on local tokens for all heads; one all-to-all turns [local tokens, all heads] into
-  [all tokens, local heads] for the attention, and one turns the result back. The exchange is a plain
-  `torch.distributed.all_to_all_single` (NCCL over NVLink on GPUs, gloo in the CPU tests); data always
-  lands in the receiver's own memory before any kernel reads it.
+  projections run on local tokens for all heads; one exchange turns [local tokens, all heads] into
+  [all tokens, local heads] for the attention, and one turns the result back. `PeerExchange` does the
+  exchange with this library's own kernels over peer memory: the buffers live in symmetric memory, every
+  rank PULLS the slices it needs (`fo_strided_gather`, plain loads over NVLink, written in their final
+  layout) and the steps are ordered by `fo_peer_barrier` (bounded waits, an error status instead of a
+  trap). `tokens_to_heads` / `heads_to_tokens` keep the `torch.distributed.all_to_all_single` form of the
+  same exchange (NCCL on GPUs, gloo in the CPU tests) for where symmetric memory cannot be set up.
 """
 
 from __future__ import annotations
@@ -81,16 +86,20 @@ def heads_to_tokens(x: torch.Tensor, num_tokens: int, group=None) -> torch.Tenso
 
 
 class PeerExchange:
-    """The Ulysses exchange over peer memory instead of a library all-to-all: the buffers that other ranks
-    read live in symmetric memory (every rank maps every rank's copy), and each rank pulls the slices it needs
-    with one strided-gather kernel (C ABI `fo_strided_gather`: plain loads over NVLink, written in their final
-    layout). Steps are ordered by the symmetric-memory barrier (a device-side signal exchange of a few
-    microseconds on the current stream).
+    """The exchanges over peer memory instead of library collectives: the buffers that other ranks read live
+    in symmetric memory (every rank maps every rank's copy), each rank pulls (or sums) the slices it needs
+    with one kernel of this library (`fo_strided_gather`, `fo_reduce_rows`: plain loads over NVLink, results
+    written in their final layout), and the steps are ordered by `fo_peer_barrier`: a single-CTA kernel per
+    rank that posts this rank's arrival into every peer's flag pad and waits, for at most `timeout_ms`, for
+    theirs. A peer that never arrives leaves FO_DEV_WAIT_TIMEOUT in the status word (`check_status()` raises);
+    nothing traps and the CUDA context stays usable.
 
     `available` is False when symmetric memory cannot be set up (CPU tensors, a torch build without it, a
-    failed rendezvous); callers then keep the `all_to_all_single` path."""
+    failed rendezvous); callers then keep the `all_to_all_single` / reduce-scatter path."""
 
-    def __init__(self, group, device, timeout_ms: int = 10000):
+    CHANNELS = 4
+
+    def __init__(self, group, device, timeout_ms: int = 2000):
         self.group = group if group is not None else dist.group.WORLD
         self.device = torch.device(device)
         self.world = dist.get_world_size(group)
@@ -98,15 +107,22 @@ class PeerExchange:
         self.timeout_ms = timeout_ms
         self.available = False
         self._sm = None
-        self._bar = None
         if self.device.type != "cuda":
             return
         try:
+            import ctypes
             import torch.distributed._symmetric_memory as sm
             self._sm = sm
-            pad = sm.empty((256,), dtype=torch.int32, device=self.device)
-            self._bar = sm.rendezvous(pad, self.group)
-            self._pad = pad
+            pad = sm.empty((self.CHANNELS * self.world,), dtype=torch.int32, device=self.device)
+            pad.zero_()
+            hdl = sm.rendezvous(pad, self.group)
+            self._pad, self._pad_hdl = pad, hdl
+            self._pads = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+            self._epoch = torch.zeros(self.CHANNELS, dtype=torch.int32, device=self.device)
+            self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            # no rank may post an arrival before every pad has been zeroed
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
             self.available = True
         except Exception as e:  # noqa: BLE001 - any failure means "not available here"
             self.reason = f"{type(e).__name__}: {e}"
@@ -120,9 +136,35 @@ class PeerExchange:
         return t, [int(p) for p in hdl.buffer_ptrs], hdl
 
     def barrier(self, channel: int = 0):
-        """All ranks' work queued before this point on their current streams is complete when the current
-        stream passes it."""
-        self._bar.barrier(channel=channel, timeout_ms=self.timeout_ms)
+        """All ranks' work queued before this point on their current streams is complete (and visible to the
+        peers) when the current stream passes it. Ranks must use the channels in the same order."""
+        from . import _native
+        rc = _native.load().fo_peer_barrier(self.world, self.rank, self._pads, channel, self.CHANNELS,
+                                            self._epoch.data_ptr(), self._status.data_ptr(), self.timeout_ms,
+                                            torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(rc, "fo_peer_barrier")
+
+    def check_status(self) -> None:
+        """Synchronises and raises if a barrier gave up waiting for a peer."""
+        if int(self._status[0].item()) != 0:
+            raise RuntimeError("flashomni_b200: a peer barrier timed out (a rank did not arrive)")
+
+    def reduce_rows(self, peer_ptrs, row0: int, n_rows: int, row_elems: int, dtype, out: torch.Tensor,
+                    init: torch.Tensor | None = None):
+        """out[:n_rows] = init[:n_rows] + sum over ranks of their partial rows [row0, row0 + n_rows):
+        `peer_ptrs[r]` is rank r's partial [rows, row_elems] in symmetric memory; fp32 accumulation."""
+        import ctypes
+        from . import _native
+        from .utils import native_dtype
+        isz = 2
+        row_bytes = row_elems * isz
+        n = len(peer_ptrs)
+        srcs = (ctypes.c_void_p * n)(*[p + row0 * row_bytes for p in peer_ptrs])
+        rc = _native.load().fo_reduce_rows(n, srcs, row_bytes, None if init is None else init.data_ptr(),
+                                           0 if init is None else init.stride(0) * isz, out.data_ptr(),
+                                           out.stride(0) * isz, n_rows, row_bytes, native_dtype(dtype),
+                                           torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(rc, "fo_reduce_rows")
 
     @staticmethod
     def gather(srcs, src_strides, n_rows, dsts, dst_strides, row_bytes: int):

@@ -51,6 +51,9 @@ enum { FO_DEV_OK = 0, FO_DEV_WAIT_TIMEOUT = 1, FO_DEV_BAD_INDEX = 2 };
 /* Thread-local description of the last error returned on this thread ("" if none). */
 FO_API const char* fo_last_error(void);
 FO_API int fo_abi_version(void);
+/* Number of kernels this library has launched (or recorded into a stream capture) in this process so far.
+ * Host-side bookkeeping for benchmarks that report their launch counts; no device call. */
+FO_API long long fo_launch_count(void);
 
 /* ---- mask packing -------------------------------------------------------------------------
  * Replaces torch.ops.flashomni_kernels.packbits / segment_packbits (csrc/flashomni_ops.cu:46-51,
@@ -68,7 +71,9 @@ FO_API int fo_segment_packbits(const uint8_t* x, const int32_t* indptr, const in
  *   items   int32 [max_items,4]  (b, h, qb, n_kept) of every active q-block, ascending (b, qb, h)
  *   kv_ptr  int32 [max_items+1]  offsets into kv_idx
  *   kv_idx  int32 [max_kept]     ascending kept kv-block indices per item
- *   order   int32 [max_items]    the processing order: item indices grouped by (b, h), q-blocks ascending
+ *   order   int32 [max_items]    the processing order: item indices grouped by (b, h); inside a group by
+ *                                descending n_kept (ties: q-blocks ascending) while
+ *                                batch * head_count * (max_nkv + 1) <= 8192, else q-blocks ascending
  *                                (the identity when batch * head_count > 20480)
  *   counters int32 [4]           n_items, total_kept, status (FO_DEV_*), max_nkv
  * n_cand = sum over requests of ceil(qo_len/sbq)*head_count and max_nkv = max ceil(kv_len/sbkv) are
@@ -90,8 +95,10 @@ FO_API int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes
  * with element strides (row, head); the innermost dimension is contiguous. lse (optional, may be
  * null): float32 [total_q, Hq], base 2. Hq here is the number of heads IN THE TENSORS; item head
  * indices are mask heads and map to tensor head (h - head_begin). q-blocks that are not listed are
- * not written. status: FOUR int32 device words that the caller zeroes once: [0] is set to
- * FO_DEV_WAIT_TIMEOUT if a bounded wait ran out; [1] (work-list cursor: items are handed to the CTAs
+ * not written. max_items is the capacity the lists were compacted with: the kernel walks
+ * min(counters[0], max_items) items, and none at all when counters[2] says that the compaction ran out of
+ * room (the output is then untouched and status[0] = FO_DEV_BAD_INDEX). status: FOUR int32 device words
+ * that the caller zeroes once: [0] is set to FO_DEV_WAIT_TIMEOUT if a bounded wait ran out; [1] (work-list cursor: items are handed to the CTAs
  * dynamically) and [2] (count of finished CTAs) are used by the kernel and are zero again when it ends, so
  * launches that share the words must not overlap; [3] is reserved.
  * This build implements D = 128 with 128-row q and kv blocks. */
@@ -136,7 +143,8 @@ FO_API int fo_gemm_dense_tile_rows(int32_t batch, int32_t m, int32_t n, int32_t 
  * contiguous; bias [n] or null. Output tile (iy, ix) of batch b is computed iff is_full or bit
  * ((num_text_tokens + iy*128)/sparse_q_size)*num_heads + head_begin + (ix*128)/head_dim of b's
  * segment is 1; other tiles of y are left untouched. head_dim = n/num_heads in the reference
- * (pass that, with head_begin = 0, for the reference behaviour). m, n multiples of 128; k of 64. */
+ * (pass that, with head_begin = 0, for the reference behaviour). m, n multiples of 128; k of 32 (the
+ * reference's rule, csrc/gemm.cu:36). */
 FO_API int fo_gemm_q(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch,
               int32_t m, int32_t n, int32_t k, int32_t num_heads, int32_t head_begin, int32_t head_dim,
               int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full, const uint8_t* sparse_info,
@@ -219,6 +227,31 @@ FO_API int32_t fo_select_blocks(const float* pooled_score, int32_t batch, int32_
 FO_API int32_t fo_strided_gather(int32_t n_src, const void* const* src, const int64_t* src_row_stride_bytes,
                                  const int64_t* n_rows, void* const* dst, const int64_t* dst_row_stride_bytes,
                                  int64_t row_bytes, void* stream);
+
+/* ---- sum of partial results held by several GPUs ------------------------------------------------
+ * No counterpart in the reference (it has no multi-GPU code). dst[r, :] = init[r, :] + sum_i src[i][r, :] for
+ * n_rows rows of row_bytes bytes of 16-bit elements (fp32 accumulation, one rounding). The sources are the
+ * partial outputs of a head-partitioned GEMM-O, one per GPU, all with the same row stride; a source may be a
+ * peer pointer (plain loads over NVLink). Each GPU calls this for the row slice it owns (pass pointers that
+ * already point at that slice), so the partials are summed where the result is wanted and each crosses the
+ * link once. init may be null. Ordering against the producers on other GPUs is the caller's business
+ * (fo_peer_barrier). Pointers, strides and row_bytes must be multiples of 16; at most 16 sources. */
+FO_API int32_t fo_reduce_rows(int32_t n_src, const void* const* src, int64_t src_row_stride_bytes, const void* init,
+                              int64_t init_row_stride_bytes, void* dst, int64_t dst_row_stride_bytes,
+                              int64_t n_rows, int64_t row_bytes, int32_t dtype, void* stream);
+
+/* ---- barrier between the GPUs of one job ---------------------------------------------------------
+ * No counterpart in the reference. One launch per GPU, each on its own device and stream; the launch ends when
+ * every rank's launch of the same (channel, epoch) has started, i.e. when everything each rank had enqueued
+ * before its call is complete and visible to the others. pads[r] (host array of `world` device pointers) is
+ * rank r's flag pad, int32 [num_channels][world], zeroed once before the first use and mapped into this
+ * process (peer memory); epoch is this GPU's own int32 [num_channels] counter array, zeroed once; the kernel
+ * advances it, so a launch replayed from a CUDA graph works. Ranks must call the channels in the same order.
+ * The wait is bounded by timeout_ms: when a peer does not arrive the launch writes FO_DEV_WAIT_TIMEOUT to
+ * *status (device word) and returns instead of trapping; the host reads the word before trusting the step. */
+FO_API int32_t fo_peer_barrier(int32_t world, int32_t rank, int32_t* const* pads, int32_t channel,
+                               int32_t num_channels, int32_t* epoch, int32_t* status, int64_t timeout_ms,
+                               void* stream);
 
 /* ---- GEMM-Q without a caller workspace ------------------------------------------------------------
  * No counterpart in the reference. Same arguments and result as fo_gemm_q minus the workspace: the

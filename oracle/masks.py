@@ -100,10 +100,12 @@ def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr,
                                ascending in (b, qb, h)
       kv_indptr  int32 [n+1]   offsets of each item's kept list inside kv_idx
       kv_idx     int32 [total] ascending kept kv-block indices of each item
-      order      int32 [n]     the processing permutation: item indices grouped by (b, h) ascending, q-blocks
-                               ascending inside a group (CTAs that run at the same time then share K / V
-                               tiles in L2); the identity when batch * head_count > 20480 (more groups
-                               than the kernel's histograms hold)
+      order      int32 [n]     the processing permutation: item indices grouped by (b, h) ascending (CTAs that
+                               run at the same time then share K / V tiles in L2); inside a group by
+                               descending list length, ties by ascending q-block, while
+                               batch * head_count * (max_nkv + 1) <= 8192 (the items drawn last are then
+                               short ones), else by ascending q-block; the identity when
+                               batch * head_count > 20480 (more groups than the kernel's histograms hold)
     With `is_full` every q-block is active and every kv-block kept (prefill.cuh:1284,1383,1434).
     """
     if head_count is None:
@@ -130,8 +132,11 @@ def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr,
                     kv_idx.extend(int(v) for v in kept)
                     kv_ptr.append(len(kv_idx))
     items_a = np.asarray(items, dtype=np.int32).reshape(-1, 4)
+    max_nkv = max([int(-(-(kv[b + 1] - kv[b]) // sbkv)) for b in range(B)], default=0)
     if len(items) and B * head_count <= 20480:
         key = items_a[:, 0].astype(np.int64) * head_count + (items_a[:, 1].astype(np.int64) - head_begin)
+        if B * head_count * (max_nkv + 1) <= 8192:
+            key = key * (max_nkv + 1) + (max_nkv - items_a[:, 3].astype(np.int64))
         order = np.argsort(key, kind="stable").astype(np.int32)
     else:
         order = np.arange(len(items), dtype=np.int32)

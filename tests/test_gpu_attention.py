@@ -305,3 +305,46 @@ def test_grouped_query_attention(cuda_device):
     w.check_status()
     ref = oa.sparse_attention(q, k, v, [0, S], [0, S], m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr)
     assert_close_bf16(o.cpu(), ref, "gqa")
+
+
+def test_undersized_kept_list_is_reported_not_walked(cuda_device):
+    """A C-ABI caller that compacts with a kv_idx capacity below the kept count: the compaction records it, and
+    the attention launch that follows touches neither the lists nor the output and reports FO_DEV_BAD_INDEX."""
+    from flashomni_b200 import _native
+    H, S = 2, 512
+    inp = wl.attention_inputs(1, H, S, 128, 1.0, seed=77)
+    w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, H)
+    lib = _native.load()
+    si, skv, ip, kp = masks_to_device(inp.masks, cuda_device)
+    ws = w._ws
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    small = 3   # 2 heads x 4 q-blocks x 4 kept blocks = 32 entries are needed
+    rc = lib.fo_mask_compact(_native.ptr(si), si.numel(), _native.ptr(skv), skv.numel(), _native.ptr(ip), _native.ptr(kp),
+                             _native.ptr(w._qo_indptr_buf), _native.ptr(w._kv_indptr_buf), 1, H, 0, H, 128, 128, 0,
+                             w._n_cand, w._max_nkv, w._n_cand, small, _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]),
+                             _native.ptr(ws["kv_idx"]), _native.ptr(ws["order"]), _native.ptr(ws["counters"]),
+                             _native.ptr(ws["scratch"]), w._scratch_bytes, stream)
+    _native.check(rc, "fo_mask_compact")
+    q, k, v = (dev(t, cuda_device) for t in (inp.q, inp.k, inp.v))
+    prior = dev(wl.randn_bf16(inp.q.shape, 5), cuda_device)
+    out = prior.clone()
+    rc = lib.fo_sparse_attn_fwd(_native.ptr(q), _native.ptr(k), _native.ptr(v), _native.ptr(out), None, _native.FO_DTYPE_BF16,
+                                S, S, H, H, 128, q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
+                                out.stride(0), out.stride(1), _native.ptr(w._qo_indptr_buf), _native.ptr(w._kv_indptr_buf),
+                                128, 128, _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
+                                _native.ptr(ws["order"]), _native.ptr(ws["counters"]), w._n_cand, 0, 128 ** -0.5,
+                                _native.ptr(ws["status"]), stream)
+    _native.check(rc, "fo_sparse_attn_fwd")
+    torch.cuda.synchronize()
+    words = w._ws_words[:8].cpu().tolist()
+    assert words[2] == _native.FO_DEV_BAD_INDEX          # the compaction's own status
+    assert words[4] == _native.FO_DEV_BAD_INDEX          # the attention launch's status word
+    assert words[5] == 0 and words[6] == 0               # cursor and arrival count are back at zero
+    assert torch.equal(out, prior)
+    # the same wrapper is usable again once the lists fit
+    w._ws_words[4:8].zero_()
+    o = w.run(q, k, v, si, skv, ip, kp)
+    w.check_status()
+    ref = oa.sparse_attention(inp.q, inp.k, inp.v, [0, S], [0, S], inp.masks.sparse_info, inp.masks.sparse_kv_info,
+                              inp.masks.info_indptr, inp.masks.kv_info_indptr)
+    assert_close_bf16(o, ref, "attention after an undersized list")

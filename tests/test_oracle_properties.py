@@ -43,9 +43,10 @@ def test_compaction_lists_cover_the_masks_exactly(case):
         kept = np.nonzero(kk[b][qb, h])[0]
         assert n == len(kept) and np.array_equal(idx[ptr[i]:ptr[i + 1]], kept)
     assert ptr[-1] == len(idx) == sum(int(kk[b][qb, h].sum()) for b, h, qb in want)
-    # the processing order is a permutation, grouped by (b, h) ascending with q-blocks ascending inside a group
+    # the processing order is a permutation, grouped by (b, h) ascending; inside a group the longest lists come
+    # first (these small cases are all below the bucket limit), ties by ascending q-block
     assert sorted(order.tolist()) == list(range(len(items)))
-    keys = [(items[i][0], items[i][1], items[i][2]) for i in order.tolist()]
+    keys = [(items[i][0], items[i][1], -items[i][3], items[i][2]) for i in order.tolist()]
     assert keys == sorted(keys)
 
 
