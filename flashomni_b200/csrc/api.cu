@@ -233,9 +233,8 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
     int r = encode_tmap_16bit(&a.tmap_q, q, 3, qd, qs, box);
     if (r == 0) r = encode_tmap_16bit(&a.tmap_k, k, 3, kd, ks, box);
     if (r == 0) r = encode_tmap_16bit(&a.tmap_v, v, 3, kd, vs, box);
-    const uint32_t obox[3] = {32, 1, 16};
     const uint64_t os[3] = {0, static_cast<uint64_t>(o_stride_h) * 2, static_cast<uint64_t>(o_stride_n) * 2};
-    if (r == 0) r = encode_tmap_16bit(&a.tmap_o, o, 3, qd, os, obox, false);
+    if (r == 0) r = encode_tmap_16bit(&a.tmap_o, o, 3, qd, os, box);  // stores of 64 columns x 128 rows
     if (r != 0) {
       char buf[96];
       snprintf(buf, sizeof(buf), "fo_sparse_attn_fwd: cuTensorMapEncodeTiled failed (%d)", r);

@@ -143,7 +143,7 @@ struct AttnArgs {
   CUtensorMap tmap_q;              // [D, H, Tq]   box 64 x 1 x 128
   CUtensorMap tmap_k;              // [D, Hkv, Tkv]
   CUtensorMap tmap_v;
-  CUtensorMap tmap_o;              // [D, Hq, Tq]   box 32 x 1 x 16, no swizzle (stores of whole q-blocks)
+  CUtensorMap tmap_o;              // [D, Hq, Tq]   box 64 x 1 x 128, 128B swizzle (stores of whole q-blocks)
   void* o;                         // [Tq, H, D] (strides below, in elements)
   float* lse;                      // [Tq, H] or null
   int64_t o_stride_n, o_stride_h;

@@ -141,6 +141,7 @@ struct Cand {
 };
 
 constexpr int kMaxBatchSmem = 1024;
+constexpr int64_t kCompactL2Bytes = 48ll << 20;   // K + V bytes of the heads of one group (a share of the 126 MB L2)
 constexpr int64_t kCompactFineBuckets = 8192;  // groups * (max_nkv + 1) up to which items are ordered by length inside a group
 
 // Fills smem prefix of candidates per request. Thread 0 computes (B is small), all read after sync.
@@ -219,7 +220,7 @@ __global__ void compact_count_kernel(CompactArgs a) {
 // inside a group, by a stable counting sort: W warps own contiguous candidate slices, each with its own
 // histogram in shared memory; bucket starts are (items of smaller keys) + (same bucket, earlier
 // slices); every warp then places its slice in ascending candidate order, 32 at a time.
-__global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int sort_warps, int by_length) {
+__global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int sort_warps, int by_length, int heads_per_group) {
   extern __shared__ int s_whist[];  // [sort_warps + 1][batch * head_count]
   __shared__ int s_warp_items[32];
   __shared__ long long s_warp_kept[32];
@@ -279,12 +280,14 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
     a.counters[3] = a.max_nkv;
     a.kv_ptr[n_items <= a.max_items ? n_items : 0] = static_cast<int>(total_kept);
   }
-  // ---- processing order: stable counting sort by (request, head), so that the CTAs that run at the same
-  // time work on neighbouring q-blocks of the same few heads and share their K / V tiles in L2
-  // With `by_length` the items of a group are ordered by descending list length (ties: q-blocks ascending):
-  // the items drawn last are then the short ones of each group and the launch ends without a long straggler.
+  // ---- processing order: stable counting sort by (request, group of heads), so that the CTAs that run at the
+  // same time work on the same few heads and share their K / V tiles in L2. A group is `heads_per_group`
+  // consecutive heads: as many as keep their K and V in L2 together (launch_attn_compact).
+  // With `by_length` the items of a group are ordered by descending list length (ties: canonical order):
+  // the items drawn last are then the short ones of the group and the launch ends without a long straggler.
   const int per_group = by_length ? a.max_nkv + 1 : 1;
-  const int nb = a.batch * a.head_count * per_group;
+  const int grp_per_req = (a.head_count + heads_per_group - 1) / heads_per_group;
+  const int nb = a.batch * grp_per_req * per_group;
   if (sort_warps <= 0) {  // too many (request, head) groups for the shared-memory histograms: canonical order
     for (int i = tid; i < n_items && i < a.max_items; i += blockDim.x) a.order[i] = i;
     return;
@@ -298,7 +301,7 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
       const int mid = (lo + hi) >> 1;
       if (s_prefix[mid] <= c) lo = mid; else hi = mid;
     }
-    const int grp = lo * a.head_count + static_cast<int>((c - s_prefix[lo]) % a.head_count);
+    const int grp = lo * grp_per_req + static_cast<int>((c - s_prefix[lo]) % a.head_count) / heads_per_group;
     if (!by_length) return grp;
     int len = a.cnt[c];
     len = len < 0 ? 0 : (len > a.max_nkv ? a.max_nkv : len);
@@ -430,12 +433,19 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
   const int threads = 256, wpb = threads / 32;
   int64_t blocks = (a.n_cand + wpb - 1) / wpb;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  // sort histograms: as many warps as fit in ~160 KB of shared memory, plus one row of bucket totals;
-  // with more (request, head) groups than fit, the kernel leaves the items in canonical order
-  // order inside a (request, head) group: by descending list length while the finer histograms still leave
-  // room for at least four sorting warps (kCompactFineBuckets buckets), q-blocks ascending otherwise
-  const int64_t groups = static_cast<int64_t>(a.batch) * a.head_count;
-  const int by_length = groups * (a.max_nkv + 1) <= kCompactFineBuckets ? 1 : 0;
+  // Groups of heads: as many consecutive heads as keep their K and V tiles in L2 together (kCompactL2Bytes for
+  // 128-row x 128-column 16-bit blocks, max_nkv of them per head and tensor), evenly sized. Inside a group the
+  // items are ordered by descending list length while the histograms (groups x lengths) stay below
+  // kCompactFineBuckets; otherwise the groups are single heads with their q-blocks ascending.
+  // Sort histograms: as many warps as fit in ~160 KB of shared memory, plus one row of bucket totals; with more
+  // groups than fit, the kernel leaves the items in canonical order.
+  int64_t hpg = kCompactL2Bytes / (static_cast<int64_t>(a.max_nkv > 0 ? a.max_nkv : 1) * 65536);
+  hpg = hpg < 1 ? 1 : (hpg > a.head_count ? a.head_count : hpg);
+  const int64_t grp_per_req = (a.head_count + hpg - 1) / hpg;
+  hpg = (a.head_count + grp_per_req - 1) / grp_per_req;
+  int by_length = static_cast<int64_t>(a.batch) * grp_per_req * (a.max_nkv + 1) <= kCompactFineBuckets ? 1 : 0;
+  if (!by_length) hpg = 1;
+  const int64_t groups = static_cast<int64_t>(a.batch) * ((a.head_count + hpg - 1) / hpg);
   const int64_t nb = by_length ? groups * (a.max_nkv + 1) : groups;
   int64_t sort_warps = nb > 0 ? (160 * 1024) / (nb * 4) - 1 : 0;
   if (sort_warps > 32) sort_warps = 32;
@@ -446,7 +456,7 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
     if (ea != cudaSuccess) return ea;
   }
   compact_count_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(a);
-  compact_scan_kernel<<<1, 1024, scan_smem, stream>>>(a, static_cast<int>(sort_warps), by_length);
+  compact_scan_kernel<<<1, 1024, scan_smem, stream>>>(a, static_cast<int>(sort_warps), by_length, static_cast<int>(hpg));
   compact_fill_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(a);
   return cudaGetLastError();
 }

@@ -113,6 +113,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Bounded wait that polls instead of parking: for the one thread whose wake-up time is on the critical path of a
+// pipeline (an MMA issuer waiting for its operand). The clock and the abort flag are looked at every 64 polls.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t n = 0;; ++n) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((n & 63u) == 63u) {
+      if (*abort_flag != 0) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // The same for a whole warp that goes on to warp-collective instructions (tcgen05.ld, __syncwarp): lane 0
 // waits and the outcome is broadcast, so that a wait that runs out never leaves the lanes of a warp on
 // different sides of it. All 32 lanes must call it.
@@ -325,7 +343,7 @@ __device__ __forceinline__ void umma_ss_x8(uint32_t d_tmem, uint32_t a_hi, uint3
 }
 // 4 x (D[tmem] (+)= A[smem] * B[smem])
 __device__ __forceinline__ void umma_ss_x4(uint32_t d_tmem, uint32_t a_hi, uint32_t b_hi, uint32_t idesc,
-                                           uint32_t acc_first, const uint32_t (&la)[4], const uint32_t (&lb)[4]) {
+                                           uint32_t acc_first, const uint32_t* la, const uint32_t* lb) {
   asm volatile(
       "{\n"
       ".reg .pred p0, p1;\n"
@@ -353,6 +371,22 @@ __device__ __forceinline__ void umma_ts_x8(uint32_t d_tmem, uint32_t b_hi, uint3
       "r"(b_hi), "r"(idesc), "r"(acc_first), "r"(ta[0]), "r"(ta[1]), "r"(ta[2]), "r"(ta[3]), "r"(ta[4]), "r"(ta[5]),
       "r"(ta[6]), "r"(ta[7]), "r"(lb[0]), "r"(lb[1]), "r"(lb[2]), "r"(lb[3]), "r"(lb[4]), "r"(lb[5]), "r"(lb[6]),
       "r"(lb[7])
+      : "memory");
+}
+
+// 4 x (D[tmem] (+)= A[tmem] * B[smem]); A advances by ta[i] columns.
+__device__ __forceinline__ void umma_ts_x4(uint32_t d_tmem, uint32_t b_hi, uint32_t idesc, uint32_t acc_first,
+                                           const uint32_t* ta, const uint32_t* lb) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, p1;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p0, %3, 0;\n"
+      "setp.eq.b32 p1, 0, 0;\n"
+      FO_MMA_TS("%4", "%8", "p0") FO_MMA_TS("%5", "%9", "p1") FO_MMA_TS("%6", "%10", "p1") FO_MMA_TS("%7", "%11", "p1")
+      "}\n" ::"r"(d_tmem),
+      "r"(b_hi), "r"(idesc), "r"(acc_first), "r"(ta[0]), "r"(ta[1]), "r"(ta[2]), "r"(ta[3]), "r"(lb[0]), "r"(lb[1]),
+      "r"(lb[2]), "r"(lb[3])
       : "memory");
 }
 

@@ -77,7 +77,10 @@ def flashomni_gemm(
     batch, M, K = A.shape
     N = B.shape[0]
     if out is None:
-        out = torch.empty((batch, M, N), device=A.device, dtype=A.dtype)
+        # the reference allocates with torch.empty (flashomni/gemm.py:168-173) and leaves the inactive tiles
+        # uninitialised; zeros are one such value, and make its own script's comparison with the masked dense
+        # result (benchmark/test_flashomni_gemm_q.py:78-89) well defined
+        out = torch.zeros((batch, M, N), device=A.device, dtype=A.dtype)
     elif tuple(out.shape) != (batch, M, N) or out.dtype != A.dtype or not out.is_contiguous():
         raise ValueError("flashomni_gemm: out must be a contiguous [batch, M, N] tensor of A's dtype")
     if head_dim is None:

@@ -71,10 +71,11 @@ FO_API int fo_segment_packbits(const uint8_t* x, const int32_t* indptr, const in
  *   items   int32 [max_items,4]  (b, h, qb, n_kept) of every active q-block, ascending (b, qb, h)
  *   kv_ptr  int32 [max_items+1]  offsets into kv_idx
  *   kv_idx  int32 [max_kept]     ascending kept kv-block indices per item
- *   order   int32 [max_items]    the processing order: item indices grouped by (b, h); inside a group by
- *                                descending n_kept (ties: q-blocks ascending) while
- *                                batch * head_count * (max_nkv + 1) <= 8192, else q-blocks ascending
- *                                (the identity when batch * head_count > 20480)
+ *   order   int32 [max_items]    the processing order: item indices grouped by (b, group of heads), a group
+ *                                being as many consecutive heads as keep K and V in L2 together (48 MiB /
+ *                                (max_nkv * 64 KiB), evened out); inside a group by descending n_kept (ties:
+ *                                list order) while batch * groups * (max_nkv + 1) <= 8192, else single-head
+ *                                groups, q-blocks ascending (the identity when batch * head_count > 20480)
  *   counters int32 [4]           n_items, total_kept, status (FO_DEV_*), max_nkv
  * n_cand = sum over requests of ceil(qo_len/sbq)*head_count and max_nkv = max ceil(kv_len/sbkv) are
  * host-known (plan time). is_full != 0 ignores the masks (they may be null). scratch must hold

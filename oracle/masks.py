@@ -89,6 +89,17 @@ def unpack_masks(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_in
     return out
 
 
+def order_groups(batch: int, head_count: int, max_nkv: int):
+    """(heads per group, by_length) of the processing order of `compact`: groups of heads whose K and V stay in
+    L2 together -- 48 MiB / (max_nkv blocks * 64 KiB per head and tensor pair), evenly sized -- ordered by length
+    inside a group while batch * groups_per_request * (max_nkv + 1) <= 8192, else single heads, q-blocks ascending."""
+    hpg = min(max((48 << 20) // (max(max_nkv, 1) * 65536), 1), head_count)
+    grp_per_req = -(-head_count // hpg)
+    hpg = -(-head_count // grp_per_req)
+    by_length = batch * grp_per_req * (max_nkv + 1) <= 8192
+    return (hpg, True) if by_length else (1, False)
+
+
 def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr, kv_indptr,
             num_heads: int, sbq: int, sbkv: int, head_begin: int = 0, head_count: int | None = None,
             is_full: bool = False):
@@ -100,12 +111,15 @@ def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr,
                                ascending in (b, qb, h)
       kv_indptr  int32 [n+1]   offsets of each item's kept list inside kv_idx
       kv_idx     int32 [total] ascending kept kv-block indices of each item
-      order      int32 [n]     the processing permutation: item indices grouped by (b, h) ascending (CTAs that
-                               run at the same time then share K / V tiles in L2); inside a group by
-                               descending list length, ties by ascending q-block, while
-                               batch * head_count * (max_nkv + 1) <= 8192 (the items drawn last are then
-                               short ones), else by ascending q-block; the identity when
-                               batch * head_count > 20480 (more groups than the kernel's histograms hold)
+      order      int32 [n]     the processing permutation: item indices grouped by (b, group of heads) ascending
+                               (CTAs that run at the same time then share K / V tiles in L2). A group is
+                               hpg consecutive heads of the window: hpg = min(head_count, max(1, 48 MiB //
+                               (max_nkv * 64 KiB))), evened out over ceil(head_count / hpg) groups. Inside a
+                               group: by descending list length, ties in canonical order, while
+                               batch * groups_per_request * (max_nkv + 1) <= 8192 (the items drawn last are then
+                               short ones); otherwise single-head groups with their q-blocks ascending; the
+                               identity when batch * head_count > 20480 (more groups than the kernel's
+                               histograms hold)
     With `is_full` every q-block is active and every kv-block kept (prefill.cuh:1284,1383,1434).
     """
     if head_count is None:
@@ -133,9 +147,11 @@ def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr,
                     kv_ptr.append(len(kv_idx))
     items_a = np.asarray(items, dtype=np.int32).reshape(-1, 4)
     max_nkv = max([int(-(-(kv[b + 1] - kv[b]) // sbkv)) for b in range(B)], default=0)
-    if len(items) and B * head_count <= 20480:
-        key = items_a[:, 0].astype(np.int64) * head_count + (items_a[:, 1].astype(np.int64) - head_begin)
-        if B * head_count * (max_nkv + 1) <= 8192:
+    hpg, by_length = order_groups(B, head_count, max_nkv)
+    grp_per_req = -(-head_count // hpg)
+    if len(items) and B * grp_per_req <= 20480:
+        key = items_a[:, 0].astype(np.int64) * grp_per_req + (items_a[:, 1].astype(np.int64) - head_begin) // hpg
+        if by_length:
             key = key * (max_nkv + 1) + (max_nkv - items_a[:, 3].astype(np.int64))
         order = np.argsort(key, kind="stable").astype(np.int32)
     else:

@@ -60,7 +60,7 @@ def test_compact_handmade():
     assert c["items"].tolist() == [[0, 0, 0, 2], [0, 0, 1, 0], [0, 1, 1, 3]]
     assert c["kv_indptr"].tolist() == [0, 2, 2, 5]
     assert c["kv_idx"].tolist() == [0, 2, 0, 1, 2]
-    assert c["order"].tolist() == [0, 1, 2]  # (b, h, -n_kept, qb): (0,0,-2,0), (0,0,0,1), (0,1,-3,1)
+    assert c["order"].tolist() == [2, 0, 1]  # one group of both heads, longest list first: n_kept = 3, 2, 0
     # head window and is_full
     c1 = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, kv, 2, 128, 128,
                     head_begin=1, head_count=1)
@@ -76,15 +76,20 @@ def test_compact_counts_match_unpacked_masks():
     assert len(c["items"]) == sum(int(q.sum()) for q in m.q_active)
     assert len(c["kv_idx"]) == wl.executed_attention_tiles(m)
     assert sorted(c["order"].tolist()) == list(range(len(c["items"])))
-    it = c["items"][c["order"]]
-    keys = [(int(b), int(h), -int(n), int(qb)) for b, h, qb, n in it.tolist()]
-    assert keys == sorted(keys)  # grouped by (request, head); longest lists first, then q-blocks ascending
-    # with more (request, head, length) buckets than the kernel sorts by, q-blocks ascend inside a group
-    mb = wl.flux_masks(1, 40, 3, 300, 0.5, seed=4, text_blocks=1)
-    qo = np.array([0, 3 * 128]); kv = np.array([0, 300 * 128])
+    # one group of all five heads per request: longest lists first, ties in list order
+    assert om.order_groups(2, 5, 9) == (5, True)
+    keys = [(int(c["items"][i][0]), -int(c["items"][i][3]), int(i)) for i in c["order"].tolist()]
+    assert keys == sorted(keys)
+    # with more (request, group, length) buckets than the kernel sorts by: single heads, q-blocks ascending
+    mb = wl.flux_masks(1, 40, 2, 604, 0.5, seed=4, text_blocks=1)
+    qo = np.array([0, 2 * 128]); kv = np.array([0, 604 * 128])
+    assert om.order_groups(1, 40, 604) == (1, False)
     cb = om.compact(mb.sparse_info, mb.sparse_kv_info, mb.info_indptr, mb.kv_info_indptr, qo, kv, 40, 128, 128)
     keys = [(int(b), int(h), int(qb)) for b, h, qb, _ in cb["items"][cb["order"]].tolist()]
     assert keys == sorted(keys)
+    # groups of heads: 24 heads of 36 kv blocks (2.25 MiB of K + V each) -> two groups of 12
+    assert om.order_groups(2, 24, 36) == (12, True)
+    assert om.order_groups(1, 3, 36) == (3, True)
 
 
 def test_gemm_lists():

@@ -43,10 +43,13 @@ def test_compaction_lists_cover_the_masks_exactly(case):
         kept = np.nonzero(kk[b][qb, h])[0]
         assert n == len(kept) and np.array_equal(idx[ptr[i]:ptr[i + 1]], kept)
     assert ptr[-1] == len(idx) == sum(int(kk[b][qb, h].sum()) for b, h, qb in want)
-    # the processing order is a permutation, grouped by (b, h) ascending; inside a group the longest lists come
-    # first (these small cases are all below the bucket limit), ties by ascending q-block
+    # the processing order is a permutation, grouped by (b, group of heads) ascending; inside a group the longest
+    # lists come first (these small cases are all below the bucket limit), ties in list order
     assert sorted(order.tolist()) == list(range(len(items)))
-    keys = [(items[i][0], items[i][1], -items[i][3], items[i][2]) for i in order.tolist()]
+    max_nkv = max(-(-int(x) // 128) for x in lens_kv)
+    hpg, by_length = om.order_groups(len(lens_q), hc, max_nkv)
+    assert by_length
+    keys = [(items[i][0], (items[i][1] - hb) // hpg, -items[i][3], i) for i in order.tolist()]
     assert keys == sorted(keys)
 
 
