@@ -169,7 +169,20 @@ class Ctx:
         if self.world > 1:
             os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # plain peer loads and rings only
             import torch.distributed as dist
-            dist.init_process_group("nccl", device_id=self.device)
+            # NCCL may announce its version on stdout when the communicator comes up; stdout carries the one JSON
+            # line only, so the file descriptor points at stderr until the first collective has run
+            sys.stdout.flush()
+            saved = os.dup(1)
+            os.dup2(2, 1)
+            try:
+                dist.init_process_group("nccl", device_id=self.device)
+                t = torch.zeros(1, device=self.device)
+                dist.all_reduce(t)
+                torch.cuda.synchronize()
+            finally:
+                sys.stdout.flush()
+                os.dup2(saved, 1)
+                os.close(saved)
             self.dist = dist
 
     def barrier(self):
