@@ -40,16 +40,19 @@ SIGNATURES = {
                                   c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                   c_int64, c_int32, c_int64, c_int64,
                                   _P, _P, _P, _P, _P, _P, c_size_t, _P]),
+    "fo_attn_units": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                c_int64, c_int64, _P, _P, _P, _P]),
+    "fo_attn_partial_bytes": (c_size_t, [c_int64]),
     "fo_sparse_attn_fwd": (c_int32, [_P, _P, _P, _P, _P, c_int32,
                                      c_int64, c_int64, c_int32, c_int32, c_int32,
                                      c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
-                                     _P, _P, c_int32, c_int32, _P, _P, _P, _P, _P,
-                                     c_int64, c_int32, c_float, _P, _P]),
+                                     c_int32, c_int32, _P, _P, _P,
+                                     c_int64, _P, _P, c_int64, c_int32, c_float, _P, _P]),
     "fo_sparse_attn_fwd_softcap": (c_int32, [_P, _P, _P, _P, _P, c_int32,
                                              c_int64, c_int64, c_int32, c_int32, c_int32,
                                              c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
-                                             _P, _P, c_int32, c_int32, _P, _P, _P, _P, _P,
-                                             c_int64, c_int32, c_float, c_float, _P, _P]),
+                                             c_int32, c_int32, _P, _P, _P,
+                                             c_int64, _P, _P, c_int64, c_int32, c_float, c_float, _P, _P]),
     "fo_gemm_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "fo_gemm_dense_tile_rows": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32]),
     "fo_gemm_q": (c_int32, [_P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32,
@@ -92,7 +95,7 @@ def load():
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.fo_abi_version() != 1:
+    if lib.fo_abi_version() != 2:
         raise RuntimeError("flashomni_b200: ABI version mismatch")
     _lib = lib
     return lib

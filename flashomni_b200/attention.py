@@ -233,19 +233,30 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
 
     begin_forward = plan
 
+    MIN_CHUNK = 16   # shortest part (kv blocks) a kv list is cut into: a unit costs a few microseconds of its own
+
     def _carve_workspace(self) -> None:
-        """Lays the work lists out in one int32 buffer: counters[4] | status[4] | items | kv_ptr | order |
-        kv_idx | scratch."""
+        """Lays the work lists out in one int32 buffer: counters[4] | status[4] | unit_counters[4] | items | kv_ptr |
+        order | arrive | units | kv_idx | scratch, and sets the partial-result scratch of split items aside (in the
+        caller's float workspace when that is large enough, as the reference's planner does with its own partial
+        outputs, flashomni/attention.py:344-352,608-623)."""
         lib = _native.load()
         n, kept = max(self._n_cand, 1), max(self._max_kept, 1)
         scratch_bytes = lib.fo_mask_compact_scratch_bytes(n, self._max_nkv)
+        # the kernel runs two streams of items per SM; kv lists are only cut when there are at most half as many
+        # items as streams, into at most streams + items <= 1.5 * streams parts
+        self._num_streams = 2 * torch.cuda.get_device_properties(self.device).multi_processor_count
+        may_split = self._n_cand <= 4 * self._num_streams   # the masks may leave few enough items
+        self._max_units = n + (self._num_streams if may_split else 0)
+        self._partial_slots = (self._num_streams + self._num_streams // 2) if may_split else 0
 
         def al(words):  # 16-byte aligned word counts
             return (words + 3) // 4 * 4
 
         offs, cur = {}, 0
-        for name, words in (("counters", 4), ("status", 4), ("items", 4 * n), ("kv_ptr", n + 1), ("order", n),
-                            ("kv_idx", kept), ("scratch", (scratch_bytes + 3) // 4)):
+        for name, words in (("counters", 4), ("status", 4), ("unit_counters", 4), ("items", 4 * n), ("kv_ptr", n + 1),
+                            ("order", n), ("arrive", max(self._partial_slots, 1)), ("units", 8 * self._max_units), ("kv_idx", kept),
+                            ("scratch", (scratch_bytes + 3) // 4)):
             offs[name] = cur
             cur += al(words)
         need = cur * 4
@@ -254,11 +265,22 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             buf = torch.zeros(need, dtype=torch.uint8, device=self.device)
             self._int_workspace_buffer = buf
         words = buf.view(torch.uint8)[: need].view(torch.int32)
-        words[offs["counters"]: offs["counters"] + 8].zero_()  # counters and status / cursor words start from zero
+        words[offs["counters"]: offs["counters"] + 12].zero_()  # counters, status / cursor words start from zero
+        words[offs["arrive"]: offs["arrive"] + max(self._partial_slots, 1)].zero_()
         self._ws = {k: words[v:] for k, v in offs.items()}
         self._ws_words = words
         self._ws_offs = offs
         self._scratch_bytes = scratch_bytes
+        pbytes = lib.fo_attn_partial_bytes(self._partial_slots)
+        fw = self._float_workspace_buffer
+        self._partials = None
+        if pbytes > 0:
+            if fw.device == self.device and fw.numel() * fw.element_size() >= pbytes + 16 and fw.is_contiguous():
+                raw = fw.view(torch.uint8).view(-1)
+                shift = (-raw.data_ptr()) % 16
+                self._partials = raw[shift: shift + pbytes]
+            else:
+                self._partials = torch.empty(pbytes, dtype=torch.uint8, device=self.device)
 
     # ------------------------------------------------------------------------------------------ run
     def run(
@@ -339,10 +361,9 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             head = (_native.ptr(q), _native.ptr(k), _native.ptr(v), _native.ptr(out), _native.ptr(lse),
                     native_dtype(q.dtype), self._total_q, self._total_kv, self._num_qo_heads, self._num_kv_heads,
                     self._head_dim, q.stride(0), q.stride(1), kn, kh, vn, vh, out.stride(0), out.stride(1),
-                    _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
-                    self._sparse_block_size_for_q, self._sparse_block_size_for_kv,
-                    _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
-                    _native.ptr(ws["order"]), _native.ptr(ws["counters"]), max(self._n_cand, 1),
+                    self._sparse_block_size_for_q, self._sparse_block_size_for_kv, _native.ptr(ws["kv_idx"]),
+                    _native.ptr(ws["units"]), _native.ptr(ws["unit_counters"]), self._max_units,
+                    _native.ptr(ws["arrive"]), _native.ptr(self._partials), self._partial_slots,
                     self._mask_head_begin, float(sm_scale))
             cap = float(self._logits_soft_cap or 0.0)
             if cap > 0:  # logits = cap * tanh(q.k * sm_scale / cap), as the reference's variant does
@@ -378,6 +399,13 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             _native.ptr(ws["order"]), _native.ptr(ws["counters"]), _native.ptr(ws["scratch"]),
             self._scratch_bytes, stream)
         _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper (mask compaction)")
+        rc = _native.load().fo_attn_units(
+            _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]), _native.ptr(ws["order"]),
+            _native.ptr(ws["counters"]), _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
+            max(self._n_cand, 1), self._max_nkv, self._sparse_block_size_for_q, self._sparse_block_size_for_kv,
+            self._num_streams, self.MIN_CHUNK, self._max_units, self._partial_slots, _native.ptr(ws["units"]),
+            _native.ptr(ws["unit_counters"]), _native.ptr(ws["arrive"]), stream)
+        _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper (work units)")
 
     def build_work_lists(self, sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                          is_full: bool = False) -> None:
@@ -426,16 +454,21 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
     # ------------------------------------------------------------------------------------------ extras
     def check_status(self) -> None:
         """Synchronises and raises if the last run() recorded a device-side problem."""
-        w = self._ws_words[:8].cpu()
-        if int(w[2]) != 0 or int(w[4]) != 0:
-            raise RuntimeError(f"flashomni_b200 attention: device status compaction={int(w[2])} kernel={int(w[4])}")
+        w = self._ws_words[:12].cpu()
+        if int(w[2]) != 0 or int(w[4]) != 0 or int(w[11]) != 0:
+            raise RuntimeError(f"flashomni_b200 attention: device status compaction={int(w[2])} units={int(w[11])} "
+                               f"kernel={int(w[4])}")
 
     def work_lists(self) -> dict:
         """Host copies of the lists of the last run() (synchronises; for tests and FLOP accounting)."""
         w = self._ws
         c = w["counters"][:4].cpu()
         n, kept = int(c[0]), int(c[1])
+        uc = w["unit_counters"][:4].cpu()
+        nu = int(uc[0])
         return {
+            "n_units": nu, "partial_slots_used": int(uc[1]), "chunk_max": int(uc[2]), "unit_status": int(uc[3]),
+            "units": w["units"][: 8 * nu].cpu().view(-1, 8).numpy(),
             "n_items": n, "total_kept": kept, "status": int(c[2]),
             "items": w["items"][: 4 * n].cpu().view(-1, 4).numpy(),
             "kv_indptr": w["kv_ptr"][: n + 1].cpu().numpy(),

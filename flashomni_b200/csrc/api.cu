@@ -190,30 +190,73 @@ int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes, const
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_mask_compact", e);
 }
 
+size_t fo_attn_partial_bytes(int64_t partial_slots) {
+  return partial_slots > 0 ? static_cast<size_t>(partial_slots) * kPartialFloats * sizeof(float) : 0;
+}
+
+int fo_attn_units(const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx, const int32_t* order,
+                  const int32_t* counters, const int32_t* qo_indptr, const int32_t* kv_indptr, int64_t max_items,
+                  int32_t max_nkv, int32_t sbq, int32_t sbkv, int32_t num_streams, int32_t min_chunk, int64_t max_units,
+                  int64_t max_slots, int32_t* units, int32_t* unit_counters, int32_t* arrive, void* stream) {
+  if (items == nullptr || kv_ptr == nullptr || kv_idx == nullptr || order == nullptr || counters == nullptr ||
+      qo_indptr == nullptr || kv_indptr == nullptr || units == nullptr || unit_counters == nullptr ||
+      (max_slots > 0 && arrive == nullptr))
+    return fail(FO_ERR_INVALID_ARG, "fo_attn_units: null pointer");
+  if (max_items <= 0 || max_units < max_items || max_slots < 0 || num_streams <= 0 || min_chunk <= 0 || max_nkv < 0 ||
+      sbq <= 0 || sbkv <= 0)
+    return fail(FO_ERR_INVALID_ARG, "fo_attn_units: max_units must cover max_items; sizes must be positive");
+  if (!aligned16(units)) return fail(FO_ERR_INVALID_ARG, "fo_attn_units: units must be 16-byte aligned");
+  UnitArgs a;
+  memset(&a, 0, sizeof(a));
+  a.items = items;
+  a.kv_ptr = kv_ptr;
+  a.kv_idx = kv_idx;
+  a.order = order;
+  a.counters = counters;
+  a.qo_indptr = qo_indptr;
+  a.kv_indptr = kv_indptr;
+  a.max_items = max_items;
+  a.max_units = max_units;
+  a.max_slots = max_slots;
+  a.num_streams = num_streams;
+  a.min_chunk = min_chunk;
+  a.max_nkv = max_nkv;
+  a.sbq = sbq;
+  a.sbkv = sbkv;
+  a.units = units;
+  a.unit_counters = unit_counters;
+  a.arrive = arrive;
+  const cudaError_t e = launch_attn_units(a, static_cast<cudaStream_t>(stream));
+  count_launches(1);
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_attn_units", e);
+}
+
 // ------------------------------------------------------------------------------------------ attention
 namespace {
 int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
                      int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
                      int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
                      int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
-                     int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t sbq,
-                     int32_t sbkv, const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx,
-                     const int32_t* order, const int32_t* counters, int64_t max_items, int32_t head_begin,
-                     float sm_scale, float logits_soft_cap, int32_t* status, void* stream) {
+                     int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
+                     const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t* arrive,
+                     float* partials, int64_t partial_slots, int32_t head_begin, float sm_scale,
+                     float logits_soft_cap, int32_t* status, void* stream) {
   if (!(logits_soft_cap >= 0.f) || !(sm_scale > 0.f))
     return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: sm_scale must be positive and logits_soft_cap >= 0");
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr)
     return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: null q/k/v/o");
-  if (qo_indptr == nullptr || kv_indptr == nullptr || items == nullptr || kv_ptr == nullptr ||
-      kv_idx == nullptr || order == nullptr || counters == nullptr || status == nullptr)
-    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: null work list / indptr / status");
+  if (kv_idx == nullptr || units == nullptr || unit_counters == nullptr || status == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: null work list / status");
+  if (!aligned16(units)) return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: units must be 16-byte aligned");
+  if (partial_slots < 0 || (partial_slots > 0 && (partials == nullptr || !aligned16(partials) || arrive == nullptr)))
+    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: partial-result scratch missing or misaligned");
   if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: bad dtype");
   if (head_dim != 128) return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: only head_dim 128 is implemented");
   if (sbq != 128 || sbkv != 128)
     return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: only 128-row q and kv sparse blocks are implemented");
   if (num_qo_heads <= 0 || num_kv_heads <= 0 || num_qo_heads % num_kv_heads != 0)
     return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: num_qo_heads must be a multiple of num_kv_heads");
-  if (total_q <= 0 || total_kv <= 0 || max_items <= 0) return FO_OK;
+  if (total_q <= 0 || total_kv <= 0 || max_units <= 0) return FO_OK;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
     return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: q/k/v/o must be 16-byte aligned");
   const int64_t strides[] = {q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h};
@@ -246,14 +289,13 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   a.o_stride_n = o_stride_n;
   a.o_stride_h = o_stride_h;
   a.lse_stride_n = num_qo_heads;
-  a.qo_indptr = qo_indptr;
-  a.kv_indptr = kv_indptr;
-  a.items = items;
-  a.kv_ptr = kv_ptr;
   a.kv_idx = kv_idx;
-  a.order = order;
-  a.counters = counters;
-  a.max_items = static_cast<int>(max_items > 0x7fffffffLL ? 0x7fffffffLL : max_items);
+  a.units = units;
+  a.unit_counters = unit_counters;
+  a.max_units = static_cast<int>(max_units > 0x7fffffffLL ? 0x7fffffffLL : max_units);
+  a.arrive = arrive;
+  a.partials = partials;
+  a.partial_slots = static_cast<int>(partial_slots > 0x7fffffffLL ? 0x7fffffffLL : partial_slots);
   a.head_begin = head_begin;
   a.group_size = num_qo_heads / num_kv_heads;
   a.is_bf16 = dtype == FO_DTYPE_BF16;
@@ -266,7 +308,7 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   }
   a.status = status;
   int64_t ctas = static_cast<int64_t>(sm_count());  // one persistent CTA per SM
-  if (ctas > max_items) ctas = max_items;
+  if (ctas > max_units) ctas = max_units;
   const cudaError_t e = launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
   count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_sparse_attn_fwd", e);
@@ -277,28 +319,28 @@ int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
                        int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
                        int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
                        int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
-                       int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t sbq,
-                       int32_t sbkv, const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx,
-                       const int32_t* order, const int32_t* counters, int64_t max_items, int32_t head_begin,
-                       float sm_scale, int32_t* status, void* stream) {
+                       int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
+                       const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t* arrive,
+                       float* partials, int64_t partial_slots, int32_t head_begin, float sm_scale, int32_t* status,
+                       void* stream) {
   return sparse_attn_impl(q, k, v, o, lse, dtype, total_q, total_kv, num_qo_heads, num_kv_heads, head_dim, q_stride_n,
-                          q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, qo_indptr,
-                          kv_indptr, sbq, sbkv, items, kv_ptr, kv_idx, order, counters, max_items, head_begin, sm_scale,
-                          0.f, status, stream);
+                          q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, sbq, sbkv,
+                          kv_idx, units, unit_counters, max_units, arrive, partials,
+                          partial_slots, head_begin, sm_scale, 0.f, status, stream);
 }
 
 int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
                                int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
                                int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
                                int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
-                               int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t sbq,
-                               int32_t sbkv, const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx,
-                               const int32_t* order, const int32_t* counters, int64_t max_items, int32_t head_begin,
-                               float sm_scale, float logits_soft_cap, int32_t* status, void* stream) {
+                               int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
+                               const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t* arrive,
+                               float* partials, int64_t partial_slots, int32_t head_begin, float sm_scale,
+                               float logits_soft_cap, int32_t* status, void* stream) {
   return sparse_attn_impl(q, k, v, o, lse, dtype, total_q, total_kv, num_qo_heads, num_kv_heads, head_dim, q_stride_n,
-                          q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, qo_indptr,
-                          kv_indptr, sbq, sbkv, items, kv_ptr, kv_idx, order, counters, max_items, head_begin, sm_scale,
-                          logits_soft_cap, status, stream);
+                          q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, sbq, sbkv,
+                          kv_idx, units, unit_counters, max_units, arrive, partials,
+                          partial_slots, head_begin, sm_scale, logits_soft_cap, status, stream);
 }
 
 // ------------------------------------------------------------------------------------------ GEMMs

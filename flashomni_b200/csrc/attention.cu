@@ -75,6 +75,7 @@ struct StreamBars {
   uint64_t wg_bar;    // bounded barrier of the stream's softmax warpgroup (count = warps)
   uint64_t iq_full[kItemQ], iq_empty[kItemQ];  // item queue: the producer draws work-list positions for the stream
   int item_q[kItemQ];
+  int merge_go;       // this stream's part of a split item delivered last and merges the item's partial results
 };
 struct Tail {
   StreamBars st[kStreams];
@@ -177,17 +178,19 @@ struct ItemRead {  // the reading roles: one thread, or all lanes of a softmax w
 template <class Src, bool kNeedKv, bool kNeedRagged>
 struct BlockSeq {
   Src src;
-  int item_no;   // index among this stream's non-empty items
-  int b, h, qb, n, j;
+  int item_no;   // index among this stream's non-empty units
+  int h, n, j;                   // head inside the q / o tensors, kv blocks of the unit, current block
+  int q_row0, q_valid, kv_row0;  // first row of the q-block in q / o, its existing rows, first kv row of the request
+  int slot, part, nparts;        // partial slot, part number and count (a whole item: nparts = 1)
   int kvb, kvb_next;  // kv-block index of the current block; the next one is fetched a block early
   int rot;            // rotation of the visiting order inside the item's kv list
   int ragged_j, ragged_valid;  // visiting step of the request's partial last kv block (-1: none) and its columns
   const int32_t* kv;
   __device__ __forceinline__ void init() {
-    item_no = -1; n = 0; j = 0; kv = nullptr;
-    b = h = qb = 0; kvb = kvb_next = 0; rot = 0; ragged_j = -1; ragged_valid = 0;
+    item_no = -1; n = 0; j = 0; kv = nullptr; slot = 0; part = 0; nparts = 1;
+    h = q_row0 = q_valid = kv_row0 = 0; kvb = kvb_next = 0; rot = 0; ragged_j = -1; ragged_valid = 0;
   }
-  // Advances to the next block; `on_empty(b, h, qb)` is called for every item without kv blocks that
+  // Advances to the next block; `on_empty(q_row0, q_valid, h)` is called for every item without kv blocks that
   // is passed on the way. Returns false at the end of the sequence.
   template <class F>
   __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
@@ -202,28 +205,26 @@ struct BlockSeq {
     while (true) {
       const int pos = src.next();
       if (pos < 0) break;
-      const int it = a.order[pos];
-      const int4 rec = *reinterpret_cast<const int4*>(a.items + 4 * it);
-      if (rec.w <= 0) { on_empty(rec.x, rec.y, rec.z); continue; }
-      b = rec.x; h = rec.y; qb = rec.z; n = rec.w; j = 0;
-      rot = rot_of(qb, n);
+      // the unit's record: everything this role needs, in one 32-byte load
+      const int4* up = reinterpret_cast<const int4*>(a.units + 8 * static_cast<int64_t>(pos));
+      const int4 u0 = up[0], u1 = up[1];
+      if (u0.x <= 0) { on_empty(u0.w, u1.x, u0.z - a.head_begin); continue; }
+      n = u0.x; j = 0;
+      h = u0.z - a.head_begin;
+      q_row0 = u0.w; q_valid = u1.x; kv_row0 = u1.y;
+      slot = static_cast<int>(static_cast<unsigned>(u1.w) >> 16); part = (u1.w >> 8) & 0xff; nparts = u1.w & 0xff;
+      rot = rot_of(q_row0 >> 7, n);
       if (kNeedKv) {
-        kv = a.kv_idx + a.kv_ptr[it];
+        kv = a.kv_idx + u0.y;
         kvb = kv[at(0)];
         if (n > 1) kvb_next = kv[at(1)];
       }
       if (kNeedRagged) {
         ragged_j = -1;
-        const int kv_len = a.kv_indptr[b + 1] - a.kv_indptr[b];
-        const int tail_cols = kv_len % kBKV;
-        if (tail_cols != 0) {
-          // lists are ascending: only the last entry can be the partial block
-          const int last_entry = a.kv_idx[a.kv_ptr[it] + n - 1];
-          if (last_entry == kv_len / kBKV) {
-            ragged_j = n - 1 - rot;
-            if (ragged_j < 0) ragged_j += n;
-            ragged_valid = tail_cols;
-          }
+        if (u1.z != 0) {  // the unit's last entry is the request's partial kv block
+          ragged_j = n - 1 - rot;
+          if (ragged_j < 0) ragged_j += n;
+          ragged_valid = u1.z;
         }
       }
       ++item_no;
@@ -287,12 +288,12 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = tail->tmem_base;
 
-  // The list may be shorter than counters[0] says: a compaction that ran out of room records it in counters[2]
+  // The lists may be incomplete: a compaction or unit builder that ran out of room records it in its status word
   // and leaves records unwritten. Nothing of such a list is dereferenced; the launch only reports it.
-  const bool list_bad = a.counters[2] != kDevOk;
-  int n_items = a.counters[0];
+  const bool list_bad = a.unit_counters[3] != kDevOk || a.unit_counters[1] > a.partial_slots;
+  int n_items = a.unit_counters[0];  // units: whole items or parts of items
   if (list_bad || n_items < 0) n_items = 0;
-  if (n_items > a.max_items) n_items = a.max_items;
+  if (n_items > a.max_units) n_items = a.max_units;
   auto ignore_empty = [](int, int, int) {};
 
   if (warp >= kSoftmaxWarps) {
@@ -312,13 +313,13 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         uint32_t g = 0;
         int kv_row0 = 0;
         while (seq.next(a, ignore_empty)) {
-          const int hq = seq.h - a.head_begin;
+          const int hq = seq.h;
           const int hk = hq / a.group_size;
           // the K slot (and, for a new item, the Q slot) is free once the Q K^T of the stream's previous block is done
           if (!mbar_wait(&sb->s_full, (g & 1u) ^ 1u, abort_flag)) break;
           if (seq.first()) {
-            kv_row0 = a.kv_indptr[seq.b];
-            const int q_row = a.qo_indptr[seq.b] + seq.qb * kBQ;
+            kv_row0 = seq.kv_row0;
+            const int q_row = seq.q_row0;
             mbar_expect_tx(&sb->q_full, kTileBytes);
             tma_load_3d(smem_q, &a.tmap_q, &sb->q_full, 0, hq, q_row);
             tma_load_3d(smem_q + kHalfBytes, &a.tmap_q, &sb->q_full, 64, hq, q_row);
@@ -455,22 +456,18 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       bool whole;   // no row of the q-block is past the end of its request
       int grow0;    // first row of the q-block in the q / o tensors
     };
-    auto row_ctx = [&](int b, int h, int qb) -> RowCtx {
+    auto row_ctx = [&](int q_row0, int q_valid, int hq) -> RowCtx {
       RowCtx c;
-      const int hq = h - a.head_begin;
-      const int q0 = a.qo_indptr[b];
-      const int q_len = a.qo_indptr[b + 1] - q0;
-      const int row_in_req = qb * kBQ + row;
-      c.row_ok = row_in_req < q_len;
-      c.whole = (qb + 1) * kBQ <= q_len;
-      c.grow0 = q0 + qb * kBQ;
-      const int64_t grow = static_cast<int64_t>(q0) + row_in_req;
+      c.row_ok = row < q_valid;
+      c.whole = q_valid == kBQ;
+      c.grow0 = q_row0;
+      const int64_t grow = static_cast<int64_t>(q_row0) + row;
       c.orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h;
       c.lse = a.lse != nullptr ? a.lse + grow * a.lse_stride_n + hq : nullptr;
       return c;
     };
-    auto on_empty = [&](int b, int h, int qb) {  // active q-block that keeps nothing: zeros, lse = -5e4
-      const RowCtx c = row_ctx(b, h, qb);
+    auto on_empty = [&](int q_row0, int q_valid, int hq) {  // active q-block that keeps nothing: zeros, lse = -5e4
+      const RowCtx c = row_ctx(q_row0, q_valid, hq);
       if (c.row_ok) {
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
@@ -579,45 +576,21 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       ++g;
 
       if (seq.last()) {
-        // ---- epilogue of the item: O / l -> 16 bit -> global. Whole q-blocks go through the stream's staging area
-        // (two rounds of 64 columns, 128-byte swizzle) and TMA stores; a q-block cut by the end of its request is
-        // written row by row.
-        const RowCtx c = row_ctx(seq.b, seq.h, seq.qb);
+        // ---- epilogue of the unit. A whole item: O / l -> 16 bit -> global. A part of a split item: the fp32 O, the
+        // row maxima and the row sums go to the item's partial slots; the part that delivers last merges them.
+        const RowCtx c = row_ctx(seq.q_row0, seq.q_valid, seq.h);
         float la, lb, lc, ld;
         unpack_f32x2(l2a, la, lb);
         unpack_f32x2(l2b, lc, ld);
         const float lsum = (la + lb) + (lc + ld);
-        const float inv_l = lsum > 0.f ? __frcp_rn(lsum) : 0.f;
-        if (c.whole && stage_busy) {  // the previous item's second store must have read the staging area
-          if (wq == 0 && lane == 0) tma_store_wait_read<0>();
-          if (!wg_sync()) { ok = false; break; }
-          stage_busy = false;
-        }
-        if (!wait_all(&sb->pv_done, (g - 1u) & 1u, abort_flag)) { ok = false; break; }  // the item's last P V
-        tc_fence_after_sync();
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          uint32_t v[64];
-          tmem_ld_x32(tmem_o + 64u * r, v);
-          tmem_ld_x32(tmem_o + 64u * r + 32u, v + 32);
-          tmem_wait_ld();
-          if (r == 1) {  // O may be overwritten by the next item
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sb->o_free);
-          }
-          uint4 outv[8];
-          uint32_t* w = reinterpret_cast<uint32_t*>(outv);
-#pragma unroll
-          for (int t = 0; t < 32; ++t) {
-            const float x0 = __uint_as_float(v[2 * t]) * inv_l;
-            const float x1 = __uint_as_float(v[2 * t + 1]) * inv_l;
-            w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
-          }
+        // Writes one round (64 columns, packed to 16 bit) of the q-block: whole q-blocks through the stream's staging
+        // area (128-byte swizzle) and a TMA store, a q-block cut by the end of its request row by row.
+        auto store_round = [&](int r, const uint4 (&outv)[8]) -> bool {
           if (c.whole) {
-            if (r == 1) {  // round 0's store must have read the staging area
+            if (stage_busy) {  // the previous store must have read the staging area
               if (wq == 0 && lane == 0) tma_store_wait_read<0>();
-              if (!wg_sync()) { ok = false; break; }
+              if (!wg_sync()) return false;
+              stage_busy = false;
             }
             uint8_t* rowp = stage + row * 128;
             const uint32_t swz = static_cast<uint32_t>(row & 7);
@@ -625,9 +598,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
             for (int q = 0; q < 8; ++q)
               *reinterpret_cast<uint4*>(rowp + ((static_cast<uint32_t>(q) ^ swz) << 4)) = outv[q];
             fence_proxy_async_smem();
-            if (!wg_sync()) { ok = false; break; }
+            if (!wg_sync()) return false;
             if (wq == 0 && lane == 0) {
-              tma_store_3d(&a.tmap_o, stage, 64 * r, seq.h - a.head_begin, c.grow0);
+              tma_store_3d(&a.tmap_o, stage, 64 * r, seq.h, c.grow0);
               tma_store_commit();
             }
             stage_busy = true;
@@ -636,9 +609,110 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 #pragma unroll
             for (int q = 0; q < 8; ++q) dst[q] = outv[q];
           }
+          return true;
+        };
+        if (!wait_all(&sb->pv_done, (g - 1u) & 1u, abort_flag)) { ok = false; break; }  // the unit's last P V
+        tc_fence_after_sync();
+        if (seq.nparts <= 1) {
+          const float inv_l = lsum > 0.f ? __frcp_rn(lsum) : 0.f;
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            uint32_t v[64];
+            tmem_ld_x32(tmem_o + 64u * r, v);
+            tmem_ld_x32(tmem_o + 64u * r + 32u, v + 32);
+            tmem_wait_ld();
+            if (r == 1) {  // O may be overwritten by the next unit
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&sb->o_free);
+            }
+            uint4 outv[8];
+            uint32_t* w = reinterpret_cast<uint32_t*>(outv);
+#pragma unroll
+            for (int t = 0; t < 32; ++t) {
+              const float x0 = __uint_as_float(v[2 * t]) * inv_l;
+              const float x1 = __uint_as_float(v[2 * t + 1]) * inv_l;
+              w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+            }
+            if (!store_round(r, outv)) { ok = false; break; }
+          }
+          if (!ok) break;
+          if (c.row_ok && c.lse != nullptr) *c.lse = (lsum > 0.f) ? (log2f(lsum) + m_run) : -5e4f;
+        } else {
+          // ---- partial result: O as [column group of 4][row][4] (a warp's store covers 512 contiguous bytes)
+          float* ps = a.partials + static_cast<size_t>(seq.slot) * kPartialFloats;
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t v[32];
+            tmem_ld_x32(tmem_o + 32u * cc, v);
+            tmem_wait_ld();
+            if (cc == 3) {  // O may be overwritten by the next unit
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&sb->o_free);
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(ps + (static_cast<size_t>(8 * cc + q) * 128 + row) * 4) =
+                  make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          }
+          ps[128 * 128 + row] = m_run;
+          ps[128 * 128 + 128 + row] = lsum;
+          __threadfence();
+          if (!wg_sync()) { ok = false; break; }
+          if (wq == 0 && lane == 0) {
+            int* cnt = a.arrive + (seq.slot - seq.part);  // a split item counts at its first slot
+            const int old = atomicAdd(cnt, 1);
+            const int mine = old == seq.nparts - 1 ? 1 : 0;
+            if (mine) *cnt = 0;  // the counter is back at zero for the next launch
+            __threadfence();
+            sb->merge_go = mine;
+          }
+          if (!wg_sync()) { ok = false; break; }
+          if (sb->merge_go != 0) {
+            // ---- this part delivered last: O = sum_p O_p 2^(m_p - m) / sum_p l_p 2^(m_p - m), m = max_p m_p
+            const float* base = a.partials + static_cast<size_t>(seq.slot - seq.part) * kPartialFloats;
+            float m_all = -INFINITY;
+            for (int pp = 0; pp < seq.nparts; ++pp)
+              m_all = fmaxf(m_all, __ldcg(base + static_cast<size_t>(pp) * kPartialFloats + 128 * 128 + row));
+            float l_all = 0.f;
+            for (int pp = 0; pp < seq.nparts; ++pp) {
+              const float* pq = base + static_cast<size_t>(pp) * kPartialFloats;
+              const float mp = __ldcg(pq + 128 * 128 + row);
+              const float wgt = (mp == -INFINITY) ? 0.f : ex2_approx(mp - m_all);
+              l_all = fmaf(__ldcg(pq + 128 * 128 + 128 + row), wgt, l_all);
+            }
+            const float inv_l = l_all > 0.f ? __frcp_rn(l_all) : 0.f;
+#pragma unroll 1
+            for (int r = 0; r < 2; ++r) {
+              float acc[64];
+#pragma unroll
+              for (int t = 0; t < 64; ++t) acc[t] = 0.f;
+              for (int pp = 0; pp < seq.nparts; ++pp) {
+                const float* pq = base + static_cast<size_t>(pp) * kPartialFloats;
+                const float mp = __ldcg(pq + 128 * 128 + row);
+                const float wgt = (mp == -INFINITY) ? 0.f : ex2_approx(mp - m_all);
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                  const float4 x = __ldcg(reinterpret_cast<const float4*>(pq + (static_cast<size_t>(16 * r + q) * 128 + row) * 4));
+                  acc[4 * q] = fmaf(x.x, wgt, acc[4 * q]);
+                  acc[4 * q + 1] = fmaf(x.y, wgt, acc[4 * q + 1]);
+                  acc[4 * q + 2] = fmaf(x.z, wgt, acc[4 * q + 2]);
+                  acc[4 * q + 3] = fmaf(x.w, wgt, acc[4 * q + 3]);
+                }
+              }
+              uint4 outv[8];
+              uint32_t* w = reinterpret_cast<uint32_t*>(outv);
+#pragma unroll
+              for (int t = 0; t < 32; ++t)
+                w[t] = kBf16 ? pack_bf16x2(acc[2 * t] * inv_l, acc[2 * t + 1] * inv_l)
+                             : pack_f16x2(acc[2 * t] * inv_l, acc[2 * t + 1] * inv_l);
+              if (!store_round(r, outv)) { ok = false; break; }
+            }
+            if (!ok) break;
+            if (c.row_ok && c.lse != nullptr) *c.lse = (l_all > 0.f) ? (log2f(l_all) + m_all) : -5e4f;
+          }
         }
-        if (!ok) break;
-        if (c.row_ok && c.lse != nullptr) *c.lse = (lsum > 0.f) ? (log2f(lsum) + m_run) : -5e4f;
       }
     }
     if (wq == 0 && lane == 0) tma_store_wait_all<0>();

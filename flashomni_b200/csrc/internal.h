@@ -56,6 +56,22 @@ cudaError_t launch_segment_packbits(const uint8_t* x, const int32_t* indptr, con
                                     int num_segments, int64_t out_bytes, int little, uint8_t* y,
                                     cudaStream_t stream);
 cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream);
+
+struct UnitArgs {
+  const int32_t* items;      // [max_items, 4] as written by the compaction
+  const int32_t* kv_ptr;     // [max_items + 1]
+  const int32_t* kv_idx;
+  const int32_t* order;      // [max_items]
+  const int32_t* counters;   // the compaction's counters (n_items, total_kept, status, max_nkv)
+  const int32_t* qo_indptr;
+  const int32_t* kv_indptr;
+  int64_t max_items, max_units, max_slots;
+  int num_streams, min_chunk, max_nkv, sbq, sbkv;
+  int32_t* units;            // [max_units, 8]
+  int32_t* unit_counters;    // [4]: n_units, partial slots in use, chunk_max, status
+  int32_t* arrive;           // [max_slots]
+};
+cudaError_t launch_attn_units(const UnitArgs& a, cudaStream_t stream);
 cudaError_t launch_gemm_q_tiles(const GemmListArgs& a, cudaStream_t stream);
 cudaError_t launch_gemm_o_rows(const GemmListArgs& a, cudaStream_t stream);
 
@@ -148,14 +164,13 @@ struct AttnArgs {
   float* lse;                      // [Tq, H] or null
   int64_t o_stride_n, o_stride_h;
   int64_t lse_stride_n;
-  const int32_t* qo_indptr;
-  const int32_t* kv_indptr;
-  const int32_t* items;            // (b, h_mask, qb, n_kept)
-  const int32_t* kv_ptr;
-  const int32_t* kv_idx;
-  const int32_t* order;
-  const int32_t* counters;         // counters[0] = n_items, counters[2] = status of the compaction
-  int max_items;                   // capacity of items / kv_ptr / order as given to the compaction
+  const int32_t* kv_idx;           // kept kv-block indices; unit records point into it
+  const int32_t* units;            // 8 words per unit (see attn_units_kernel), processing order
+  const int32_t* unit_counters;    // n_units, partial slots in use, chunk_max, status
+  int max_units;                   // capacity of the unit list
+  int32_t* arrive;                 // per partial slot (a split item counts at its first slot): parts delivered; zero between launches
+  float* partials;                 // partial results of split items: partial_slots x kPartialFloats floats
+  int partial_slots;
   int head_begin;                  // tensor head = item head - head_begin
   int group_size;                  // H / Hkv
   int is_bf16;
@@ -163,6 +178,8 @@ struct AttnArgs {
   float soft_cap_pre;              // 0: no soft cap; else sm_scale / cap (logits = cap * tanh(q.k * sm_scale / cap))
   int32_t* status;
 };
+// floats of one partial result: O (32 column groups x 128 rows x 4), then the row maxima and the row sums
+constexpr int kPartialFloats = 128 * 128 + 2 * 128;
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream);
 
 // ------------------------------------------------------------------ host helpers

@@ -462,6 +462,115 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Attention work units (self-contained records; split of long kv lists)
+// ---------------------------------------------------------------------------------------------
+// Walks the items in processing order and writes one 32-byte record per unit of work, holding everything the
+// attention kernel's roles need (no chain of dependent loads at a unit boundary):
+//   [0] n          kv blocks of the unit (0: an active q-block that keeps nothing)
+//   [1] kv_off     offset of the unit's first entry in kv_idx
+//   [2] h          mask head
+//   [3] q_row0     first row of the q-block in the q / o tensors
+//   [4] q_valid    rows of the q-block that exist (1..sbq)
+//   [5] kv_row0    first kv row of the request
+//   [6] ragged     columns of the request's partial last kv block if the unit's list ends with it, else 0
+//   [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
+// A kv list is cut into n_parts = ceil(n_kept / chunk_max) parts of (almost) equal length only when the launch has
+// at most half as many items as streams (whole items would leave streams idle): chunk_max = max(min_chunk,
+// ceil(total_kept / num_streams), ceil(max_nkv / 255)); otherwise every item is one unit.
+// unit_counters: n_units, partial slots in use, chunk_max, status. arrive[slot] = 0 for every slot.
+__global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
+  __shared__ int s_warp_u[32], s_warp_p[32];
+  __shared__ int s_carry_u, s_carry_p;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool list_ok = a.counters[2] == kDevOk;
+  int n_items = a.counters[0];
+  if (!list_ok || n_items < 0) n_items = 0;
+  if (n_items > a.max_items) n_items = static_cast<int>(a.max_items);
+  const long long total_kept = a.counters[1];
+  int chunk_max = 0x7fffffff;
+  if (n_items > 0 && 2 * n_items <= a.num_streams) {
+    long long c = (total_kept + a.num_streams - 1) / a.num_streams;
+    if (c < a.min_chunk) c = a.min_chunk;
+    const long long c255 = (static_cast<long long>(a.max_nkv) + 254) / 255;
+    if (c < c255) c = c255;
+    chunk_max = static_cast<int>(c);
+  }
+  for (int64_t i = tid; i < a.max_slots; i += blockDim.x) a.arrive[i] = 0;
+  if (tid == 0) { s_carry_u = 0; s_carry_p = 0; }
+  __syncthreads();
+  for (int base = 0; base < n_items; base += blockDim.x) {
+    const int pos = base + tid;
+    int it = 0, n = 0, np = 0;
+    int4 rec = make_int4(0, 0, 0, 0);
+    if (pos < n_items) {
+      it = a.order[pos];
+      rec = *reinterpret_cast<const int4*>(a.items + 4 * it);  // (b, mask head, qb, n_kept)
+      n = rec.w > 0 ? rec.w : 0;
+      np = n > chunk_max ? (n + chunk_max - 1) / chunk_max : 1;
+    }
+    const int sp = np > 1 ? np : 0;
+    int xu = np, xp = sp;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int yu = __shfl_up_sync(0xffffffffu, xu, o);
+      const int yp = __shfl_up_sync(0xffffffffu, xp, o);
+      if (lane >= o) { xu += yu; xp += yp; }
+    }
+    if (lane == 31) { s_warp_u[warp] = xu; s_warp_p[warp] = xp; }
+    __syncthreads();
+    if (warp == 0) {
+      int wu = s_warp_u[lane], wp = s_warp_p[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int yu = __shfl_up_sync(0xffffffffu, wu, o);
+        const int yp = __shfl_up_sync(0xffffffffu, wp, o);
+        if (lane >= o) { wu += yu; wp += yp; }
+      }
+      s_warp_u[lane] = wu;
+      s_warp_p[lane] = wp;
+    }
+    __syncthreads();
+    const int off_u = s_carry_u + (warp ? s_warp_u[warp - 1] : 0) + xu - np;
+    const int off_p = s_carry_p + (warp ? s_warp_p[warp - 1] : 0) + xp - sp;
+    if (pos < n_items) {
+      const int q0 = a.qo_indptr[rec.x], q_len = a.qo_indptr[rec.x + 1] - q0;
+      const int k0 = a.kv_indptr[rec.x], kv_len = a.kv_indptr[rec.x + 1] - k0;
+      const int kvp = a.kv_ptr[it];
+      int q_valid = q_len - rec.z * a.sbq;
+      q_valid = q_valid > a.sbq ? a.sbq : (q_valid < 0 ? 0 : q_valid);
+      int ragged = 0;
+      const int tail_cols = kv_len % a.sbkv;
+      // lists are ascending: only the item's last entry can be the request's partial block
+      if (tail_cols != 0 && n > 0 && a.kv_idx[kvp + n - 1] == kv_len / a.sbkv) ragged = tail_cols;
+      for (int p = 0; p < np; ++p) {
+        const int j0 = static_cast<int>(static_cast<long long>(n) * p / np);
+        const int j1 = static_cast<int>(static_cast<long long>(n) * (p + 1) / np);
+        if (off_u + p < a.max_units) {
+          int4* dst = reinterpret_cast<int4*>(a.units + 8 * static_cast<int64_t>(off_u + p));
+          const int sp_word = np > 1 ? (((off_p + p) & 0xffff) << 16) | (p << 8) | np : (0xffff << 16) | 1;
+          dst[0] = make_int4(j1 - j0, kvp + j0, rec.y, q0 + rec.z * a.sbq);
+          dst[1] = make_int4(q_valid, k0, p == np - 1 ? ragged : 0, sp_word);
+        }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) { s_carry_u += s_warp_u[31]; s_carry_p += s_warp_p[31]; }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    a.unit_counters[0] = s_carry_u;
+    a.unit_counters[1] = s_carry_p;
+    a.unit_counters[2] = chunk_max;
+    a.unit_counters[3] = (!list_ok || s_carry_u > a.max_units || s_carry_p > a.max_slots || s_carry_p > 0xffff) ? kDevBadIndex : kDevOk;
+  }
+}
+
+cudaError_t launch_attn_units(const UnitArgs& a, cudaStream_t stream) {
+  attn_units_kernel<<<1, 1024, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
 // GEMM work lists (single CTA: the candidate counts are a few thousand at most)
 // ---------------------------------------------------------------------------------------------
 // GEMM-Q: tile records (b, iy, ix0, ix1). Per row block (b, iy) the active column blocks are taken two

@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define FO_ABI_VERSION 1
+#define FO_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define FO_API __attribute__((visibility("default")))
@@ -89,29 +89,63 @@ FO_API int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes
                     int64_t max_kept, int32_t* items, int32_t* kv_ptr, int32_t* kv_idx, int32_t* order,
                     int32_t* counters, void* scratch, size_t scratch_bytes, void* stream);
 
+/* ---- attention work units (no counterpart op in the reference; its planner chunks kv ranges on the host,
+ * include/flashomni/attention/scheduler.cuh:35-64, and merges with attention/cascade.cuh:346-437) -----------
+ * Turns the compaction's lists into the unit list the attention kernel walks, in processing order: one
+ * self-contained record of eight int32 per unit,
+ *   [0] n         kv blocks of the unit (0: an active q-block that keeps nothing)
+ *   [1] kv_off    offset of the unit's first entry in kv_idx
+ *   [2] h         mask head
+ *   [3] q_row0    first row of the q-block in the q / o tensors
+ *   [4] q_valid   rows of the q-block that exist (1..sbq)
+ *   [5] kv_row0   first kv row of the request
+ *   [6] ragged    columns of the request's partial last kv block if the unit's list ends with it, else 0
+ *   [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
+ * An item is one unit unless its kv list is cut: lists are cut only when the launch has at most half as many
+ * items as streams (num_streams = 2 x the number of SMs: the kernel runs two streams of items per SM), into
+ * n_parts = ceil(n_kept / chunk_max) parts of (almost) equal length, chunk_max = max(min_chunk,
+ * ceil(total_kept / num_streams), ceil(max_nkv / 255)). Cuts fall between list ENTRIES, so no part is ever
+ * empty and every part of a split item delivers a partial result before the merge (the reference's split path
+ * cuts kv ranges and merges partials that an early-returning q-block never wrote). Parts of an item are adjacent
+ * and use consecutive partial slots.
+ *   units          int32 [max_units,8]  16-byte aligned
+ *   unit_counters  int32 [4]            n_units, partial slots in use, chunk_max, status (FO_DEV_*)
+ *   arrive         int32 [max_slots]    per slot: parts delivered (a split item counts at its first slot); zeroed
+ *                                       here, and put back to zero by the kernel
+ * max_units >= max_items + num_streams and max_slots >= num_streams + num_streams / 2 always suffice. */
+FO_API int fo_attn_units(const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx, const int32_t* order,
+                         const int32_t* counters, const int32_t* qo_indptr, const int32_t* kv_indptr,
+                         int64_t max_items, int32_t max_nkv, int32_t sbq, int32_t sbkv, int32_t num_streams,
+                         int32_t min_chunk, int64_t max_units, int64_t max_slots, int32_t* units,
+                         int32_t* unit_counters, int32_t* arrive, void* stream);
+/* Bytes of partial-result scratch for `partial_slots` slots (fp32 O of a 128-row q-block plus row maxima and sums). */
+FO_API size_t fo_attn_partial_bytes(int64_t partial_slots);
+
 /* ---- block-sparse attention ------------------------------------------------------------------
  * Replaces torch.ops.flashomni_kernels.batch_sparseFA_with_ragged_kv_run
- * (csrc/batch_sparseFA.cu:67-201 -> include/flashomni/attention/prefill.cuh:1203-1636), consuming
- * the work lists of fo_mask_compact. q [total_q, Hq, D], k/v [total_kv, Hkv, D], o [total_q, Hq, D]
- * with element strides (row, head); the innermost dimension is contiguous. lse (optional, may be
- * null): float32 [total_q, Hq], base 2. Hq here is the number of heads IN THE TENSORS; item head
- * indices are mask heads and map to tensor head (h - head_begin). q-blocks that are not listed are
- * not written. max_items is the capacity the lists were compacted with: the kernel walks
- * min(counters[0], max_items) items, and none at all when counters[2] says that the compaction ran out of
- * room (the output is then untouched and status[0] = FO_DEV_BAD_INDEX). status: FOUR int32 device words
- * that the caller zeroes once: [0] is set to FO_DEV_WAIT_TIMEOUT if a bounded wait ran out; [1] (work-list cursor: items are handed to the CTAs
- * dynamically) and [2] (count of finished CTAs) are used by the kernel and are zero again when it ends, so
- * launches that share the words must not overlap; [3] is reserved.
+ * (csrc/batch_sparseFA.cu:67-201 -> include/flashomni/attention/prefill.cuh:1203-1636), consuming kv_idx of
+ * fo_mask_compact and the units of fo_attn_units. q [total_q, Hq, D], k/v [total_kv, Hkv, D],
+ * o [total_q, Hq, D] with element strides (row, head); the innermost dimension is contiguous. lse (optional,
+ * may be null): float32 [total_q, Hq], base 2. Hq here is the number of heads IN THE TENSORS; unit heads
+ * are mask heads and map to tensor head (h - head_begin). q-blocks that are not listed are
+ * not written. The kernel walks min(unit_counters[0], max_units) units, and none at all when unit_counters[3]
+ * is not FO_DEV_OK or more partial slots are in use than `partial_slots` (the output is then untouched and
+ * status[0] = FO_DEV_BAD_INDEX). The parts of a split item write fp32 partial results into `partials`
+ * (fo_attn_partial_bytes(partial_slots) bytes, 16-byte aligned; null when partial_slots = 0) and the
+ * part that delivers last merges them and writes the rows. status: FOUR int32 device words
+ * that the caller zeroes once: [0] is set to FO_DEV_WAIT_TIMEOUT if a bounded wait ran out;
+ * [1] (unit cursor: units are handed to the streams dynamically) and [2] (count of finished CTAs) are used by
+ * the kernel and are zero again when it ends, so launches that share the words (or `arrive`, `partials`) must
+ * not overlap; [3] is reserved.
  * This build implements D = 128 with 128-row q and kv blocks. */
 FO_API int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
                        int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
                        int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
                        int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
-                       int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr,
-                       int32_t sbq, int32_t sbkv, const int32_t* items, const int32_t* kv_ptr,
-                       const int32_t* kv_idx, const int32_t* order, const int32_t* counters,
-                       int64_t max_items, int32_t head_begin, float sm_scale, int32_t* status,
-                       void* stream);
+                       int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
+                       const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t* arrive,
+                       float* partials, int64_t partial_slots, int32_t head_begin, float sm_scale,
+                       int32_t* status, void* stream);
 
 /* The same with the reference's logits soft cap (include/flashomni/attention/variants.cuh:47-50,72-74: the
  * logit of a (q, k) pair is cap * tanh(q.k * sm_scale / cap) before the softmax). logits_soft_cap = 0 is
@@ -120,11 +154,10 @@ FO_API int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* 
                        int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
                        int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
                        int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
-                       int64_t o_stride_h, const int32_t* qo_indptr, const int32_t* kv_indptr,
-                       int32_t sbq, int32_t sbkv, const int32_t* items, const int32_t* kv_ptr,
-                       const int32_t* kv_idx, const int32_t* order, const int32_t* counters,
-                       int64_t max_items, int32_t head_begin, float sm_scale, float logits_soft_cap,
-                       int32_t* status, void* stream);
+                       int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
+                       const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t* arrive,
+                       float* partials, int64_t partial_slots, int32_t head_begin, float sm_scale,
+                       float logits_soft_cap, int32_t* status, void* stream);
 
 /* ---- GEMM-Q / GEMM-O ---------------------------------------------------------------------------
  * Workspace (device, caller-owned, 16-byte aligned) of fo_gemm_workspace_bytes(...) bytes, laid out

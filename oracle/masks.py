@@ -164,6 +164,50 @@ def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr,
     }
 
 
+def attn_units(lists: dict, qo_indptr, kv_indptr, num_streams: int, min_chunk: int = 16, sbq: int = 128,
+               sbkv: int = 128):
+    """Canonical work units of the attention kernel, from the outputs of `compact` (`lists`): the items in
+    processing order, one self-contained record of eight int32 per unit:
+      [0] n kv blocks of the unit (0: an active q-block that keeps nothing)   [1] offset of its first entry in kv_idx
+      [2] mask head   [3] first row of the q-block in q / o   [4] existing rows of the q-block (1..sbq)
+      [5] first kv row of the request   [6] columns of the request's partial last kv block if the unit ends with it
+      [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
+    A kv list longer than chunk_max is cut into ceil(n_kept / chunk_max) parts of (almost) equal length, part p
+    covering entries [n_kept * p // n_parts, n_kept * (p + 1) // n_parts) -- only when the launch has at most half as
+    many items as streams: chunk_max = max(min_chunk, ceil(total_kept / num_streams), ceil(max_nkv / 255)); otherwise
+    every item is one unit. (The reference's planner cuts kv RANGES instead, include/flashomni/attention/
+    scheduler.cuh:35-64, which with block masks leaves parts without any kept block; cutting the kept LIST cannot.)
+    Returns (units int32 [n_units, 8], partial slots in use, chunk_max)."""
+    items, order, kvp, kv_idx = lists["items"], lists["order"], lists["kv_indptr"], lists["kv_idx"]
+    qo = np.asarray(qo_indptr, dtype=np.int64)
+    kv = np.asarray(kv_indptr, dtype=np.int64)
+    n_items = len(items)
+    total = int(items[:, 3].clip(min=0).sum()) if n_items else 0
+    max_nkv = max([int(-(-(kv[b + 1] - kv[b]) // sbkv)) for b in range(len(kv) - 1)], default=0)
+    chunk_max = 0x7fffffff
+    if 0 < n_items and 2 * n_items <= num_streams:
+        chunk_max = max(min_chunk, -(-total // num_streams), -(-max_nkv // 255))
+    units, slots = [], 0
+    for it in order.tolist():
+        b, h, qb, n = (int(x) for x in items[it])
+        n = max(n, 0)
+        n_parts = -(-n // chunk_max) if n > chunk_max else 1
+        q0, q_len = int(qo[b]), int(qo[b + 1] - qo[b])
+        k0, kv_len = int(kv[b]), int(kv[b + 1] - kv[b])
+        q_valid = min(max(q_len - qb * sbq, 0), sbq)
+        ragged = 0
+        if kv_len % sbkv and n > 0 and int(kv_idx[kvp[it] + n - 1]) == kv_len // sbkv:
+            ragged = kv_len % sbkv
+        for p in range(n_parts):
+            j0, j1 = n * p // n_parts, n * (p + 1) // n_parts
+            word = (((slots + p) & 0xffff) << 16) | (p << 8) | n_parts if n_parts > 1 else (0xffff << 16) | 1
+            word = word - (1 << 32) if word >= (1 << 31) else word
+            units.append((j1 - j0, int(kvp[it]) + j0, h, q0 + qb * sbq, q_valid, k0, ragged if p == n_parts - 1 else 0, word))
+        if n_parts > 1:
+            slots += n_parts
+    return np.asarray(units, dtype=np.int32).reshape(-1, 8), slots, chunk_max
+
+
 def gemm_q_tiles(sparse_info, info_indptr, batch: int, m: int, n: int, num_heads: int,
                  sparse_q_size: int = 128, num_text_tokens: int = 0, is_full: bool = False,
                  head_begin: int = 0, head_dim: int | None = None) -> np.ndarray:

@@ -29,7 +29,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
     assert set(declared) == set(_native.SIGNATURES), "ctypes prototypes and header differ"
-    assert lib.fo_abi_version() == 1
+    assert lib.fo_abi_version() == 2
 
 
 def test_argument_errors_are_reported_not_raised_as_faults():
@@ -40,7 +40,7 @@ def test_argument_errors_are_reported_not_raised_as_faults():
     assert lib.fo_gemm_q(None, None, None, None, 1, 1, 128, 128, 64, 1, 0, 128, 128, 0, 1, None, 0, None, None,
                          0, None) == _native.FO_ERR_INVALID_ARG
     rc = lib.fo_sparse_attn_fwd(*([None] * 5), 1, 128, 128, 1, 1, 128, 128, 128, 128, 128, 128, 128, 128, 128,
-                                *([None] * 2), 128, 128, *([None] * 5), 1, 0, ctypes.c_float(1.0), None, None)
+                                128, 128, *([None] * 3), 1, None, None, 0, 0, ctypes.c_float(1.0), None, None)
     assert rc == _native.FO_ERR_INVALID_ARG
     assert lib.fo_gemm_workspace_bytes(1, 128, 128, 128, 128) >= 64
     assert lib.fo_mask_compact_scratch_bytes(10, 3) >= 10 * 16

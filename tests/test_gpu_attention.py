@@ -325,19 +325,26 @@ def test_undersized_kept_list_is_reported_not_walked(cuda_device):
                              _native.ptr(ws["kv_idx"]), _native.ptr(ws["order"]), _native.ptr(ws["counters"]),
                              _native.ptr(ws["scratch"]), w._scratch_bytes, stream)
     _native.check(rc, "fo_mask_compact")
+    rc = lib.fo_attn_units(_native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
+                           _native.ptr(ws["order"]), _native.ptr(ws["counters"]), _native.ptr(w._qo_indptr_buf),
+                           _native.ptr(w._kv_indptr_buf), w._n_cand, w._max_nkv, 128, 128, w._num_streams, w.MIN_CHUNK,
+                           w._max_units, w._partial_slots, _native.ptr(ws["units"]), _native.ptr(ws["unit_counters"]),
+                           _native.ptr(ws["arrive"]), stream)
+    _native.check(rc, "fo_attn_units")
     q, k, v = (dev(t, cuda_device) for t in (inp.q, inp.k, inp.v))
     prior = dev(wl.randn_bf16(inp.q.shape, 5), cuda_device)
     out = prior.clone()
     rc = lib.fo_sparse_attn_fwd(_native.ptr(q), _native.ptr(k), _native.ptr(v), _native.ptr(out), None, _native.FO_DTYPE_BF16,
                                 S, S, H, H, 128, q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1),
-                                out.stride(0), out.stride(1), _native.ptr(w._qo_indptr_buf), _native.ptr(w._kv_indptr_buf),
-                                128, 128, _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
-                                _native.ptr(ws["order"]), _native.ptr(ws["counters"]), w._n_cand, 0, 128 ** -0.5,
+                                out.stride(0), out.stride(1), 128, 128, _native.ptr(ws["kv_idx"]),
+                                _native.ptr(ws["units"]), _native.ptr(ws["unit_counters"]), w._max_units,
+                                _native.ptr(ws["arrive"]), _native.ptr(w._partials), w._partial_slots, 0, 128 ** -0.5,
                                 _native.ptr(ws["status"]), stream)
     _native.check(rc, "fo_sparse_attn_fwd")
     torch.cuda.synchronize()
-    words = w._ws_words[:8].cpu().tolist()
+    words = w._ws_words[:12].cpu().tolist()
     assert words[2] == _native.FO_DEV_BAD_INDEX          # the compaction's own status
+    assert words[11] == _native.FO_DEV_BAD_INDEX         # the unit builder passes it on
     assert words[4] == _native.FO_DEV_BAD_INDEX          # the attention launch's status word
     assert words[5] == 0 and words[6] == 0               # cursor and arrival count are back at zero
     assert torch.equal(out, prior)
@@ -348,3 +355,52 @@ def test_undersized_kept_list_is_reported_not_walked(cuda_device):
     ref = oa.sparse_attention(inp.q, inp.k, inp.v, [0, S], [0, S], inp.masks.sparse_info, inp.masks.sparse_kv_info,
                               inp.masks.info_indptr, inp.masks.kv_info_indptr)
     assert_close_bf16(o, ref, "attention after an undersized list")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_split_kv_lists_merge_to_the_oracle(cuda_device, dtype):
+    """Few items with long kv lists: the lists are cut into parts that run on different streams, and the part that
+    delivers last merges the partial results (maxima, sums, fp32 O). Against the fp32 oracle, with the log-sum-exp,
+    prior contents for skipped q-blocks, an empty item and a ragged last block; twice in a row on the same wrapper
+    (the per-item arrival counters must be back at zero)."""
+    H, lens = 3, [40 * 128, 17 * 128 + 40]
+    rng = np.random.default_rng(61)
+    qa = [(rng.random((-(-n // 128), H)) < 0.8).astype(np.uint8) for n in lens]
+    kk = [(rng.random((-(-n // 128), H, -(-n // 128))) < 0.8).astype(np.uint8) * a[:, :, None] for n, a in zip(lens, qa)]
+    qa[0][3, 1] = 1; kk[0][3, 1, :] = 0            # an active q-block that keeps nothing
+    qa[1][17, 2] = 1; kk[1][17, 2, :] = 1          # the ragged last q-block against every kv block (ragged last one too)
+    m = wl.pack_masks(qa, kk)
+    T = sum(lens)
+    q, k, v = (wl.randn_bf16((T, H, 128), 62 + i, dtype=dtype) for i in range(3))
+    qo = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    w = _wrapper(cuda_device, qo, qo, H, dtype)
+    prior = wl.randn_bf16(q.shape, 70, dtype=dtype)
+    ref, ref_lse = oa.sparse_attention(q, k, v, qo, qo, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                                       out_prior=prior, return_lse=True)
+    for _ in range(2):
+        o, lse = _run(cuda_device, w, q, k, v, m, out=dev(prior, cuda_device).clone(), return_lse=True)
+        lists = w.work_lists()
+        assert lists["partial_slots_used"] > 0 and lists["n_units"] > lists["n_items"]
+        assert_close_bf16(o, ref, f"split attention {dtype}")
+        act = torch.zeros(T, H, dtype=torch.bool)
+        for b, n in enumerate(lens):
+            for qb in range(-(-n // 128)):
+                for h in range(H):
+                    if qa[b][qb, h]:
+                        act[qo[b] + qb * 128: min(qo[b] + (qb + 1) * 128, qo[b + 1]), h] = True
+        assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-3)
+        assert torch.equal(o.cpu()[~act], prior[~act])
+
+
+def test_split_kv_three_heads_of_the_4608_token_layer(cuda_device):
+    """Three heads of the 4608-token layer, two requests (a rank's share when 24 heads are split over 8 GPUs): about
+    120 items for 296 streams, so lists above 16 blocks are cut."""
+    inp = wl.attention_inputs(2, 3, 4608, 128, 0.5, seed=91)
+    w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, 3)
+    o = _run(cuda_device, w, inp.q, inp.k, inp.v, inp.masks)
+    lists = w.work_lists()
+    assert lists["partial_slots_used"] > 0
+    m = inp.masks
+    ref = oa.sparse_attention(inp.q, inp.k, inp.v, [0, 4608, 9216], [0, 4608, 9216], m.sparse_info, m.sparse_kv_info,
+                              m.info_indptr, m.kv_info_indptr)
+    assert_close_bf16(o, ref, "three heads of the 4608-token layer, split lists")

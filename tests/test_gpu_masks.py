@@ -178,3 +178,37 @@ def test_strided_gather_matches_torch(cuda_device):
     assert torch.equal(back[:, 6:8], srcs[1][:, 6:8]) and int(back[:, :6].abs().sum()) == 0
     with pytest.raises(ValueError):
         PeerExchange.gather([out.data_ptr() + 2], [row], [1], [back.data_ptr()], [row], row)   # misaligned
+
+
+@pytest.mark.parametrize("case", ["few_items_cut", "many_items_whole", "ragged"])
+def test_attention_work_units_bit_exact(cuda_device, case):
+    """The unit list the attention kernel walks (fo_attn_units) against the oracle's statement: long kv lists are
+    cut into parts when the launch has few items per stream, never otherwise."""
+    if case == "few_items_cut":
+        H, lens = 3, [36 * 128]
+        m = wl.flux_masks(1, H, 36, 36, 0.9, seed=21)
+    elif case == "many_items_whole":
+        H, lens = 24, [36 * 128, 36 * 128]
+        m = wl.flux_masks(2, H, 36, 36, 0.9, seed=22)
+    else:
+        H, lens = 3, [700, 128 * 9 + 5, 40]
+        rng = np.random.default_rng(23)
+        qa = [(rng.random((-(-n // 128), H)) < 0.8).astype(np.uint8) for n in lens]
+        kk = [(rng.random((-(-n // 128), H, -(-n // 128))) < 0.7).astype(np.uint8) * a[:, :, None] for n, a in zip(lens, qa)]
+        m = wl.pack_masks(qa, kk)
+    qo = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1024, dtype=torch.uint8, device=cuda_device))
+    w.plan(dev(qo, cuda_device), dev(qo, cuda_device), H, H, 128, q_data_type=torch.bfloat16)
+    w.build_work_lists(*masks_to_device(m, cuda_device))
+    torch.cuda.synchronize()
+    got = w.work_lists()
+    ref = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, qo, H, 128, 128)
+    _assert_lists_equal(got, ref)
+    units, slots, chunk = om.attn_units(ref, qo, qo, w._num_streams, w.MIN_CHUNK)
+    assert got["unit_status"] == 0 and got["chunk_max"] == chunk and got["partial_slots_used"] == slots
+    assert got["n_units"] == len(units) and np.array_equal(got["units"], units)
+    if case == "many_items_whole":
+        assert slots == 0 and len(units) == len(ref["items"])
+    if case == "few_items_cut":
+        assert slots > 0
+    assert got["n_units"] <= w._max_units and slots <= w._partial_slots

@@ -92,6 +92,44 @@ def test_compact_counts_match_unpacked_masks():
     assert om.order_groups(1, 3, 36) == (3, True)
 
 
+def test_attention_units_cut_long_lists_only_when_items_are_few():
+    m = wl.flux_masks(1, 6, 20, 20, 0.7, seed=9, text_blocks=2)
+    qo = kv = np.array([0, 20 * 128 - 50])           # ragged last q and kv block
+    c = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, kv, 6, 128, 128)
+    n = len(c["items"])
+    # more than half as many items as streams: one unit per item, in processing order, no partial slots
+    u, slots, chunk = om.attn_units(c, qo, kv, num_streams=2 * n - 2)
+    assert slots == 0 and chunk == 0x7fffffff and len(u) == n
+    for r, it in zip(u.tolist(), c["order"].tolist()):
+        b, h, qb, nk = c["items"][it].tolist()
+        assert r[0] == nk and r[1] == c["kv_indptr"][it] and r[2] == h and r[3] == qb * 128
+        assert r[4] == (128 if qb < 19 else 128 - 50) and r[5] == 0
+        last_is_partial = nk > 0 and c["kv_idx"][c["kv_indptr"][it] + nk - 1] == 19
+        assert r[6] == (128 - 50 if last_is_partial else 0) and (r[7] & 0xffffffff) == 0xffff0001
+    # few items per stream: lists longer than chunk_max are cut into parts that tile the list without gaps
+    u, slots, chunk = om.attn_units(c, qo, kv, num_streams=2 * n, min_chunk=6)
+    assert chunk == max(6, -(-int(c["items"][:, 3].sum()) // (2 * n)))
+    pos, used = 0, 0
+    for it in c["order"].tolist():
+        nk = int(c["items"][it][3])
+        n_parts = -(-nk // chunk) if nk > chunk else 1
+        recs = u[pos: pos + n_parts].tolist()
+        pos += n_parts
+        assert sum(r[0] for r in recs) == nk and all(r[0] > 0 for r in recs) or nk == 0
+        off = int(c["kv_indptr"][it])
+        for p, r in enumerate(recs):
+            assert r[1] == off
+            off += r[0]
+            w = r[7] & 0xffffffff
+            if n_parts > 1:
+                assert (w & 0xff) == n_parts and ((w >> 8) & 0xff) == p and (w >> 16) == used + p
+            else:
+                assert w == 0xffff0001
+            assert r[6] == 0 or p == n_parts - 1          # only the last part can end with the partial block
+        used += n_parts if n_parts > 1 else 0
+    assert pos == len(u) and used == slots and slots > 0
+
+
 def test_gemm_lists():
     m = wl.flux_masks(2, 4, 6, 6, 0.5, seed=5, text_blocks=1)
     tiles = om.gemm_q_tiles(m.sparse_info, m.info_indptr, 2, 6 * 128, 4 * 128, 4)
