@@ -1151,7 +1151,7 @@ def main():
     ap.add_argument("--no-video", action="store_true", help="skip the video-layer leg of the default run")
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled-row parity checks")
     ap.add_argument("--quick", action="store_true", help="skip the sweeps, the mask-path figures and the baselines")
-    ap.add_argument("--schedule", default="q_first", choices=["q_first", "kv_first"],
+    ap.add_argument("--schedule", default="kv_first", choices=["q_first", "kv_first"],
                     help="flux_block: order of the projections and where the list kernels run")
     ap.add_argument("--graph", dest="graph", action="store_true", default=True,
                     help="replay the step from a CUDA graph (device-resident leg; the default: at 8 GPUs a step is "

@@ -30,7 +30,7 @@ class BlockWeights:
 class SparseDiTAttentionBlock:
     def __init__(self, weights: BlockWeights, num_heads: int, head_dim: int, batch: int, seq: int,
                  head_begin: int = 0, head_count: Optional[int] = None, device=None, dtype=torch.bfloat16,
-                 schedule: str = "q_first", add_cache: bool = True, fuse_kv: bool = True):
+                 schedule: str = "kv_first", add_cache: bool = True, fuse_kv: bool = True):
         """`add_cache=False`: GEMM-O adds nothing to the active heads' sum (a rank of a head partition whose
         partial is summed with the others' later; only one rank, or the sum itself, adds the cache).
         `fuse_kv`: the dense K and V projections run as one GEMM over the stacked weights [W_k; W_v], writing
@@ -39,7 +39,7 @@ class SparseDiTAttentionBlock:
             raise ValueError("schedule must be 'q_first' or 'kv_first'")
         self.schedule = schedule
         self.add_cache = add_cache
-        self.fuse_kv = fuse_kv and schedule == "q_first"
+        self.fuse_kv = fuse_kv
         self._side = None
         self._q_list = self._o_list = None
         self.w = weights
@@ -122,19 +122,27 @@ class SparseDiTAttentionBlock:
             self._side = torch.cuda.Stream(dev)
             self._start = torch.cuda.Event()
         self._start.record(cur)            # everything of the previous step precedes this event
-        flashomni_gemm(x, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
-        self._side.wait_event(self._start)
         n_local = self.hc * D
+        if self.fuse_kv:
+            flashomni_gemm(x, self.wkv, H, is_full=True, out=self.kv, head_dim=D)
+        else:
+            flashomni_gemm(x, self.w.wk, H, is_full=True, out=self.k, head_dim=D)
+        self._side.wait_event(self._start)
         self._q_list = prepare_gemm_q_list(self.B, self.S, n_local, H, sparse_info, sparse_info_indptr, 0,
                                            head_begin=hb, head_dim=D, into=self._q_list, stream=self._side)
         self.wrapper.prepare_masks(sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                                    stream=self._side, after=self._start)
         self._o_list = prepare_gemm_o_list(self.B, self.S, n_local, H, sparse_info, sparse_info_indptr, 0,
                                            head_begin=hb, head_dim=D, into=self._o_list, stream=self._side)
-        flashomni_gemm(x, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
+        if self.fuse_kv:
+            kv = self.kv.view(T, 2 * self.hc, D)
+            k, v = kv[:, :self.hc], kv[:, self.hc:]
+        else:
+            flashomni_gemm(x, self.w.wv, H, is_full=True, out=self.v, head_dim=D)
+            k, v = self.k.view(T, self.hc, D), self.v.view(T, self.hc, D)
         flashomni_gemm(x, self.w.wq, H, sparse_info, sparse_info_indptr, 0, None, out=self.q,
                        head_begin=hb, head_dim=D, worklist=self._q_list)
-        self.wrapper.run(self.q.view(T, self.hc, D), self.k.view(T, self.hc, D), self.v.view(T, self.hc, D),
+        self.wrapper.run(self.q.view(T, self.hc, D), k, v,
                          sparse_info, sparse_kv_info, sparse_info_indptr, sparse_kv_info_indptr,
                          out=self.attn.view(T, self.hc, D))
         flashomni_gemm_reduction(self.attn, self.w.wo, H, sparse_info, sparse_info_indptr, 0,
