@@ -234,6 +234,7 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
     begin_forward = plan
 
     MIN_CHUNK = 16   # shortest part (kv blocks) a kv list is cut into: a unit costs a few microseconds of its own
+    KERNEL = None    # None: chosen from the planned shape; "tile" / "streams" force one of the two kernels (tests)
 
     def _carve_workspace(self) -> None:
         """Lays the work lists out in one int32 buffer: counters[4] | status[4] | unit_counters[4] | items | kv_ptr |
@@ -243,10 +244,12 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         lib = _native.load()
         n, kept = max(self._n_cand, 1), max(self._max_kept, 1)
         scratch_bytes = lib.fo_mask_compact_scratch_bytes(n, self._max_nkv)
-        # the kernel runs two streams of items per SM; kv lists are only cut when there are at most half as many
-        # items as streams, into at most streams + items <= 1.5 * streams parts
+        # Two kernels walk the unit list. With at most as many candidate items as streams (two per SM) the launch
+        # goes to the two-stream kernel, whose kv lists may be cut into parts (at most streams + items <= 1.5 * streams
+        # of them) with partial results in scratch; with more, every SM gets several whole items and the one-tile
+        # kernel is the faster shape.
         self._num_streams = 2 * torch.cuda.get_device_properties(self.device).multi_processor_count
-        may_split = self._n_cand <= 4 * self._num_streams   # the masks may leave few enough items
+        may_split = self._n_cand <= self._num_streams if self.KERNEL is None else self.KERNEL == "streams"
         self._max_units = n + (self._num_streams if may_split else 0)
         self._partial_slots = (self._num_streams + self._num_streams // 2) if may_split else 0
 

@@ -278,6 +278,8 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
     if (r == 0) r = encode_tmap_16bit(&a.tmap_v, v, 3, kd, vs, box);
     const uint64_t os[3] = {0, static_cast<uint64_t>(o_stride_h) * 2, static_cast<uint64_t>(o_stride_n) * 2};
     if (r == 0) r = encode_tmap_16bit(&a.tmap_o, o, 3, qd, os, box);  // stores of 64 columns x 128 rows
+    const uint32_t obox16[3] = {32, 1, 16};
+    if (r == 0) r = encode_tmap_16bit(&a.tmap_o16, o, 3, qd, os, obox16, false);
     if (r != 0) {
       char buf[96];
       snprintf(buf, sizeof(buf), "fo_sparse_attn_fwd: cuTensorMapEncodeTiled failed (%d)", r);
@@ -309,7 +311,11 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   a.status = status;
   int64_t ctas = static_cast<int64_t>(sm_count());  // one persistent CTA per SM
   if (ctas > max_units) ctas = max_units;
-  const cudaError_t e = launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
+  // Two kernels read the same unit records: with room for partial results (partial_slots > 0: the caller expects
+  // few units, and the unit builder may have cut kv lists) two streams of units run per SM; without, one unit at a
+  // time per SM with two softmax groups on alternate kv blocks, the faster shape when every SM gets several units.
+  const cudaError_t e = partial_slots > 0 ? launch_attention_streams(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream))
+                                          : launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
   count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_sparse_attn_fwd", e);
 }

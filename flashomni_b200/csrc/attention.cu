@@ -1,4 +1,5 @@
-// Block-sparse prefill attention on tcgen05 / TMEM / TMA, driven by compacted work lists.
+// Block-sparse prefill attention on tcgen05 / TMEM / TMA, driven by compacted work lists: the kernel for launches
+// with MANY work units (several per SM). Launches with few units take attention_streams.cu instead.
 //
 // What it computes (reference: include/flashomni/attention/prefill.cuh:1203-1531): for every work
 // item (b, h, qb) -- an active 128-row q-block of one head -- and its ascending list of kept
@@ -6,25 +7,30 @@
 // base-2 online softmax, output rounded to the input dtype. q-blocks that are not in the list are
 // never written. An item with an empty list writes zeros (lse = -5e4), like the reference.
 //
-// One persistent CTA per SM runs TWO independent streams of items, A and B. A stream owns a q tile in
-// shared memory, one K and one V tile slot, an S and an O accumulator in TMEM (S_A, S_B, O_A, O_B = 512
-// columns), a softmax warpgroup, a TMA producer thread and an MMA issuer thread, and walks its items as one
-// sequence of kv blocks:
+// One persistent CTA per SM walks its items as ONE sequence of kv blocks g = 0, 1, 2, ... and
+// software-pipelines it:
 //
-//   issuer     S = Q K_j^T                      ... O (+)= P V_j,  then S = Q K_{j+1}^T ...
-//   softmax             S -> registers -> P (16 bit, written over S)
+//   tensor pipe     S[g&1] = Q K_g^T   (QK issuer)   and   O (+)= P[g&1] V_g   (PV issuer)
+//   softmax group   g&1:  S[g&1] -> registers -> P[g&1]
 //
-// Inside a stream these steps depend on each other (P lives in S's columns, so the next Q K^T follows the
-// P V that reads it); the tensor pipe and the exponential unit are kept busy by the OTHER stream, which is
-// in the opposite phase. Nothing is shared between the streams but the hardware: no running maximum handed
-// between groups, no exchange between threads of a row (one thread owns a whole row of S: TMEM lane = row).
-// Items are positions of the work list's processing order, handed out dynamically: the first 2 x grid
-// positions go to the streams in launch order, the rest are drawn from a device-wide cursor by the stream's
-// producer and passed to its other roles through a small shared-memory queue.
-// Warps: 0-3 softmax A, 4-7 softmax B (`setmaxnreg` gives them 224 registers: a row of S is held in
-// registers, read from TMEM once), 8 / 9 TMA producers of A / B (Q, K, V tiles of 32 KB; K and V one slot
-// each), 10 / 11 MMA issuers of A / B. Whole q-blocks leave through a 16 KB staging area per stream (two
-// rounds of 64 columns, 128-byte swizzle) and TMA stores. Every mbarrier wait is bounded.
+// Items are positions of the work list's processing order, handed out dynamically: position i < grid
+// size goes to CTA i, the rest are drawn from a device-wide cursor by the K producer and passed to the
+// other roles through a small shared-memory queue.
+// TMEM (512 columns): S0, S1 (fp32, 128 each), O (fp32, 128), P0, P1 (16 bit, 64 each). S is
+// double-buffered and P does not alias S, so the QK and PV batches are independent of each other and
+// of the softmax in between; they are issued by two different threads, because a thread that issues a
+// batch is held until the batch has drained.
+// The softmax is split into two groups of eight warps that take alternate blocks (group = g & 1), two
+// threads per q row with 64 columns each: while one group is in its exponentials the other one loads,
+// reduces and hands over. S is read twice (row maximum, then exponentials) instead of being held in
+// registers across the exchanges; the two halves of a row meet through shared memory; the running
+// maximum passes from block to block through shared memory (m_pub / m_ready); each thread keeps its
+// own partial row sum, and the four of a row are merged, with the output, in the epilogue (whole
+// q-blocks leave through a per-warp staging area and TMA box stores).
+// Warps: 0-7 softmax group 0, 8-15 softmax group 1 (TMEM lane = q row; `setmaxnreg` gives them 112
+// registers), 16 TMA producer of Q (double-buffered) and K (two-slot FIFO of 32 KB tiles) and drawer of
+// work-list positions, 17 QK issuer, 18 PV issuer, 19 TMA producer of V (its own two-slot FIFO).
+// Every mbarrier wait is bounded.
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -39,52 +45,54 @@ namespace {
 constexpr int kBQ = 128, kBKV = 128, kD = 128;
 constexpr int kTileBytes = 128 * kD * 2;    // 32 KB: a 128-row tile of Q, K or V
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half (one swizzle-atom column)
-constexpr int kStreams = 2;
-constexpr int kWgWarps = 4;                 // warps of a softmax warpgroup (one thread per q row)
-constexpr int kSoftmaxWarps = kStreams * kWgWarps;
-constexpr int kWarpProducer = kSoftmaxWarps;          // + stream
-constexpr int kWarpIssuer = kSoftmaxWarps + kStreams;  // + stream
-constexpr int kWarpTmem = kWarpIssuer;                 // owner of the TMEM allocation
-constexpr int kThreads = (kSoftmaxWarps + 2 * kStreams) * 32;  // 384
-constexpr int kRegsSoftmax = 224, kRegsOther = 56;  // register split between the warpgroups (setmaxnreg)
+constexpr int kRingK = 2, kRingV = 2;  // separate FIFOs of 32 KB tiles for K and V
+constexpr int kRing = kRingK + kRingV;
+constexpr int kQBufs = 2;
+constexpr int kGroupWarps = 8;                  // warps of one softmax group (two threads per q row)
+constexpr int kSoftmaxWarps = 2 * kGroupWarps;
+constexpr int kWarpProducer = kSoftmaxWarps;
+constexpr int kWarpQK = kSoftmaxWarps + 1;      // issues S = Q K^T
+constexpr int kWarpPV = kSoftmaxWarps + 2;      // issues O += P V
+constexpr int kWarpProducerV = kSoftmaxWarps + 3;
+constexpr int kWarpMma = kWarpQK;               // owner of the TMEM allocation
+constexpr int kThreads = (kSoftmaxWarps + 4) * 32;  // 640: four softmax warpgroups and the producer / issuer warpgroup
+constexpr int kRegsSoftmax = 112, kRegsOther = 32;  // register split between the warpgroups (setmaxnreg)
 // setmaxnreg.inc waits until the registers are free in the pool the CTA was launched with (threads x the
 // per-thread count the compiler settles on for this block size): a split that asks for more never returns.
 constexpr int kRegsAtLaunch = (65536 / kThreads) / 8 * 8;
 static_assert(kSoftmaxWarps * 32 * kRegsSoftmax + (kThreads - kSoftmaxWarps * 32) * kRegsOther <= kThreads * kRegsAtLaunch,
               "register split exceeds the CTA's register pool");
 constexpr int kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColO = 256;  // + 128 * stream; P (16 bit) occupies the first 64 columns of S
+constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 constexpr int kRotStep = FO_ROT_STEP;       // q-block qb starts its kv list at entry (qb * kRotStep) mod length
-constexpr int kItemQ = 4;                   // entries of a stream's item queue
-constexpr int kItemReaders = kWgWarps + 1;  // the stream's softmax warps and its MMA issuer
-constexpr float kRescaleThreshold = 8.0f;   // lazy rescale: keep the old max while exp2 stays <= 2^8
-#ifndef FO_SPLIT_P
-#define FO_SPLIT_P 1
-#endif
-constexpr bool kSplitP = FO_SPLIT_P != 0;  // hand P to the P V in two halves
-constexpr int kStageBytes = 128 * 128;      // output staging of a stream: 128 rows x 64 columns
+constexpr int kItemQ = 8;                   // entries of the item queue
+constexpr int kItemReaders = kSoftmaxWarps + 3;  // softmax warps, V producer, the two MMA issuers
+constexpr float kRescaleThreshold = 8.0f;  // lazy rescale: keep the old max while exp2 stays <= 2^8
 
-struct StreamBars {
-  // One mbarrier per EVENT, waited for by every role that depends on it (a tcgen05.commit between two MMA batches
-  // costs tensor-pipe time, so a turn commits twice: once behind its P V, once behind its Q K^T).
-  uint64_t q_full, k_full, v_full;  // TMA loads landed
-  uint64_t s_full;    // Q K^T of a block complete: S may be read; the K slot (and after an item's last block the Q slot) is free
-  uint64_t p_half[2]; // P written by the softmax warps, kv columns 0-63 / 64-127 of the block (count = warps)
-  uint64_t pv_done;   // P V of a block complete: the V slot is free, O may be rescaled, after an item's last block O is final
-  uint64_t o_free;    // O copied to registers by the epilogue (count = warps)
-  uint64_t wg_bar;    // bounded barrier of the stream's softmax warpgroup (count = warps)
-  uint64_t iq_full[kItemQ], iq_empty[kItemQ];  // item queue: the producer draws work-list positions for the stream
-  int item_q[kItemQ];
-  int merge_go;       // this stream's part of a split item delivered last and merges the item's partial results
-};
 struct Tail {
-  StreamBars st[kStreams];
+  uint64_t q_full[kQBufs], q_empty[kQBufs];
+  uint64_t k_full[kRingK], k_empty[kRingK], v_full[kRingV], v_empty[kRingV];
+  uint64_t s_full[2], s_free[2];  // S buffer written by QK / copied to registers by its softmax group
+  uint64_t p_full[2], pv_done[2];  // indexed by block parity, so that no waiter can fall two phases behind
+  uint64_t m_ready[2];             // running maximum after a block of this parity has been published
+  uint64_t stats_ready[2];         // indexed by item parity: both groups have published (m, l) of the item
+  uint64_t o_full, o_free;
+  uint64_t iq_full[kItemQ], iq_empty[kItemQ];  // item queue: the K producer draws work-list positions for the CTA
+  int item_q[kItemQ];
   uint32_t tmem_base;
   int abort_flag;
-  int pipe_token;   // held by the issuer whose MMAs go into the tensor pipe next
+  uint64_t pair_bar[2][4];   // [group][quadrant]: the two warps that share 32 rows
+  float m_pub[2][128];       // [block parity][row]: running maximum in use after that block
+  float xmax[2][2][2][128];  // [group][parity of the group's block count][column half][row]: half-row maxima
+  float stats_m[2][4][128];  // [item parity][2 * group + half][row]: the maximum the partial sum refers to
+  float stats_l[2][4][128];  // [item parity][2 * group + half][row]: partial row sum
 };
 
-constexpr int kSmemBytes = kStreams * 3 * kTileBytes + kStreams * kStageBytes + 1024 + static_cast<int>(sizeof(Tail));
+
+
+constexpr int kOutStageBytes = 16 * 64;  // per softmax warp: 16 rows x 32 output columns
+constexpr int kSmemBytes = (kQBufs + kRing) * kTileBytes + kSoftmaxWarps * kOutStageBytes + 1024 +
+                           static_cast<int>(sizeof(Tail));
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 
 // The kept kv blocks of an item are visited in rotated order (the online softmax does not care):
@@ -93,40 +101,33 @@ __device__ __forceinline__ int rot_of(int qb, int n) {
   return static_cast<int>(static_cast<unsigned>(qb * kRotStep) % static_cast<unsigned>(n));
 }
 
-// A whole warp waits (every lane takes the acquire) and agrees on the outcome, so that a wait that runs out
-// never leaves the lanes of a warp on different sides of a warp-collective instruction.
-__device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
-}
-
-// Work-list positions are handed out dynamically: position blockIdx.x + stream * gridDim.x goes to the stream
-// at launch, the following ones are drawn from a device-wide cursor by the stream's producer, which passes them
-// to the other roles through a small shared-memory queue (entry k in slot k % kItemQ, -1 ends the sequence).
+// Work-list positions are handed out dynamically: position i < gridDim.x goes to CTA i, the following ones are
+// drawn from a device-wide cursor by the CTA's K producer, which passes them to the other roles through a small
+// shared-memory queue (entry k in slot k % kItemQ, -1 ends the sequence). A CTA that got short items draws more.
 struct ItemDraw {  // the drawing role (one thread)
-  StreamBars* sb;
+  Tail* tail;
   int32_t* cursor;
   volatile int* abort_flag;
   int n_items, n_pub;
   int p0, p1, p2;  // current, published next, drawn (still in flight) after next: the atomic never sits between two items
   bool started, ended;
   __device__ __forceinline__ int draw() {
-    const int p = atomicAdd(cursor, 1) + kStreams * static_cast<int>(gridDim.x);
+    const int p = atomicAdd(cursor, 1) + static_cast<int>(gridDim.x);
     return p < n_items ? p : -1;
   }
   __device__ __forceinline__ bool publish(int v) {
     if (ended) return true;
     const int slot = n_pub % kItemQ;
-    if (!mbar_wait(&sb->iq_empty[slot], (static_cast<uint32_t>(n_pub / kItemQ) & 1u) ^ 1u, abort_flag)) return false;
-    sb->item_q[slot] = v;
-    mbar_arrive(&sb->iq_full[slot]);
+    if (!mbar_wait(&tail->iq_empty[slot], (static_cast<uint32_t>(n_pub / kItemQ) & 1u) ^ 1u, abort_flag)) return false;
+    tail->item_q[slot] = v;
+    mbar_arrive(&tail->iq_full[slot]);
     ++n_pub;
     if (v < 0) ended = true;
     return true;
   }
-  __device__ __forceinline__ void init(StreamBars* s, int stream, int32_t* cur, volatile int* ab, int n) {
-    sb = s; cursor = cur; abort_flag = ab; n_items = n; n_pub = 0; started = false; ended = false;
-    const int first = static_cast<int>(blockIdx.x) + stream * static_cast<int>(gridDim.x);
-    p0 = first < n ? first : -1;
+  __device__ __forceinline__ void init(Tail* t, int32_t* cur, volatile int* ab, int n) {
+    tail = t; cursor = cur; abort_flag = ab; n_items = n; n_pub = 0; started = false; ended = false;
+    p0 = static_cast<int>(blockIdx.x) < n ? static_cast<int>(blockIdx.x) : -1;
     p1 = p2 = -1;
     bool ok = publish(p0);
     if (ok && p0 >= 0) {
@@ -149,59 +150,39 @@ struct ItemDraw {  // the drawing role (one thread)
 
 template <bool kWholeWarp>
 struct ItemRead {  // the reading roles: one thread, or all lanes of a softmax warp
-  StreamBars* sb;
+  Tail* tail;
   volatile int* abort_flag;
   int k;
-  __device__ __forceinline__ void init(StreamBars* s, volatile int* ab) { sb = s; abort_flag = ab; k = 0; }
+  __device__ __forceinline__ void init(Tail* t, volatile int* ab) { tail = t; abort_flag = ab; k = 0; }
   __device__ __forceinline__ int next() {
     const int slot = k % kItemQ;
-    if (kWholeWarp) {
-      if (!wait_all(&sb->iq_full[slot], static_cast<uint32_t>(k / kItemQ) & 1u, abort_flag)) return -1;
-    } else {
-      if (!mbar_wait(&sb->iq_full[slot], static_cast<uint32_t>(k / kItemQ) & 1u, abort_flag)) return -1;
-    }
-    const int v = sb->item_q[slot];
+    if (!mbar_wait(&tail->iq_full[slot], static_cast<uint32_t>(k / kItemQ) & 1u, abort_flag)) return -1;
+    const int v = tail->item_q[slot];
     if (kWholeWarp) {
       __syncwarp();
-      if ((threadIdx.x & 31) == 0) mbar_arrive(&sb->iq_empty[slot]);
+      if ((threadIdx.x & 31) == 0) mbar_arrive(&tail->iq_empty[slot]);
     } else {
-      mbar_arrive(&sb->iq_empty[slot]);
+      mbar_arrive(&tail->iq_empty[slot]);
     }
     ++k;
     return v;
   }
 };
 
-// The walk of a stream's items as a flat sequence of kv blocks. kNeedKv: the role needs the kv-block indices
-// (the producer); the others only need the shape of the sequence (and the softmax warps which step, if any, is
-// the ragged last block of its request). No global load sits between two blocks of an item.
-template <class Src, bool kNeedKv, bool kNeedRagged>
-struct BlockSeq {
-  Src src;
-  int item_no;   // index among this stream's non-empty units
-  int h, n, j;                   // head inside the q / o tensors, kv blocks of the unit, current block
-  int q_row0, q_valid, kv_row0;  // first row of the q-block in q / o, its existing rows, first kv row of the request
-  int slot, part, nparts;        // partial slot, part number and count (a whole item: nparts = 1)
-  int kvb, kvb_next;  // kv-block index of the current block; the next one is fetched a block early
-  int rot;            // rotation of the visiting order inside the item's kv list
+// The same walk for the softmax groups, which do not need the kv-block indices: only which step of an
+// item (if any) is the ragged last block of its request. No global load sits between two blocks.
+struct GroupSeq {
+  ItemRead<true> src;
+  int h, n, j;            // head inside the q / o tensors, kv blocks of the unit, current block
+  int q_row0, q_valid;    // first row of the q-block in q / o, its existing rows
   int ragged_j, ragged_valid;  // visiting step of the request's partial last kv block (-1: none) and its columns
-  const int32_t* kv;
-  __device__ __forceinline__ void init() {
-    item_no = -1; n = 0; j = 0; kv = nullptr; slot = 0; part = 0; nparts = 1;
-    h = q_row0 = q_valid = kv_row0 = 0; kvb = kvb_next = 0; rot = 0; ragged_j = -1; ragged_valid = 0;
+  __device__ __forceinline__ void init(Tail* tail, volatile int* abort_flag) {
+    src.init(tail, abort_flag); n = 0; j = 0;
+    h = q_row0 = q_valid = 0; ragged_j = -1; ragged_valid = 0;
   }
-  // Advances to the next block; `on_empty(q_row0, q_valid, h)` is called for every item without kv blocks that
-  // is passed on the way. Returns false at the end of the sequence.
   template <class F>
   __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
-    if (j + 1 < n) {
-      ++j;
-      if (kNeedKv) {
-        kvb = kvb_next;
-        if (j + 1 < n) kvb_next = kv[at(j + 1)];
-      }
-      return true;
-    }
+    if (j + 1 < n) { ++j; return true; }
     while (true) {
       const int pos = src.next();
       if (pos < 0) break;
@@ -210,23 +191,59 @@ struct BlockSeq {
       const int4 u0 = up[0], u1 = up[1];
       if (u0.x <= 0) { on_empty(u0.w, u1.x, u0.z - a.head_begin); continue; }
       n = u0.x; j = 0;
-      h = u0.z - a.head_begin;
-      q_row0 = u0.w; q_valid = u1.x; kv_row0 = u1.y;
-      slot = static_cast<int>(static_cast<unsigned>(u1.w) >> 16); part = (u1.w >> 8) & 0xff; nparts = u1.w & 0xff;
+      h = u0.z - a.head_begin; q_row0 = u0.w; q_valid = u1.x;
+      ragged_j = -1;
+      if (u1.z != 0) {  // the unit's last entry is the request's partial kv block
+        ragged_j = n - 1 - rot_of(q_row0 >> 7, n);
+        if (ragged_j < 0) ragged_j += n;
+        ragged_valid = u1.z;
+      }
+      return true;
+    }
+    n = 0; j = 0;
+    return false;
+  }
+  __device__ __forceinline__ bool first() const { return j == 0; }
+  __device__ __forceinline__ bool last() const { return j == n - 1; }
+  __device__ __forceinline__ int valid() const { return j == ragged_j ? ragged_valid : kBKV; }
+};
+
+// Walks the CTA's share of the schedule as a flat sequence of kv blocks.
+template <class Src>
+struct BlockSeq {
+  Src src;
+  int item_no;   // index among this CTA's non-empty units (selects the Q buffer, o_full / o_free phases)
+  int h, n, j;
+  int q_row0, kv_row0;  // first row of the q-block in q / o, first kv row of the request
+  int kvb, kvb_next;  // kv-block index of the current block; the next one is fetched a block early
+  int rot;            // rotation of the visiting order inside the unit's kv list
+  const int32_t* kv;
+  __device__ __forceinline__ void init() {
+    item_no = -1; n = 0; j = 0; kv = nullptr;
+    h = q_row0 = kv_row0 = 0; kvb = kvb_next = 0; rot = 0;
+  }
+  // Advances to the next block; `on_empty(q_row0, q_valid, h)` is called for every item without kv blocks that
+  // is passed on the way. Returns false at the end of the sequence.
+  template <class F>
+  __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
+    if (j + 1 < n) {
+      ++j;
+      kvb = kvb_next;
+      if (j + 1 < n) kvb_next = kv[at(j + 1)];
+      return true;
+    }
+    while (true) {
+      const int pos = src.next();
+      if (pos < 0) break;
+      const int4* up = reinterpret_cast<const int4*>(a.units + 8 * static_cast<int64_t>(pos));
+      const int4 u0 = up[0], u1 = up[1];
+      if (u0.x <= 0) { on_empty(u0.w, u1.x, u0.z - a.head_begin); continue; }
+      n = u0.x; j = 0;
+      h = u0.z - a.head_begin; q_row0 = u0.w; kv_row0 = u1.y;
+      kv = a.kv_idx + u0.y;
       rot = rot_of(q_row0 >> 7, n);
-      if (kNeedKv) {
-        kv = a.kv_idx + u0.y;
-        kvb = kv[at(0)];
-        if (n > 1) kvb_next = kv[at(1)];
-      }
-      if (kNeedRagged) {
-        ragged_j = -1;
-        if (u1.z != 0) {  // the unit's last entry is the request's partial kv block
-          ragged_j = n - 1 - rot;
-          if (ragged_j < 0) ragged_j += n;
-          ragged_valid = u1.z;
-        }
-      }
+      kvb = kv[at(0)];
+      if (n > 1) kvb_next = kv[at(1)];
       ++item_no;
       return true;
     }
@@ -239,7 +256,6 @@ struct BlockSeq {
   }
   __device__ __forceinline__ bool first() const { return j == 0; }
   __device__ __forceinline__ bool last() const { return j == n - 1; }
-  __device__ __forceinline__ int valid() const { return j == ragged_j ? ragged_valid : kBKV; }
 };
 
 template <bool kBf16, bool kSoftCap>
@@ -247,39 +263,43 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
-  // per stream: Q, K, V tiles; then the two staging areas; then the barriers
-  uint8_t* smem_stage = smem + kStreams * 3 * kTileBytes;
-  Tail* tail = reinterpret_cast<Tail*>(smem_stage + kStreams * kStageBytes);
+  uint8_t* smem_q = smem;                           // kQBufs tiles
+  uint8_t* smem_ring = smem + kQBufs * kTileBytes;  // kRing tiles
+  uint8_t* smem_ostage = smem + (kQBufs + kRing) * kTileBytes;  // output staging of the softmax warps
+  Tail* tail = reinterpret_cast<Tail*>(smem_ostage + kSoftmaxWarps * kOutStageBytes);
   volatile int* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int x = 0; x < kStreams; ++x) {
-      StreamBars* sb = &tail->st[x];
-      mbar_init(&sb->q_full, 1);
-      mbar_init(&sb->k_full, 1);
-      mbar_init(&sb->v_full, 1);
-      mbar_init(&sb->s_full, 1);
-      mbar_init(&sb->p_half[0], kWgWarps);
-      mbar_init(&sb->p_half[1], kWgWarps);
-      mbar_init(&sb->pv_done, 1);
-      mbar_init(&sb->o_free, kWgWarps);
-      mbar_init(&sb->wg_bar, kWgWarps);
-      for (int i = 0; i < kItemQ; ++i) { mbar_init(&sb->iq_full[i], 1); mbar_init(&sb->iq_empty[i], kItemReaders); }
+    for (int i = 0; i < kQBufs; ++i) { mbar_init(&tail->q_full[i], 1); mbar_init(&tail->q_empty[i], 1); }
+    for (int i = 0; i < kRingK; ++i) { mbar_init(&tail->k_full[i], 1); mbar_init(&tail->k_empty[i], 1); }
+    for (int i = 0; i < kRingV; ++i) { mbar_init(&tail->v_full[i], 1); mbar_init(&tail->v_empty[i], 1); }
+    mbar_init(&tail->s_full[0], 1);
+    mbar_init(&tail->s_full[1], 1);
+    mbar_init(&tail->s_free[0], kGroupWarps);
+    mbar_init(&tail->s_free[1], kGroupWarps);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tail->p_full[i], kGroupWarps);
+      mbar_init(&tail->pv_done[i], 1);
+      mbar_init(&tail->m_ready[i], kGroupWarps);
+      mbar_init(&tail->stats_ready[i], kSoftmaxWarps);
     }
+    mbar_init(&tail->o_full, 1);
+    mbar_init(&tail->o_free, kSoftmaxWarps);
+    for (int i = 0; i < kItemQ; ++i) { mbar_init(&tail->iq_full[i], 1); mbar_init(&tail->iq_empty[i], kItemReaders); }
+    for (int i = 0; i < 8; ++i) mbar_init(&tail->pair_bar[i >> 2][i & 3], 2);
     tail->abort_flag = 0;
-    tail->pipe_token = 0;
     fence_barrier_init();
   }
   if (warp == kWarpProducer && lane == 0) {
     tma_prefetch_desc(&a.tmap_q);
     tma_prefetch_desc(&a.tmap_k);
     tma_prefetch_desc(&a.tmap_v);
-    tma_prefetch_desc(&a.tmap_o);
+    tma_prefetch_desc(&a.tmap_o16);
   }
-  if (warp == kWarpTmem) {
+  if (warp == kWarpMma) {
     tmem_alloc(&tail->tmem_base, kTmemCols);
     tmem_relinquish();
   }
@@ -288,182 +308,195 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = tail->tmem_base;
 
-  // The lists may be incomplete: a compaction or unit builder that ran out of room records it in its status word
+  // The list may be shorter than counters[0] says: a compaction that ran out of room records it in counters[2]
   // and leaves records unwritten. Nothing of such a list is dereferenced; the launch only reports it.
-  const bool list_bad = a.unit_counters[3] != kDevOk || a.unit_counters[1] > a.partial_slots;
-  int n_items = a.unit_counters[0];  // units: whole items or parts of items
+  // lists are never cut for this kernel (the unit builder is told so): every unit is a whole item
+  const bool list_bad = a.unit_counters[3] != kDevOk || a.unit_counters[1] != 0;
+  int n_items = a.unit_counters[0];
   if (list_bad || n_items < 0) n_items = 0;
   if (n_items > a.max_units) n_items = a.max_units;
   auto ignore_empty = [](int, int, int) {};
 
+  // The softmax warps take the registers that the producer / issuer warpgroup does not need.
   if (warp >= kSoftmaxWarps) {
-    // ================================================================== producers and issuers (one thread each)
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-    const int X = (warp - kSoftmaxWarps) & 1;
-    StreamBars* sb = &tail->st[X];
-    uint8_t* smem_q = smem + X * 3 * kTileBytes;
-    uint8_t* smem_k = smem_q + kTileBytes;
-    uint8_t* smem_v = smem_k + kTileBytes;
-    if (warp < kWarpIssuer) {
-      // ---------------------------------------------------------------- TMA producer of the stream's Q, K and V tiles
-      if (lane == 0) {
-        BlockSeq<ItemDraw, true, false> seq;
-        seq.init();
-        seq.src.init(sb, X, a.status + 1, abort_flag, n_items);
-        uint32_t g = 0;
-        int kv_row0 = 0;
-        while (seq.next(a, ignore_empty)) {
-          const int hq = seq.h;
-          const int hk = hq / a.group_size;
-          // the K slot (and, for a new item, the Q slot) is free once the Q K^T of the stream's previous block is done
-          if (!mbar_wait(&sb->s_full, (g & 1u) ^ 1u, abort_flag)) break;
-          if (seq.first()) {
-            kv_row0 = seq.kv_row0;
-            const int q_row = seq.q_row0;
-            mbar_expect_tx(&sb->q_full, kTileBytes);
-            tma_load_3d(smem_q, &a.tmap_q, &sb->q_full, 0, hq, q_row);
-            tma_load_3d(smem_q + kHalfBytes, &a.tmap_q, &sb->q_full, 64, hq, q_row);
-          }
-          const int row = kv_row0 + seq.kvb * kBKV;
-          mbar_expect_tx(&sb->k_full, kTileBytes);
-          tma_load_3d(smem_k, &a.tmap_k, &sb->k_full, 0, hk, row);
-          tma_load_3d(smem_k + kHalfBytes, &a.tmap_k, &sb->k_full, 64, hk, row);
-          // the V slot is free once the P V of the previous block is done
-          if (!mbar_wait(&sb->pv_done, (g & 1u) ^ 1u, abort_flag)) break;
-          mbar_expect_tx(&sb->v_full, kTileBytes);
-          tma_load_3d(smem_v, &a.tmap_v, &sb->v_full, 0, hk, row);
-          tma_load_3d(smem_v + kHalfBytes, &a.tmap_v, &sb->v_full, 64, hk, row);
-          ++g;
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+  if (warp == kWarpProducer) {
+    // ------------------------------------------------------------------ TMA producer of Q and K tiles
+    // K and V have their own producer threads: a K tile is requested as soon as its slot has been
+    // read by the QK two blocks earlier, whatever the state of the V FIFO (and the other way round).
+    if (lane == 0) {
+      BlockSeq<ItemDraw> seq;
+      seq.init();
+      seq.src.init(tail, a.status + 1, abort_flag, n_items);
+      uint32_t nk = 0;                   // K tiles pushed so far
+      uint32_t q_uses[kQBufs] = {0, 0};  // loads issued per Q buffer
+      int kv_row0 = 0;                   // first kv row of the current item's request
+      bool ok = true;
+      while (ok && seq.next(a, ignore_empty)) {
+        const int hq = seq.h;
+        const int hk = hq / a.group_size;
+        if (seq.first()) {  // new item: its Q tile goes to buffer item_no & 1
+          kv_row0 = seq.kv_row0;
+          const int qb_i = seq.item_no & 1;
+          if (!mbar_wait(&tail->q_empty[qb_i], (q_uses[qb_i] & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          ++q_uses[qb_i];
+          const int q_row = seq.q_row0;
+          uint8_t* dst = smem_q + qb_i * kTileBytes;
+          mbar_expect_tx(&tail->q_full[qb_i], kTileBytes);
+          tma_load_3d(dst, &a.tmap_q, &tail->q_full[qb_i], 0, hq, q_row);
+          tma_load_3d(dst + kHalfBytes, &a.tmap_q, &tail->q_full[qb_i], 64, hq, q_row);
         }
+        const int slot = static_cast<int>(nk % kRingK);
+        if (!mbar_wait(&tail->k_empty[slot], ((nk / kRingK) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        ++nk;
+        uint8_t* dst = smem_ring + slot * kTileBytes;
+        const int row = kv_row0 + seq.kvb * kBKV;
+        mbar_expect_tx(&tail->k_full[slot], kTileBytes);
+        tma_load_3d(dst, &a.tmap_k, &tail->k_full[slot], 0, hk, row);
+        tma_load_3d(dst + kHalfBytes, &a.tmap_k, &tail->k_full[slot], 64, hk, row);
       }
-    } else {
-      // ---------------------------------------------------------------- MMA issuer of the stream
-      if (lane == 0) {
-        constexpr uint32_t idesc_qk = make_idesc_f16(kBQ, kBKV, kBf16, 0, 0);
-        constexpr uint32_t idesc_pv = make_idesc_f16(kBQ, kD, kBf16, 0, 1);
-        // descriptors: constant high word, low word holds the address. Q and K are K-major (128-byte swizzle);
-        // V is MN-major: its two 64-column halves are 16 KB apart (leading byte offset)
-        const uint64_t dq = make_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
-        const uint32_t hi_k = static_cast<uint32_t>(dq >> 32);
-        const uint32_t q_lo = static_cast<uint32_t>(dq);
-        const uint32_t k_lo = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(smem_k), 16, 1024));
-        const uint64_t dv = make_smem_desc_sw128(smem_u32(smem_v), kHalfBytes, 1024);
-        const uint32_t hi_v = static_cast<uint32_t>(dv >> 32), v_lo = static_cast<uint32_t>(dv);
-        const uint32_t tmem_s = tmem_base + kColS + static_cast<uint32_t>(X) * 128u;
-        const uint32_t tmem_o = tmem_base + kColO + static_cast<uint32_t>(X) * 128u;
-        uint32_t la[8], lb[8], ta[8], lv[8];
+    }
+  } else if (warp == kWarpProducerV) {
+    // ------------------------------------------------------------------ TMA producer of V tiles
+    if (lane == 0) {
+      BlockSeq<ItemRead<false>> seq;
+      seq.init();
+      seq.src.init(tail, abort_flag);
+      uint32_t nv = 0;
+      int kv_row0 = 0;
+      bool ok = true;
+      while (ok && seq.next(a, ignore_empty)) {
+        const int hk = seq.h / a.group_size;
+        if (seq.first()) kv_row0 = seq.kv_row0;
+        const int slot = static_cast<int>(nv % kRingV);
+        if (!mbar_wait(&tail->v_empty[slot], ((nv / kRingV) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        ++nv;
+        uint8_t* dst = smem_ring + (kRingK + slot) * kTileBytes;
+        const int row = kv_row0 + seq.kvb * kBKV;
+        mbar_expect_tx(&tail->v_full[slot], kTileBytes);
+        tma_load_3d(dst, &a.tmap_v, &tail->v_full[slot], 0, hk, row);
+        tma_load_3d(dst + kHalfBytes, &a.tmap_v, &tail->v_full[slot], 64, hk, row);
+      }
+    }
+  } else if (warp == kWarpQK) {
+    // ------------------------------------------------------------------ QK issuer: S[g&1] = Q K_g^T
+    // Two threads feed the tensor pipe (this one and the PV issuer): an issuing thread is blocked while
+    // its batch drains, so with a single issuer the pipe would idle during that thread's bookkeeping.
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(kBQ, kBKV, kBf16, 0, 0);
+      // descriptors: constant high word (K-major, 128-byte swizzle), low word holds the address
+      const uint64_t d0 = make_smem_desc_sw128(smem_u32(smem_q), 16, 1024);
+      const uint32_t hi = static_cast<uint32_t>(d0 >> 32);
+      const uint32_t q_lo0 = static_cast<uint32_t>(d0);
+      const uint32_t k_lo0 = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(smem_ring), 16, 1024));
+      BlockSeq<ItemRead<false>> seq;
+      seq.init();
+      seq.src.init(tail, abort_flag);
+      uint32_t g = 0, nk = 0;
+      uint32_t q_uses[kQBufs] = {0, 0};
+      bool ok = true;
+      while (ok && seq.next(a, ignore_empty)) {
+        const uint32_t sb = g & 1u;
+        const int qb_i = seq.item_no & 1;
+        // S[sb] is free once the softmax has copied block g-2 into registers
+        if (g >= 2u && !mbar_wait(&tail->s_free[sb], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (seq.first()) {
+          if (!mbar_wait(&tail->q_full[qb_i], q_uses[qb_i] & 1u, abort_flag)) { ok = false; break; }
+          ++q_uses[qb_i];
+        }
+        const int slot = static_cast<int>(nk % kRingK);
+        if (!mbar_wait(&tail->k_full[slot], (nk / kRingK) & 1u, abort_flag)) { ok = false; break; }
+        ++nk;
+        tc_fence_after_sync();
+        const uint32_t q_lo = q_lo0 + static_cast<uint32_t>((qb_i * kTileBytes) >> 4);
+        const uint32_t k_lo = k_lo0 + static_cast<uint32_t>((slot * kTileBytes) >> 4);
+        uint32_t la[8], lb[8];
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          // Q K^T: 16 elements further along K = +32 B inside a 64-column half, +16 KB for the second half
+          // 16 elements further along K: +32 B inside a 64-column half, +16 KB for the second half
           const uint32_t off = static_cast<uint32_t>(((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4);
           la[kk] = q_lo + off;
           lb[kk] = k_lo + off;
-          // P V: 16 kv rows further = 16 * 128 B in the V tile, 8 columns further in the 16-bit P tile
-          ta[kk] = tmem_s + static_cast<uint32_t>(kk * 8);
-          lv[kk] = v_lo + static_cast<uint32_t>((kk * 2048) >> 4);
         }
-        BlockSeq<ItemRead<false>, false, false> seq;
-        seq.init();
-        seq.src.init(sb, abort_flag);
-        // The tensor pipe serves the two streams' issuers in turns: a turn is the P V of a block followed at once by
-        // the Q K^T of the stream's next block (or the first Q K^T of an item), taken under a CTA-wide token. The
-        // stream that comes second starts its softmax a turn later, which puts the streams in opposite phases (one in
-        // its exponentials while the other one's MMAs run) instead of leaving both on the exponential unit together.
-        auto take_pipe = [&]() -> bool {
-          const uint64_t t0 = global_timer_ns();
-          while (atomicCAS(&tail->pipe_token, 0, 1) != 0) {
-            if (*abort_flag != 0) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
-          }
-          return true;
-        };
-        auto give_pipe = [&]() { atomicExch(&tail->pipe_token, 0); };
-        // The token goes back while the last four MMAs of the turn are still being issued: an issuing thread is held
-        // until the pipe has room, so the other stream's first MMAs queue up behind these instead of after a gap.
-        auto issue_qk = [&]() {
-          tc_fence_after_sync();
-          // S is free: its last reader was the P V of the previous block, issued by this thread before
-          umma_ss_x4(tmem_s, hi_k, hi_k, idesc_qk, 0u, la, lb);
-          give_pipe();
-          umma_ss_x4(tmem_s, hi_k, hi_k, idesc_qk, 1u, la + 4, lb + 4);
-          umma_commit(&sb->s_full);
-        };
-        uint32_t g = 0;
-        while (seq.next(a, ignore_empty)) {
-          const uint32_t item = static_cast<uint32_t>(seq.item_no);
-          if (seq.first()) {  // the item's first Q K^T (the later ones ride behind the previous block's P V)
-            if (!mbar_wait(&sb->q_full, item & 1u, abort_flag)) break;
-            if (!mbar_wait(&sb->k_full, g & 1u, abort_flag)) break;
-            if (!take_pipe()) break;
-            issue_qk();
-          }
-          // everything but P first (long since there), so that only P is waited for on the critical path
-          if (!mbar_wait(&sb->v_full, g & 1u, abort_flag)) break;
-          if (!seq.last() && !mbar_wait(&sb->k_full, (g + 1u) & 1u, abort_flag)) break;
-          if (seq.first() && item > 0u) {  // O must have been drained by the previous item's epilogue
-            if (!mbar_wait(&sb->o_free, (item - 1u) & 1u, abort_flag)) break;
-          }
-          if (kSplitP) {
-            // P V in two halves of four MMAs: the first half runs while the softmax warps still compute the second
-            if (!mbar_wait_spin(&sb->p_half[0], g & 1u, abort_flag)) break;
-            if (!take_pipe()) break;
-            tc_fence_after_sync();
-            umma_ts_x4(tmem_o, hi_v, idesc_pv, seq.first() ? 0u : 1u, ta, lv);
-            if (!mbar_wait_spin(&sb->p_half[1], g & 1u, abort_flag)) { give_pipe(); break; }
-            tc_fence_after_sync();
-            umma_ts_x4(tmem_o, hi_v, idesc_pv, 1u, ta + 4, lv + 4);
-          } else {
-            if (!mbar_wait_spin(&sb->p_half[1], g & 1u, abort_flag)) break;
-            if (!take_pipe()) break;
-            tc_fence_after_sync();
-            umma_ts_x8(tmem_o, hi_v, idesc_pv, seq.first() ? 0u : 1u, ta, lv);
-          }
-          umma_commit(&sb->pv_done);
-          if (!seq.last()) issue_qk(); else give_pipe();
-          ++g;
-        }
+        umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
+        umma_commit(&tail->s_full[sb]);
+        umma_commit(&tail->k_empty[slot]);
+        if (seq.last()) umma_commit(&tail->q_empty[qb_i]);
+        ++g;
       }
     }
+  } else if (warp == kWarpPV) {
+    // ------------------------------------------------------------------ PV issuer: O (+)= P[g&1] V_g
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = make_idesc_f16(kBQ, kD, kBf16, 0, 1);
+      // V is MN-major: its two 64-column halves are 16 KB apart (leading byte offset)
+      const uint64_t d0 = make_smem_desc_sw128(smem_u32(smem_ring + kRingK * kTileBytes), kHalfBytes, 1024);
+      const uint32_t hi = static_cast<uint32_t>(d0 >> 32), v_lo0 = static_cast<uint32_t>(d0);
+      BlockSeq<ItemRead<false>> seq;
+      seq.init();
+      seq.src.init(tail, abort_flag);
+      uint32_t g = 0, nv = 0, items_started = 0;
+      bool ok = true;
+      while (ok && seq.next(a, ignore_empty)) {
+        const uint32_t sb = g & 1u;
+        if (!mbar_wait(&tail->p_full[sb], (g >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (seq.first() && items_started > 0) {  // O must have been drained by the previous item's epilogue
+          if (!mbar_wait(&tail->o_free, (items_started - 1u) & 1u, abort_flag)) { ok = false; break; }
+        }
+        const int slot = static_cast<int>(nv % kRingV);
+        if (!mbar_wait(&tail->v_full[slot], (nv / kRingV) & 1u, abort_flag)) { ok = false; break; }
+        ++nv;
+        tc_fence_after_sync();
+        const uint32_t tmem_p = tmem_base + kColP + sb * 64u;
+        const uint32_t v_lo = v_lo0 + static_cast<uint32_t>((slot * kTileBytes) >> 4);
+        uint32_t ta[8], lb[8];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // 16 kv rows further = 16 * 128 B in the V tile, 8 columns further in the 16-bit P tile
+          ta[kk] = tmem_p + static_cast<uint32_t>(kk * 8);
+          lb[kk] = v_lo + static_cast<uint32_t>((kk * 2048) >> 4);
+        }
+        umma_ts_x8(tmem_base + kColO, hi, idesc_pv, seq.first() ? 0u : 1u, ta, lb);
+        umma_commit(&tail->pv_done[sb]);
+        umma_commit(&tail->v_empty[slot]);
+        if (seq.last()) umma_commit(&tail->o_full);
+        if (seq.first()) ++items_started;
+        ++g;
+      }
+    }
+  }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-    // ================================================================== softmax / epilogue warpgroup of stream X
-    // Thread (warp w of the group, lane) owns q row 32 w + lane = its TMEM lane: the whole row of S, of P and of O.
-    const int X = warp / kWgWarps;
-    const int wq = warp % kWgWarps;
-    StreamBars* sb = &tail->st[X];
-    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t tmem_s = tmem_base + lane_base + kColS + static_cast<uint32_t>(X) * 128u;
-    const uint32_t tmem_o = tmem_base + lane_base + kColO + static_cast<uint32_t>(X) * 128u;
-    const int row = wq * 32 + lane;
-    uint8_t* stage = smem_stage + X * kStageBytes;
+    // ------------------------------------------------------------------ softmax / epilogue warps 0..15
+    // Group X = warp / 8 takes the blocks with g & 1 == X. Two threads per q row: thread
+    // (quadrant = warp & 3, half ch = (warp >> 2) & 1, lane) owns row 32 * quadrant + lane (its TMEM lane)
+    // and the columns [64 ch, 64 ch + 64) of S[X], P[X] and (in a rescale) O; in the epilogue the 16 warps
+    // cover O in 32-column quarters.
+    const uint32_t X = static_cast<uint32_t>(warp >> 3), Y = X ^ 1u;
+    const uint32_t ch = static_cast<uint32_t>((warp >> 2) & 1);
+    const int quad = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_base + kColS + X * 128u + ch * 64u;
+    const uint32_t tmem_p = tmem_base + lane_base + kColP + X * 64u + ch * 32u;
+    const uint32_t tmem_o = tmem_base + lane_base + kColO;
+    const uint32_t ocol = 64u * X + 32u * ch;  // this thread's quarter of O in the epilogue
+    const int row = quad * 32 + lane;
+    uint64_t* pair_bar = &tail->pair_bar[X][quad];
+    uint32_t pair_phase = 0;
     uint16_t* o16 = reinterpret_cast<uint16_t*>(a.o);
-    uint32_t wg_phase = 0;
     bool ok = true;
 
-    // bounded barrier of the four warps of this group
-    auto wg_sync = [&]() -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sb->wg_bar);
-      const bool r = wait_all(&sb->wg_bar, wg_phase, abort_flag);
-      wg_phase ^= 1u;
-      return r;
-    };
-
-    struct RowCtx {  // where an item's row lives in global memory
+    struct RowCtx {  // where an item's row lives in global memory (this thread's 32-column quarter)
       uint16_t* orow;
       float* lse;
       bool row_ok;
-      bool whole;   // no row of the q-block is past the end of its request
-      int grow0;    // first row of the q-block in the q / o tensors
     };
     auto row_ctx = [&](int q_row0, int q_valid, int hq) -> RowCtx {
       RowCtx c;
       c.row_ok = row < q_valid;
-      c.whole = q_valid == kBQ;
-      c.grow0 = q_row0;
       const int64_t grow = static_cast<int64_t>(q_row0) + row;
-      c.orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h;
-      c.lse = a.lse != nullptr ? a.lse + grow * a.lse_stride_n + hq : nullptr;
+      c.orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h + ocol;
+      c.lse = (a.lse != nullptr && ocol == 0u) ? a.lse + grow * a.lse_stride_n + hq : nullptr;
       return c;
     };
     auto on_empty = [&](int q_row0, int q_valid, int hq) {  // active q-block that keeps nothing: zeros, lse = -5e4
@@ -471,251 +504,238 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       if (c.row_ok) {
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) reinterpret_cast<uint4*>(c.orow)[i] = z;
+        for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(c.orow)[i] = z;
         if (c.lse != nullptr) *c.lse = -5e4f;
       }
     };
 
-    BlockSeq<ItemRead<true>, false, true> seq;
-    seq.init();
-    seq.src.init(sb, abort_flag);
-    uint32_t g = 0;            // blocks of this stream so far
-    float m_run = -INFINITY;   // the maximum the row's sum and O refer to
-    uint64_t l2a = 0, l2b = 0; // row sum (two packed pairs of partial sums)
-    bool stage_busy = false;   // a TMA store of this stream may still be reading the staging area
+    GroupSeq seq;
+    seq.init(tail, abort_flag);
+    uint32_t g = 0;          // global block index (both parities)
+    uint32_t my_blocks = 0;  // blocks this group has processed
+    uint32_t items_seen = 0; // items whose last block has been passed
+    float m_ref = -INFINITY; // the maximum this thread's partial sum refers to
+    uint64_t l2a = 0, l2b = 0;  // partial row sum over this thread's columns of the group's blocks
+    // an item whose statistics have been published and whose O is still being accumulated
+    bool pend = false;
+    uint32_t pend_item = 0;
+    int pend_q_row0 = 0, pend_q_valid = 0, pend_h = 0;
+
+    auto epilogue = [&]() -> bool {
+      const uint32_t ip = pend_item & 1u;
+      if (!mbar_wait(&tail->stats_ready[ip], (pend_item >> 1) & 1u, abort_flag)) return false;
+      float lsum = 0.f, m_fin = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) m_fin = fmaxf(m_fin, tail->stats_m[ip][i][row]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float mi = tail->stats_m[ip][i][row];
+        const float ci = (mi == m_fin) ? 1.f : ex2_approx(mi - m_fin);
+        lsum = fmaf(tail->stats_l[ip][i][row], ci, lsum);
+      }
+      if (!mbar_wait(&tail->o_full, pend_item & 1u, abort_flag)) return false;
+      tc_fence_after_sync();
+      const float inv_l = lsum > 0.f ? __frcp_rn(lsum) : 0.f;
+      uint32_t v[32];
+      tmem_ld_x32(tmem_o + ocol, v);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->o_free);  // O may be overwritten by the next item
+      const RowCtx pend_ctx = row_ctx(pend_q_row0, pend_q_valid, pend_h);
+      uint4 outv[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float x0 = __uint_as_float(v[8 * q + 2 * t]) * inv_l;
+          const float x1 = __uint_as_float(v[8 * q + 2 * t + 1]) * inv_l;
+          w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+        }
+        outv[q] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      const bool whole = pend_q_valid == kBQ;  // no row of the q-block is past the request
+      if (whole) {
+        // Through a 1 KB staging area per warp (16 rows x 64 bytes, plain row-major) and a TMA store of one
+        // 16-row x 32-column box: a store instruction of a warp would otherwise write 32 scattered 16-byte pieces.
+        uint8_t* stg = smem_ostage + warp * kOutStageBytes;
+        const int grow0 = pend_q_row0 + quad * 32;
+#pragma unroll
+        for (int ph = 0; ph < 2; ++ph) {
+          if (lane == 0) tma_store_wait_read<0>();  // the staging area is free once its last store has read it
+          __syncwarp();
+          if ((lane >> 4) == ph) {
+            const int r = lane & 15;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(stg + r * 64 + c * 16) = outv[c];
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&a.tmap_o16, stg, static_cast<int>(ocol), pend_h, grow0 + ph * 16);
+            tma_store_commit();
+          }
+        }
+      } else if (pend_ctx.row_ok) {
+        uint4* dst = reinterpret_cast<uint4*>(pend_ctx.orow);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dst[q] = outv[q];
+      }
+      if (pend_ctx.row_ok && pend_ctx.lse != nullptr) *pend_ctx.lse = (lsum > 0.f) ? (log2f(lsum) + m_fin) : -5e4f;
+      pend = false;
+      return true;
+    };
 
     while (ok && seq.next(a, on_empty)) {
       if (seq.first()) {
-        m_run = -INFINITY;
+        m_ref = -INFINITY;
         l2a = 0;
         l2b = 0;
       }
-      // ---- S -> registers (the whole row, once)
-      if (!wait_all(&sb->s_full, g & 1u, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
-      uint32_t s[128];
-      tmem_ld_x32(tmem_s, s);
-      tmem_ld_x32(tmem_s + 32u, s + 32);
-      tmem_ld_x32(tmem_s + 64u, s + 64);
-      tmem_ld_x32(tmem_s + 96u, s + 96);
-      tmem_wait_ld();
-      if constexpr (kSoftCap) {  // logit = cap * tanh(q.k * sm_scale / cap); the factor cap is part of sm_scale_log2
-#pragma unroll
-        for (int t = 0; t < 128; ++t) s[t] = __float_as_uint(tanh_approx(__uint_as_float(s[t]) * a.soft_cap_pre));
-      }
-      const int valid = seq.valid();
-      if (valid < kBKV) {
-#pragma unroll
-        for (int t = 0; t < 128; ++t)
-          if (t >= valid) s[t] = 0xff800000u;  // -inf: excluded from the maximum, exp2 gives 0
-      }
-      float mx;
-      {
-        float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int t = 0; t < 16; ++t) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            mxs[i] = fmax3(mxs[i], __uint_as_float(s[8 * t + 2 * i]), __uint_as_float(s[8 * t + 2 * i + 1]));
-        }
-        mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
-      }
-      const float m_new = fmaxf(m_run, mx * a.sm_scale_log2);
-      // lazy rescale: the row keeps its old reference maximum while the new one is at most 2^8 above it
-      const bool need = (m_new - m_run) > kRescaleThreshold;
-      const bool rescale = !seq.first() && __any_sync(0xffffffffu, need);
-      const float m_used = (seq.first() || need) ? m_new : m_run;
-      if (rescale) {
-        // O is rescaled after the P V of the previous block has completed (and before this block's P is handed over)
-        if (!wait_all(&sb->pv_done, (g - 1u) & 1u, abort_flag)) { ok = false; break; }
+      if ((g & 1u) == X) {
+        // ---- pass 1: the maximum of this thread's half row of S[X], 32 columns at a time (the values are
+        // read again for the exponentials: holding them across the exchanges below would cost registers)
+        if (!mbar_wait(&tail->s_full[X], my_blocks & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const float alpha = need ? ex2_approx(m_run - m_new) : 1.0f;
+        const int valid = seq.valid() - static_cast<int>(64u * ch);  // of my columns, how many exist
+        float mx;
+        {
+          float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_x32(tmem_o + 32u * c, v);
-          tmem_wait_ld();
+          for (int c = 0; c < 2; ++c) {
+            uint32_t s[32];
+            tmem_ld_x32(tmem_s + 32u * c, s);
+            tmem_wait_ld();
+            if (valid < 32 * c + 32) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
-          tmem_st_x32(tmem_o + 32u * c, v);
+              for (int t = 0; t < 32; ++t)
+                if (32 * c + t >= valid) s[t] = 0xff800000u;  // -inf
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                mxs[i] = fmax3(mxs[i], __uint_as_float(s[8 * t + 2 * i]), __uint_as_float(s[8 * t + 2 * i + 1]));
+            }
+          }
+          mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
         }
-      }
-      if (m_run != m_used) {  // the row sum follows the maximum in use (first block: the sum is zero anyway)
-        const float beta = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_used);
-        const uint64_t beta2 = pack_f32x2(beta, beta);
-        l2a = ffma2(l2a, beta2, 0ull);
-        l2b = ffma2(l2b, beta2, 0ull);
-        m_run = m_used;
-      }
-      // ---- P = exp2(S * scale - m_used), row sum, P (16 bit) over the first 64 columns of S: one FMA and one
-      // add per PAIR of columns
-      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      const uint64_t scale2 = pack_f32x2(a.sm_scale_log2, a.sm_scale_log2);
-      const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
+        // ---- the two halves of a row exchange their maxima (the warps `warp` and `warp ^ 4`)
+        tail->xmax[X][my_blocks & 1u][ch][row] = mx;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pair_bar);
+        if (!mbar_wait(pair_bar, pair_phase, abort_flag)) { ok = false; break; }
+        pair_phase ^= 1u;
+        mx = fmaxf(mx, tail->xmax[X][my_blocks & 1u][ch ^ 1u][row]);
+        // ---- the running maximum after block g-1 comes from the other group (every block waits, so
+        // that the two groups stay within one phase of each other)
+        if (g >= 1u && !mbar_wait(&tail->m_ready[Y], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        const float m_prev = seq.first() ? -INFINITY : tail->m_pub[Y][row];
+        // with a soft cap the logit is cap * tanh(s * sm_scale / cap): monotonic, so the maximum is transformed once
+        if constexpr (kSoftCap) mx = (mx == -INFINITY) ? mx : tanh_approx(mx * a.soft_cap_pre);
+        const float m_new = fmaxf(m_prev, mx * a.sm_scale_log2);
+        // lazy rescale (the decision is the same in both warps of a row: same rows, same values)
+        const bool need = (m_new - m_prev) > kRescaleThreshold;
+        const bool rescale = !seq.first() && __any_sync(0xffffffffu, need);
+        const float m_used = (seq.first() || (rescale && need)) ? m_new : m_prev;
+        if (ch == 0u) tail->m_pub[X][row] = m_used;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->m_ready[X]);
+        if (rescale) {
+          // O is rescaled only after the PV of block g-1 has completed; that PV may be the first of
+          // its item and wait for the previous item's epilogue, so this thread's share of it goes first
+          if (pend && !epilogue()) { ok = false; break; }
+          if (!mbar_wait(&tail->pv_done[Y], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const float alpha = need ? ex2_approx(m_prev - m_new) : 1.0f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32];
+            tmem_ld_x32(tmem_o + 64u * ch + 32u * c, v);
+            tmem_wait_ld();
 #pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          const int e = 32 * c + 2 * t;
-          const uint64_t x2 = ffma2(pack_f32x2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
-          float x0, x1;
-          unpack_f32x2(x2, x0, x1);
-          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-          if (t & 1) l2b = fadd2(l2b, pack_f32x2(p0, p1)); else l2a = fadd2(l2a, pack_f32x2(p0, p1));
-          pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+            for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
+            tmem_st_x32(tmem_o + 64u * ch + 32u * c, v);
+          }
         }
-        tmem_st_x16(tmem_s + 16u * c, pk);
-        if (kSplitP ? (c & 1) : (c == 3)) {  // a half of P (64 kv columns) is complete: its four MMAs may start
-          tmem_wait_st();
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sb->p_half[c >> 1]);
+        // this thread's partial sum follows the maximum in use
+        if (m_ref != m_used) {
+          const float beta = ex2_approx(m_ref - m_used);
+          const uint64_t beta2 = pack_f32x2(beta, beta);
+          l2a = ffma2(l2a, beta2, 0ull);
+          l2b = ffma2(l2b, beta2, 0ull);
+          m_ref = m_used;
         }
+        // P[X] was last read by the PV of this group's previous block
+        if (my_blocks >= 1u && !mbar_wait(&tail->pv_done[X], (my_blocks - 1u) & 1u, abort_flag)) { ok = false; break; }
+        // ---- pass 2: P = exp2(S * scale - m_used), row sum, P (16 bit) to TMEM: one FMA and one add per
+        // PAIR of columns
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        const uint64_t scale2 = pack_f32x2(a.sm_scale_log2, a.sm_scale_log2);
+        const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
+        uint32_t s[64];
+        tmem_ld_x32(tmem_s, s);
+        tmem_ld_x32(tmem_s + 32u, s + 32);
+        tmem_wait_ld();
+        // the QK of this group's next block may overwrite S[X]
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->s_free[X]);
+        if constexpr (kSoftCap) {
+#pragma unroll
+          for (int t = 0; t < 64; ++t) s[t] = __float_as_uint(tanh_approx(__uint_as_float(s[t]) * a.soft_cap_pre));
+        }
+        if (valid < 64) {
+#pragma unroll
+          for (int t = 0; t < 64; ++t)
+            if (t >= valid) s[t] = 0xff800000u;  // -inf: exp2 gives 0
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const int e = 32 * c + 2 * t;
+            const uint64_t x2 = ffma2(pack_f32x2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
+            float x0, x1;
+            unpack_f32x2(x2, x0, x1);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            if (t & 1) l2b = fadd2(l2b, pack_f32x2(p0, p1)); else l2a = fadd2(l2a, pack_f32x2(p0, p1));
+            pk[t] = kBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+          }
+          tmem_st_x16(tmem_p + 16u * c, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->p_full[X]);
+        ++my_blocks;
+        // the previous item's epilogue runs after this group's first block of the next item, so that
+        // the item's last PV overlaps a softmax step (running it before the block, in the wait for S,
+        // frees O earlier for the next item's first PV but measured 9 % slower: it delays the group's
+        // own chain, which is the longer one)
+        if (pend && !epilogue()) { ok = false; break; }
       }
-      ++g;
-
       if (seq.last()) {
-        // ---- epilogue of the unit. A whole item: O / l -> 16 bit -> global. A part of a split item: the fp32 O, the
-        // row maxima and the row sums go to the item's partial slots; the part that delivers last merges them.
-        const RowCtx c = row_ctx(seq.q_row0, seq.q_valid, seq.h);
+        if (pend && !epilogue()) { ok = false; break; }
+        const uint32_t ip = items_seen & 1u;
         float la, lb, lc, ld;
         unpack_f32x2(l2a, la, lb);
         unpack_f32x2(l2b, lc, ld);
-        const float lsum = (la + lb) + (lc + ld);
-        // Writes one round (64 columns, packed to 16 bit) of the q-block: whole q-blocks through the stream's staging
-        // area (128-byte swizzle) and a TMA store, a q-block cut by the end of its request row by row.
-        auto store_round = [&](int r, const uint4 (&outv)[8]) -> bool {
-          if (c.whole) {
-            if (stage_busy) {  // the previous store must have read the staging area
-              if (wq == 0 && lane == 0) tma_store_wait_read<0>();
-              if (!wg_sync()) return false;
-              stage_busy = false;
-            }
-            uint8_t* rowp = stage + row * 128;
-            const uint32_t swz = static_cast<uint32_t>(row & 7);
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<uint4*>(rowp + ((static_cast<uint32_t>(q) ^ swz) << 4)) = outv[q];
-            fence_proxy_async_smem();
-            if (!wg_sync()) return false;
-            if (wq == 0 && lane == 0) {
-              tma_store_3d(&a.tmap_o, stage, 64 * r, seq.h, c.grow0);
-              tma_store_commit();
-            }
-            stage_busy = true;
-          } else if (c.row_ok) {
-            uint4* dst = reinterpret_cast<uint4*>(c.orow + 64 * r);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) dst[q] = outv[q];
-          }
-          return true;
-        };
-        if (!wait_all(&sb->pv_done, (g - 1u) & 1u, abort_flag)) { ok = false; break; }  // the unit's last P V
-        tc_fence_after_sync();
-        if (seq.nparts <= 1) {
-          const float inv_l = lsum > 0.f ? __frcp_rn(lsum) : 0.f;
-#pragma unroll
-          for (int r = 0; r < 2; ++r) {
-            uint32_t v[64];
-            tmem_ld_x32(tmem_o + 64u * r, v);
-            tmem_ld_x32(tmem_o + 64u * r + 32u, v + 32);
-            tmem_wait_ld();
-            if (r == 1) {  // O may be overwritten by the next unit
-              tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&sb->o_free);
-            }
-            uint4 outv[8];
-            uint32_t* w = reinterpret_cast<uint32_t*>(outv);
-#pragma unroll
-            for (int t = 0; t < 32; ++t) {
-              const float x0 = __uint_as_float(v[2 * t]) * inv_l;
-              const float x1 = __uint_as_float(v[2 * t + 1]) * inv_l;
-              w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
-            }
-            if (!store_round(r, outv)) { ok = false; break; }
-          }
-          if (!ok) break;
-          if (c.row_ok && c.lse != nullptr) *c.lse = (lsum > 0.f) ? (log2f(lsum) + m_run) : -5e4f;
-        } else {
-          // ---- partial result: O as [column group of 4][row][4] (a warp's store covers 512 contiguous bytes)
-          float* ps = a.partials + static_cast<size_t>(seq.slot) * kPartialFloats;
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            uint32_t v[32];
-            tmem_ld_x32(tmem_o + 32u * cc, v);
-            tmem_wait_ld();
-            if (cc == 3) {  // O may be overwritten by the next unit
-              tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&sb->o_free);
-            }
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<uint4*>(ps + (static_cast<size_t>(8 * cc + q) * 128 + row) * 4) =
-                  make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-          }
-          ps[128 * 128 + row] = m_run;
-          ps[128 * 128 + 128 + row] = lsum;
-          __threadfence();
-          if (!wg_sync()) { ok = false; break; }
-          if (wq == 0 && lane == 0) {
-            int* cnt = a.arrive + (seq.slot - seq.part);  // a split item counts at its first slot
-            const int old = atomicAdd(cnt, 1);
-            const int mine = old == seq.nparts - 1 ? 1 : 0;
-            if (mine) *cnt = 0;  // the counter is back at zero for the next launch
-            __threadfence();
-            sb->merge_go = mine;
-          }
-          if (!wg_sync()) { ok = false; break; }
-          if (sb->merge_go != 0) {
-            // ---- this part delivered last: O = sum_p O_p 2^(m_p - m) / sum_p l_p 2^(m_p - m), m = max_p m_p
-            const float* base = a.partials + static_cast<size_t>(seq.slot - seq.part) * kPartialFloats;
-            float m_all = -INFINITY;
-            for (int pp = 0; pp < seq.nparts; ++pp)
-              m_all = fmaxf(m_all, __ldcg(base + static_cast<size_t>(pp) * kPartialFloats + 128 * 128 + row));
-            float l_all = 0.f;
-            for (int pp = 0; pp < seq.nparts; ++pp) {
-              const float* pq = base + static_cast<size_t>(pp) * kPartialFloats;
-              const float mp = __ldcg(pq + 128 * 128 + row);
-              const float wgt = (mp == -INFINITY) ? 0.f : ex2_approx(mp - m_all);
-              l_all = fmaf(__ldcg(pq + 128 * 128 + 128 + row), wgt, l_all);
-            }
-            const float inv_l = l_all > 0.f ? __frcp_rn(l_all) : 0.f;
-#pragma unroll 1
-            for (int r = 0; r < 2; ++r) {
-              float acc[64];
-#pragma unroll
-              for (int t = 0; t < 64; ++t) acc[t] = 0.f;
-              for (int pp = 0; pp < seq.nparts; ++pp) {
-                const float* pq = base + static_cast<size_t>(pp) * kPartialFloats;
-                const float mp = __ldcg(pq + 128 * 128 + row);
-                const float wgt = (mp == -INFINITY) ? 0.f : ex2_approx(mp - m_all);
-#pragma unroll
-                for (int q = 0; q < 16; ++q) {
-                  const float4 x = __ldcg(reinterpret_cast<const float4*>(pq + (static_cast<size_t>(16 * r + q) * 128 + row) * 4));
-                  acc[4 * q] = fmaf(x.x, wgt, acc[4 * q]);
-                  acc[4 * q + 1] = fmaf(x.y, wgt, acc[4 * q + 1]);
-                  acc[4 * q + 2] = fmaf(x.z, wgt, acc[4 * q + 2]);
-                  acc[4 * q + 3] = fmaf(x.w, wgt, acc[4 * q + 3]);
-                }
-              }
-              uint4 outv[8];
-              uint32_t* w = reinterpret_cast<uint32_t*>(outv);
-#pragma unroll
-              for (int t = 0; t < 32; ++t)
-                w[t] = kBf16 ? pack_bf16x2(acc[2 * t] * inv_l, acc[2 * t + 1] * inv_l)
-                             : pack_f16x2(acc[2 * t] * inv_l, acc[2 * t + 1] * inv_l);
-              if (!store_round(r, outv)) { ok = false; break; }
-            }
-            if (!ok) break;
-            if (c.row_ok && c.lse != nullptr) *c.lse = (l_all > 0.f) ? (log2f(l_all) + m_all) : -5e4f;
-          }
-        }
+        tail->stats_m[ip][2u * X + ch][row] = m_ref;
+        tail->stats_l[ip][2u * X + ch][row] = (la + lb) + (lc + ld);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->stats_ready[ip]);
+        pend = true;
+        pend_item = items_seen;
+        pend_q_row0 = seq.q_row0; pend_q_valid = seq.q_valid; pend_h = seq.h;
+        ++items_seen;
       }
+      ++g;
     }
-    if (wq == 0 && lane == 0) tma_store_wait_all<0>();
+    if (ok && pend) epilogue();
+    if (lane == 0) tma_store_wait_all<0>();
   }
 
   // ------------------------------------------------------------------ common exit
@@ -729,7 +749,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     __syncthreads();
   }
   if (list_bad && blockIdx.x == 0 && threadIdx.x == 0) atomicCAS(a.status, kDevOk, kDevBadIndex);
-  if (warp == kWarpTmem) {
+  if (warp == kWarpMma) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -743,6 +763,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
   }
 }
 
+}  // namespace
+
+
+namespace {
 template <bool kBf16, bool kSoftCap>
 cudaError_t launch_one(const AttnArgs& a, int ctas, cudaStream_t stream) {
   const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -751,7 +775,6 @@ cudaError_t launch_one(const AttnArgs& a, int ctas, cudaStream_t stream) {
   attention_kernel<kBf16, kSoftCap><<<ctas, kThreads, kSmemBytes, stream>>>(a);
   return cudaGetLastError();
 }
-
 }  // namespace
 
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream) {

@@ -159,7 +159,8 @@ struct AttnArgs {
   CUtensorMap tmap_q;              // [D, H, Tq]   box 64 x 1 x 128
   CUtensorMap tmap_k;              // [D, Hkv, Tkv]
   CUtensorMap tmap_v;
-  CUtensorMap tmap_o;              // [D, Hq, Tq]   box 64 x 1 x 128, 128B swizzle (stores of whole q-blocks)
+  CUtensorMap tmap_o;              // [D, Hq, Tq]   box 64 x 1 x 128, 128B swizzle (stores of whole q-blocks, two-stream kernel)
+  CUtensorMap tmap_o16;            // [D, Hq, Tq]   box 32 x 1 x 16, no swizzle (stores of whole q-blocks, one-tile kernel)
   void* o;                         // [Tq, H, D] (strides below, in elements)
   float* lse;                      // [Tq, H] or null
   int64_t o_stride_n, o_stride_h;
@@ -180,7 +181,9 @@ struct AttnArgs {
 };
 // floats of one partial result: O (32 column groups x 128 rows x 4), then the row maxima and the row sums
 constexpr int kPartialFloats = 128 * 128 + 2 * 128;
+// one unit at a time per SM (launches with many units) / two streams of units per SM with split kv lists (few units)
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream);
+cudaError_t launch_attention_streams(const AttnArgs& a, int max_ctas, cudaStream_t stream);
 
 // ------------------------------------------------------------------ host helpers
 // Encodes a tiled tensor map (bf16/f16 elements, 128-byte swizzle or none). dims/strides innermost first;

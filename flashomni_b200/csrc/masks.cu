@@ -474,8 +474,8 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
 //   [5] kv_row0    first kv row of the request
 //   [6] ragged     columns of the request's partial last kv block if the unit's list ends with it, else 0
 //   [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
-// A kv list is cut into n_parts = ceil(n_kept / chunk_max) parts of (almost) equal length only when the launch has
-// at most half as many items as streams (whole items would leave streams idle): chunk_max = max(min_chunk,
+// A kv list is cut into n_parts = ceil(n_kept / chunk_max) parts of (almost) equal length only when there is room for
+// partial results (max_slots > 0) and the launch has at most half as many items as streams (whole items would leave streams idle): chunk_max = max(min_chunk,
 // ceil(total_kept / num_streams), ceil(max_nkv / 255)); otherwise every item is one unit.
 // unit_counters: n_units, partial slots in use, chunk_max, status. arrive[slot] = 0 for every slot.
 __global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
@@ -488,7 +488,7 @@ __global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
   if (n_items > a.max_items) n_items = static_cast<int>(a.max_items);
   const long long total_kept = a.counters[1];
   int chunk_max = 0x7fffffff;
-  if (n_items > 0 && 2 * n_items <= a.num_streams) {
+  if (n_items > 0 && a.max_slots > 0 && 2 * n_items <= a.num_streams) {
     long long c = (total_kept + a.num_streams - 1) / a.num_streams;
     if (c < a.min_chunk) c = a.min_chunk;
     const long long c255 = (static_cast<long long>(a.max_nkv) + 254) / 255;

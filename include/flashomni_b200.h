@@ -132,7 +132,11 @@ FO_API size_t fo_attn_partial_bytes(int64_t partial_slots);
  * is not FO_DEV_OK or more partial slots are in use than `partial_slots` (the output is then untouched and
  * status[0] = FO_DEV_BAD_INDEX). The parts of a split item write fp32 partial results into `partials`
  * (fo_attn_partial_bytes(partial_slots) bytes, 16-byte aligned; null when partial_slots = 0) and the
- * part that delivers last merges them and writes the rows. status: FOUR int32 device words
+ * part that delivers last merges them and writes the rows. partial_slots also selects the kernel: with room for
+ * partial results (the caller expects few units: at most one candidate item per stream) two streams of units run
+ * per SM; with partial_slots = 0 (fo_attn_units then never cuts a list) one unit at a time runs per SM with two
+ * softmax groups on alternate kv blocks, the faster shape when every SM gets several units. status: FOUR int32
+ * device words
  * that the caller zeroes once: [0] is set to FO_DEV_WAIT_TIMEOUT if a bounded wait ran out;
  * [1] (unit cursor: units are handed to the streams dynamically) and [2] (count of finished CTAs) are used by
  * the kernel and are zero again when it ends, so launches that share the words (or `arrive`, `partials`) must

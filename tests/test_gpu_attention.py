@@ -14,6 +14,14 @@ from helpers import assert_close_bf16, dev, masks_to_device
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["tile", "streams"])
+def attention_kernel_choice(request, monkeypatch):
+    """Every test of this file runs on both attention kernels: the one-tile kernel (launches with many units) and
+    the two-stream kernel (few units, kv lists cut into parts). The wrapper's own choice is tested separately."""
+    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "KERNEL", request.param)
+    return request.param
+
+
 def _wrapper(device, qo, kv, H, dtype=torch.bfloat16, layout="NHD", **kw):
     w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=device), layout)
     w.plan(dev(np.asarray(qo, np.int32), device), dev(np.asarray(kv, np.int32), device), H, H, 128,
@@ -358,11 +366,13 @@ def test_undersized_kept_list_is_reported_not_walked(cuda_device):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_split_kv_lists_merge_to_the_oracle(cuda_device, dtype):
+def test_split_kv_lists_merge_to_the_oracle(cuda_device, dtype, attention_kernel_choice):
     """Few items with long kv lists: the lists are cut into parts that run on different streams, and the part that
     delivers last merges the partial results (maxima, sums, fp32 O). Against the fp32 oracle, with the log-sum-exp,
     prior contents for skipped q-blocks, an empty item and a ragged last block; twice in a row on the same wrapper
     (the per-item arrival counters must be back at zero)."""
+    if attention_kernel_choice != "streams":
+        pytest.skip("kv lists are only cut for the two-stream kernel")
     H, lens = 3, [40 * 128, 17 * 128 + 40]
     rng = np.random.default_rng(61)
     qa = [(rng.random((-(-n // 128), H)) < 0.8).astype(np.uint8) for n in lens]
@@ -392,9 +402,11 @@ def test_split_kv_lists_merge_to_the_oracle(cuda_device, dtype):
         assert torch.equal(o.cpu()[~act], prior[~act])
 
 
-def test_split_kv_three_heads_of_the_4608_token_layer(cuda_device):
+def test_split_kv_three_heads_of_the_4608_token_layer(cuda_device, attention_kernel_choice):
     """Three heads of the 4608-token layer, two requests (a rank's share when 24 heads are split over 8 GPUs): about
     120 items for 296 streams, so lists above 16 blocks are cut."""
+    if attention_kernel_choice != "streams":
+        pytest.skip("kv lists are only cut for the two-stream kernel")
     inp = wl.attention_inputs(2, 3, 4608, 128, 0.5, seed=91)
     w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, 3)
     o = _run(cuda_device, w, inp.q, inp.k, inp.v, inp.masks)
@@ -404,3 +416,15 @@ def test_split_kv_three_heads_of_the_4608_token_layer(cuda_device):
     ref = oa.sparse_attention(inp.q, inp.k, inp.v, [0, 4608, 9216], [0, 4608, 9216], m.sparse_info, m.sparse_kv_info,
                               m.info_indptr, m.kv_info_indptr)
     assert_close_bf16(o, ref, "three heads of the 4608-token layer, split lists")
+
+
+def test_kernel_choice_follows_the_planned_shape(cuda_device, monkeypatch):
+    """Few candidate items (at most one per stream): the two-stream kernel with room for partial results; many: the
+    one-tile kernel, no list is ever cut."""
+    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "KERNEL", None)
+    streams = 2 * torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    few = _wrapper(cuda_device, [0, 4608, 9216], [0, 4608, 9216], 3)      # 216 candidates
+    many = _wrapper(cuda_device, [0, 4608, 9216], [0, 4608, 9216], 24)    # 1728 candidates
+    assert few._n_cand <= streams < many._n_cand
+    assert few._partial_slots > 0 and few._max_units == few._n_cand + streams
+    assert many._partial_slots == 0 and many._max_units == many._n_cand and many._partials is None

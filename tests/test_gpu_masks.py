@@ -204,7 +204,7 @@ def test_attention_work_units_bit_exact(cuda_device, case):
     got = w.work_lists()
     ref = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, qo, H, 128, 128)
     _assert_lists_equal(got, ref)
-    units, slots, chunk = om.attn_units(ref, qo, qo, w._num_streams, w.MIN_CHUNK)
+    units, slots, chunk = om.attn_units(ref, qo, qo, w._num_streams, w.MIN_CHUNK, max_slots=w._partial_slots)
     assert got["unit_status"] == 0 and got["chunk_max"] == chunk and got["partial_slots_used"] == slots
     assert got["n_units"] == len(units) and np.array_equal(got["units"], units)
     if case == "many_items_whole":
