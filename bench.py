@@ -802,6 +802,29 @@ def run_mask_path(ctx, args, peaks):
                          "us": round(tc["mean"] * 1e3, 1), "gbs": round(cb / (tc["mean"] * 1e-3) / 1e9, 1),
                          "frac_of_hbm": r4(cb / (tc["mean"] * 1e-3) / 1e9 / peaks["hbm_gbs"]),
                          "bytes_are": "packed masks + indptrs read, items / kv_ptr / order / kv_idx written"}
+    # block selection (pooled scores -> packed masks) at both mask sizes, beside the reference's torch + Triton
+    # path as the fixture generator timed it on a B200 (tests/golden/make_selection_golden.py)
+    ref_us = {}
+    try:
+        import json as _json
+        z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests", "golden", "reference_selection.npz"))
+        ref_us = _json.loads(bytes(z["timing_us"]).decode())
+    except Exception:
+        pass
+    sel = {}
+    for name, Hs, ns, t2t in (("flux", 24, 36, 4), ("video", 40, 604, 4)):
+        sc = torch.from_numpy((np.random.default_rng(9).standard_normal((1, Hs, ns, ns)) * 2.0).astype(np.float32)).to(device)
+        for _ in range(3):
+            fo.select_blocks(sc, t2t, 0.3, 0.3)
+        ts = event_time(lambda: fo.select_blocks(sc, t2t, 0.3, 0.3), args.steps)
+        sb = int(sc.numel() * 4 + (ns * Hs * ns + 7) // 8 + (ns * Hs + 7) // 8)
+        sel[name] = {"heads": Hs, "blocks": ns, "us": round(ts["mean"] * 1e3, 1), "bytes": sb,
+                     "gbs": round(sb / (ts["mean"] * 1e-3) / 1e9, 1),
+                     "frac_of_hbm": r4(sb / (ts["mean"] * 1e-3) / 1e9 / peaks["hbm_gbs"]),
+                     "reference_torch_triton_us": round(ref_us[name]["us"], 1) if name in ref_us else None}
+    sel["bytes_are"] = "fp32 scores read, packed masks written"
+    sel["reference_us_from"] = "tests/golden/reference_selection.npz (the generator's CUDA-event timing on a B200)"
+    res["block_selection"] = sel
     res["peak_gbs"] = peaks["hbm_gbs"]
     return res
 

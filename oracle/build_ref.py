@@ -3,7 +3,7 @@ around the reference's own CUDA kernels, compiled from the reference headers whe
 
     python oracle/build_ref.py [--force]
 
-Needs the reference checkout (its directory is taken from FLASHOMNI_REFERENCE_DIR, with a built-in default) and the
+Needs the reference checkout (FLASHOMNI_REFERENCE_DIR, else a directory `reference` beside this repository) and the
 CUTLASS / CuTe headers the reference's GEMMs include (taken from the installed flashinfer wheel; the
 reference's own 3rdparty/cutlass submodule is empty). Nothing is copied from the reference; the only
 output is the shared library under oracle/_ref/, which is git-ignored. Does nothing (exit 0) when the
@@ -21,6 +21,15 @@ OUT = os.path.join(HERE, "_ref", "libflashomni_ref.so")
 SRC = os.path.join(HERE, "ref_harness.cu")
 
 
+def reference_dir() -> str:
+    """The reference checkout: FLASHOMNI_REFERENCE_DIR, else `reference` beside the repository; "" if neither exists."""
+    env = os.environ.get("FLASHOMNI_REFERENCE_DIR", "")
+    if env:
+        return env if os.path.isdir(env) else ""
+    sibling = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return sibling if os.path.isdir(sibling) else ""
+
+
 def _cutlass_root():
     try:
         import flashinfer
@@ -33,7 +42,7 @@ def _cutlass_root():
 
 
 def build(force: bool = False) -> str | None:
-    ref = os.environ.get("FLASHOMNI_REFERENCE_DIR", "/root/reference")
+    ref = reference_dir()
     inc = os.path.join(ref, "include")
     if not os.path.isdir(os.path.join(inc, "flashomni")):
         print("build_ref: reference headers not found, skipping")

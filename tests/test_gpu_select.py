@@ -63,3 +63,18 @@ def test_feeds_the_hot_path(cuda_device):
     b = w.run(q, k, v, *ref_masks)
     w.check_status()
     assert torch.equal(a, b)
+
+
+def test_matches_the_reference_masks(cuda_device):
+    """fo_select_blocks against the masks the reference's own torch + Triton path produced
+    (tests/golden/reference_selection.npz), same rule for rows at the threshold as the CPU statement's test."""
+    from helpers import check_selection_against_golden, load_selection_golden
+    from oracle.masks import unpack_segment
+    cases, _ = load_selection_golden()
+    for c in cases:
+        B, H, n = c["B"], c["H"], c["n"]
+        info, kv, ip, kp = _run(c["score"], c["t2t"], torch.from_numpy(c["q_threshold"]),
+                                torch.from_numpy(c["kv_threshold"]), False, cuda_device)
+        qa = np.stack([unpack_segment(info, int(ip[b]), n * H).reshape(n, H) for b in range(B)])
+        kk = np.stack([unpack_segment(kv, int(kp[b]), n * H * n).reshape(n, H, n) for b in range(B)])
+        check_selection_against_golden(c, qa, kk)
