@@ -49,8 +49,10 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
 
     Extensions (keyword-only in `plan`, default = reference behaviour): `mask_num_heads` and
     `mask_head_begin` describe a head window when the tensors hold only heads
-    [mask_head_begin, mask_head_begin + num_qo_heads) of a mask laid out for `mask_num_heads` heads
-    (used when heads are partitioned over GPUs).
+    [mask_head_begin, mask_head_begin + num_kv_heads) of a mask laid out for `mask_num_heads` heads
+    (used when heads are partitioned over GPUs). With `num_qo_heads > num_kv_heads` the masks have one bit per
+    (128 packed rows, kv head) as in the reference's kernel: a q-block is 128 / group tokens of all the q heads
+    that share a kv head.
     """
 
     def __init__(
@@ -160,6 +162,9 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         native_dtype(q_data_type)
         if num_kv_heads <= 0 or num_qo_heads % num_kv_heads != 0:
             raise ValueError("num_qo_heads must be a multiple of num_kv_heads")
+        group = num_qo_heads // num_kv_heads
+        if group not in (1, 2, 4, 8, 16):
+            raise NotImplementedError("flashomni_b200: num_qo_heads / num_kv_heads must be 1, 2, 4, 8 or 16")
         if head_dim_qk != 128 or head_dim_vo != 128:
             raise NotImplementedError("flashomni_b200: only head_dim 128 is implemented")
         if sparse_block_size_for_q != 128 or sparse_block_size_for_kv != 128:
@@ -191,20 +196,26 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         self._cached_q_data_type = q_data_type
         self._cached_kv_data_type = kv_data_type
 
+        # With grouped heads the masks are indexed as the reference's kernel indexes them
+        # (include/flashomni/attention/prefill.cuh:1283-1291): one bit per (block of 128 packed rows, kv head), a
+        # packed row being a (token, q head of the group) pair in token-major order, i.e. a q-block covers
+        # 128 / group tokens for all the q heads of one kv head. group = 1 is the plain (128 tokens, head) layout.
+        mask_heads_here = num_kv_heads
         if mask_num_heads is None:
-            mask_num_heads = num_qo_heads
-        if mask_head_begin < 0 or mask_head_begin + num_qo_heads > mask_num_heads:
+            mask_num_heads = mask_heads_here
+        if mask_head_begin < 0 or mask_head_begin + mask_heads_here > mask_num_heads:
             raise ValueError("mask head window out of range")
 
         ql = (qo_indptr_host[1:] - qo_indptr_host[:-1]).to(torch.int64)
         kl = (kv_indptr_host[1:] - kv_indptr_host[:-1]).to(torch.int64)
         if bool((ql < 0).any()) or bool((kl < 0).any()):
             raise ValueError("indptr arrays must be non-decreasing")
-        nq = (ql + sparse_block_size_for_q - 1) // sparse_block_size_for_q
+        self._q_block_tokens = sparse_block_size_for_q // group
+        nq = (ql + self._q_block_tokens - 1) // self._q_block_tokens
         nkv = (kl + sparse_block_size_for_kv - 1) // sparse_block_size_for_kv
-        self._n_cand = int((nq * num_qo_heads).sum())
+        self._n_cand = int((nq * mask_heads_here).sum())
         self._max_nkv = int(nkv.max()) if batch_size > 0 else 0
-        self._max_kept = int((nq * nkv * num_qo_heads).sum())
+        self._max_kept = int((nq * nkv * mask_heads_here).sum())
         self._batch_size = batch_size
         self._num_qo_heads = num_qo_heads
         self._num_kv_heads = num_kv_heads
@@ -395,8 +406,8 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             _native.ptr(sparse_kv_info), 0 if sparse_kv_info is None else sparse_kv_info.numel(),
             _native.ptr(sparse_info_indptr), _native.ptr(sparse_kv_info_indptr),
             _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
-            self._batch_size, self._mask_num_heads, self._mask_head_begin, self._num_qo_heads,
-            self._sparse_block_size_for_q, self._sparse_block_size_for_kv, 1 if is_full else 0,
+            self._batch_size, self._mask_num_heads, self._mask_head_begin, self._num_kv_heads,
+            self._q_block_tokens, self._sparse_block_size_for_kv, 1 if is_full else 0,
             self._n_cand, self._max_nkv, max(self._n_cand, 1), max(self._max_kept, 1),
             _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
             _native.ptr(ws["order"]), _native.ptr(ws["counters"]), _native.ptr(ws["scratch"]),
@@ -405,7 +416,7 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         rc = _native.load().fo_attn_units(
             _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]), _native.ptr(ws["order"]),
             _native.ptr(ws["counters"]), _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
-            max(self._n_cand, 1), self._max_nkv, self._sparse_block_size_for_q, self._sparse_block_size_for_kv,
+            max(self._n_cand, 1), self._max_nkv, self._q_block_tokens, self._sparse_block_size_for_kv,
             self._num_streams, self.MIN_CHUNK, self._max_units, self._partial_slots, _native.ptr(ws["units"]),
             _native.ptr(ws["unit_counters"]), _native.ptr(ws["arrive"]), stream)
         _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper (work units)")

@@ -61,8 +61,48 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 }  // namespace
 
+// A tensor map is a pure function of (base, extents, strides, box, swizzle): encoded maps are kept in a small
+// per-thread table and reused when a call passes the same tensors again (a step that runs the same buffers every
+// time never re-encodes).
+namespace {
+struct TmapKey {
+  const void* base;
+  uint64_t dims[5];
+  uint64_t strides[5];
+  uint32_t box[5];
+  int32_t rank;
+  int32_t swizzle;
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kTmapSlots = 64;
+thread_local TmapSlot t_tmaps[kTmapSlots];
+}  // namespace
+
 int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+  if (rank < 1 || rank > 5) return -2;
+  TmapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.rank = rank;
+  key.swizzle = swizzle128 ? 1 : 0;
+  uint64_t h = reinterpret_cast<uint64_t>(base) * 0x9E3779B97F4A7C15ull + static_cast<uint64_t>(rank * 2 + key.swizzle);
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.strides[i] = i > 0 ? strides_bytes[i] : 0;
+    key.box[i] = box[i];
+    h = (h ^ (dims[i] + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2))) * 0xff51afd7ed558ccdull;
+    h ^= key.strides[i] * 0xc4ceb9fe1a85ec53ull + box[i];
+  }
+  TmapSlot& slot = t_tmaps[(h >> 32) % kTmapSlots];
+  if (slot.used && memcmp(&slot.key, &key, sizeof(key)) == 0) {
+    *out = slot.map;
+    return 0;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
   cuuint64_t gdim[5];
@@ -79,7 +119,11 @@ int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64
                         gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+  if (r != CUDA_SUCCESS) return static_cast<int>(r);
+  slot.key = key;
+  slot.map = *out;
+  slot.used = true;
+  return 0;
 }
 
 }  // namespace fo
@@ -264,21 +308,27 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
     if (s <= 0 || (s % 8) != 0)
       return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: strides must be positive multiples of 8 elements");
 
+  // With several q heads per kv head a q tile is 128 rows of (token, q head of the group) pairs, token-major, as the
+  // reference packs them (include/flashomni/attention/prefill.cuh:1283-1291): a box of group heads x 128 / group tokens.
+  const uint32_t group = static_cast<uint32_t>(num_qo_heads / num_kv_heads);
+  if (group > 16 || (16 % group) != 0)
+    return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: num_qo_heads / num_kv_heads must be 1, 2, 4, 8 or 16");
   AttnArgs a;
   memset(&a, 0, sizeof(a));
   {
     const uint32_t box[3] = {64, 1, 128};
+    const uint32_t qbox[3] = {64, group, 128 / group};
     const uint64_t qd[3] = {128, static_cast<uint64_t>(num_qo_heads), static_cast<uint64_t>(total_q)};
     const uint64_t qs[3] = {0, static_cast<uint64_t>(q_stride_h) * 2, static_cast<uint64_t>(q_stride_n) * 2};
     const uint64_t kd[3] = {128, static_cast<uint64_t>(num_kv_heads), static_cast<uint64_t>(total_kv)};
     const uint64_t ks[3] = {0, static_cast<uint64_t>(k_stride_h) * 2, static_cast<uint64_t>(k_stride_n) * 2};
     const uint64_t vs[3] = {0, static_cast<uint64_t>(v_stride_h) * 2, static_cast<uint64_t>(v_stride_n) * 2};
-    int r = encode_tmap_16bit(&a.tmap_q, q, 3, qd, qs, box);
+    int r = encode_tmap_16bit(&a.tmap_q, q, 3, qd, qs, qbox);
     if (r == 0) r = encode_tmap_16bit(&a.tmap_k, k, 3, kd, ks, box);
     if (r == 0) r = encode_tmap_16bit(&a.tmap_v, v, 3, kd, vs, box);
     const uint64_t os[3] = {0, static_cast<uint64_t>(o_stride_h) * 2, static_cast<uint64_t>(o_stride_n) * 2};
-    if (r == 0) r = encode_tmap_16bit(&a.tmap_o, o, 3, qd, os, box);  // stores of 64 columns x 128 rows
-    const uint32_t obox16[3] = {32, 1, 16};
+    if (r == 0) r = encode_tmap_16bit(&a.tmap_o, o, 3, qd, os, qbox);  // stores of 64 columns x 128 rows
+    const uint32_t obox16[3] = {32, group, 16 / group};
     if (r == 0) r = encode_tmap_16bit(&a.tmap_o16, o, 3, qd, os, obox16, false);
     if (r != 0) {
       char buf[96];
@@ -299,7 +349,7 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   a.partials = partials;
   a.partial_slots = static_cast<int>(partial_slots > 0x7fffffffLL ? 0x7fffffffLL : partial_slots);
   a.head_begin = head_begin;
-  a.group_size = num_qo_heads / num_kv_heads;
+  a.group_size = static_cast<int>(group);
   a.is_bf16 = dtype == FO_DTYPE_BF16;
   if (logits_soft_cap > 0.f) {
     a.soft_cap_pre = sm_scale / logits_soft_cap;
@@ -368,7 +418,7 @@ size_t fo_gemm_workspace_bytes(int32_t batch, int32_t m, int32_t n, int32_t k, i
   const size_t mt = static_cast<size_t>(m) / 128, nt = static_cast<size_t>(n) / 128;
   const size_t rows = static_cast<size_t>(batch) * mt;
   const size_t lh = static_cast<size_t>(k) / static_cast<size_t>(head_dim);
-  const size_t words_q = 8 + 4 * rows * ((nt + 1) / 2);
+  const size_t words_q = 8 + 4 * rows * nt;
   const size_t words_o = 8 + (rows + 1) + rows * (lh > 0 ? lh : 1) + rows;
   const size_t words = words_q > words_o ? words_q : words_o;
   return ((words * 4 + 255) / 256) * 256;
@@ -416,7 +466,8 @@ GemmListArgs make_list_args(const GemmShape& s, const uint8_t* sparse_info, int6
   const int rows = s.batch * (s.m / 128);
   const int lh = s.k / s.head_dim;
   a.tiles = w + 8;
-  a.max_tiles = rows * ((s.n / 128 + 1) / 2);
+  a.max_tiles = rows * (s.n / 128);
+  a.n_ctas = sm_count();
   a.row_indptr = w + 8;
   a.row_heads = w + 8 + rows + 1;
   a.row_order = w + 8 + rows + 1 + rows * (lh > 0 ? lh : 1);

@@ -333,8 +333,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       int kv_row0 = 0;                   // first kv row of the current item's request
       bool ok = true;
       while (ok && seq.next(a, ignore_empty)) {
-        const int hq = seq.h;
-        const int hk = hq / a.group_size;
+        const int hk = seq.h;                 // a unit's head is the kv head; its q tile holds the
+        const int hq = hk * a.group_size;     // group's q heads of 128 / group tokens, token-major
         if (seq.first()) {  // new item: its Q tile goes to buffer item_no & 1
           kv_row0 = seq.kv_row0;
           const int qb_i = seq.item_no & 1;
@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       int kv_row0 = 0;
       bool ok = true;
       while (ok && seq.next(a, ignore_empty)) {
-        const int hk = seq.h / a.group_size;
+        const int hk = seq.h;
         if (seq.first()) kv_row0 = seq.kv_row0;
         const int slot = static_cast<int>(nv % kRingV);
         if (!mbar_wait(&tail->v_empty[slot], ((nv / kRingV) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
@@ -491,10 +491,13 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       float* lse;
       bool row_ok;
     };
-    auto row_ctx = [&](int q_row0, int q_valid, int hq) -> RowCtx {
+    // Row r of a tile is token q_row0 + r / group, q head h * group + r % group (group = 1: the row itself).
+    const int grp = a.group_size;
+    auto row_ctx = [&](int q_row0, int q_valid, int h) -> RowCtx {
       RowCtx c;
-      c.row_ok = row < q_valid;
-      const int64_t grow = static_cast<int64_t>(q_row0) + row;
+      c.row_ok = static_cast<int>(row) < q_valid * grp;
+      const int64_t grow = static_cast<int64_t>(q_row0) + static_cast<int>(row) / grp;
+      const int hq = h * grp + static_cast<int>(row) % grp;
       c.orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h + ocol;
       c.lse = (a.lse != nullptr && ocol == 0u) ? a.lse + grow * a.lse_stride_n + hq : nullptr;
       return c;
@@ -555,12 +558,12 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         }
         outv[q] = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      const bool whole = pend_q_valid == kBQ;  // no row of the q-block is past the request
+      const bool whole = pend_q_valid * grp == kBQ;  // no row of the q-block is past the request
       if (whole) {
         // Through a 1 KB staging area per warp (16 rows x 64 bytes, plain row-major) and a TMA store of one
         // 16-row x 32-column box: a store instruction of a warp would otherwise write 32 scattered 16-byte pieces.
         uint8_t* stg = smem_ostage + warp * kOutStageBytes;
-        const int grow0 = pend_q_row0 + quad * 32;
+        const int grow0 = pend_q_row0 + (quad * 32) / grp;
 #pragma unroll
         for (int ph = 0; ph < 2; ++ph) {
           if (lane == 0) tma_store_wait_read<0>();  // the staging area is free once its last store has read it
@@ -573,7 +576,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&a.tmap_o16, stg, static_cast<int>(ocol), pend_h, grow0 + ph * 16);
+            tma_store_3d(&a.tmap_o16, stg, static_cast<int>(ocol), pend_h * grp, grow0 + (ph * 16) / grp);
             tma_store_commit();
           }
         }

@@ -315,8 +315,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_streams_kernel(const __
         uint32_t g = 0;
         int kv_row0 = 0;
         while (seq.next(a, ignore_empty)) {
-          const int hq = seq.h;
-          const int hk = hq / a.group_size;
+          const int hk = seq.h;               // a unit's head is the kv head; its q tile holds the
+          const int hq = hk * a.group_size;   // group's q heads of 128 / group tokens, token-major
           // the K slot (and, for a new item, the Q slot) is free once the Q K^T of the stream's previous block is done
           if (!mbar_wait(&sb->s_full, (g & 1u) ^ 1u, abort_flag)) break;
           if (seq.first()) {
@@ -458,12 +458,15 @@ __global__ void __launch_bounds__(kThreads, 1) attention_streams_kernel(const __
       bool whole;   // no row of the q-block is past the end of its request
       int grow0;    // first row of the q-block in the q / o tensors
     };
-    auto row_ctx = [&](int q_row0, int q_valid, int hq) -> RowCtx {
+    // Row r of a tile is token q_row0 + r / group, q head h * group + r % group (group = 1: the row itself).
+    const int grp = a.group_size;
+    auto row_ctx = [&](int q_row0, int q_valid, int h) -> RowCtx {
       RowCtx c;
-      c.row_ok = row < q_valid;
-      c.whole = q_valid == kBQ;
+      c.row_ok = static_cast<int>(row) < q_valid * grp;
+      c.whole = q_valid * grp == kBQ;
       c.grow0 = q_row0;
-      const int64_t grow = static_cast<int64_t>(q_row0) + row;
+      const int64_t grow = static_cast<int64_t>(q_row0) + static_cast<int>(row) / grp;
+      const int hq = h * grp + static_cast<int>(row) % grp;
       c.orow = o16 + grow * a.o_stride_n + static_cast<int64_t>(hq) * a.o_stride_h;
       c.lse = a.lse != nullptr ? a.lse + grow * a.lse_stride_n + hq : nullptr;
       return c;
@@ -602,7 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_streams_kernel(const __
             fence_proxy_async_smem();
             if (!wg_sync()) return false;
             if (wq == 0 && lane == 0) {
-              tma_store_3d(&a.tmap_o, stage, 64 * r, seq.h, c.grow0);
+              tma_store_3d(&a.tmap_o, stage, 64 * r, seq.h * grp, c.grow0);
               tma_store_commit();
             }
             stage_busy = true;

@@ -67,12 +67,12 @@ struct TileInfo {
 __device__ __forceinline__ int pairs_per_row(const GemmArgs& a) { return (a.n / kBNH + 1) / 2; }
 
 __device__ __forceinline__ int num_tiles(const GemmArgs& a) {
-  const int cap = a.batch * (a.m / kBM) * pairs_per_row(a);
   if (a.mode == kGemmQ && a.tiles != nullptr) {
+    const int cap = a.batch * (a.m / kBM) * (a.n / kBNH);  // a list holds at most one record per 128x128 tile
     const int n = *a.n_tiles_ptr;
     return n < cap ? (n < 0 ? 0 : n) : cap;
   }
-  return cap;
+  return a.batch * (a.m / kBM) * pairs_per_row(a);
 }
 
 __device__ __forceinline__ TileInfo get_tile(const GemmArgs& a, int t) {
@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
 
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream) {
-  const int cap = a.batch * (a.m / kBM) * ((a.n / kBNH + 1) / 2);
+  const int cap = a.batch * (a.m / kBM) * ((a.mode == kGemmQ && a.tiles != nullptr) ? a.n / kBNH : (a.n / kBNH + 1) / 2);
   if (cap <= 0) return cudaSuccess;
   const int grid = cap < max_ctas ? cap : max_ctas;
   cudaError_t e;

@@ -45,6 +45,7 @@ struct GemmListArgs {
   int is_full, is_for_cache;
   int32_t* tiles;                  // GEMM-Q: [max_tiles, 4] pair records (b, iy, ix0, ix1)
   int max_tiles;
+  int n_ctas;                      // CTAs of the GEMM launch that will draw the records (GEMM-Q list rule)
   int32_t* row_indptr;             // GEMM-O: [rows + 1]
   int32_t* row_heads;              // GEMM-O: [rows * local_heads]
   int32_t* row_order;              // GEMM-O: [rows]

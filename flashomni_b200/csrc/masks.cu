@@ -576,13 +576,39 @@ cudaError_t launch_attn_units(const UnitArgs& a, cudaStream_t stream) {
 // GEMM-Q: tile records (b, iy, ix0, ix1). Per row block (b, iy) the active column blocks are taken two
 // at a time in ascending order; a leftover single block has ix1 = -1. All two-block records come first,
 // the single-block records after them, each part in ascending (b, iy) order: the GEMM hands tiles to its
-// CTAs in list order, and the half-size tiles at the end fill the last wave.
+// CTAs in list order, and the half-size tiles at the end fill the last wave. The last `k` two-block records
+// are cut into two single-block records each, k chosen so that the launch ends earliest when `n_ctas` CTAs draw
+// the records in list order (gemm_q_split_rule: a two-block tile costs 20 time units, a single-block tile 13).
 // counters[0] = number of records, counters[1] = number of active 128x128 tiles, counters[3] = number
 // of two-block records. The kernel walks the row blocks twice: totals first, then the records.
+constexpr int kPairCost = 20, kSingleCost = 13;
+
+// Time at which the last CTA ends when `n` CTAs draw `pairs` two-block tiles and then `singles` single-block tiles
+// in list order, every tile going to the CTA that is free first.
+__device__ __forceinline__ int gemm_q_makespan(int pairs, int singles, int n) {
+  const int full = pairs / n, r = pairs % n;
+  int t_a = full * kPairCost, c_a = n - r;        // CTAs free after the full rounds
+  int t_b = (full + 1) * kPairCost, c_b = r;      // CTAs that run one more two-block tile
+  int end = (full + (r ? 1 : 0)) * kPairCost;
+  int m = singles;
+  while (m > 0) {
+    if (c_a > 0 && (c_b == 0 || t_a <= t_b)) {
+      m -= c_a;
+      t_a += kSingleCost;
+      end = end > t_a ? end : t_a;
+    } else {
+      m -= c_b;
+      t_b += kSingleCost;
+      end = end > t_b ? end : t_b;
+    }
+  }
+  return end;
+}
+
 __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
   __shared__ int s_warp[32];
   __shared__ int s_warp_t[32];
-  __shared__ int s_carry, s_carry_t, s_pairs_total;
+  __shared__ int s_carry, s_carry_t, s_pairs_total, s_best;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int mt = a.m / 128, nt = a.n / 128;
   const int rows = a.batch * mt;
@@ -590,6 +616,8 @@ __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
     if (tid == 0) { s_carry = 0; s_carry_t = 0; }
     __syncthreads();
     const int pairs_total = pass == 0 ? 0 : s_pairs_total;
+    const int n_split = pass == 0 ? 0 : (s_best & 0xffff);   // two-block records cut into singles
+    const int pairs_kept = pairs_total - n_split;
     for (int base = 0; base < rows; base += blockDim.x) {
       const int r = base + tid;
       int cnt = 0;
@@ -641,7 +669,7 @@ __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
       __syncthreads();
       if (pass == 1 && r < rows && cnt > 0) {
         int pos = s_carry + (warp ? s_warp[warp - 1] : 0) + x - npair;
-        const int spos = pairs_total + s_carry_t + (warp ? s_warp_t[warp - 1] : 0) + xt - nsingle;
+        const int spos = pairs_total + n_split + s_carry_t + (warp ? s_warp_t[warp - 1] : 0) + xt - nsingle;
         const int b = r / mt, iy = r % mt;
         int first = -1;
         for (int ix = 0; ix < nt; ++ix) {
@@ -651,7 +679,15 @@ __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
           if (first < 0) {
             first = ix;
           } else {
-            if (pos < a.max_tiles) *reinterpret_cast<int4*>(a.tiles + 4 * pos) = make_int4(b, iy, first, ix);
+            if (pos < pairs_kept) {
+              if (pos < a.max_tiles) *reinterpret_cast<int4*>(a.tiles + 4 * pos) = make_int4(b, iy, first, ix);
+            } else {
+              const int sp = pairs_kept + 2 * (pos - pairs_kept);
+              if (sp + 1 < a.max_tiles) {
+                *reinterpret_cast<int4*>(a.tiles + 4 * sp) = make_int4(b, iy, first, -1);
+                *reinterpret_cast<int4*>(a.tiles + 4 * sp + 4) = make_int4(b, iy, ix, -1);
+              }
+            }
             ++pos;
             first = -1;
           }
@@ -662,15 +698,27 @@ __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
       if (tid == 0) { s_carry += s_warp[31]; s_carry_t += s_warp_t[31]; }
       __syncthreads();
     }
-    if (pass == 0 && tid == 0) s_pairs_total = s_carry;
-    __syncthreads();
+    if (pass == 0) {
+      if (tid == 0) { s_pairs_total = s_carry; s_best = 0x7fffffff; }
+      __syncthreads();
+      // thread k rates the list with its last k two-block records cut; the smallest (end time, k) wins
+      const int P = s_carry, S = s_carry_t, n = a.n_ctas > 0 ? a.n_ctas : 1;
+      if (tid <= P && tid <= n && P + S + tid <= a.max_tiles) {
+        const int t = gemm_q_makespan(P - tid, S + 2 * tid, n);
+        atomicMin(&s_best, ((t < 32767 ? t : 32767) << 16) | tid);
+      }
+      __syncthreads();
+      if (tid == 0 && s_best == 0x7fffffff) s_best = 0;  // a list that does not fit is reported below, uncut
+      __syncthreads();
+    }
   }
   if (tid == 0) {
-    const int n_rec = s_carry + s_carry_t;
+    const int n_split = s_best & 0xffff;
+    const int n_rec = s_carry + s_carry_t + n_split;
     a.counters[0] = n_rec;
     a.counters[1] = 2 * s_carry + s_carry_t;
     a.counters[2] = n_rec > a.max_tiles ? kDevBadIndex : kDevOk;
-    a.counters[3] = s_carry;
+    a.counters[3] = s_carry - n_split;
     a.counters[4] = kDevOk;  // status word of the GEMM kernel that follows
     a.counters[5] = 0;       // its tile cursor
   }

@@ -13,10 +13,20 @@
  *   - malformed device-side data (bad indptr, list overflow, a wait that ran out) never faults:
  *     the kernels record a code in the status word the call was given (see each function).
  *   - dtype: FO_DTYPE_F16 or FO_DTYPE_BF16 (inputs and outputs share it; accumulation is fp32).
+ *   - state between calls lives in memory the CALLER hands in, never in the library: the attention status words
+ *     (unit cursor, count of finished CTAs), `arrive` and `partials`, and the GEMM `workspace` (work list, tile
+ *     cursor, status word) are read and written by the launch that gets them. Two launches that share any of them
+ *     must be ordered on one stream (or by events); launches on different streams need their own copies. The
+ *     Python layer keeps one such set per wrapper object and one GEMM workspace per (device, stream). The only
+ *     memory the library owns is the static scratch of fo_gemm_q_static (one stream at a time, see there) and a
+ *     per-thread host table of encoded tensor maps.
  *
  * Bit layout of the packed masks (reference: include/flashomni/attention/prefill.cuh:1284-1294,
  * 1385-1394; include/flashomni/gemm/w16a16/gemm.cuh:50-58): request b's segment starts at byte
  * indptr[b]; q-block bit = qb*H + h; kv-block bit = (qb*H + h)*nkv + kvb; bit i = (seg[i>>3] >> (i&7)) & 1.
+ * With grouped heads (Hq > Hkv) the attention reads the masks as the reference's kernel does
+ * (prefill.cuh:1283-1291): H = Hkv, and a q-block is 128 PACKED rows, a packed row being a (token, q head of the
+ * group) pair in token-major order, i.e. 128 / group tokens of all the q heads that share kv head h.
  */
 #ifndef FLASHOMNI_B200_H_
 #define FLASHOMNI_B200_H_
@@ -126,9 +136,11 @@ FO_API size_t fo_attn_partial_bytes(int64_t partial_slots);
  * (csrc/batch_sparseFA.cu:67-201 -> include/flashomni/attention/prefill.cuh:1203-1636), consuming kv_idx of
  * fo_mask_compact and the units of fo_attn_units. q [total_q, Hq, D], k/v [total_kv, Hkv, D],
  * o [total_q, Hq, D] with element strides (row, head); the innermost dimension is contiguous. lse (optional,
- * may be null): float32 [total_q, Hq], base 2. Hq here is the number of heads IN THE TENSORS; unit heads
- * are mask heads and map to tensor head (h - head_begin). q-blocks that are not listed are
- * not written. The kernel walks min(unit_counters[0], max_units) units, and none at all when unit_counters[3]
+ * may be null): float32 [total_q, Hq], base 2. Hq / Hkv here are the numbers of heads IN THE TENSORS; unit heads
+ * are mask heads and map to kv head (h - head_begin) of the tensors and its q heads (h - head_begin) * group + j.
+ * With group = Hq / Hkv > 1 (1, 2, 4, 8 or 16) the units are built with fo_mask_compact / fo_attn_units given
+ * head_count = Hkv and sbq = 128 / group tokens; a unit's q tile is then 128 / group tokens x group q heads.
+ * q-blocks that are not listed are not written. The kernel walks min(unit_counters[0], max_units) units, and none at all when unit_counters[3]
  * is not FO_DEV_OK or more partial slots are in use than `partial_slots` (the output is then untouched and
  * status[0] = FO_DEV_BAD_INDEX). The parts of a split item write fp32 partial results into `partials`
  * (fo_attn_partial_bytes(partial_slots) bytes, 16-byte aligned; null when partial_slots = 0) and the

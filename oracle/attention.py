@@ -35,12 +35,10 @@ def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info=None, sparse_kv_
     """q [Tq, H, D], k/v [Tkv, Hkv, D] (any float dtype, computed in `dtype`). Returns fp32 `out`
     (and base-2 `lse`). With `logits_soft_cap` > 0 the logits are cap * tanh(q.k * sm_scale / cap)
     (include/flashomni/attention/variants.cuh:47-50,72-74). `out_prior` supplies the rows of skipped q-blocks (zeros if None, as
-    flashomni/attention.py:778-781 allocates). Heads of q map to mask heads `head_begin + h`."""
+    flashomni/attention.py:778-781 allocates). kv head `hk` reads mask head `head_begin + hk` (of `num_mask_heads`)."""
     Tq, H, D = q.shape
     Hkv = k.shape[1]
     group = H // Hkv
-    if num_mask_heads is None:
-        num_mask_heads = H
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
     qf, kf, vf = q.to(dtype), k.to(dtype), v.to(dtype)
@@ -53,37 +51,47 @@ def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info=None, sparse_kv_
     if not is_full:
         sparse_info = np.asarray(sparse_info, dtype=np.uint8)
         sparse_kv_info = np.asarray(sparse_kv_info, dtype=np.uint8)
+    # Grouped heads (H > Hkv): the reference's kernel works on packed rows, a packed row being a (token, q head of
+    # the group) pair in token-major order; a q tile is 128 packed rows of ONE kv head and the masks hold one bit per
+    # (packed block, kv head) (prefill.cuh:1283-1291: `qo_tile_idx * CTA_TILE_Q / sbq * num_kv_heads + kv_head_idx`).
+    # A mask q-block therefore covers sbq / group tokens of all `group` q heads of a kv head. group = 1 is the plain
+    # (sbq tokens, head) layout.
+    if sbq % group != 0:
+        raise ValueError("sbq must be a multiple of num_qo_heads / num_kv_heads")
+    qtok = sbq // group
+    if num_mask_heads is None:
+        num_mask_heads = Hkv
     for b in range(len(qo) - 1):
         q0, q1, k0, k1 = int(qo[b]), int(qo[b + 1]), int(kv[b]), int(kv[b + 1])
-        nq = -(-(q1 - q0) // sbq)
+        nq = -(-(q1 - q0) // qtok)
         nkv = -(-(k1 - k0) // sbkv)
         if not is_full:
             qa = _masks.unpack_segment(sparse_info, int(info_indptr[b]),
                                        nq * num_mask_heads).reshape(nq, num_mask_heads)
             kk = _masks.unpack_segment(sparse_kv_info, int(kv_info_indptr[b]),
                                        nq * num_mask_heads * nkv).reshape(nq, num_mask_heads, nkv)
-        for h in range(H):
-            mh = head_begin + h
-            hk = h // group
+        for hk in range(Hkv):
+            mh = head_begin + hk
             for qb in range(nq):
                 if not is_full and not qa[qb, mh]:
                     continue
-                r0, r1 = q0 + qb * sbq, min(q0 + (qb + 1) * sbq, q1)
+                r0, r1 = q0 + qb * qtok, min(q0 + (qb + 1) * qtok, q1)
                 kept = np.arange(nkv) if is_full else np.nonzero(kk[qb, mh])[0]
-                if len(kept) == 0:
-                    out[r0:r1, h] = 0
+                for h in range(hk * group, (hk + 1) * group):
+                    if len(kept) == 0:
+                        out[r0:r1, h] = 0
+                        if return_lse:
+                            lse[r0:r1, h] = NEG_INF_LSE
+                        continue
+                    cols = np.concatenate([np.arange(k0 + j * sbkv, min(k0 + (j + 1) * sbkv, k1)) for j in kept])
+                    cols_t = torch.from_numpy(cols)
+                    s = (qf[r0:r1, h] @ kf[cols_t, hk].T) * sm_scale
+                    if logits_soft_cap > 0:
+                        s = torch.tanh(s / logits_soft_cap) * logits_soft_cap
+                    p = torch.softmax(s, dim=-1)
+                    out[r0:r1, h] = p @ vf[cols_t, hk]
                     if return_lse:
-                        lse[r0:r1, h] = NEG_INF_LSE
-                    continue
-                cols = np.concatenate([np.arange(k0 + j * sbkv, min(k0 + (j + 1) * sbkv, k1)) for j in kept])
-                cols_t = torch.from_numpy(cols)
-                s = (qf[r0:r1, h] @ kf[cols_t, hk].T) * sm_scale
-                if logits_soft_cap > 0:
-                    s = torch.tanh(s / logits_soft_cap) * logits_soft_cap
-                p = torch.softmax(s, dim=-1)
-                out[r0:r1, h] = p @ vf[cols_t, hk]
-                if return_lse:
-                    lse[r0:r1, h] = torch.logsumexp(s, dim=-1) * math.log2(math.e)
+                        lse[r0:r1, h] = torch.logsumexp(s, dim=-1) * math.log2(math.e)
     return (out, lse) if return_lse else out
 
 

@@ -232,14 +232,53 @@ def gemm_q_tiles(sparse_info, info_indptr, batch: int, m: int, n: int, num_heads
     return np.asarray(tiles, dtype=np.int32).reshape(-1, 3)
 
 
+GEMM_Q_PAIR_COST, GEMM_Q_SINGLE_COST = 20, 13
+
+
+def gemm_q_makespan(pairs: int, singles: int, n: int) -> int:
+    """End time of the last of `n` CTAs that draw `pairs` two-block tiles (cost 20) and then `singles` single-block
+    tiles (cost 13) in list order, every tile going to the CTA that is free first."""
+    full, r = divmod(pairs, n)
+    t_a, c_a = full * GEMM_Q_PAIR_COST, n - r
+    t_b, c_b = (full + 1) * GEMM_Q_PAIR_COST, r
+    end = (full + (1 if r else 0)) * GEMM_Q_PAIR_COST
+    m = singles
+    while m > 0:
+        if c_a > 0 and (c_b == 0 or t_a <= t_b):
+            m -= c_a
+            t_a += GEMM_Q_SINGLE_COST
+            end = max(end, t_a)
+        else:
+            m -= c_b
+            t_b += GEMM_Q_SINGLE_COST
+            end = max(end, t_b)
+    return end
+
+
+def gemm_q_split_rule(pairs: int, singles: int, n_ctas: int, max_records: int) -> int:
+    """How many of the last two-block records are cut into two single-block records: the k in
+    [0, min(pairs, n_ctas, 1023)] with pairs + singles + k <= max_records that gives the smallest end time
+    (clamped to 32767), the smallest such k."""
+    best = None
+    for k in range(0, min(pairs, n_ctas, 1023) + 1):
+        if pairs + singles + k > max_records:
+            break
+        t = min(gemm_q_makespan(pairs - k, singles + 2 * k, max(n_ctas, 1)), 32767)
+        if best is None or t < best[0]:
+            best = (t, k)
+    return 0 if best is None else best[1]
+
+
 def gemm_q_tile_pairs(sparse_info, info_indptr, batch: int, m: int, n: int, num_heads: int,
                       sparse_q_size: int = 128, num_text_tokens: int = 0, is_full: bool = False,
-                      head_begin: int = 0, head_dim: int | None = None) -> np.ndarray:
+                      head_begin: int = 0, head_dim: int | None = None, num_ctas: int | None = None) -> np.ndarray:
     """The work list GEMM-Q runs over: int32 [n_records, 4] = (b, iy, ix0, ix1). Per row block (b, iy),
     ascending, the active column blocks of `gemm_q_tiles` are taken two at a time in ascending order; a
     leftover single block has ix1 = -1. The list holds all two-block records first and the single-block
     records after them (both in ascending (b, iy) order): the GEMM hands tiles to its CTAs in list order,
-    and the half-size tiles at the end fill the last wave."""
+    and the half-size tiles at the end fill the last wave. With `num_ctas` (the CTAs of the launch, one per SM)
+    the last k two-block records are cut into two single-block records each (`gemm_q_split_rule`), placed between
+    the remaining two-block records and the leftover singles."""
     tiles = gemm_q_tiles(sparse_info, info_indptr, batch, m, n, num_heads, sparse_q_size, num_text_tokens,
                          is_full, head_begin, head_dim)
     pairs, singles = [], []
@@ -252,6 +291,13 @@ def gemm_q_tile_pairs(sparse_info, info_indptr, batch: int, m: int, n: int, num_
         else:
             singles.append((b, iy, ix, -1))
             i += 1
+    if num_ctas is not None:
+        k = gemm_q_split_rule(len(pairs), len(singles), num_ctas, batch * (m // 128) * (n // 128))
+        if k > 0:
+            cut = []
+            for (b, iy, i0, i1) in pairs[len(pairs) - k:]:
+                cut += [(b, iy, i0, -1), (b, iy, i1, -1)]
+            pairs = pairs[:len(pairs) - k] + cut
     return np.asarray(pairs + singles, dtype=np.int32).reshape(-1, 4)
 
 

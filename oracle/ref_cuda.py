@@ -40,14 +40,15 @@ def _stream(dev):
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
-def plan_unsplit(qo_indptr, kv_indptr, device):
+def plan_unsplit(qo_indptr, kv_indptr, device, group=1):
     """Work arrays of the reference planner for the un-split case (scheduler.cuh:67-168 with
-    cta_tile_q = 128 and kv_chunk_size >= every kv length): one entry per (request, 128-row q tile)."""
+    cta_tile_q = 128 and kv_chunk_size >= every kv length): one entry per (request, q tile of 128 packed rows),
+    a request having qo_len * group packed rows (scheduler.cuh:82)."""
     qo = np.asarray(qo_indptr, dtype=np.int64)
     kv = np.asarray(kv_indptr, dtype=np.int64)
     req, tile = [], []
     for b in range(len(qo) - 1):
-        for t in range(int(-(-(qo[b + 1] - qo[b]) // 128))):
+        for t in range(int(-(-((qo[b + 1] - qo[b]) * group) // 128))):
             req.append(b)
             tile.append(t)
     mk = lambda a: torch.tensor(a, dtype=torch.int32, device=device)
@@ -61,7 +62,7 @@ def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info, sparse_kv_info,
     """q [Tq, H, 128], k/v [Tkv, Hkv, 128] (NHD), `out` is written in place (only active q-blocks)."""
     dev = q.device
     if plan is None:
-        plan = plan_unsplit(qo_indptr.cpu().numpy(), kv_indptr.cpu().numpy(), dev)
+        plan = plan_unsplit(qo_indptr.cpu().numpy(), kv_indptr.cpu().numpy(), dev, q.shape[1] // k.shape[1])
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
     u = ctypes.c_uint32

@@ -10,32 +10,43 @@ from flashomni_b200 import workloads as wl
 
 
 def attention_case(name):
+    group = 1
     if name == "attn_uniform":
         H, lens_q, lens_kv, density, seed = 2, [512], [512], 0.6, 101
     elif name == "attn_ragged":
         H, lens_q, lens_kv, density, seed = 3, [300, 205], [256, 333], 0.7, 102
+    elif name == "attn_gqa":     # 4 q heads on 2 kv heads: mask q-blocks are 64 tokens x the 2 q heads of a kv head
+        H, lens_q, lens_kv, density, seed, group = 4, [320, 205], [256, 333], 0.7, 103, 2
+    elif name == "attn_gqa4":    # 8 q heads on 2 kv heads: 32 tokens x 4 q heads
+        H, lens_q, lens_kv, density, seed, group = 8, [100, 256], [384, 130], 0.6, 104, 4
     else:
         raise KeyError(name)
+    Hkv = H // group
+    qtok = 128 // group           # tokens per mask q-block (128 packed rows)
     qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
     kv = np.concatenate([[0], np.cumsum(lens_kv)]).astype(np.int32)
     rng = np.random.default_rng(seed)
-    qa = [(rng.random((-(-a // 128), H)) < density).astype(np.uint8) for a in lens_q]
-    kk = [(rng.random((-(-a // 128), H, -(-b // 128))) < density).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    qa = [(rng.random((-(-a // qtok), Hkv)) < density).astype(np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // qtok), Hkv, -(-b // 128))) < density).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
     for a, b in zip(qa, kk):
         a[0, 0] = 1
         b[0, 0, 0] = 1          # at least one non-trivial item
         b *= a[:, :, None]
         # the reference writes garbage-free output only if an active q-block keeps something; keep >= 1
         for qb in range(a.shape[0]):
-            for h in range(H):
+            for h in range(Hkv):
                 if a[qb, h] and b[qb, h].sum() == 0:
                     b[qb, h, 0] = 1
     m = wl.pack_masks(qa, kk)
     q = wl.randn_bf16((int(qo[-1]), H, 128), seed + 1)
-    k = wl.randn_bf16((int(kv[-1]), H, 128), seed + 2)
-    v = wl.randn_bf16((int(kv[-1]), H, 128), seed + 3)
+    k = wl.randn_bf16((int(kv[-1]), Hkv, 128), seed + 2)
+    v = wl.randn_bf16((int(kv[-1]), Hkv, 128), seed + 3)
     prior = wl.randn_bf16((int(qo[-1]), H, 128), seed + 4)
-    return {"q": q, "k": k, "v": v, "qo": qo, "kv": kv, "masks": m, "prior": prior, "H": H}
+    return {"q": q, "k": k, "v": v, "qo": qo, "kv": kv, "masks": m, "prior": prior, "H": H, "Hkv": Hkv, "group": group,
+            "q_block_tokens": qtok}
+
+
+ATTENTION_CASES = ("attn_uniform", "attn_ragged", "attn_gqa", "attn_gqa4")
 
 
 def gemm_case(name):

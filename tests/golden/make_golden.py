@@ -25,7 +25,7 @@ def main(out_path):
     dev = torch.device("cuda:0")
     res = {}
     d = lambda a, dt=None: (torch.from_numpy(a) if isinstance(a, np.ndarray) else a).to(dev)
-    for name in ("attn_uniform", "attn_ragged"):
+    for name in cases.ATTENTION_CASES:
         c = cases.attention_case(name)
         m = c["masks"]
         out = d(c["prior"]).clone()

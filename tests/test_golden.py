@@ -26,7 +26,7 @@ def test_packbits_bit_exact_vs_reference_kernel():
 
 
 def test_attention_oracle_vs_reference_kernel():
-    for name in ("attn_uniform", "attn_ragged"):
+    for name in cases.ATTENTION_CASES:
         c = cases.attention_case(name)
         m = c["masks"]
         out, lse = oa.sparse_attention(c["q"], c["k"], c["v"], c["qo"], c["kv"], m.sparse_info, m.sparse_kv_info,
@@ -34,20 +34,20 @@ def test_attention_oracle_vs_reference_kernel():
         gold = cases.from_bits(GOLD[name + "_out"])
         # the reference output is itself bf16-rounded: same tolerance as for our kernels
         assert_close_bf16(gold, out, name)
-        # rows of inactive q-blocks are untouched by the reference kernel: bit-identical to the prior
-        for b in range(len(c["qo"]) - 1):
-            for qb in range(m.q_active[b].shape[0]):
-                for h in range(c["H"]):
-                    if not m.q_active[b][qb, h]:
-                        r0 = int(c["qo"][b]) + qb * 128
-                        r1 = min(r0 + 128, int(c["qo"][b + 1]))
-                        assert torch.equal(gold[r0:r1, h], c["prior"][r0:r1, h])
+        # rows of inactive q-blocks are untouched by the reference kernel: bit-identical to the prior. A mask q-block
+        # is q_block_tokens tokens of the `group` q heads that share a kv head (128 packed rows).
+        g, qt = c["group"], c["q_block_tokens"]
         act = torch.zeros(out.shape[0], c["H"], dtype=torch.bool)
         for b in range(len(c["qo"]) - 1):
             for qb in range(m.q_active[b].shape[0]):
-                r0 = int(c["qo"][b]) + qb * 128
-                r1 = min(r0 + 128, int(c["qo"][b + 1]))
-                act[r0:r1] |= torch.from_numpy(m.q_active[b][qb].astype(bool))[None, :]
+                r0 = int(c["qo"][b]) + qb * qt
+                r1 = min(r0 + qt, int(c["qo"][b + 1]))
+                for hk in range(c["Hkv"]):
+                    heads = slice(hk * g, (hk + 1) * g)
+                    if m.q_active[b][qb, hk]:
+                        act[r0:r1, heads] = True
+                    else:
+                        assert torch.equal(gold[r0:r1, heads], c["prior"][r0:r1, heads])
         g_lse = torch.from_numpy(GOLD[name + "_lse"])
         assert torch.allclose(g_lse[act], lse[act], atol=2e-2, rtol=1e-4)
 

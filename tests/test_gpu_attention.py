@@ -297,22 +297,46 @@ def test_video_layer_size_sampled_rows(cuda_device):
         assert_close_bf16(o[qb * 128:(qb + 1) * 128, h].cpu(), ref.cpu(), f"video layer head {h} q-block {qb}")
 
 
-def test_grouped_query_attention(cuda_device):
-    """kv head = qo head // group (reference: prefill.cuh:1283-1287); the masks are indexed by qo head."""
-    H, Hkv, S = 8, 2, 640
-    rng = np.random.default_rng(3)
-    m = wl.flux_masks(1, H, S // 128, S // 128, 0.6, seed=31, text_blocks=1)
-    q = wl.randn_bf16((S, H, 128), 32)
-    k = wl.randn_bf16((S, Hkv, 128), 33)
-    v = wl.randn_bf16((S, Hkv, 128), 34)
+@pytest.mark.parametrize("H,Hkv", [(8, 2), (4, 2), (16, 1), (6, 3)])
+def test_grouped_query_attention(cuda_device, H, Hkv):
+    """Several q heads per kv head: the masks are indexed the way the reference's kernel indexes them
+    (prefill.cuh:1283-1291), one bit per (128 packed rows, kv head), a packed row being a (token, q head of the
+    group) pair: a mask q-block covers 128 / group tokens. Ragged requests, lse, rows of switched-off blocks kept."""
+    g = H // Hkv
+    qt = 128 // g
+    lens_q, lens_kv = [200, 75], [300, 128]
+    qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(lens_kv)]).astype(np.int32)
+    rng = np.random.default_rng(3 + H)
+    qa = [(rng.random((-(-a // qt), Hkv)) < 0.7).astype(np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // qt), Hkv, -(-b // 128))) < 0.6).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    kk[0][0, 0, :] = 0            # an active q-block that keeps nothing: zeros, lse -5e4
+    qa[0][0, 0] = 1
+    m = wl.pack_masks(qa, kk)
+    q = wl.randn_bf16((int(qo[-1]), H, 128), 32)
+    k = wl.randn_bf16((int(kv[-1]), Hkv, 128), 33)
+    v = wl.randn_bf16((int(kv[-1]), Hkv, 128), 34)
+    prior = wl.randn_bf16((int(qo[-1]), H, 128), 35)
     si, skv, ip, kp = masks_to_device(m, cuda_device)
-    indptr = torch.tensor([0, S], dtype=torch.int32, device=cuda_device)
     w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
-    w.plan(indptr, indptr, H, Hkv, 128, q_data_type=torch.bfloat16)
-    o = w.run(dev(q, cuda_device), dev(k, cuda_device), dev(v, cuda_device), si, skv, ip, kp)
+    w.plan(dev(qo, cuda_device), dev(kv, cuda_device), H, Hkv, 128, q_data_type=torch.bfloat16)
+    o, lse = w.run(dev(q, cuda_device), dev(k, cuda_device), dev(v, cuda_device), si, skv, ip, kp,
+                   out=dev(prior, cuda_device).clone(), return_lse=True)
     w.check_status()
-    ref = oa.sparse_attention(q, k, v, [0, S], [0, S], m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr)
+    ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                                       out_prior=prior, return_lse=True)
     assert_close_bf16(o.cpu(), ref, "gqa")
+    act = torch.zeros(int(qo[-1]), H, dtype=torch.bool)
+    for b in range(2):
+        for qb in range(qa[b].shape[0]):
+            r0 = int(qo[b]) + qb * qt
+            r1 = min(r0 + qt, int(qo[b + 1]))
+            for hk in range(Hkv):
+                if qa[b][qb, hk]:
+                    act[r0:r1, hk * g:(hk + 1) * g] = True
+                else:
+                    assert torch.equal(o[r0:r1, hk * g:(hk + 1) * g].cpu(), prior[r0:r1, hk * g:(hk + 1) * g])
+    assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-4)
 
 
 def test_undersized_kept_list_is_reported_not_walked(cuda_device):

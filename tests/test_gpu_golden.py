@@ -26,19 +26,33 @@ def test_packbits_vs_reference_kernel_output(cuda_device):
         assert np.array_equal(y.cpu().numpy(), GOLD["packbits_" + order])
 
 
-@pytest.mark.parametrize("name", ["attn_uniform", "attn_ragged"])
+@pytest.mark.parametrize("name", cases.ATTENTION_CASES)
 def test_attention_vs_reference_kernel_output(cuda_device, name):
     c = cases.attention_case(name)
     m = c["masks"]
     w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
-    w.plan(dev(c["qo"], cuda_device), dev(c["kv"], cuda_device), c["H"], c["H"], 128, q_data_type=torch.bfloat16)
+    w.plan(dev(c["qo"], cuda_device), dev(c["kv"], cuda_device), c["H"], c["Hkv"], 128, q_data_type=torch.bfloat16)
     si, skv, ip, kp = masks_to_device(m, cuda_device)
-    o = w.run(dev(c["q"], cuda_device), dev(c["k"], cuda_device), dev(c["v"], cuda_device), si, skv, ip, kp,
-              out=dev(c["prior"], cuda_device).clone())
+    o, lse = w.run(dev(c["q"], cuda_device), dev(c["k"], cuda_device), dev(c["v"], cuda_device), si, skv, ip, kp,
+                   out=dev(c["prior"], cuda_device).clone(), return_lse=True)
     w.check_status()
     gold = cases.from_bits(GOLD[name + "_out"])
     # two bf16-rounded results of the same value may differ by one ulp
     assert_close_bf16(o, gold.float(), name, allow_ulp=1.0)
+    # rows of switched-off q-blocks: bit-identical to what the reference left there (the prior); lse on the others
+    g, qt = c["group"], c["q_block_tokens"]
+    act = torch.zeros(o.shape[0], c["H"], dtype=torch.bool)
+    for b in range(len(c["qo"]) - 1):
+        for qb in range(m.q_active[b].shape[0]):
+            r0 = int(c["qo"][b]) + qb * qt
+            r1 = min(r0 + qt, int(c["qo"][b + 1]))
+            for hk in range(c["Hkv"]):
+                heads = slice(hk * g, (hk + 1) * g)
+                if m.q_active[b][qb, hk]:
+                    act[r0:r1, heads] = True
+                else:
+                    assert torch.equal(o[r0:r1, heads].cpu(), gold[r0:r1, heads])
+    assert torch.allclose(lse.cpu()[act], torch.from_numpy(GOLD[name + "_lse"])[act], atol=2e-2, rtol=1e-4)
 
 
 def test_gemms_vs_reference_kernel_output(cuda_device):

@@ -135,15 +135,21 @@ def test_gemm_worklists_bit_exact(cuda_device):
     nbytes = lib.fo_gemm_workspace_bytes(B, M, N, K, 128)
     ws = torch.zeros(nbytes, dtype=torch.uint8, device=cuda_device)
     st = torch.cuda.current_stream(cuda_device).cuda_stream
+    sms = torch.cuda.get_device_properties(cuda_device).multi_processor_count
     for ntt, m_rows in ((0, M), (512, M - 512)):
-        rc = lib.fo_gemm_q_worklist(B, m_rows, N, H, 0, 128, 128, ntt, 0, _native.ptr(si), si.numel(), _native.ptr(ip),
-                                    _native.ptr(ws), ws.numel(), st)
-        _native.check(rc, "fo_gemm_q_worklist")
-        w = ws.view(torch.int32).cpu().numpy()
-        ref = om.gemm_q_tile_pairs(m.sparse_info, m.info_indptr, B, m_rows, N, H, 128, ntt)
-        assert w[0] == len(ref) and w[2] == 0
-        assert w[1] == len(om.gemm_q_tiles(m.sparse_info, m.info_indptr, B, m_rows, N, H, 128, ntt))
-        assert np.array_equal(w[8:8 + 4 * len(ref)].reshape(-1, 4), ref)
+        # all heads, and head windows as a rank of 2 / 8 has them (few records: the rule cuts more of them)
+        for hb, hc in ((0, H), (12, 12), (21, 3)):
+            rc = lib.fo_gemm_q_worklist(B, m_rows, hc * 128, H, hb, 128, 128, ntt, 0, _native.ptr(si), si.numel(),
+                                        _native.ptr(ip), _native.ptr(ws), ws.numel(), st)
+            _native.check(rc, "fo_gemm_q_worklist")
+            w = ws.view(torch.int32).cpu().numpy()
+            ref = om.gemm_q_tile_pairs(m.sparse_info, m.info_indptr, B, m_rows, hc * 128, H, 128, ntt, head_begin=hb,
+                                       head_dim=128, num_ctas=sms)
+            assert w[0] == len(ref) and w[2] == 0
+            assert w[1] == len(om.gemm_q_tiles(m.sparse_info, m.info_indptr, B, m_rows, hc * 128, H, 128, ntt,
+                                               head_begin=hb, head_dim=128))
+            assert w[3] == int((ref[:, 3] >= 0).sum())
+            assert np.array_equal(w[8:8 + 4 * len(ref)].reshape(-1, 4), ref)
         for cache in (0, 1):
             rc = lib.fo_gemm_o_worklist(B, m_rows, K, H, 0, 128, 128, ntt, cache, _native.ptr(si), si.numel(),
                                         _native.ptr(ip), _native.ptr(ws), ws.numel(), st)

@@ -159,3 +159,28 @@ def test_gemm_lists():
             r += 1
     cnt = (ip[1:] - ip[:-1])[order]
     assert np.all(cnt[:-1] >= cnt[1:])
+
+
+def test_gemm_q_split_rule():
+    # 463 two-block and 32 single-block tiles on 148 CTAs: three full rounds of two-block tiles (444), the other
+    # 19 cut into 38 singles, so the launch ends after 3 * 20 + 13 instead of 4 * 20 time units
+    assert om.gemm_q_makespan(463, 32, 148) == 80
+    assert om.gemm_q_split_rule(463, 32, 148, 10 ** 6) == 19
+    assert om.gemm_q_makespan(444, 70, 148) == 73
+    # one round with room to spare: nothing to gain below one two-block tile unless every tile is cut
+    assert om.gemm_q_split_rule(101, 38, 148, 10 ** 6) == 0
+    assert om.gemm_q_split_rule(37, 41, 148, 10 ** 6) == 37 and om.gemm_q_makespan(0, 115, 148) == 13
+    # capacity: records may not exceed max_records
+    assert om.gemm_q_split_rule(37, 41, 148, 80) == 0
+    assert om.gemm_q_split_rule(0, 5, 148, 100) == 0
+    # the list with a cut: same tiles, two-block records first, cut records between them and the leftover singles
+    m = wl.flux_masks(2, 4, 6, 6, 0.5, seed=5, text_blocks=1)
+    plain = om.gemm_q_tile_pairs(m.sparse_info, m.info_indptr, 2, 6 * 128, 4 * 128, 4)
+    P, S = int((plain[:, 3] >= 0).sum()), int((plain[:, 3] < 0).sum())
+    cut = om.gemm_q_tile_pairs(m.sparse_info, m.info_indptr, 2, 6 * 128, 4 * 128, 4, num_ctas=11)
+    k = om.gemm_q_split_rule(P, S, 11, 2 * 6 * 4)
+    assert k > 0 and len(cut) == P + S + k
+    assert np.array_equal(cut[:P - k], plain[:P - k]) and np.array_equal(cut[P + k:], plain[P:])
+    for j in range(k):
+        b, iy, i0, i1 = plain[P - k + j]
+        assert cut[P - k + 2 * j].tolist() == [b, iy, i0, -1] and cut[P - k + 2 * j + 1].tolist() == [b, iy, i1, -1]
