@@ -413,6 +413,20 @@ int fo_gemm_dense_tile_rows(int32_t batch, int32_t m, int32_t n, int32_t k, int3
   return gemm_tall_applies(g, sm_count) ? 256 : 128;
 }
 
+int fo_gemm_dense_tile_cols(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t has_full_init, int32_t sm_count) {
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.mode = kGemmQ;
+  g.init_mode = has_full_init ? kInitFull : kInitNone;
+  g.batch = batch;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  const int c = tall_tile_cols(g, sm_count);
+  return c != 0 ? c : 256;
+}
+
 size_t fo_gemm_workspace_bytes(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim) {
   if (batch <= 0 || m <= 0 || n <= 0 || k <= 0 || head_dim <= 0) return 64;
   const size_t mt = static_cast<size_t>(m) / 128, nt = static_cast<size_t>(n) / 128;
@@ -532,7 +546,7 @@ int encode_gemm_maps(const char* who, GemmArgs& g, const void* x, const void* w,
 
 namespace {
 // `prepared`: the work list is already in the workspace (built by fo_gemm_q_worklist on any stream ordered
-// before this call); only the status word and the tile cursor are reset here.
+// before this call); nothing is reset here (the kernel leaves the tile cursor at zero when it ends).
 int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t dtype, int32_t batch, int32_t m,
                 int32_t n, int32_t k, int32_t num_heads, int32_t head_begin, int32_t head_dim,
                 int32_t sparse_q_size, int32_t num_text_tokens, int32_t is_full, const uint8_t* sparse_info,
@@ -558,14 +572,13 @@ int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t
   if (!is_full) {
     GemmListArgs la = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
     la.is_full = 0;
-    e = prepared ? cudaMemsetAsync(wsw + 4, 0, 2 * sizeof(int32_t), st) : launch_gemm_q_tiles(la, st);
+    // A prepared list needs nothing here: the kernel leaves its cursor at zero when it ends, and the status word
+    // (set only when a bounded wait runs out) stays as it is until the next list is built.
+    e = prepared ? cudaSuccess : launch_gemm_q_tiles(la, st);
     if (e != cudaSuccess) return fail_cuda("fo_gemm_q (work list)", e);
     count_launches(prepared ? 0 : 1);
     g.tiles = la.tiles;
     g.n_tiles_ptr = la.counters;
-  } else {
-    e = cudaMemsetAsync(wsw + 4, 0, 2 * sizeof(int32_t), st);  // status word and tile cursor (the list kernel does this on the sparse path)
-    if (e != cudaSuccess) return fail_cuda("fo_gemm_q (status reset)", e);
   }
   g.y = y;
   g.init = bias;
@@ -586,6 +599,13 @@ int gemm_q_impl(const void* x, const void* w, void* y, const void* bias, int32_t
     const uint64_t yst[2] = {0, static_cast<uint64_t>(n) * 2};
     if (encode_tmap_16bit(&g.tmap_y, y, 2, yd, yst, ybox) != 0)
       return fail(FO_ERR_CUDA, "fo_gemm_q: cuTensorMapEncodeTiled failed (output boxes)");
+    if (tall_tile_cols(g, sm_count()) == 192) {
+      const uint32_t wbox[2] = {64, 64};
+      const uint64_t wd[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+      const uint64_t wst[2] = {0, static_cast<uint64_t>(k) * 2};
+      if (encode_tmap_16bit(&g.tmap_b64, w, 2, wd, wst, wbox) != 0)
+        return fail(FO_ERR_CUDA, "fo_gemm_q: cuTensorMapEncodeTiled failed (64-row weight boxes)");
+    }
     e = launch_gemm_tall(g, sm_count(), st);
   } else {
     e = launch_gemm(g, sm_count(), st);
@@ -635,7 +655,7 @@ int gemm_o_impl(const void* x, const void* w, void* y, const void* init, int32_t
   if (rc != FO_OK) return rc;
   GemmListArgs la = make_list_args(s, sparse_info, sparse_info_bytes, sparse_info_indptr, workspace);
   la.is_for_cache = is_for_cache;
-  cudaError_t e = prepared ? cudaMemsetAsync(wsw + 4, 0, 2 * sizeof(int32_t), st) : launch_gemm_o_rows(la, st);
+  cudaError_t e = prepared ? cudaSuccess : launch_gemm_o_rows(la, st);
   if (e != cudaSuccess) return fail_cuda("fo_gemm_o (work list)", e);
   count_launches(prepared ? 1 : 2);
   g.y = y;

@@ -101,8 +101,7 @@ __device__ __forceinline__ bool wait_all(uint64_t* bar, uint32_t parity, volatil
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
 }
 
-// Work-list positions are handed out dynamically: position blockIdx.x + stream * gridDim.x goes to the stream
-// at launch, the following ones are drawn from a device-wide cursor by the stream's producer, which passes them
+// Work-list positions are handed out dynamically: one position per stream is fixed at launch (ItemDraw::init), the following ones are drawn from a device-wide cursor by the stream's producer, which passes them
 // to the other roles through a small shared-memory queue (entry k in slot k % kItemQ, -1 ends the sequence).
 struct ItemDraw {  // the drawing role (one thread)
   StreamBars* sb;
@@ -127,7 +126,10 @@ struct ItemDraw {  // the drawing role (one thread)
   }
   __device__ __forceinline__ void init(StreamBars* s, int stream, int32_t* cur, volatile int* ab, int n) {
     sb = s; cursor = cur; abort_flag = ab; n_items = n; n_pub = 0; started = false; ended = false;
-    const int first = static_cast<int>(blockIdx.x) + stream * static_cast<int>(gridDim.x);
+    // Units come longest first. Stream 0 of CTA c starts with unit c, stream 1 with unit 2 * CTAs - 1 - c: the SM
+    // that got the longest unit of the first round gets the shortest of the second.
+    const int first = stream == 0 ? static_cast<int>(blockIdx.x)
+                                  : kStreams * static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
     p0 = first < n ? first : -1;
     p1 = p2 = -1;
     bool ok = publish(p0);

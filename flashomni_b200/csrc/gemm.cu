@@ -445,6 +445,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  // the last CTA to get here puts the tile cursor (and its own arrival count, the word after it) back to zero,
+  // so the next launch over the same workspace needs no reset in between
+  if (threadIdx.x == 0 && a.cursor != nullptr) {
+    __threadfence();
+    if (atomicAdd(a.cursor + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      atomicExch(a.cursor, 0);
+      atomicExch(a.cursor + 1, 0);
+    }
+  }
 }
 
 }  // namespace

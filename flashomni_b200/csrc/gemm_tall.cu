@@ -1,10 +1,13 @@
-// Dense projection GEMM with 256x256 output tiles: Y[rows, n] = X[rows, k] W[n, k]^T (+ bias).
+// Dense projection GEMM with 256x256 (or 256x192) output tiles: Y[rows, n] = X[rows, k] W[n, k]^T (+ bias).
 //
 // Why a second GEMM kernel: the path from L2 to the SMs is what limits the 128x256 tiles of gemm.cu (48 KB
 // of operands per 512 tensor clocks = 94 B/clk per SM against about 84 B/clk that all SMs can pull from L2 at
 // once). A 256x256 tile needs 64 KB per 1024 tensor clocks (62.5 B/clk): two 128-row halves of X share one
 // 256-column block of W in shared memory. Only the dense mode uses it (a sparse GEMM-Q would need two row
-// blocks with the same active heads); shapes whose N is not a multiple of 256 fall back to gemm.cu.
+// blocks with the same active heads); shapes whose N is not a multiple of 256 or 192 fall back to gemm.cu.
+// The 192-column variant (56 KB per 768 tensor clocks, 73 B/clk) exists for shapes whose tiles fill the SMs
+// badly at 256 columns: a narrow projection (one GPU's share of the heads) gets 4/3 as many tiles, each 3/4 as
+// long, and the launch lasts as long as its fullest SM (tall_tile_cols picks the width).
 //
 // One persistent CTA per SM, 384 threads. Warp 8: TMA producer, 3 stages of 64 KB (X top, X bottom, W, W).
 // Warps 9 and 10: MMA issuers, per K block of 64 four 128x256x16 MMAs into the top accumulator (TMEM columns
@@ -21,10 +24,10 @@
 namespace fo {
 namespace {
 
-constexpr int kBM = 128, kBN = 256, kBK = 64;
+constexpr int kBM = 128, kBK = 64;
 constexpr int kStages = 3;
 constexpr int kHalfBytes = kBM * kBK * 2;          // 16 KB: a 128-row K block of X or W
-constexpr int kStageBytes = 4 * kHalfBytes;        // X top | X bottom | W rows 0-127 | W rows 128-255
+constexpr int kStageBytesMax = 4 * kHalfBytes;     // X top | X bottom | W rows 0-127 | W rows 128-(kBN-1)
 constexpr int kEpiWarps = 8;
 constexpr int kWarpProducer = kEpiWarps, kWarpMma = kEpiWarps + 1;  // warps 9 and 10 issue the MMAs of one half each
 constexpr int kThreads = (kEpiWarps + 4) * 32;     // 384: three warpgroups (warp 11 only takes part in the set-up)
@@ -42,15 +45,17 @@ struct Tail {
   int abort_flag;
 };
 constexpr int kStageWarpBytes = 16 * 128;          // store staging per epilogue warp
-constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kStageWarpBytes + 1024 + static_cast<int>(sizeof(Tail));
+constexpr int kSmemBytes = kStages * kStageBytesMax + kEpiWarps * kStageWarpBytes + 1024 + static_cast<int>(sizeof(Tail));
 
 
-template <bool kBf16>
+template <bool kBf16, int kBN>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_constant__ GemmArgs a) {
+  static_assert(kBN == 256 || kBN == 192, "tile width");
+  constexpr int kStageBytes = 2 * kHalfBytes + kBN * kBK * 2;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
-  uint8_t* smem_stage = smem + kStages * kStageBytes;
+  uint8_t* smem_stage = smem + kStages * kStageBytesMax;
   Tail* tail = reinterpret_cast<Tail*>(smem_stage + kEpiWarps * kStageWarpBytes);
   volatile int* abort_flag = &tail->abort_flag;
   const int warp = threadIdx.x >> 5;
@@ -71,6 +76,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
   if (warp == kWarpProducer && lane == 0) {
     tma_prefetch_desc(&a.tmap_a);
     tma_prefetch_desc(&a.tmap_b);
+    if (kBN != 256) tma_prefetch_desc(&a.tmap_b64);
     tma_prefetch_desc(&a.tmap_y);
   }
   if (warp == kWarpMma) {
@@ -106,7 +112,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
           tma_load_2d(s, &a.tmap_a, &tail->full[stage], j * kBK, a_row);
           tma_load_2d(s + kHalfBytes, &a.tmap_a, &tail->full[stage], j * kBK, a_row + kBM);
           tma_load_2d(s + 2 * kHalfBytes, &a.tmap_b, &tail->full[stage], j * kBK, w_row);
-          tma_load_2d(s + 3 * kHalfBytes, &a.tmap_b, &tail->full[stage], j * kBK, w_row + kBM);
+          if (kBN == 256) tma_load_2d(s + 3 * kHalfBytes, &a.tmap_b, &tail->full[stage], j * kBK, w_row + kBM);
+          else tma_load_2d(s + 3 * kHalfBytes, &a.tmap_b64, &tail->full[stage], j * kBK, w_row + kBM);  // 64 rows
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -120,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
       constexpr uint32_t idesc = make_idesc_f16(kBM, kBN, kBf16, 0, 0);
       const uint64_t desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
       const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32), desc_lo0 = static_cast<uint32_t>(desc0);
-      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(half * kBN);
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(half * 256);
       int stage = 0;
       uint32_t phase = 0, tile_phase = 0;
       bool ok = true;
@@ -148,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
     // ------------------------------------------------------------- epilogue: warpgroup `half` drains its accumulator
     const int half = warp >> 2;
-    const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(half * kBN);
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(half * 256);
     const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(a.init);
     uint32_t tile_phase = 0;
     bool ok = true;
@@ -243,36 +250,52 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tall_kernel(const __grid_con
 }  // namespace
 
 
-bool gemm_tall_applies(const GemmArgs& a, int sm_count) {
+// Tile width for a dense launch: 256 or 192 columns (0: leave the launch to the 128x256 tiles of gemm.cu). All
+// kernels deal equal tiles in fixed shares, so a launch lasts as long as its fullest SM: rounds of tiles times the
+// tile's length, in units of a 128x256 tile of this kernel (a 256x256 tile is 2, a 256x192 tile 1.5; the 128x256
+// tiles of gemm.cu run at about 0.93 of this kernel's rate). The other kernel gets the launch only when it is
+// clearly ahead; between the two widths of this kernel the wider wins ties.
+int tall_tile_cols(const GemmArgs& a, int sm_count) {
   const bool fits = a.mode == kGemmQ && a.tiles == nullptr && (a.init_mode == kInitNone || a.init_mode == kInitBias1D) &&
                     (static_cast<int64_t>(a.batch) * a.m) % kBM == 0 && static_cast<int64_t>(a.batch) * a.m >= 2 * kBM &&
-                    a.n % kBN == 0 && a.k % kBK == 0 && a.k > 0;
-  if (!fits || sm_count <= 0) return fits;
-  // Both kernels deal equal tiles in fixed shares, so a launch lasts as long as its fullest SM: compare how well
-  // the 256x256 tiles and the 128x256 tiles of the other kernel fill whole waves (that kernel's tiles run at about
-  // 0.93 of this one's rate), and leave the launch to the other kernel only when it is clearly ahead.
+                    a.k % kBK == 0 && a.k > 0 && a.n > 0;
+  if (!fits) return 0;
+  const bool ok256 = a.n % 256 == 0, ok192 = a.n % 192 == 0;
+  if (!ok256 && !ok192) return 0;
+  if (sm_count <= 0) return ok256 ? 256 : 192;
   const int64_t rows = static_cast<int64_t>(a.batch) * a.m;
-  const int64_t t_tall = ((rows + 2 * kBM - 1) / (2 * kBM)) * (a.n / kBN);
-  const int64_t t_wide = (rows / kBM) * (a.n / kBN);
-  auto fill = [&](int64_t t) { return static_cast<double>(t) / static_cast<double>(((t + sm_count - 1) / sm_count) * sm_count); };
-  return !(fill(t_wide) * 0.93 > fill(t_tall) * 1.05);
+  const int64_t row_pairs = (rows + 2 * kBM - 1) / (2 * kBM);
+  auto rounds = [&](int64_t t) { return static_cast<double>((t + sm_count - 1) / sm_count); };
+  const double c256 = ok256 ? rounds(row_pairs * (a.n / 256)) * 2.0 : 1e30;
+  const double c192 = ok192 ? rounds(row_pairs * (a.n / 192)) * 1.5 : 1e30;
+  const int cols = c192 < c256 ? 192 : 256;
+  const double c_tall = c192 < c256 ? c192 : c256;
+  // the other kernel: 128-row tiles of two column blocks (a last single block of an odd count rated as a pair)
+  const double c_wide = rounds((rows / kBM) * ((a.n + 255) / 256)) / 0.93;
+  if (c_wide * 1.05 < c_tall) return 0;
+  return cols;
 }
 
+bool gemm_tall_applies(const GemmArgs& a, int sm_count) { return tall_tile_cols(a, sm_count) != 0; }
+
+namespace {
+template <bool kBf16, int kBN>
+cudaError_t launch_tall(const GemmArgs& a, int grid, cudaStream_t stream) {
+  const cudaError_t e = cudaFuncSetAttribute(gemm_tall_kernel<kBf16, kBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  gemm_tall_kernel<kBf16, kBN><<<grid, kThreads, kSmemBytes, stream>>>(a);
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_gemm_tall(const GemmArgs& a, int max_ctas, cudaStream_t stream) {
-  const int64_t tiles = ((static_cast<int64_t>(a.batch) * a.m + 2 * kBM - 1) / (2 * kBM)) * (a.n / kBN);
+  const int cols = tall_tile_cols(a, max_ctas);
+  if (cols == 0) return cudaErrorInvalidValue;
+  const int64_t tiles = ((static_cast<int64_t>(a.batch) * a.m + 2 * kBM - 1) / (2 * kBM)) * (a.n / cols);
   if (tiles <= 0) return cudaSuccess;
   const int grid = tiles < max_ctas ? static_cast<int>(tiles) : max_ctas;
-  cudaError_t e;
-  if (a.is_bf16) {
-    e = cudaFuncSetAttribute(gemm_tall_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
-    gemm_tall_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(a);
-  } else {
-    e = cudaFuncSetAttribute(gemm_tall_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
-    gemm_tall_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(a);
-  }
-  return cudaGetLastError();
+  if (cols == 256) return a.is_bf16 ? launch_tall<true, 256>(a, grid, stream) : launch_tall<false, 256>(a, grid, stream);
+  return a.is_bf16 ? launch_tall<true, 192>(a, grid, stream) : launch_tall<false, 192>(a, grid, stream);
 }
 
 }  // namespace fo

@@ -84,6 +84,7 @@ struct GemmArgs {
   CUtensorMap tmap_a;              // X as [batch*m, k], box 64 x 128, 128B swizzle
   CUtensorMap tmap_b;              // W as [n, k],       box 64 x 128, 128B swizzle
   CUtensorMap tmap_y;              // Y as [batch*m, n], box 64 x 128, 128B swizzle (TMA stores)
+  CUtensorMap tmap_b64;            // W with a box of 64 x 64 (the 192-column tiles of gemm_tall.cu)
   void* y;                         // [batch, m, n]
   const void* init;                // bias [n] or cache [batch, m, n] or null
   int init_mode;
@@ -102,6 +103,7 @@ struct GemmArgs {
 cudaError_t launch_gemm(const GemmArgs& a, int max_ctas, cudaStream_t stream);
 // dense projections whose shape divides into 256x256 tiles take the tall-tile kernel (gemm_tall.cu)
 bool gemm_tall_applies(const GemmArgs& a, int sm_count);
+int tall_tile_cols(const GemmArgs& a, int sm_count);   // 256, 192 or 0 (not applicable)
 cudaError_t launch_gemm_tall(const GemmArgs& a, int max_ctas, cudaStream_t stream);
 
 // ------------------------------------------------------------------ block selection

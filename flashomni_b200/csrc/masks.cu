@@ -721,6 +721,7 @@ __global__ void __launch_bounds__(1024) gemm_q_tiles_kernel(GemmListArgs a) {
     a.counters[3] = s_carry - n_split;
     a.counters[4] = kDevOk;  // status word of the GEMM kernel that follows
     a.counters[5] = 0;       // its tile cursor
+    a.counters[6] = 0;       // and the count of CTAs that have finished
   }
 }
 
@@ -805,6 +806,7 @@ __global__ void __launch_bounds__(1024) gemm_o_rows_kernel(GemmListArgs a) {
     a.counters[2] = kDevOk;
     a.counters[4] = kDevOk;  // status word of the GEMM kernel that follows
     a.counters[5] = 0;       // its tile cursor
+    a.counters[6] = 0;       // and the count of CTAs that have finished
     // bucket starts, descending count
     int acc = 0;
     for (int k = local_heads; k >= 0; --k) { const int v = s_hist[k]; s_hist[k] = acc; acc += v; }

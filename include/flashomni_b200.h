@@ -177,15 +177,22 @@ FO_API int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* 
 
 /* ---- GEMM-Q / GEMM-O ---------------------------------------------------------------------------
  * Workspace (device, caller-owned, 16-byte aligned) of fo_gemm_workspace_bytes(...) bytes, laid out
- * as int32 words: [0..3] counters (count, aux, list status, 0), [4] kernel status (FO_DEV_*),
- * [8...] the work list built from the mask. */
+ * as int32 words: [0..3] counters (count, aux, list status, two-block records), [4] kernel status (FO_DEV_*,
+ * cleared when a list is built, set when a bounded wait of a GEMM kernel ran out, otherwise left alone),
+ * [5] tile cursor and [6] count of finished CTAs of the running GEMM kernel (both zero again when it ends),
+ * [8...] the work list built from the mask. The caller zeroes the workspace once before its first use; launches
+ * that share a workspace must not overlap. */
 FO_API size_t fo_gemm_workspace_bytes(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim);
 
 /* Host-only query (no device call): the row count of the output tiles, 256 or 128, that a dense launch
  * (is_full) of fo_gemm_q uses for this shape on a device with sm_count SMs; 0 for an empty shape. Both
- * dense kernels deal equal tiles in fixed shares, so the choice goes to the shape that fills whole waves
- * of SMs better. has_full_init: the launch adds a [batch, m, n] tensor (not reachable through fo_gemm_q). */
+ * dense kernels deal equal tiles in fixed shares, so the choice goes to the shape whose fullest SM ends first
+ * (rounds of tiles times the tile's length). has_full_init: the launch adds a [batch, m, n] tensor (not reachable through fo_gemm_q). */
 FO_API int fo_gemm_dense_tile_rows(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t has_full_init,
+                                   int32_t sm_count);
+/* The column count of those tiles: 256, or 192 where the 256-row kernel runs its narrower tiles (more, shorter
+ * tiles for a narrow projection whose 256-column tiles would leave SMs idle). */
+FO_API int fo_gemm_dense_tile_cols(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t has_full_init,
                                    int32_t sm_count);
 
 /* Replaces torch.ops.flashomni_kernels.flashomni_gemm (csrc/gemm.cu:24-59 ->
@@ -217,8 +224,12 @@ FO_API int fo_gemm_o(const void* x, const void* w, void* y, const void* init, in
 /* The list builders that fo_gemm_q / fo_gemm_o run first (exposed so that the lists can be checked
  * bit for bit). They fill the same workspace layout: GEMM-Q: words [8 + 4*i ..] = (b, iy, ix0, ix1), the
  * i-th pair record: per row block (b, iy), ascending, its active 128-column blocks taken two at a
- * time (ix1 = -1 for a leftover single block); counters[0] = record count, counters[1] = active
- * tile count. GEMM-O with R = batch*m/128 row blocks and
+ * time (ix1 = -1 for a leftover single block), all two-block records first, then the single-block ones; the
+ * last k two-block records are cut into two single-block records each, k being the value in [0, min(P, SMs)]
+ * (P two-block, S single-block records before the cut) for which the launch ends earliest when one CTA per SM
+ * draws the records in list order at 20 time units per two-block and 13 per single-block tile (smallest k on a
+ * tie; see oracle/masks.py gemm_q_split_rule); counters[0] = record count, counters[1] = active tile count,
+ * counters[3] = two-block records. GEMM-O with R = batch*m/128 row blocks and
  * L = k/head_dim local heads: words [8 .. 8+R] row_indptr, then [8+R+1 ..] row_heads (R*L words
  * reserved), then row_order (R words): row blocks by descending list length (stable). */
 FO_API int fo_gemm_q_worklist(int32_t batch, int32_t m, int32_t n, int32_t num_heads, int32_t head_begin,
@@ -236,7 +247,8 @@ FO_API int fo_gemm_o_worklist(int32_t batch, int32_t m, int32_t k, int32_t num_h
  * No counterpart in the reference. Same computation as fo_gemm_q (sparse) / fo_gemm_o, but the work list is
  * taken from `workspace` as fo_gemm_q_worklist / fo_gemm_o_worklist left it (same batch, m, n / k, head_dim),
  * built on any stream that is ordered before this call -- e.g. a side stream, beside the dense projections,
- * since the list depends on the mask only. Only the kernel status word and the tile cursor are reset here. */
+ * since the list depends on the mask only. Nothing is reset here: a list may be used by any number of launches,
+ * one after another. */
 FO_API int32_t fo_gemm_q_prepared(const void* x, const void* w, void* y, const void* bias, int32_t dtype,
                                   int32_t batch, int32_t m, int32_t n, int32_t k, int32_t head_dim,
                                   void* workspace, size_t workspace_bytes, void* stream);

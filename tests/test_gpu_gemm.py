@@ -21,7 +21,8 @@ def _status_ok():
 
 @pytest.mark.parametrize("shape", [(1, 128, 128, 64), (1, 256, 384, 256), (2, 512, 512, 1024), (1, 128, 256, 3072),
                                    (1, 384, 512, 192), (3, 640, 256, 320), (2, 128, 768, 64),
-                                   (1, 256, 256, 96), (2, 128, 384, 32), (1, 512, 512, 288)])   # K = 32 mod 64 too
+                                   (1, 256, 256, 96), (2, 128, 384, 32), (1, 512, 512, 288),    # K = 32 mod 64 too
+                                   (2, 512, 768, 256), (1, 256, 1152, 128), (2, 1280, 1536, 192)])  # 192-column tiles
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_dense_gemm_is_full(cuda_device, shape, dtype):
     B, M, N, K = shape

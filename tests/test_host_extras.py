@@ -50,16 +50,19 @@ def test_block_schedule_name_is_checked_before_anything_else():
 
 
 def test_dense_gemm_tile_choice_fills_whole_waves():
-    """Host-only query of the dense dispatch on a 148-SM device: 256-row tiles unless the 128-row tiles of the
-    other kernel fill whole waves clearly better (the heads of the flux block split over two GPUs: 216 tiles of
-    256x256 are 1.46 waves, 432 tiles of 128x256 are 2.92)."""
+    """Host-only query of the dense dispatch on a 148-SM device: the launch goes to the tile shape whose fullest SM
+    ends first: 256x256 tiles, 256x192 tiles where those fill the SMs better (the heads of the flux block split over
+    two GPUs: 216 tiles of 256x256 are two rounds of length 2, 288 tiles of 256x192 two rounds of length 1.5), or
+    the 128-row tiles of the other kernel."""
     from flashomni_b200 import _native
     lib = _native.load()
     q = lambda b, m, n, k, full=0, sms=148: lib.fo_gemm_dense_tile_rows(b, m, n, k, full, sms)
     assert q(2, 4608, 3072, 3072) == 256          # flux block, one GPU: 432 tall tiles, 2.92 waves
-    assert q(2, 4608, 1536, 3072) == 128          # heads over two GPUs
-    assert q(2, 4608, 768, 3072) == 256           # over four: one wave either way
-    assert q(2, 4608, 384, 3072) == 128           # over eight: 384 columns do not divide into 256-column tiles
+    c = lambda b, m, n, k, full=0, sms=148: lib.fo_gemm_dense_tile_cols(b, m, n, k, full, sms)
+    assert c(2, 4608, 3072, 3072) == 256 and c(2, 4608, 6144, 3072) == 256   # ties go to the wider tile
+    assert q(2, 4608, 1536, 3072) == 256 and c(2, 4608, 1536, 3072) == 192   # heads over two GPUs
+    assert q(2, 4608, 768, 3072) == 256 and c(2, 4608, 768, 3072) == 192     # over four: 144 tiles, one round
+    assert q(2, 4608, 384, 3072) == 128           # over eight: one round of 128-row tiles beats one of 256x192
     assert q(1, 77312, 5120, 5120) == 256         # video layer
     assert q(1, 9728, 5120, 5120) == 256          # its token shard on eight GPUs
     assert q(1, 128, 256, 64) == 128              # a single row block
