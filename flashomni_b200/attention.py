@@ -244,8 +244,14 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
 
     begin_forward = plan
 
-    MIN_CHUNK = 16   # shortest part (kv blocks) a kv list is cut into: a unit costs a few microseconds of its own
-    KERNEL = None    # None: chosen from the planned shape; "tile" / "streams" force one of the two kernels (tests)
+    # Cutting kv lists into parts (split-KV with a merge of partial results) is built and tested but OFF by default:
+    # on a B200 it measured slower at every shape tried (a GPU's share of 3, 6 or 12 heads of the 4608-token layer:
+    # 35 -> 43, 70 -> 79 and 113 -> 138 microseconds). The part is power-capped: SMs that end early leave their share
+    # of the budget to the SMs with long lists, so an even spread of the blocks gains little, and every part pays
+    # an epilogue (fp32 partial result, a CTA-wide hand-over, the merge).
+    UNITS_PER_SM = 0      # > 0: kv lists are cut when the launch has more than one and at most this many items per SM
+    MIN_CHUNK = 16        # shortest part (kv blocks) a kv list is cut into
+    FORCE_SPLIT = False   # cut every list into parts of two blocks (tests: every case then runs the merge path)
 
     def _carve_workspace(self) -> None:
         """Lays the work lists out in one int32 buffer: counters[4] | status[4] | unit_counters[4] | items | kv_ptr |
@@ -255,14 +261,23 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         lib = _native.load()
         n, kept = max(self._n_cand, 1), max(self._max_kept, 1)
         scratch_bytes = lib.fo_mask_compact_scratch_bytes(n, self._max_nkv)
-        # Two kernels walk the unit list. With at most as many candidate items as streams (two per SM) the launch
-        # goes to the two-stream kernel, whose kv lists may be cut into parts (at most streams + items <= 1.5 * streams
-        # of them) with partial results in scratch; with more, every SM gets several whole items and the one-tile
-        # kernel is the faster shape.
-        self._num_streams = 2 * torch.cuda.get_device_properties(self.device).multi_processor_count
-        may_split = self._n_cand <= self._num_streams if self.KERNEL is None else self.KERNEL == "streams"
-        self._max_units = n + (self._num_streams if may_split else 0)
-        self._partial_slots = (self._num_streams + self._num_streams // 2) if may_split else 0
+        # One persistent CTA per SM draws units, longest first. With UNITS_PER_SM > 0 and between one and that many
+        # candidate items per SM the lists are cut into parts of about total / (UNITS_PER_SM * SMs) blocks (at least
+        # MIN_CHUNK) whose partial results (fp32 O, row maxima and sums) go to scratch and are merged by the part
+        # that delivers last.
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._num_streams = max(self.UNITS_PER_SM * sms, 1)
+        self._min_chunk = self.MIN_CHUNK
+        self._min_items = sms
+        may_split = self.UNITS_PER_SM > 0 and sms < self._n_cand <= self._num_streams
+        extra_units = self._num_streams
+        slots = extra_units + extra_units // 2
+        if self.FORCE_SPLIT and self._max_kept <= 4096:
+            may_split, self._min_chunk, self._min_items = True, 2, 0
+            self._num_streams = max(self._num_streams, self._n_cand, self._max_kept)
+            extra_units = slots = self._max_kept // 2 + n + 1      # parts of at least two blocks
+        self._max_units = n + (extra_units if may_split else 0)
+        self._partial_slots = slots if may_split else 0
 
         def al(words):  # 16-byte aligned word counts
             return (words + 3) // 4 * 4
@@ -417,7 +432,8 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             _native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]), _native.ptr(ws["order"]),
             _native.ptr(ws["counters"]), _native.ptr(self._qo_indptr_buf), _native.ptr(self._kv_indptr_buf),
             max(self._n_cand, 1), self._max_nkv, self._q_block_tokens, self._sparse_block_size_for_kv,
-            self._num_streams, self.MIN_CHUNK, self._max_units, self._partial_slots, _native.ptr(ws["units"]),
+            self._min_items, self._num_streams, self._min_chunk, self._max_units, self._partial_slots,
+            _native.ptr(ws["units"]),
             _native.ptr(ws["unit_counters"]), _native.ptr(ws["arrive"]), stream)
         _native.check(rc, "BatchFlashOmniFAWithRaggedKVWrapper (work units)")
 

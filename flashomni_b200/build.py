@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(HERE, "lib", "obj")
 LIB = os.path.join(LIBDIR, "libflashomni_b200.so")
-SOURCES = ["api.cu", "masks.cu", "gemm.cu", "attention.cu", "attention_streams.cu", "static_scratch.cu", "exchange.cu", "select.cu", "gemm_tall.cu"]
+SOURCES = ["api.cu", "masks.cu", "gemm.cu", "attention.cu", "static_scratch.cu", "exchange.cu", "select.cu", "gemm_tall.cu"]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -240,7 +240,7 @@ size_t fo_attn_partial_bytes(int64_t partial_slots) {
 
 int fo_attn_units(const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx, const int32_t* order,
                   const int32_t* counters, const int32_t* qo_indptr, const int32_t* kv_indptr, int64_t max_items,
-                  int32_t max_nkv, int32_t sbq, int32_t sbkv, int32_t num_streams, int32_t min_chunk, int64_t max_units,
+                  int32_t max_nkv, int32_t sbq, int32_t sbkv, int32_t min_items, int32_t num_streams, int32_t min_chunk, int64_t max_units,
                   int64_t max_slots, int32_t* units, int32_t* unit_counters, int32_t* arrive, void* stream) {
   if (items == nullptr || kv_ptr == nullptr || kv_idx == nullptr || order == nullptr || counters == nullptr ||
       qo_indptr == nullptr || kv_indptr == nullptr || units == nullptr || unit_counters == nullptr ||
@@ -263,6 +263,7 @@ int fo_attn_units(const int32_t* items, const int32_t* kv_ptr, const int32_t* kv
   a.max_units = max_units;
   a.max_slots = max_slots;
   a.num_streams = num_streams;
+  a.min_items = min_items < 0 ? 0 : min_items;
   a.min_chunk = min_chunk;
   a.max_nkv = max_nkv;
   a.sbq = sbq;
@@ -361,11 +362,7 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   a.status = status;
   int64_t ctas = static_cast<int64_t>(sm_count());  // one persistent CTA per SM
   if (ctas > max_units) ctas = max_units;
-  // Two kernels read the same unit records: with room for partial results (partial_slots > 0: the caller expects
-  // few units, and the unit builder may have cut kv lists) two streams of units run per SM; without, one unit at a
-  // time per SM with two softmax groups on alternate kv blocks, the faster shape when every SM gets several units.
-  const cudaError_t e = partial_slots > 0 ? launch_attention_streams(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream))
-                                          : launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
+  const cudaError_t e = launch_attention(a, static_cast<int>(ctas), static_cast<cudaStream_t>(stream));
   count_launches(1);
   return e == cudaSuccess ? FO_OK : fail_cuda("fo_sparse_attn_fwd", e);
 }

@@ -78,9 +78,11 @@ struct Tail {
   uint64_t stats_ready[2];         // indexed by item parity: both groups have published (m, l) of the item
   uint64_t o_full, o_free;
   uint64_t iq_full[kItemQ], iq_empty[kItemQ];  // item queue: the K producer draws work-list positions for the CTA
+  uint64_t ep_bar;                 // all softmax warps, in the epilogue of a part of a split item
   int item_q[kItemQ];
   uint32_t tmem_base;
   int abort_flag;
+  int merge_go;                    // this CTA's part of a split item delivered last and merges the partial results
   uint64_t pair_bar[2][4];   // [group][quadrant]: the two warps that share 32 rows
   float m_pub[2][128];       // [block parity][row]: running maximum in use after that block
   float xmax[2][2][2][128];  // [group][parity of the group's block count][column half][row]: half-row maxima
@@ -176,9 +178,10 @@ struct GroupSeq {
   int h, n, j;            // head inside the q / o tensors, kv blocks of the unit, current block
   int q_row0, q_valid;    // first row of the q-block in q / o, its existing rows
   int ragged_j, ragged_valid;  // visiting step of the request's partial last kv block (-1: none) and its columns
+  int parts;              // slot << 16 | part << 8 | number of parts (a whole item: one part)
   __device__ __forceinline__ void init(Tail* tail, volatile int* abort_flag) {
     src.init(tail, abort_flag); n = 0; j = 0;
-    h = q_row0 = q_valid = 0; ragged_j = -1; ragged_valid = 0;
+    h = q_row0 = q_valid = 0; ragged_j = -1; ragged_valid = 0; parts = 1;
   }
   template <class F>
   __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
@@ -191,7 +194,7 @@ struct GroupSeq {
       const int4 u0 = up[0], u1 = up[1];
       if (u0.x <= 0) { on_empty(u0.w, u1.x, u0.z - a.head_begin); continue; }
       n = u0.x; j = 0;
-      h = u0.z - a.head_begin; q_row0 = u0.w; q_valid = u1.x;
+      h = u0.z - a.head_begin; q_row0 = u0.w; q_valid = u1.x; parts = u1.w;
       ragged_j = -1;
       if (u1.z != 0) {  // the unit's last entry is the request's partial kv block
         ragged_j = n - 1 - rot_of(q_row0 >> 7, n);
@@ -258,7 +261,9 @@ struct BlockSeq {
   __device__ __forceinline__ bool last() const { return j == n - 1; }
 };
 
-template <bool kBf16, bool kSoftCap>
+// kParts: the launch may hold parts of split items (partial results and their merge in the epilogue); the
+// instantiation without carries none of that code.
+template <bool kBf16, bool kSoftCap, bool kParts>
 __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -288,6 +293,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     }
     mbar_init(&tail->o_full, 1);
     mbar_init(&tail->o_free, kSoftmaxWarps);
+    mbar_init(&tail->ep_bar, kSoftmaxWarps);
     for (int i = 0; i < kItemQ; ++i) { mbar_init(&tail->iq_full[i], 1); mbar_init(&tail->iq_empty[i], kItemReaders); }
     for (int i = 0; i < 8; ++i) mbar_init(&tail->pair_bar[i >> 2][i & 3], 2);
     tail->abort_flag = 0;
@@ -310,8 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 
   // The list may be shorter than counters[0] says: a compaction that ran out of room records it in counters[2]
   // and leaves records unwritten. Nothing of such a list is dereferenced; the launch only reports it.
-  // lists are never cut for this kernel (the unit builder is told so): every unit is a whole item
-  const bool list_bad = a.unit_counters[3] != kDevOk || a.unit_counters[1] != 0;
+  const bool list_bad = a.unit_counters[3] != kDevOk || a.unit_counters[1] > (kParts ? a.partial_slots : 0);
   int n_items = a.unit_counters[0];
   if (list_bad || n_items < 0) n_items = 0;
   if (n_items > a.max_units) n_items = a.max_units;
@@ -522,7 +527,16 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     // an item whose statistics have been published and whose O is still being accumulated
     bool pend = false;
     uint32_t pend_item = 0;
-    int pend_q_row0 = 0, pend_q_valid = 0, pend_h = 0;
+    int pend_q_row0 = 0, pend_q_valid = 0, pend_h = 0, pend_parts = 1;
+    uint32_t ep_phase = 0;
+    // bounded barrier of the softmax warps (only the epilogue of a part of a split item uses it)
+    auto ep_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->ep_bar);
+      const bool r = __all_sync(0xffffffffu, mbar_wait(&tail->ep_bar, ep_phase, abort_flag) ? 1 : 0) != 0;
+      ep_phase ^= 1u;
+      return r;
+    };
 
     auto epilogue = [&]() -> bool {
       const uint32_t ip = pend_item & 1u;
@@ -538,7 +552,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       }
       if (!mbar_wait(&tail->o_full, pend_item & 1u, abort_flag)) return false;
       tc_fence_after_sync();
-      const float inv_l = lsum > 0.f ? __frcp_rn(lsum) : 0.f;
       uint32_t v[32];
       tmem_ld_x32(tmem_o + ocol, v);
       tmem_wait_ld();
@@ -546,14 +559,73 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->o_free);  // O may be overwritten by the next item
       const RowCtx pend_ctx = row_ctx(pend_q_row0, pend_q_valid, pend_h);
+      const int nparts = pend_parts & 0xff;
+      float m_out = m_fin, l_out = lsum;
+      if constexpr (kParts) {
+        if (nparts > 1) {
+          // ---- a part of a split item: the fp32 O (relative to m_fin), m_fin and the row sum go to the part's slot
+          // as [column group of 4][row][4] (a warp's store covers 512 contiguous bytes); the part that delivers last
+          // merges all of them, in ascending order whichever part it is (the result does not depend on it):
+          // O = sum_p O_p 2^(m_p - m) / sum_p l_p 2^(m_p - m), m = max_p m_p.
+          const int slot = static_cast<int>(static_cast<uint32_t>(pend_parts) >> 16), part = (pend_parts >> 8) & 0xff;
+          float* ps = a.partials + static_cast<size_t>(slot) * kPartialFloats;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(ps + (static_cast<size_t>(ocol / 4u + q) * 128 + row) * 4) =
+                make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          if (ocol == 0u) {
+            ps[128 * 128 + row] = m_fin;
+            ps[128 * 128 + 128 + row] = lsum;
+          }
+          __threadfence();
+          if (!ep_sync()) return false;
+          if (warp == 0 && lane == 0) {
+            int* cnt = a.arrive + (slot - part);  // a split item counts at its first slot
+            const int old = atomicAdd(cnt, 1);
+            const int mine = old == nparts - 1 ? 1 : 0;
+            if (mine) *cnt = 0;  // the counter is back at zero for the next launch
+            __threadfence();
+            tail->merge_go = mine;
+          }
+          if (!ep_sync()) return false;
+          if (tail->merge_go == 0) {  // another part will merge
+            pend = false;
+            return true;
+          }
+          const float* base = a.partials + static_cast<size_t>(slot - part) * kPartialFloats;
+          float m_all = -INFINITY;
+          for (int pp = 0; pp < nparts; ++pp)
+            m_all = fmaxf(m_all, __ldcg(base + static_cast<size_t>(pp) * kPartialFloats + 128 * 128 + row));
+          float l_all = 0.f;
+#pragma unroll
+          for (int t = 0; t < 32; ++t) v[t] = 0u;  // v becomes the accumulator (fp32 bit patterns)
+          for (int pp = 0; pp < nparts; ++pp) {
+            const float* pq = base + static_cast<size_t>(pp) * kPartialFloats;
+            const float mp = __ldcg(pq + 128 * 128 + row);
+            const float wgt = (mp == -INFINITY) ? 0.f : ex2_approx(mp - m_all);
+            l_all = fmaf(__ldcg(pq + 128 * 128 + 128 + row), wgt, l_all);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 x = __ldcg(reinterpret_cast<const float4*>(pq + (static_cast<size_t>(ocol / 4u + q) * 128 + row) * 4));
+              v[4 * q] = __float_as_uint(fmaf(x.x, wgt, __uint_as_float(v[4 * q])));
+              v[4 * q + 1] = __float_as_uint(fmaf(x.y, wgt, __uint_as_float(v[4 * q + 1])));
+              v[4 * q + 2] = __float_as_uint(fmaf(x.z, wgt, __uint_as_float(v[4 * q + 2])));
+              v[4 * q + 3] = __float_as_uint(fmaf(x.w, wgt, __uint_as_float(v[4 * q + 3])));
+            }
+          }
+          m_out = m_all;
+          l_out = l_all;
+        }
+      }
+      const float inv_out = l_out > 0.f ? __frcp_rn(l_out) : 0.f;
       uint4 outv[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint32_t w[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          const float x0 = __uint_as_float(v[8 * q + 2 * t]) * inv_l;
-          const float x1 = __uint_as_float(v[8 * q + 2 * t + 1]) * inv_l;
+          const float x0 = __uint_as_float(v[8 * q + 2 * t]) * inv_out;
+          const float x1 = __uint_as_float(v[8 * q + 2 * t + 1]) * inv_out;
           w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
         }
         outv[q] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -585,7 +657,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 #pragma unroll
         for (int q = 0; q < 4; ++q) dst[q] = outv[q];
       }
-      if (pend_ctx.row_ok && pend_ctx.lse != nullptr) *pend_ctx.lse = (lsum > 0.f) ? (log2f(lsum) + m_fin) : -5e4f;
+      if (pend_ctx.row_ok && pend_ctx.lse != nullptr) *pend_ctx.lse = (l_out > 0.f) ? (log2f(l_out) + m_out) : -5e4f;
       pend = false;
       return true;
     };
@@ -732,7 +804,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (lane == 0) mbar_arrive(&tail->stats_ready[ip]);
         pend = true;
         pend_item = items_seen;
-        pend_q_row0 = seq.q_row0; pend_q_valid = seq.q_valid; pend_h = seq.h;
+        pend_q_row0 = seq.q_row0; pend_q_valid = seq.q_valid; pend_h = seq.h; pend_parts = seq.parts;
         ++items_seen;
       }
       ++g;
@@ -770,21 +842,27 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 
 
 namespace {
-template <bool kBf16, bool kSoftCap>
+template <bool kBf16, bool kSoftCap, bool kParts>
 cudaError_t launch_one(const AttnArgs& a, int ctas, cudaStream_t stream) {
-  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kSmemBytes);
+  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap, kParts>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
-  attention_kernel<kBf16, kSoftCap><<<ctas, kThreads, kSmemBytes, stream>>>(a);
+  attention_kernel<kBf16, kSoftCap, kParts><<<ctas, kThreads, kSmemBytes, stream>>>(a);
   return cudaGetLastError();
+}
+template <bool kBf16, bool kSoftCap>
+cudaError_t launch_two(const AttnArgs& a, int ctas, cudaStream_t stream) {
+  // room for partial results means that the unit builder may have cut lists: the instantiation with the merge
+  return a.partial_slots > 0 ? launch_one<kBf16, kSoftCap, true>(a, ctas, stream)
+                             : launch_one<kBf16, kSoftCap, false>(a, ctas, stream);
 }
 }  // namespace
 
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream) {
   if (max_ctas <= 0) return cudaSuccess;
   const bool cap = a.soft_cap_pre > 0.f;
-  if (a.is_bf16) return cap ? launch_one<true, true>(a, max_ctas, stream) : launch_one<true, false>(a, max_ctas, stream);
-  return cap ? launch_one<false, true>(a, max_ctas, stream) : launch_one<false, false>(a, max_ctas, stream);
+  if (a.is_bf16) return cap ? launch_two<true, true>(a, max_ctas, stream) : launch_two<true, false>(a, max_ctas, stream);
+  return cap ? launch_two<false, true>(a, max_ctas, stream) : launch_two<false, false>(a, max_ctas, stream);
 }
 
 }  // namespace fo

@@ -67,7 +67,7 @@ struct UnitArgs {
   const int32_t* qo_indptr;
   const int32_t* kv_indptr;
   int64_t max_items, max_units, max_slots;
-  int num_streams, min_chunk, max_nkv, sbq, sbkv;
+  int min_items, num_streams, min_chunk, max_nkv, sbq, sbkv;
   int32_t* units;            // [max_units, 8]
   int32_t* unit_counters;    // [4]: n_units, partial slots in use, chunk_max, status
   int32_t* arrive;           // [max_slots]
@@ -186,7 +186,6 @@ struct AttnArgs {
 constexpr int kPartialFloats = 128 * 128 + 2 * 128;
 // one unit at a time per SM (launches with many units) / two streams of units per SM with split kv lists (few units)
 cudaError_t launch_attention(const AttnArgs& a, int max_ctas, cudaStream_t stream);
-cudaError_t launch_attention_streams(const AttnArgs& a, int max_ctas, cudaStream_t stream);
 
 // ------------------------------------------------------------------ host helpers
 // Encodes a tiled tensor map (bf16/f16 elements, 128-byte swizzle or none). dims/strides innermost first;

@@ -478,6 +478,8 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
 // partial results (max_slots > 0) and the launch has at most half as many items as streams (whole items would leave streams idle): chunk_max = max(min_chunk,
 // ceil(total_kept / num_streams), ceil(max_nkv / 255)); otherwise every item is one unit.
 // unit_counters: n_units, partial slots in use, chunk_max, status. arrive[slot] = 0 for every slot.
+constexpr int kUnitSortMax = 2048;
+
 __global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
   __shared__ int s_warp_u[32], s_warp_p[32];
   __shared__ int s_carry_u, s_carry_p;
@@ -488,7 +490,7 @@ __global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
   if (n_items > a.max_items) n_items = static_cast<int>(a.max_items);
   const long long total_kept = a.counters[1];
   int chunk_max = 0x7fffffff;
-  if (n_items > 0 && a.max_slots > 0 && 2 * n_items <= a.num_streams) {
+  if (n_items > a.min_items && a.max_slots > 0 && n_items <= a.num_streams) {
     long long c = (total_kept + a.num_streams - 1) / a.num_streams;
     if (c < a.min_chunk) c = a.min_chunk;
     const long long c255 = (static_cast<long long>(a.max_nkv) + 254) / 255;
@@ -556,6 +558,41 @@ __global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
     __syncthreads();
     if (tid == 0) { s_carry_u += s_warp_u[31]; s_carry_p += s_warp_p[31]; }
     __syncthreads();
+  }
+  // When lists were cut, the units are put in descending order of their length (stable: equal lengths keep the
+  // order above), so that the CTAs, which draw units in list order, take the short ones last. Every thread holds
+  // its records in registers before any is written back.
+  const int n_units = s_carry_u;
+  if (chunk_max != 0x7fffffff && n_units <= kUnitSortMax && n_units <= a.max_units) {
+    __shared__ int s_len[kUnitSortMax];
+    int4 r0[kUnitSortMax / 1024], r1[kUnitSortMax / 1024];
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kUnitSortMax / 1024; ++k) {
+      const int u = tid + k * 1024;
+      if (u < n_units) {
+        const int4* src = reinterpret_cast<const int4*>(a.units + 8 * static_cast<int64_t>(u));
+        r0[k] = src[0];
+        r1[k] = src[1];
+        s_len[u] = r0[k].x;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kUnitSortMax / 1024; ++k) {
+      const int u = tid + k * 1024;
+      if (u < n_units) {
+        const int len = r0[k].x;
+        int pos = 0;
+        for (int v = 0; v < n_units; ++v) {
+          const int lv = s_len[v];
+          pos += (lv > len || (lv == len && v < u)) ? 1 : 0;
+        }
+        int4* dst = reinterpret_cast<int4*>(a.units + 8 * static_cast<int64_t>(pos));
+        dst[0] = r0[k];
+        dst[1] = r1[k];
+      }
+    }
   }
   if (tid == 0) {
     a.unit_counters[0] = s_carry_u;

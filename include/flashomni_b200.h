@@ -111,13 +111,16 @@ FO_API int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes
  *   [5] kv_row0   first kv row of the request
  *   [6] ragged    columns of the request's partial last kv block if the unit's list ends with it, else 0
  *   [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
- * An item is one unit unless its kv list is cut: lists are cut only when the launch has at most half as many
- * items as streams (num_streams = 2 x the number of SMs: the kernel runs two streams of items per SM), into
- * n_parts = ceil(n_kept / chunk_max) parts of (almost) equal length, chunk_max = max(min_chunk,
- * ceil(total_kept / num_streams), ceil(max_nkv / 255)). Cuts fall between list ENTRIES, so no part is ever
- * empty and every part of a split item delivers a partial result before the merge (the reference's split path
- * cuts kv ranges and merges partials that an early-returning q-block never wrote). Parts of an item are adjacent
- * and use consecutive partial slots.
+ * An item is one unit unless its kv list is cut: lists are cut only when max_slots > 0 and the launch has more than
+ * min_items and at most num_streams items (num_streams: the unit count the caller aims at, a few per SM; min_items:
+ * the number of SMs, or 0: with at most one item per SM, cutting measured slower on a power-capped part, since the
+ * SMs that end early leave their share of the power to the long items), into n_parts = ceil(n_kept / chunk_max) parts of (almost) equal length, chunk_max =
+ * max(min_chunk, ceil(total_kept / num_streams), ceil(max_nkv / 255)). Cuts fall between list ENTRIES, so no
+ * part is ever empty and every part of a split item delivers a partial result before the merge (the reference's
+ * split path cuts kv ranges and merges partials that an early-returning q-block never wrote). The parts of an item
+ * use consecutive partial slots. When lists were cut (and the launch has at most 2048 units) the units are put in
+ * descending order of their length (stable), so that the CTAs, which draw units in list order, take the short
+ * ones last.
  *   units          int32 [max_units,8]  16-byte aligned
  *   unit_counters  int32 [4]            n_units, partial slots in use, chunk_max, status (FO_DEV_*)
  *   arrive         int32 [max_slots]    per slot: parts delivered (a split item counts at its first slot); zeroed
@@ -125,8 +128,8 @@ FO_API int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes
  * max_units >= max_items + num_streams and max_slots >= num_streams + num_streams / 2 always suffice. */
 FO_API int fo_attn_units(const int32_t* items, const int32_t* kv_ptr, const int32_t* kv_idx, const int32_t* order,
                          const int32_t* counters, const int32_t* qo_indptr, const int32_t* kv_indptr,
-                         int64_t max_items, int32_t max_nkv, int32_t sbq, int32_t sbkv, int32_t num_streams,
-                         int32_t min_chunk, int64_t max_units, int64_t max_slots, int32_t* units,
+                         int64_t max_items, int32_t max_nkv, int32_t sbq, int32_t sbkv, int32_t min_items,
+                         int32_t num_streams, int32_t min_chunk, int64_t max_units, int64_t max_slots, int32_t* units,
                          int32_t* unit_counters, int32_t* arrive, void* stream);
 /* Bytes of partial-result scratch for `partial_slots` slots (fp32 O of a 128-row q-block plus row maxima and sums). */
 FO_API size_t fo_attn_partial_bytes(int64_t partial_slots);
@@ -144,13 +147,10 @@ FO_API size_t fo_attn_partial_bytes(int64_t partial_slots);
  * is not FO_DEV_OK or more partial slots are in use than `partial_slots` (the output is then untouched and
  * status[0] = FO_DEV_BAD_INDEX). The parts of a split item write fp32 partial results into `partials`
  * (fo_attn_partial_bytes(partial_slots) bytes, 16-byte aligned; null when partial_slots = 0) and the
- * part that delivers last merges them and writes the rows. partial_slots also selects the kernel: with room for
- * partial results (the caller expects few units: at most one candidate item per stream) two streams of units run
- * per SM; with partial_slots = 0 (fo_attn_units then never cuts a list) one unit at a time runs per SM with two
- * softmax groups on alternate kv blocks, the faster shape when every SM gets several units. status: FOUR int32
- * device words
+ * part that delivers last merges them and writes the rows. One persistent CTA per SM draws the units in list
+ * order, one unit at a time, with two softmax groups on alternate kv blocks. status: FOUR int32 device words
  * that the caller zeroes once: [0] is set to FO_DEV_WAIT_TIMEOUT if a bounded wait ran out;
- * [1] (unit cursor: units are handed to the streams dynamically) and [2] (count of finished CTAs) are used by
+ * [1] (unit cursor: units are handed to the CTAs dynamically) and [2] (count of finished CTAs) are used by
  * the kernel and are zero again when it ends, so launches that share the words (or `arrive`, `partials`) must
  * not overlap; [3] is reserved.
  * This build implements D = 128 with 128-row q and kv blocks. */

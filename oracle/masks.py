@@ -165,7 +165,7 @@ def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr,
 
 
 def attn_units(lists: dict, qo_indptr, kv_indptr, num_streams: int, min_chunk: int = 16, sbq: int = 128,
-               sbkv: int = 128, max_slots: int = 1 << 30):
+               sbkv: int = 128, max_slots: int = 1 << 30, min_items: int = 0):
     """Canonical work units of the attention kernel, from the outputs of `compact` (`lists`): the items in
     processing order, one self-contained record of eight int32 per unit:
       [0] n kv blocks of the unit (0: an active q-block that keeps nothing)   [1] offset of its first entry in kv_idx
@@ -174,8 +174,11 @@ def attn_units(lists: dict, qo_indptr, kv_indptr, num_streams: int, min_chunk: i
       [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
     A kv list longer than chunk_max is cut into ceil(n_kept / chunk_max) parts of (almost) equal length, part p
     covering entries [n_kept * p // n_parts, n_kept * (p + 1) // n_parts) -- only when there is room for partial
-    results (max_slots > 0) and the launch has at most half as many items as streams: chunk_max = max(min_chunk, ceil(total_kept / num_streams), ceil(max_nkv / 255)); otherwise
-    every item is one unit. (The reference's planner cuts kv RANGES instead, include/flashomni/attention/
+    results (max_slots > 0) and the launch has more than `min_items` and at most `num_streams` items (the unit count
+    the caller aims at: a few per SM): chunk_max = max(min_chunk, ceil(total_kept / num_streams), ceil(max_nkv / 255)); otherwise
+    every item is one unit. When lists were cut (and there are at most 2048 units) the units are then put in
+    descending order of their length (stable), so that the CTAs, which draw units in list order, take the short
+    ones last. (The reference's planner cuts kv RANGES instead, include/flashomni/attention/
     scheduler.cuh:35-64, which with block masks leaves parts without any kept block; cutting the kept LIST cannot.)
     Returns (units int32 [n_units, 8], partial slots in use, chunk_max)."""
     items, order, kvp, kv_idx = lists["items"], lists["order"], lists["kv_indptr"], lists["kv_idx"]
@@ -185,7 +188,7 @@ def attn_units(lists: dict, qo_indptr, kv_indptr, num_streams: int, min_chunk: i
     total = int(items[:, 3].clip(min=0).sum()) if n_items else 0
     max_nkv = max([int(-(-(kv[b + 1] - kv[b]) // sbkv)) for b in range(len(kv) - 1)], default=0)
     chunk_max = 0x7fffffff
-    if 0 < n_items and max_slots > 0 and 2 * n_items <= num_streams:
+    if max(min_items, 0) < n_items and max_slots > 0 and n_items <= num_streams:
         chunk_max = max(min_chunk, -(-total // num_streams), -(-max_nkv // 255))
     units, slots = [], 0
     for it in order.tolist():
@@ -205,6 +208,8 @@ def attn_units(lists: dict, qo_indptr, kv_indptr, num_streams: int, min_chunk: i
             units.append((j1 - j0, int(kvp[it]) + j0, h, q0 + qb * sbq, q_valid, k0, ragged if p == n_parts - 1 else 0, word))
         if n_parts > 1:
             slots += n_parts
+    if chunk_max != 0x7fffffff and len(units) <= 2048:
+        units.sort(key=lambda r: -r[0])      # stable: equal lengths keep the order above
     return np.asarray(units, dtype=np.int32).reshape(-1, 8), slots, chunk_max
 
 

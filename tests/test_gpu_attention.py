@@ -14,11 +14,12 @@ from helpers import assert_close_bf16, dev, masks_to_device
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["tile", "streams"])
+@pytest.fixture(autouse=True, params=["default", "split"])
 def attention_kernel_choice(request, monkeypatch):
-    """Every test of this file runs on both attention kernels: the one-tile kernel (launches with many units) and
-    the two-stream kernel (few units, kv lists cut into parts). The wrapper's own choice is tested separately."""
-    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "KERNEL", request.param)
+    """Every test of this file runs twice: with the wrapper's own rule for cutting kv lists into parts, and with
+    every list of more than two blocks cut (small cases only), so that each case also goes through the partial
+    results and their merge. The wrapper's own rule is tested separately."""
+    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "FORCE_SPLIT", request.param == "split")
     return request.param
 
 
@@ -359,7 +360,7 @@ def test_undersized_kept_list_is_reported_not_walked(cuda_device):
     _native.check(rc, "fo_mask_compact")
     rc = lib.fo_attn_units(_native.ptr(ws["items"]), _native.ptr(ws["kv_ptr"]), _native.ptr(ws["kv_idx"]),
                            _native.ptr(ws["order"]), _native.ptr(ws["counters"]), _native.ptr(w._qo_indptr_buf),
-                           _native.ptr(w._kv_indptr_buf), w._n_cand, w._max_nkv, 128, 128, w._num_streams, w.MIN_CHUNK,
+                           _native.ptr(w._kv_indptr_buf), w._n_cand, w._max_nkv, 128, 128, w._min_items, w._num_streams, w.MIN_CHUNK,
                            w._max_units, w._partial_slots, _native.ptr(ws["units"]), _native.ptr(ws["unit_counters"]),
                            _native.ptr(ws["arrive"]), stream)
     _native.check(rc, "fo_attn_units")
@@ -390,14 +391,13 @@ def test_undersized_kept_list_is_reported_not_walked(cuda_device):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_split_kv_lists_merge_to_the_oracle(cuda_device, dtype, attention_kernel_choice):
+def test_split_kv_lists_merge_to_the_oracle(cuda_device, dtype, attention_kernel_choice, monkeypatch):
     """Few items with long kv lists: the lists are cut into parts that run on different streams, and the part that
     delivers last merges the partial results (maxima, sums, fp32 O). Against the fp32 oracle, with the log-sum-exp,
     prior contents for skipped q-blocks, an empty item and a ragged last block; twice in a row on the same wrapper
     (the per-item arrival counters must be back at zero)."""
-    if attention_kernel_choice != "streams":
-        pytest.skip("kv lists are only cut for the two-stream kernel")
-    H, lens = 3, [40 * 128, 17 * 128 + 40]
+    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "UNITS_PER_SM", 2)
+    H, lens = 4, [40 * 128, 17 * 128 + 40]       # about 185 items: more than one per SM, fewer than two
     rng = np.random.default_rng(61)
     qa = [(rng.random((-(-n // 128), H)) < 0.8).astype(np.uint8) for n in lens]
     kk = [(rng.random((-(-n // 128), H, -(-n // 128))) < 0.8).astype(np.uint8) * a[:, :, None] for n, a in zip(lens, qa)]
@@ -426,29 +426,37 @@ def test_split_kv_lists_merge_to_the_oracle(cuda_device, dtype, attention_kernel
         assert torch.equal(o.cpu()[~act], prior[~act])
 
 
-def test_split_kv_three_heads_of_the_4608_token_layer(cuda_device, attention_kernel_choice):
-    """Three heads of the 4608-token layer, two requests (a rank's share when 24 heads are split over 8 GPUs): about
-    120 items for 296 streams, so lists above 16 blocks are cut."""
-    if attention_kernel_choice != "streams":
-        pytest.skip("kv lists are only cut for the two-stream kernel")
-    inp = wl.attention_inputs(2, 3, 4608, 128, 0.5, seed=91)
-    w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, 3)
+@pytest.mark.parametrize("heads", [6, 3])
+def test_split_kv_a_share_of_the_heads_of_the_4608_token_layer(cuda_device, heads, monkeypatch):
+    """A rank's share of the 4608-token layer, two requests, with list cutting switched on (up to four units per SM).
+    Six heads (24 heads over 4 GPUs): about 240 items for 148 SMs, so the lists are cut; three heads (over 8 GPUs):
+    about 120 items, at most one per SM, nothing is cut."""
+    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "UNITS_PER_SM", 4)
+    inp = wl.attention_inputs(2, heads, 4608, 128, 0.5, seed=91)
+    w = _wrapper(cuda_device, inp.qo_indptr, inp.kv_indptr, heads)
     o = _run(cuda_device, w, inp.q, inp.k, inp.v, inp.masks)
     lists = w.work_lists()
-    assert lists["partial_slots_used"] > 0
+    sms = torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    assert (lists["partial_slots_used"] > 0) == (sms < lists["n_items"] <= 4 * sms)
+    assert (lists["partial_slots_used"] > 0) == (heads == 6) or sms != 148
     m = inp.masks
     ref = oa.sparse_attention(inp.q, inp.k, inp.v, [0, 4608, 9216], [0, 4608, 9216], m.sparse_info, m.sparse_kv_info,
                               m.info_indptr, m.kv_info_indptr)
-    assert_close_bf16(o, ref, "three heads of the 4608-token layer, split lists")
+    assert_close_bf16(o, ref, f"{heads} heads of the 4608-token layer")
 
 
-def test_kernel_choice_follows_the_planned_shape(cuda_device, monkeypatch):
-    """Few candidate items (at most one per stream): the two-stream kernel with room for partial results; many: the
-    one-tile kernel, no list is ever cut."""
-    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "KERNEL", None)
-    streams = 2 * torch.cuda.get_device_properties(cuda_device).multi_processor_count
+def test_split_rule_follows_the_planned_shape(cuda_device, monkeypatch):
+    """By default no list is ever cut and no scratch is set aside. With cutting switched on: room for partial
+    results when the launch has between one and UNITS_PER_SM candidate items per SM."""
+    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "FORCE_SPLIT", False)
     few = _wrapper(cuda_device, [0, 4608, 9216], [0, 4608, 9216], 3)      # 216 candidates
+    assert few._partial_slots == 0 and few._max_units == few._n_cand and few._partials is None
+    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "UNITS_PER_SM", 2)
+    streams = 2 * torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    few = _wrapper(cuda_device, [0, 4608, 9216], [0, 4608, 9216], 3)
     many = _wrapper(cuda_device, [0, 4608, 9216], [0, 4608, 9216], 24)    # 1728 candidates
-    assert few._n_cand <= streams < many._n_cand
+    one_per_sm = _wrapper(cuda_device, [0, 4608], [0, 4608], 3)           # 108 candidates
+    assert streams // 2 < few._n_cand <= streams < many._n_cand
     assert few._partial_slots > 0 and few._max_units == few._n_cand + streams
     assert many._partial_slots == 0 and many._max_units == many._n_cand and many._partials is None
+    assert one_per_sm._partial_slots == 0

@@ -187,11 +187,12 @@ def test_strided_gather_matches_torch(cuda_device):
 
 
 @pytest.mark.parametrize("case", ["few_items_cut", "many_items_whole", "ragged"])
-def test_attention_work_units_bit_exact(cuda_device, case):
+def test_attention_work_units_bit_exact(cuda_device, case, monkeypatch):
     """The unit list the attention kernel walks (fo_attn_units) against the oracle's statement: long kv lists are
     cut into parts when the launch has few items per stream, never otherwise."""
+    monkeypatch.setattr(fo.BatchFlashOmniFAWithRaggedKVWrapper, "UNITS_PER_SM", 2)   # list cutting on
     if case == "few_items_cut":
-        H, lens = 3, [36 * 128]
+        H, lens = 6, [36 * 128]                      # about 195 items: between one and two per SM
         m = wl.flux_masks(1, H, 36, 36, 0.9, seed=21)
     elif case == "many_items_whole":
         H, lens = 24, [36 * 128, 36 * 128]
@@ -210,7 +211,8 @@ def test_attention_work_units_bit_exact(cuda_device, case):
     got = w.work_lists()
     ref = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, qo, H, 128, 128)
     _assert_lists_equal(got, ref)
-    units, slots, chunk = om.attn_units(ref, qo, qo, w._num_streams, w.MIN_CHUNK, max_slots=w._partial_slots)
+    units, slots, chunk = om.attn_units(ref, qo, qo, w._num_streams, w.MIN_CHUNK, max_slots=w._partial_slots,
+                                        min_items=w._min_items)
     assert got["unit_status"] == 0 and got["chunk_max"] == chunk and got["partial_slots_used"] == slots
     assert got["n_units"] == len(units) and np.array_equal(got["units"], units)
     if case == "many_items_whole":

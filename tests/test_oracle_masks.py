@@ -97,8 +97,8 @@ def test_attention_units_cut_long_lists_only_when_items_are_few():
     qo = kv = np.array([0, 20 * 128 - 50])           # ragged last q and kv block
     c = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, qo, kv, 6, 128, 128)
     n = len(c["items"])
-    # more than half as many items as streams: one unit per item, in processing order, no partial slots
-    u, slots, chunk = om.attn_units(c, qo, kv, num_streams=2 * n - 2)
+    # more items than the unit count aimed at: one unit per item, in processing order, no partial slots
+    u, slots, chunk = om.attn_units(c, qo, kv, num_streams=n - 1)
     assert slots == 0 and chunk == 0x7fffffff and len(u) == n
     for r, it in zip(u.tolist(), c["order"].tolist()):
         b, h, qb, nk = c["items"][it].tolist()
@@ -109,16 +109,20 @@ def test_attention_units_cut_long_lists_only_when_items_are_few():
     # few items per stream: lists longer than chunk_max are cut into parts that tile the list without gaps
     u, slots, chunk = om.attn_units(c, qo, kv, num_streams=2 * n, min_chunk=6)
     assert chunk == max(6, -(-int(c["items"][:, 3].sum()) // (2 * n)))
-    pos, used = 0, 0
+    assert om.attn_units(c, qo, kv, num_streams=n, min_chunk=6)[1] > 0     # exactly as many items: still cut
+    lens_u = u[:, 0].tolist()
+    assert lens_u == sorted(lens_u, reverse=True)            # cut lists: units in descending order of length
+    by_off = {int(r[1]): r for r in u.tolist() if r[0] > 0}  # non-empty units by their first kv_idx entry
+    used, seen = 0, 0
     for it in c["order"].tolist():
         nk = int(c["items"][it][3])
+        if nk == 0:
+            continue
         n_parts = -(-nk // chunk) if nk > chunk else 1
-        recs = u[pos: pos + n_parts].tolist()
-        pos += n_parts
-        assert sum(r[0] for r in recs) == nk and all(r[0] > 0 for r in recs) or nk == 0
         off = int(c["kv_indptr"][it])
-        for p, r in enumerate(recs):
-            assert r[1] == off
+        for p in range(n_parts):
+            r = by_off[off]
+            assert r[0] > 0
             off += r[0]
             w = r[7] & 0xffffffff
             if n_parts > 1:
@@ -126,8 +130,12 @@ def test_attention_units_cut_long_lists_only_when_items_are_few():
             else:
                 assert w == 0xffff0001
             assert r[6] == 0 or p == n_parts - 1          # only the last part can end with the partial block
+            seen += 1
+        assert off == int(c["kv_indptr"][it]) + nk           # the parts tile the list without gaps
         used += n_parts if n_parts > 1 else 0
-    assert pos == len(u) and used == slots and slots > 0
+    n_empty = int((c["items"][:, 3] == 0).sum())
+    assert seen + n_empty == len(u) and int((u[:, 0] == 0).sum()) == n_empty
+    assert used == slots and slots > 0
 
 
 def test_gemm_lists():
