@@ -41,7 +41,7 @@ HID, H, D, S, B, DENSITY, SEED = 3072, 24, 128, 4608, 2, 0.5, 2024
 FL_ATTN_TILE = 4 * 128 * 128 * 128
 FL_GEMM_TILE = 2 * 128 * 128 * HID
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised under profiles/
-NCU_TRAFFIC = {"attention_kernel": 165.3e6, "gemm_kernel": 111.0e6, "gemm_tall_kernel": 140.0e6}
+NCU_TRAFFIC = {"attention_kernel": 169.3e6, "gemm_kernel": 121.1e6, "gemm_tall_kernel": 233.5e6}
 
 
 # ---------------------------------------------------------------------------------------------- helpers
@@ -580,7 +580,7 @@ def run_flux(ctx, args, peaks):
                kentry("gemm_kernel<bf16> (GEMM-Q, active tiles)", "gemm_q", fl["gemm_q"], 1),
                kentry("gemm_kernel<bf16> (GEMM-O, active heads)", "gemm_o", fl["gemm_o"], 1),
                kentry(dense_name + "<bf16> (dense K/V projection)", "gemm_kv", fl["gemm_kv"], kv_launches)]
-    top = max(kernels, key=lambda e: e["ms_per_step"])
+    top = max(kernels[:3], key=lambda e: e["ms_per_step"])
     base = top["kernel"].split("<")[0]
     if world > 1:
         for e in kernels:
@@ -591,7 +591,8 @@ def run_flux(ctx, args, peaks):
                 "traffic_note": "dram read+write bytes per launch from the ncu captures summarised under profiles/",
                 "peak_source": peaks["src"] + " cuBLAS bf16, the burst figure: every kernel is timed alone and the "
                                "whole step lasts well under a millisecond",
-                "selection": "the kernel with the largest share of the step",
+                "selection": "the kernel of the sparse path (attention, GEMM-Q, GEMM-O) with the largest share of the "
+                             "step; the dense K/V projection, a plain GEMM, is listed under kernels",
                 "kernels": kernels,
                 "mask_compaction": {"kernel": "compact_count / compact_scan / compact_fill", "bound": "hbm",
                                     "launches_per_step": 3, "ms_per_step": r4(kt["compact"]["mean"]),
