@@ -165,8 +165,8 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         group = num_qo_heads // num_kv_heads
         if group not in (1, 2, 4, 8, 16):
             raise NotImplementedError("flashomni_b200: num_qo_heads / num_kv_heads must be 1, 2, 4, 8 or 16")
-        if head_dim_qk != 128 or head_dim_vo != 128:
-            raise NotImplementedError("flashomni_b200: only head_dim 128 is implemented")
+        if head_dim_qk != head_dim_vo or head_dim_qk not in (64, 128):
+            raise NotImplementedError("flashomni_b200: head_dim 64 and 128 are implemented (qk and vo equal)")
         if sparse_block_size_for_q != 128 or sparse_block_size_for_kv != 128:
             raise NotImplementedError("flashomni_b200: only 128-row sparse blocks are implemented")
 
@@ -235,14 +235,30 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         self._sm_scale = sm_scale
         self._rope_scale = rope_scale
         self._rope_theta = rope_theta
-        self._sparse_info_indptr_base = _compute_sparse_info_indptr(
-            self._qo_indptr_buf, num_qo_heads, sparse_block_size_for_q, device=self.device)
-        self._sparse_kv_info_indptr_base = _compute_sparse_kv_info_indptr(
-            self._qo_indptr_buf, self._kv_indptr_buf, num_qo_heads, sparse_block_size_for_q,
-            sparse_block_size_for_kv, device=self.device)
+        # the element indptrs of the unpacked masks (what callers feed to segment_packbits) are derived on first use:
+        # a dozen small torch kernels that plan() itself does not need
+        self._indptr_bases = None
         self._planned = True
 
     begin_forward = plan
+
+    def _bases(self):
+        if self._indptr_bases is None:
+            self._indptr_bases = (
+                _compute_sparse_info_indptr(self._qo_indptr_buf, self._num_qo_heads, self._sparse_block_size_for_q,
+                                            device=self.device),
+                _compute_sparse_kv_info_indptr(self._qo_indptr_buf, self._kv_indptr_buf, self._num_qo_heads,
+                                               self._sparse_block_size_for_q, self._sparse_block_size_for_kv,
+                                               device=self.device))
+        return self._indptr_bases
+
+    @property
+    def _sparse_info_indptr_base(self) -> torch.Tensor:
+        return self._bases()[0]
+
+    @property
+    def _sparse_kv_info_indptr_base(self) -> torch.Tensor:
+        return self._bases()[1]
 
     # Cutting kv lists into parts (split-KV with a merge of partial results) is built and tested but OFF by default:
     # on a B200 it measured slower at every shape tried (a GPU's share of 3, 6 or 12 heads of the 4608-token layer:

@@ -296,7 +296,8 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   if (partial_slots < 0 || (partial_slots > 0 && (partials == nullptr || !aligned16(partials) || arrive == nullptr)))
     return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: partial-result scratch missing or misaligned");
   if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: bad dtype");
-  if (head_dim != 128) return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: only head_dim 128 is implemented");
+  if (head_dim != 128 && head_dim != 64)
+    return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: head_dim must be 128 or 64");
   if (sbq != 128 || sbkv != 128)
     return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: only 128-row q and kv sparse blocks are implemented");
   if (num_qo_heads <= 0 || num_kv_heads <= 0 || num_qo_heads % num_kv_heads != 0)
@@ -319,9 +320,9 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   {
     const uint32_t box[3] = {64, 1, 128};
     const uint32_t qbox[3] = {64, group, 128 / group};
-    const uint64_t qd[3] = {128, static_cast<uint64_t>(num_qo_heads), static_cast<uint64_t>(total_q)};
+    const uint64_t qd[3] = {static_cast<uint64_t>(head_dim), static_cast<uint64_t>(num_qo_heads), static_cast<uint64_t>(total_q)};
     const uint64_t qs[3] = {0, static_cast<uint64_t>(q_stride_h) * 2, static_cast<uint64_t>(q_stride_n) * 2};
-    const uint64_t kd[3] = {128, static_cast<uint64_t>(num_kv_heads), static_cast<uint64_t>(total_kv)};
+    const uint64_t kd[3] = {static_cast<uint64_t>(head_dim), static_cast<uint64_t>(num_kv_heads), static_cast<uint64_t>(total_kv)};
     const uint64_t ks[3] = {0, static_cast<uint64_t>(k_stride_h) * 2, static_cast<uint64_t>(k_stride_n) * 2};
     const uint64_t vs[3] = {0, static_cast<uint64_t>(v_stride_h) * 2, static_cast<uint64_t>(v_stride_n) * 2};
     int r = encode_tmap_16bit(&a.tmap_q, q, 3, qd, qs, qbox);
@@ -350,6 +351,7 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   a.partials = partials;
   a.partial_slots = static_cast<int>(partial_slots > 0x7fffffffLL ? 0x7fffffffLL : partial_slots);
   a.head_begin = head_begin;
+  a.head_dim = head_dim;
   a.group_size = static_cast<int>(group);
   a.is_bf16 = dtype == FO_DTYPE_BF16;
   if (logits_soft_cap > 0.f) {

@@ -42,8 +42,8 @@
 namespace fo {
 namespace {
 
-constexpr int kBQ = 128, kBKV = 128, kD = 128;
-constexpr int kTileBytes = 128 * kD * 2;    // 32 KB: a 128-row tile of Q, K or V
+constexpr int kBQ = 128, kBKV = 128;
+constexpr int kTileBytes = 128 * 128 * 2;   // 32 KB: the slot of a 128-row tile of Q, K or V (head_dim 64 fills half of it)
 constexpr int kHalfBytes = kTileBytes / 2;  // one 64-column half (one swizzle-atom column)
 constexpr int kRingK = 2, kRingV = 2;  // separate FIFOs of 32 KB tiles for K and V
 constexpr int kRing = kRingK + kRingV;
@@ -263,8 +263,12 @@ struct BlockSeq {
 
 // kParts: the launch may hold parts of split items (partial results and their merge in the epilogue); the
 // instantiation without carries none of that code.
-template <bool kBf16, bool kSoftCap, bool kParts>
+// kD: head dimension, 128 or 64. With 64 a tile is one 64-column half: the second TMA box, the upper four of the
+// eight Q K^T MMAs and the upper 64 columns of O are left out; everything else is the same code.
+template <bool kBf16, bool kSoftCap, bool kParts, int kD>
 __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
+  static_assert(kD == 128 || kD == 64, "head dimension");
+  constexpr int kLoadBytes = 128 * kD * 2;   // bytes of one tile load
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -347,18 +351,18 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           ++q_uses[qb_i];
           const int q_row = seq.q_row0;
           uint8_t* dst = smem_q + qb_i * kTileBytes;
-          mbar_expect_tx(&tail->q_full[qb_i], kTileBytes);
+          mbar_expect_tx(&tail->q_full[qb_i], kLoadBytes);
           tma_load_3d(dst, &a.tmap_q, &tail->q_full[qb_i], 0, hq, q_row);
-          tma_load_3d(dst + kHalfBytes, &a.tmap_q, &tail->q_full[qb_i], 64, hq, q_row);
+          if constexpr (kD == 128) tma_load_3d(dst + kHalfBytes, &a.tmap_q, &tail->q_full[qb_i], 64, hq, q_row);
         }
         const int slot = static_cast<int>(nk % kRingK);
         if (!mbar_wait(&tail->k_empty[slot], ((nk / kRingK) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         ++nk;
         uint8_t* dst = smem_ring + slot * kTileBytes;
         const int row = kv_row0 + seq.kvb * kBKV;
-        mbar_expect_tx(&tail->k_full[slot], kTileBytes);
+        mbar_expect_tx(&tail->k_full[slot], kLoadBytes);
         tma_load_3d(dst, &a.tmap_k, &tail->k_full[slot], 0, hk, row);
-        tma_load_3d(dst + kHalfBytes, &a.tmap_k, &tail->k_full[slot], 64, hk, row);
+        if constexpr (kD == 128) tma_load_3d(dst + kHalfBytes, &a.tmap_k, &tail->k_full[slot], 64, hk, row);
       }
     }
   } else if (warp == kWarpProducerV) {
@@ -378,9 +382,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         ++nv;
         uint8_t* dst = smem_ring + (kRingK + slot) * kTileBytes;
         const int row = kv_row0 + seq.kvb * kBKV;
-        mbar_expect_tx(&tail->v_full[slot], kTileBytes);
+        mbar_expect_tx(&tail->v_full[slot], kLoadBytes);
         tma_load_3d(dst, &a.tmap_v, &tail->v_full[slot], 0, hk, row);
-        tma_load_3d(dst + kHalfBytes, &a.tmap_v, &tail->v_full[slot], 64, hk, row);
+        if constexpr (kD == 128) tma_load_3d(dst + kHalfBytes, &a.tmap_v, &tail->v_full[slot], 64, hk, row);
       }
     }
   } else if (warp == kWarpQK) {
@@ -423,7 +427,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           la[kk] = q_lo + off;
           lb[kk] = k_lo + off;
         }
-        umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
+        if constexpr (kD == 128) umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
+        else umma_ss_x4(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
         umma_commit(&tail->s_full[sb]);
         umma_commit(&tail->k_empty[slot]);
         if (seq.last()) umma_commit(&tail->q_empty[qb_i]);
@@ -485,6 +490,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     const uint32_t tmem_p = tmem_base + lane_base + kColP + X * 64u + ch * 32u;
     const uint32_t tmem_o = tmem_base + lane_base + kColO;
     const uint32_t ocol = 64u * X + 32u * ch;  // this thread's quarter of O in the epilogue
+    const bool has_cols = ocol < static_cast<uint32_t>(kD);  // head_dim 64: the second group's threads own no column of O
     const int row = quad * 32 + lane;
     uint64_t* pair_bar = &tail->pair_bar[X][quad];
     uint32_t pair_phase = 0;
@@ -509,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     };
     auto on_empty = [&](int q_row0, int q_valid, int hq) {  // active q-block that keeps nothing: zeros, lse = -5e4
       const RowCtx c = row_ctx(q_row0, q_valid, hq);
-      if (c.row_ok) {
+      if (c.row_ok && has_cols) {
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(c.orow)[i] = z;
@@ -553,8 +559,13 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       if (!mbar_wait(&tail->o_full, pend_item & 1u, abort_flag)) return false;
       tc_fence_after_sync();
       uint32_t v[32];
-      tmem_ld_x32(tmem_o + ocol, v);
-      tmem_wait_ld();
+      if (has_cols) {
+        tmem_ld_x32(tmem_o + ocol, v);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] = 0u;
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->o_free);  // O may be overwritten by the next item
@@ -569,10 +580,12 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           // O = sum_p O_p 2^(m_p - m) / sum_p l_p 2^(m_p - m), m = max_p m_p.
           const int slot = static_cast<int>(static_cast<uint32_t>(pend_parts) >> 16), part = (pend_parts >> 8) & 0xff;
           float* ps = a.partials + static_cast<size_t>(slot) * kPartialFloats;
+          if (has_cols) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            *reinterpret_cast<uint4*>(ps + (static_cast<size_t>(ocol / 4u + q) * 128 + row) * 4) =
-                make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(ps + (static_cast<size_t>(ocol / 4u + q) * 128 + row) * 4) =
+                  make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          }
           if (ocol == 0u) {
             ps[128 * 128 + row] = m_fin;
             ps[128 * 128 + 128 + row] = lsum;
@@ -604,6 +617,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
             const float mp = __ldcg(pq + 128 * 128 + row);
             const float wgt = (mp == -INFINITY) ? 0.f : ex2_approx(mp - m_all);
             l_all = fmaf(__ldcg(pq + 128 * 128 + 128 + row), wgt, l_all);
+            if (!has_cols) continue;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const float4 x = __ldcg(reinterpret_cast<const float4*>(pq + (static_cast<size_t>(ocol / 4u + q) * 128 + row) * 4));
@@ -631,7 +645,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         outv[q] = make_uint4(w[0], w[1], w[2], w[3]);
       }
       const bool whole = pend_q_valid * grp == kBQ;  // no row of the q-block is past the request
-      if (whole) {
+      if (!has_cols) {
+        // head_dim 64: this thread's quarter of O does not exist
+      } else if (whole) {
         // Through a 1 KB staging area per warp (16 rows x 64 bytes, plain row-major) and a TMA store of one
         // 16-row x 32-column box: a store instruction of a warp would otherwise write 32 scattered 16-byte pieces.
         uint8_t* stg = smem_ostage + warp * kOutStageBytes;
@@ -725,13 +741,13 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           tc_fence_after_sync();
           const float alpha = need ? ex2_approx(m_prev - m_new) : 1.0f;
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < kD / 64; ++c) {  // this thread's half of the row of O: kD / 2 columns
             uint32_t v[32];
-            tmem_ld_x32(tmem_o + 64u * ch + 32u * c, v);
+            tmem_ld_x32(tmem_o + static_cast<uint32_t>(kD / 2) * ch + 32u * c, v);
             tmem_wait_ld();
 #pragma unroll
             for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
-            tmem_st_x32(tmem_o + 64u * ch + 32u * c, v);
+            tmem_st_x32(tmem_o + static_cast<uint32_t>(kD / 2) * ch + 32u * c, v);
           }
         }
         // this thread's partial sum follows the maximum in use
@@ -842,19 +858,22 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 
 
 namespace {
-template <bool kBf16, bool kSoftCap, bool kParts>
+template <bool kBf16, bool kSoftCap, bool kParts, int kD>
 cudaError_t launch_one(const AttnArgs& a, int ctas, cudaStream_t stream) {
-  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap, kParts>,
+  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap, kParts, kD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
-  attention_kernel<kBf16, kSoftCap, kParts><<<ctas, kThreads, kSmemBytes, stream>>>(a);
+  attention_kernel<kBf16, kSoftCap, kParts, kD><<<ctas, kThreads, kSmemBytes, stream>>>(a);
   return cudaGetLastError();
 }
 template <bool kBf16, bool kSoftCap>
 cudaError_t launch_two(const AttnArgs& a, int ctas, cudaStream_t stream) {
   // room for partial results means that the unit builder may have cut lists: the instantiation with the merge
-  return a.partial_slots > 0 ? launch_one<kBf16, kSoftCap, true>(a, ctas, stream)
-                             : launch_one<kBf16, kSoftCap, false>(a, ctas, stream);
+  if (a.head_dim == 64)
+    return a.partial_slots > 0 ? launch_one<kBf16, kSoftCap, true, 64>(a, ctas, stream)
+                               : launch_one<kBf16, kSoftCap, false, 64>(a, ctas, stream);
+  return a.partial_slots > 0 ? launch_one<kBf16, kSoftCap, true, 128>(a, ctas, stream)
+                             : launch_one<kBf16, kSoftCap, false, 128>(a, ctas, stream);
 }
 }  // namespace
 

@@ -175,6 +175,7 @@ struct AttnArgs {
   int32_t* arrive;                 // per partial slot (a split item counts at its first slot): parts delivered; zero between launches
   float* partials;                 // partial results of split items: partial_slots x kPartialFloats floats
   int partial_slots;
+  int head_dim;                    // 128 or 64
   int head_begin;                  // tensor head = item head - head_begin
   int group_size;                  // H / Hkv
   int is_bf16;

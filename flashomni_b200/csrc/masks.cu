@@ -230,13 +230,22 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) { s_carry_items = 0; s_carry_kept = 0; }
   __syncthreads();
-  for (int64_t base = 0; base < a.n_cand; base += blockDim.x) {
-    const int64_t c = base + tid;
-    const int v = (c < a.n_cand) ? a.cnt[c] : -1;
-    const int flag = v >= 0;
-    const int kept = flag ? v : 0;
-    int xi = flag;
-    long long xk = kept;
+  // kScanPer consecutive candidates per thread and pass: a thread scans its own run, the CTA scans the run totals
+  constexpr int kScanPer = 8;
+  for (int64_t base = 0; base < a.n_cand; base += static_cast<int64_t>(blockDim.x) * kScanPer) {
+    const int64_t c0 = base + static_cast<int64_t>(tid) * kScanPer;
+    int vals[kScanPer];
+#pragma unroll
+    for (int k = 0; k < kScanPer; ++k) vals[k] = (c0 + k < a.n_cand) ? a.cnt[c0 + k] : -1;
+    int run_i = 0;
+    long long run_k = 0;
+#pragma unroll
+    for (int k = 0; k < kScanPer; ++k) {
+      run_i += vals[k] >= 0;
+      run_k += vals[k] >= 0 ? vals[k] : 0;
+    }
+    int xi = run_i;
+    long long xk = run_k;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int yi = __shfl_up_sync(0xffffffffu, xi, o);
@@ -258,11 +267,17 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
       s_warp_kept[lane] = wk;
     }
     __syncthreads();
-    const int pre_i = s_carry_items + (warp ? s_warp_items[warp - 1] : 0) + xi - flag;
-    const long long pre_k = s_carry_kept + (warp ? s_warp_kept[warp - 1] : 0) + xk - kept;
-    if (c < a.n_cand) {
-      a.item_pos[c] = flag ? pre_i : -1;
-      a.kv_off[c] = pre_k;
+    int pre_i = s_carry_items + (warp ? s_warp_items[warp - 1] : 0) + xi - run_i;
+    long long pre_k = s_carry_kept + (warp ? s_warp_kept[warp - 1] : 0) + xk - run_k;
+#pragma unroll
+    for (int k = 0; k < kScanPer; ++k) {
+      if (c0 + k < a.n_cand) {
+        const bool flag = vals[k] >= 0;
+        a.item_pos[c0 + k] = flag ? pre_i : -1;
+        a.kv_off[c0 + k] = pre_k;
+        pre_i += flag;
+        pre_k += flag ? vals[k] : 0;
+      }
     }
     __syncthreads();
     if (tid == 0) {
@@ -295,7 +310,7 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
   int* s_total = s_whist + sort_warps * nb;  // [nb] bucket totals, then bucket starts
   for (int i = tid; i < (sort_warps + 1) * nb; i += blockDim.x) s_whist[i] = 0;
   build_cand_prefix(a, s_prefix);
-  auto key_of = [&](int64_t c) -> int {
+  auto key_of = [&](int64_t c, int len) -> int {   // len = cnt[c], already fetched by the caller
     int lo = 0, hi = a.batch;
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
@@ -303,17 +318,22 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
     }
     const int grp = lo * grp_per_req + static_cast<int>((c - s_prefix[lo]) % a.head_count) / heads_per_group;
     if (!by_length) return grp;
-    int len = a.cnt[c];
     len = len < 0 ? 0 : (len > a.max_nkv ? a.max_nkv : len);
     return grp * per_group + (a.max_nkv - len);
   };
   const int64_t slice = ((a.n_cand + sort_warps - 1) / sort_warps + 31) / 32 * 32;
   const int64_t my0 = static_cast<int64_t>(warp) * slice;
   const int64_t my1 = (my0 + slice < a.n_cand) ? my0 + slice : a.n_cand;
+  constexpr int kAhead = 4;  // candidate counts fetched ahead: the loads of four steps are in flight together
   if (warp < sort_warps) {
     int* h = s_whist + warp * nb;
-    for (int64_t c = my0 + lane; c < my1; c += 32) {
-      if (a.cnt[c] >= 0) atomicAdd(&h[key_of(c)], 1);
+    for (int64_t c0 = my0 + lane; c0 < my1; c0 += 32 * kAhead) {
+      int v[kAhead];
+#pragma unroll
+      for (int k = 0; k < kAhead; ++k) v[k] = (c0 + 32 * k < my1) ? a.cnt[c0 + 32 * k] : -1;
+#pragma unroll
+      for (int k = 0; k < kAhead; ++k)
+        if (v[k] >= 0) atomicAdd(&h[key_of(c0 + 32 * k, v[k])], 1);
     }
   }
   __syncthreads();
@@ -349,10 +369,21 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
   __syncthreads();
   if (warp < sort_warps) {
     int* h = s_whist + warp * nb;
-    for (int64_t base = my0; base < my1; base += 32) {
+    for (int64_t base0 = my0; base0 < my1; base0 += 32 * kAhead) {
+      int cv[kAhead], ip[kAhead];
+#pragma unroll
+      for (int k = 0; k < kAhead; ++k) {
+        const int64_t c = base0 + 32 * k + lane;
+        cv[k] = (c < my1) ? a.cnt[c] : -1;
+        ip[k] = (c < my1) ? a.item_pos[c] : -1;
+      }
+#pragma unroll
+      for (int k = 0; k < kAhead; ++k) {
+      const int64_t base = base0 + 32 * k;
+      if (base >= my1) break;
       const int64_t c = base + lane;
-      const bool flag = (c < my1) && a.cnt[c] >= 0;
-      const int v = flag ? key_of(c) : -1 - lane;
+      const bool flag = (c < my1) && cv[k] >= 0;
+      const int v = flag ? key_of(c, cv[k]) : -1 - lane;
       const unsigned grp = __match_any_sync(0xffffffffu, v);
       const int rank_in_grp = __popc(grp & ((1u << lane) - 1u));
       const int leader = __ffs(grp) - 1;
@@ -364,9 +395,10 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
       start = __shfl_sync(0xffffffffu, start, leader);
       if (flag) {
         const int pos = start + rank_in_grp;
-        if (pos < a.max_items) a.order[pos] = a.item_pos[c];
+        if (pos < a.max_items) a.order[pos] = ip[k];
       }
       __syncwarp();
+      }
     }
   }
 }
@@ -602,7 +634,47 @@ __global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
   }
 }
 
+// The same records when no list can be cut (no room for partial results): every item is exactly one unit at its
+// position in the processing order, so the items are independent of one another: one thread per item, any number
+// of CTAs.
+__global__ void __launch_bounds__(256) attn_units_whole_kernel(UnitArgs a) {
+  const bool list_ok = a.counters[2] == kDevOk;
+  int n_items = a.counters[0];
+  if (!list_ok || n_items < 0) n_items = 0;
+  if (n_items > a.max_items) n_items = static_cast<int>(a.max_items);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    a.unit_counters[0] = n_items;
+    a.unit_counters[1] = 0;
+    a.unit_counters[2] = 0x7fffffff;
+    a.unit_counters[3] = (!list_ok || n_items > a.max_units) ? kDevBadIndex : kDevOk;
+  }
+  for (int64_t pos = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; pos < n_items && pos < a.max_units;
+       pos += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int it = a.order[pos];
+    const int4 rec = *reinterpret_cast<const int4*>(a.items + 4 * it);  // (b, mask head, qb, n_kept)
+    const int n = rec.w > 0 ? rec.w : 0;
+    const int q0 = a.qo_indptr[rec.x], q_len = a.qo_indptr[rec.x + 1] - q0;
+    const int k0 = a.kv_indptr[rec.x], kv_len = a.kv_indptr[rec.x + 1] - k0;
+    const int kvp = a.kv_ptr[it];
+    int q_valid = q_len - rec.z * a.sbq;
+    q_valid = q_valid > a.sbq ? a.sbq : (q_valid < 0 ? 0 : q_valid);
+    int ragged = 0;
+    const int tail_cols = kv_len % a.sbkv;
+    if (tail_cols != 0 && n > 0 && a.kv_idx[kvp + n - 1] == kv_len / a.sbkv) ragged = tail_cols;
+    int4* dst = reinterpret_cast<int4*>(a.units + 8 * pos);
+    dst[0] = make_int4(n, kvp, rec.y, q0 + rec.z * a.sbq);
+    dst[1] = make_int4(q_valid, k0, ragged, (0xffff << 16) | 1);
+  }
+}
+
 cudaError_t launch_attn_units(const UnitArgs& a, cudaStream_t stream) {
+  if (a.max_slots <= 0) {
+    int64_t blocks = (a.max_items + 255) / 256;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks < 1) blocks = 1;
+    attn_units_whole_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(a);
+    return cudaGetLastError();
+  }
   attn_units_kernel<<<1, 1024, 0, stream>>>(a);
   return cudaGetLastError();
 }

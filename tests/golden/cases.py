@@ -10,7 +10,7 @@ from flashomni_b200 import workloads as wl
 
 
 def attention_case(name):
-    group = 1
+    group, D = 1, 128
     if name == "attn_uniform":
         H, lens_q, lens_kv, density, seed = 2, [512], [512], 0.6, 101
     elif name == "attn_ragged":
@@ -19,6 +19,10 @@ def attention_case(name):
         H, lens_q, lens_kv, density, seed, group = 4, [320, 205], [256, 333], 0.7, 103, 2
     elif name == "attn_gqa4":    # 8 q heads on 2 kv heads: 32 tokens x 4 q heads
         H, lens_q, lens_kv, density, seed, group = 8, [100, 256], [384, 130], 0.6, 104, 4
+    elif name == "attn_hd64":    # head dimension 64, ragged
+        H, lens_q, lens_kv, density, seed, D = 3, [300, 205], [256, 333], 0.7, 105, 64
+    elif name == "attn_hd64_gqa":
+        H, lens_q, lens_kv, density, seed, group, D = 4, [130, 256], [384, 130], 0.6, 106, 2, 64
     else:
         raise KeyError(name)
     Hkv = H // group
@@ -38,15 +42,15 @@ def attention_case(name):
                 if a[qb, h] and b[qb, h].sum() == 0:
                     b[qb, h, 0] = 1
     m = wl.pack_masks(qa, kk)
-    q = wl.randn_bf16((int(qo[-1]), H, 128), seed + 1)
-    k = wl.randn_bf16((int(kv[-1]), Hkv, 128), seed + 2)
-    v = wl.randn_bf16((int(kv[-1]), Hkv, 128), seed + 3)
-    prior = wl.randn_bf16((int(qo[-1]), H, 128), seed + 4)
+    q = wl.randn_bf16((int(qo[-1]), H, D), seed + 1)
+    k = wl.randn_bf16((int(kv[-1]), Hkv, D), seed + 2)
+    v = wl.randn_bf16((int(kv[-1]), Hkv, D), seed + 3)
+    prior = wl.randn_bf16((int(qo[-1]), H, D), seed + 4)
     return {"q": q, "k": k, "v": v, "qo": qo, "kv": kv, "masks": m, "prior": prior, "H": H, "Hkv": Hkv, "group": group,
-            "q_block_tokens": qtok}
+            "q_block_tokens": qtok, "D": D}
 
 
-ATTENTION_CASES = ("attn_uniform", "attn_ragged", "attn_gqa", "attn_gqa4")
+ATTENTION_CASES = ("attn_uniform", "attn_ragged", "attn_gqa", "attn_gqa4", "attn_hd64", "attn_hd64_gqa")
 
 
 def gemm_case(name):

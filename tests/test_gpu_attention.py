@@ -340,6 +340,73 @@ def test_grouped_query_attention(cuda_device, H, Hkv):
     assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-4)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("soft_cap", [0.0, 30.0])
+def test_head_dim_64(cuda_device, dtype, soft_cap):
+    """Head dimension 64 (second instantiation of the kernel: half tiles, four Q K^T MMAs, 64 columns of O): ragged
+    requests, an active q-block that keeps nothing, lse, rows of switched-off blocks kept, with and without the cap."""
+    H, D = 3, 64
+    lens_q, lens_kv = [300, 205, 128], [256, 333, 70]
+    qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(lens_kv)]).astype(np.int32)
+    rng = np.random.default_rng(64)
+    qa = [(rng.random((-(-a // 128), H)) < 0.7).astype(np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // 128), H, -(-b // 128))) < 0.6).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    qa[0][1, 2] = 1; kk[0][1, 2, :] = 0
+    m = wl.pack_masks(qa, kk)
+    q = wl.randn_bf16((int(qo[-1]), H, D), 65, dtype=dtype)
+    k = wl.randn_bf16((int(kv[-1]), H, D), 66, dtype=dtype)
+    v = wl.randn_bf16((int(kv[-1]), H, D), 67, dtype=dtype)
+    prior = wl.randn_bf16((int(qo[-1]), H, D), 68, dtype=dtype)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
+    w.plan(dev(qo, cuda_device), dev(kv, cuda_device), H, H, D, q_data_type=dtype,
+           logits_soft_cap=soft_cap if soft_cap > 0 else None)
+    si, skv, ip, kp = masks_to_device(m, cuda_device)
+    o, lse = w.run(dev(q, cuda_device), dev(k, cuda_device), dev(v, cuda_device), si, skv, ip, kp,
+                   out=dev(prior, cuda_device).clone(), return_lse=True)
+    w.check_status()
+    ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                                       out_prior=prior, return_lse=True, logits_soft_cap=soft_cap)
+    assert_close_bf16(o.cpu(), ref, f"head_dim 64 {dtype} cap {soft_cap}")
+    act = torch.zeros(int(qo[-1]), H, dtype=torch.bool)
+    for b in range(len(lens_q)):
+        for qb in range(qa[b].shape[0]):
+            r0 = int(qo[b]) + qb * 128
+            r1 = min(r0 + 128, int(qo[b + 1]))
+            for h in range(H):
+                if qa[b][qb, h]:
+                    act[r0:r1, h] = True
+                else:
+                    assert torch.equal(o[r0:r1, h].cpu(), prior[r0:r1, h])
+    assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-3)
+
+
+def test_head_dim_64_flux_size(cuda_device):
+    """24 heads of dimension 64 over 4608 tokens at density 0.5 against the oracle on sampled (head, q-block) rows."""
+    H, S, D = 24, 4608, 64
+    inp = wl.attention_inputs(1, H, S, D, 0.5, seed=97)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
+    ind = inp.qo_indptr.to(cuda_device)
+    w.plan(ind, ind, H, H, D, q_data_type=torch.bfloat16)
+    si, skv, ip, kp = masks_to_device(inp.masks, cuda_device)
+    q, k, v = (dev(t, cuda_device) for t in (inp.q, inp.k, inp.v))
+    o = w.run(q, k, v, si, skv, ip, kp)
+    w.check_status()
+    m = inp.masks
+    rng = np.random.default_rng(5)
+    done = 0
+    while done < 8:
+        h, qb = int(rng.integers(H)), int(rng.integers(S // 128))
+        if not m.q_active[0][qb, h]:
+            continue
+        kept = np.nonzero(m.kv_kept[0][qb, h])[0]
+        cols = torch.from_numpy(np.concatenate([np.arange(b * 128, b * 128 + 128) for b in kept]))
+        s_ = (inp.q[qb * 128:(qb + 1) * 128, h].float() @ inp.k[cols, h].float().T) / math.sqrt(D)
+        ref = torch.softmax(s_, -1) @ inp.v[cols, h].float()
+        assert_close_bf16(o[qb * 128:(qb + 1) * 128, h].cpu(), ref, f"head_dim 64 head {h} q-block {qb}")
+        done += 1
+
+
 def test_undersized_kept_list_is_reported_not_walked(cuda_device):
     """A C-ABI caller that compacts with a kv_idx capacity below the kept count: the compaction records it, and
     the attention launch that follows touches neither the lists nor the output and reports FO_DEV_BAD_INDEX."""
