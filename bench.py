@@ -1152,6 +1152,10 @@ def run_ours(args):
     peaks = load_peaks()
     if args.workload == "video":
         run_video(ctx, args, peaks, standalone=True)
+    elif args.workload == "masks":   # the mask path alone (packing, compaction, block selection at the video mask)
+        if ctx.rank == 0:
+            print(json.dumps({"metric": "mask path at the video layer's mask", "unit": "GB/s", "n_gpus": 1,
+                              "steps": args.steps, "mask_path": run_mask_path(ctx, args, peaks)}), flush=True)
     else:
         out, keep = run_flux(ctx, args, peaks)
         if ctx.world == 1 and not args.quick:
@@ -1178,7 +1182,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="flux_block", choices=["flux_block", "video"])
+    ap.add_argument("--workload", default="flux_block", choices=["flux_block", "video", "masks"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-video", action="store_true", help="skip the video-layer leg of the default run")
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled-row parity checks")

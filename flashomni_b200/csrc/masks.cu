@@ -303,7 +303,67 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
   const int per_group = by_length ? a.max_nkv + 1 : 1;
   const int grp_per_req = (a.head_count + heads_per_group - 1) / heads_per_group;
   const int nb = a.batch * grp_per_req * per_group;
-  if (sort_warps <= 0) {  // too many (request, head) groups for the shared-memory histograms: canonical order
+  if (!by_length) {
+    // Single heads with their q-blocks ascending: the candidates read in (request, head, q-block) order instead of
+    // (request, q-block, head); the running count of active ones is the position. One more scan, no sort.
+    build_cand_prefix(a, s_prefix);
+    if (tid == 0) s_carry_items = 0;
+    __syncthreads();
+    for (int64_t base = 0; base < a.n_cand; base += static_cast<int64_t>(blockDim.x) * kScanPer) {
+      const int64_t j0 = base + static_cast<int64_t>(tid) * kScanPer;
+      int ip[kScanPer];
+#pragma unroll
+      for (int k = 0; k < kScanPer; ++k) {
+        const int64_t j = j0 + k;
+        ip[k] = -1;
+        if (j < a.n_cand) {
+          int lo = 0, hi = a.batch;
+          while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_prefix[mid] <= j) lo = mid; else hi = mid;
+          }
+          const int64_t local = j - s_prefix[lo];
+          const int64_t nq = (s_prefix[lo + 1] - s_prefix[lo]) / a.head_count;
+          const int64_t h = local / nq, qb = local % nq;
+          ip[k] = a.item_pos[s_prefix[lo] + qb * a.head_count + h];
+        }
+      }
+      int run = 0;
+#pragma unroll
+      for (int k = 0; k < kScanPer; ++k) run += ip[k] >= 0;
+      int x = run;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      if (lane == 31) s_warp_items[warp] = x;
+      __syncthreads();
+      if (warp == 0) {
+        int w = s_warp_items[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, w, o);
+          if (lane >= o) w += y;
+        }
+        s_warp_items[lane] = w;
+      }
+      __syncthreads();
+      int pos = s_carry_items + (warp ? s_warp_items[warp - 1] : 0) + x - run;
+#pragma unroll
+      for (int k = 0; k < kScanPer; ++k) {
+        if (ip[k] >= 0) {
+          if (pos < a.max_items) a.order[pos] = ip[k];
+          ++pos;
+        }
+      }
+      __syncthreads();
+      if (tid == 0) s_carry_items += s_warp_items[31];
+      __syncthreads();
+    }
+    return;
+  }
+  if (sort_warps <= 0) {  // too many (request, group, length) buckets for the shared-memory histograms: canonical order
     for (int i = tid; i < n_items && i < a.max_items; i += blockDim.x) a.order[i] = i;
     return;
   }

@@ -85,7 +85,7 @@ FO_API int fo_segment_packbits(const uint8_t* x, const int32_t* indptr, const in
  *                                being as many consecutive heads as keep K and V in L2 together (48 MiB /
  *                                (max_nkv * 64 KiB), evened out); inside a group by descending n_kept (ties:
  *                                list order) while batch * groups * (max_nkv + 1) <= 8192, else single-head
- *                                groups, q-blocks ascending (the identity when batch * head_count > 20480)
+ *                                groups, q-blocks ascending
  *   counters int32 [4]           n_items, total_kept, status (FO_DEV_*), max_nkv
  * n_cand = sum over requests of ceil(qo_len/sbq)*head_count and max_nkv = max ceil(kv_len/sbkv) are
  * host-known (plan time). is_full != 0 ignores the masks (they may be null). scratch must hold

@@ -117,9 +117,7 @@ def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr,
                                (max_nkv * 64 KiB))), evened out over ceil(head_count / hpg) groups. Inside a
                                group: by descending list length, ties in canonical order, while
                                batch * groups_per_request * (max_nkv + 1) <= 8192 (the items drawn last are then
-                               short ones); otherwise single-head groups with their q-blocks ascending; the
-                               identity when batch * head_count > 20480 (more groups than the kernel's
-                               histograms hold)
+                               short ones); otherwise single-head groups with their q-blocks ascending
     With `is_full` every q-block is active and every kv-block kept (prefill.cuh:1284,1383,1434).
     """
     if head_count is None:
@@ -149,7 +147,7 @@ def compact(sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, qo_indptr,
     max_nkv = max([int(-(-(kv[b + 1] - kv[b]) // sbkv)) for b in range(B)], default=0)
     hpg, by_length = order_groups(B, head_count, max_nkv)
     grp_per_req = -(-head_count // hpg)
-    if len(items) and B * grp_per_req <= 20480:
+    if len(items):
         key = items_a[:, 0].astype(np.int64) * grp_per_req + (items_a[:, 1].astype(np.int64) - head_begin) // hpg
         if by_length:
             key = key * (max_nkv + 1) + (max_nkv - items_a[:, 3].astype(np.int64))

@@ -286,6 +286,12 @@ def test_video_layer_size_sampled_rows(cuda_device):
     w.check_status()
     lists = w.work_lists()
     assert lists["n_items"] == H * nblk and lists["total_kept"] == wl.executed_attention_tiles(m)
+    # the lists of this size, entry by entry, against the oracle's statement (items, offsets, kept indices, order)
+    from oracle import masks as om
+    ref_lists = om.compact(m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr, np.array([0, S]),
+                           np.array([0, S]), H, 128, 128)
+    for key in ("items", "kv_indptr", "kv_idx", "order"):
+        assert np.array_equal(lists[key], ref_lists[key]), key
     rng = np.random.default_rng(5)
     rows = [(0, 0), (1, 3), (2, 4), (3, nblk - 1), (0, 33), (1, 34)] + [(int(rng.integers(H)), int(rng.integers(nblk)))
                                                                           for _ in range(10)]
