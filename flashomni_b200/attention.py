@@ -151,8 +151,6 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         # csrc/batch_sparseFA_config.inc:42-43):
         if custom_mask is not None or packed_custom_mask is not None:
             raise NotImplementedError("flashomni_b200: custom attention masks are not implemented")
-        if causal:
-            raise NotImplementedError("flashomni_b200: causal masking is not implemented (DiT path is non-causal)")
         if PosEncodingMode[pos_encoding_mode] != PosEncodingMode.NONE:
             raise NotImplementedError("flashomni_b200: in-kernel positional encoding is not implemented")
         if logits_soft_cap < 0:
@@ -224,6 +222,7 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         self._mask_head_begin = mask_head_begin
         self._total_q = total_num_rows
         self._total_kv = int(kv_indptr_host[-1])
+        self._causal = causal
         self._carve_workspace()
 
         self._sparse_block_size_for_q = sparse_block_size_for_q
@@ -292,6 +291,8 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             may_split, self._min_chunk, self._min_items = True, 2, 0
             self._num_streams = max(self._num_streams, self._n_cand, self._max_kept)
             extra_units = slots = self._max_kept // 2 + n + 1      # parts of at least two blocks
+        if self._causal:   # the causal instantiation handles whole items only
+            may_split = False
         self._max_units = n + (extra_units if may_split else 0)
         self._partial_slots = slots if may_split else 0
 
@@ -411,7 +412,10 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
                     _native.ptr(ws["arrive"]), _native.ptr(self._partials), self._partial_slots,
                     self._mask_head_begin, float(sm_scale))
             cap = float(self._logits_soft_cap or 0.0)
-            if cap > 0:  # logits = cap * tanh(q.k * sm_scale / cap), as the reference's variant does
+            if self._causal:  # whole items only: no partial-result scratch on this path
+                rc = lib.fo_sparse_attn_fwd_causal(*head[:25], self._mask_head_begin, float(sm_scale), cap,
+                                                   _native.ptr(ws["status"]), stream)
+            elif cap > 0:  # logits = cap * tanh(q.k * sm_scale / cap), as the reference's variant does
                 rc = lib.fo_sparse_attn_fwd_softcap(*head, cap, _native.ptr(ws["status"]), stream)
             else:
                 rc = lib.fo_sparse_attn_fwd(*head, _native.ptr(ws["status"]), stream)

@@ -173,8 +173,15 @@ struct ItemRead {  // the reading roles: one thread, or all lanes of a softmax w
 
 // The same walk for the softmax groups, which do not need the kv-block indices: only which step of an
 // item (if any) is the ragged last block of its request. No global load sits between two blocks.
+template <bool kWithKv>
 struct GroupSeq {
   ItemRead<true> src;
+  const int32_t* kv;
+  int rot, kvb, kvb_next, causal_base;
+  __device__ __forceinline__ int at(int jj) const {
+    const int t = jj + rot;
+    return t >= n ? t - n : t;
+  }
   int h, n, j;            // head inside the q / o tensors, kv blocks of the unit, current block
   int q_row0, q_valid;    // first row of the q-block in q / o, its existing rows
   int ragged_j, ragged_valid;  // visiting step of the request's partial last kv block (-1: none) and its columns
@@ -182,24 +189,39 @@ struct GroupSeq {
   __device__ __forceinline__ void init(Tail* tail, volatile int* abort_flag) {
     src.init(tail, abort_flag); n = 0; j = 0;
     h = q_row0 = q_valid = 0; ragged_j = -1; ragged_valid = 0; parts = 1;
+    kv = nullptr; rot = 0; kvb = kvb_next = 0; causal_base = 0;
   }
   template <class F>
   __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
-    if (j + 1 < n) { ++j; return true; }
+    if (j + 1 < n) {
+      ++j;
+      if (kWithKv) {
+        kvb = kvb_next;
+        if (j + 1 < n) kvb_next = kv[at(j + 1)];
+      }
+      return true;
+    }
     while (true) {
       const int pos = src.next();
       if (pos < 0) break;
       // the unit's record: everything this role needs, in one 32-byte load
       const int4* up = reinterpret_cast<const int4*>(a.units + 8 * static_cast<int64_t>(pos));
       const int4 u0 = up[0], u1 = up[1];
-      if (u0.x <= 0) { on_empty(u0.w, u1.x, u0.z - a.head_begin); continue; }
+      if (u0.x <= 0) { on_empty(u0.w, u1.x & 0xffff, u0.z - a.head_begin); continue; }
       n = u0.x; j = 0;
-      h = u0.z - a.head_begin; q_row0 = u0.w; q_valid = u1.x; parts = u1.w;
+      h = u0.z - a.head_begin; q_row0 = u0.w; q_valid = u1.x & 0xffff; parts = u1.w;
+      causal_base = u1.z;
       ragged_j = -1;
-      if (u1.z != 0) {  // the unit's last entry is the request's partial kv block
+      if ((u1.x >> 16) != 0) {  // the unit's last entry is the request's partial kv block
         ragged_j = n - 1 - rot_of(q_row0 >> 7, n);
         if (ragged_j < 0) ragged_j += n;
-        ragged_valid = u1.z;
+        ragged_valid = u1.x >> 16;
+      }
+      if (kWithKv) {  // the kv-block indices too (a causal mask needs the block's position)
+        kv = a.kv_idx + u0.y;
+        rot = rot_of(q_row0 >> 7, n);
+        kvb = kv[at(0)];
+        if (n > 1) kvb_next = kv[at(1)];
       }
       return true;
     }
@@ -240,7 +262,7 @@ struct BlockSeq {
       if (pos < 0) break;
       const int4* up = reinterpret_cast<const int4*>(a.units + 8 * static_cast<int64_t>(pos));
       const int4 u0 = up[0], u1 = up[1];
-      if (u0.x <= 0) { on_empty(u0.w, u1.x, u0.z - a.head_begin); continue; }
+      if (u0.x <= 0) { on_empty(u0.w, u1.x & 0xffff, u0.z - a.head_begin); continue; }
       n = u0.x; j = 0;
       h = u0.z - a.head_begin; q_row0 = u0.w; kv_row0 = u1.y;
       kv = a.kv_idx + u0.y;
@@ -265,7 +287,9 @@ struct BlockSeq {
 // instantiation without carries none of that code.
 // kD: head dimension, 128 or 64. With 64 a tile is one 64-column half: the second TMA box, the upper four of the
 // eight Q K^T MMAs and the upper 64 columns of O are left out; everything else is the same code.
-template <bool kBf16, bool kSoftCap, bool kParts, int kD>
+// kCausal: a kv position is visible to a q token only up to token + kv_len - q_len (the reference's
+// MaskMode::kCausal, prefill.cuh:746-751); the softmax warps then also read the kv-block indices.
+template <bool kBf16, bool kSoftCap, bool kParts, int kD, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
   static_assert(kD == 128 || kD == 64, "head dimension");
   constexpr int kLoadBytes = 128 * kD * 2;   // bytes of one tile load
@@ -523,7 +547,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       }
     };
 
-    GroupSeq seq;
+    GroupSeq<kCausal> seq;
     seq.init(tail, abort_flag);
     uint32_t g = 0;          // global block index (both parities)
     uint32_t my_blocks = 0;  // blocks this group has processed
@@ -689,7 +713,13 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         // read again for the exponentials: holding them across the exchanges below would cost registers)
         if (!mbar_wait(&tail->s_full[X], my_blocks & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const int valid = seq.valid() - static_cast<int>(64u * ch);  // of my columns, how many exist
+        int valid = seq.valid() - static_cast<int>(64u * ch);  // of my columns, how many exist
+        if constexpr (kCausal) {
+          // ... and how many this row's token may attend to: kv positions up to causal_base + token
+          const int lim = seq.causal_base + row / grp - seq.kvb * kBKV + 1;
+          const int vc = (lim > kBKV ? kBKV : lim) - static_cast<int>(64u * ch);
+          valid = valid < vc ? valid : vc;
+        }
         float mx;
         {
           float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -858,16 +888,21 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 
 
 namespace {
-template <bool kBf16, bool kSoftCap, bool kParts, int kD>
+template <bool kBf16, bool kSoftCap, bool kParts, int kD, bool kCausal = false>
 cudaError_t launch_one(const AttnArgs& a, int ctas, cudaStream_t stream) {
-  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap, kParts, kD>,
+  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap, kParts, kD, kCausal>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
-  attention_kernel<kBf16, kSoftCap, kParts, kD><<<ctas, kThreads, kSmemBytes, stream>>>(a);
+  attention_kernel<kBf16, kSoftCap, kParts, kD, kCausal><<<ctas, kThreads, kSmemBytes, stream>>>(a);
   return cudaGetLastError();
 }
 template <bool kBf16, bool kSoftCap>
 cudaError_t launch_two(const AttnArgs& a, int ctas, cudaStream_t stream) {
+  if (a.causal) {  // whole items only (the caller gives no room for partial results)
+    if (a.partial_slots > 0) return cudaErrorInvalidValue;
+    return a.head_dim == 64 ? launch_one<kBf16, kSoftCap, false, 64, true>(a, ctas, stream)
+                            : launch_one<kBf16, kSoftCap, false, 128, true>(a, ctas, stream);
+  }
   // room for partial results means that the unit builder may have cut lists: the instantiation with the merge
   if (a.head_dim == 64)
     return a.partial_slots > 0 ? launch_one<kBf16, kSoftCap, true, 64>(a, ctas, stream)

@@ -176,6 +176,7 @@ struct AttnArgs {
   float* partials;                 // partial results of split items: partial_slots x kPartialFloats floats
   int partial_slots;
   int head_dim;                    // 128 or 64
+  int causal;                      // kv position <= q token + kv_len - q_len only
   int head_begin;                  // tensor head = item head - head_begin
   int group_size;                  // H / Hkv
   int is_bf16;

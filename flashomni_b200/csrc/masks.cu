@@ -562,12 +562,14 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
 //   [1] kv_off     offset of the unit's first entry in kv_idx
 //   [2] h          mask head
 //   [3] q_row0     first row of the q-block in the q / o tensors
-//   [4] q_valid    rows of the q-block that exist (1..sbq)
+//   [4] q_valid | ragged << 16   rows (tokens) of the q-block that exist (1..sbq); columns of the request's partial
+//                  last kv block if the unit's list ends with it, else 0
 //   [5] kv_row0    first kv row of the request
-//   [6] ragged     columns of the request's partial last kv block if the unit's list ends with it, else 0
+//   [6] causal     qb * sbq + kv_len - q_len: the last kv position that the q-block's first token may attend to
+//                  under a causal mask (token t of the block: causal + t)
 //   [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
 // A kv list is cut into n_parts = ceil(n_kept / chunk_max) parts of (almost) equal length only when there is room for
-// partial results (max_slots > 0) and the launch has at most half as many items as streams (whole items would leave streams idle): chunk_max = max(min_chunk,
+// partial results (max_slots > 0) and the launch has more than min_items and at most num_streams items: chunk_max = max(min_chunk,
 // ceil(total_kept / num_streams), ceil(max_nkv / 255)); otherwise every item is one unit.
 // unit_counters: n_units, partial slots in use, chunk_max, status. arrive[slot] = 0 for every slot.
 constexpr int kUnitSortMax = 2048;
@@ -643,7 +645,7 @@ __global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
           int4* dst = reinterpret_cast<int4*>(a.units + 8 * static_cast<int64_t>(off_u + p));
           const int sp_word = np > 1 ? (((off_p + p) & 0xffff) << 16) | (p << 8) | np : (0xffff << 16) | 1;
           dst[0] = make_int4(j1 - j0, kvp + j0, rec.y, q0 + rec.z * a.sbq);
-          dst[1] = make_int4(q_valid, k0, p == np - 1 ? ragged : 0, sp_word);
+          dst[1] = make_int4(q_valid | ((p == np - 1 ? ragged : 0) << 16), k0, rec.z * a.sbq + kv_len - q_len, sp_word);
         }
       }
     }
@@ -723,7 +725,7 @@ __global__ void __launch_bounds__(256) attn_units_whole_kernel(UnitArgs a) {
     if (tail_cols != 0 && n > 0 && a.kv_idx[kvp + n - 1] == kv_len / a.sbkv) ragged = tail_cols;
     int4* dst = reinterpret_cast<int4*>(a.units + 8 * pos);
     dst[0] = make_int4(n, kvp, rec.y, q0 + rec.z * a.sbq);
-    dst[1] = make_int4(q_valid, k0, ragged, (0xffff << 16) | 1);
+    dst[1] = make_int4(q_valid | (ragged << 16), k0, rec.z * a.sbq + kv_len - q_len, (0xffff << 16) | 1);
   }
 }
 

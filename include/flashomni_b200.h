@@ -107,9 +107,10 @@ FO_API int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes
  *   [1] kv_off    offset of the unit's first entry in kv_idx
  *   [2] h         mask head
  *   [3] q_row0    first row of the q-block in the q / o tensors
- *   [4] q_valid   rows of the q-block that exist (1..sbq)
+ *   [4] q_valid | ragged << 16   rows of the q-block that exist (1..sbq); columns of the request's partial last kv
+ *                 block if the unit's list ends with it, else 0
  *   [5] kv_row0   first kv row of the request
- *   [6] ragged    columns of the request's partial last kv block if the unit's list ends with it, else 0
+ *   [6] causal    qb * sbq + kv_len - q_len: the last kv position the q-block's first token sees under a causal mask
  *   [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
  * An item is one unit unless its kv list is cut: lists are cut only when max_slots > 0 and the launch has more than
  * min_items and at most num_streams items (num_streams: the unit count the caller aims at, a few per SM; min_items:
@@ -174,6 +175,20 @@ FO_API int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* 
                        const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t* arrive,
                        float* partials, int64_t partial_slots, int32_t head_begin, float sm_scale,
                        float logits_soft_cap, int32_t* status, void* stream);
+
+/* The same under a causal mask (the reference's MaskMode::kCausal, include/flashomni/attention/prefill.cuh:746-751):
+ * inside the kept kv-blocks, kv position j of a request is visible to q token i only if j <= i + kv_len - q_len
+ * (positions and lengths of the request; with grouped heads i is the token of the packed row). The units carry
+ * the position (word [6]); whole items only, so there is no partial-result scratch. A row whose kept blocks hold no
+ * visible position gets zeros and lse = -5e4, like a q-block that keeps nothing (the reference fills masked logits
+ * with -5e4 instead of -inf and would return the mean of V over those positions there). logits_soft_cap = 0: no cap. */
+FO_API int fo_sparse_attn_fwd_causal(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                       int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                       int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                       int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
+                       const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t head_begin,
+                       float sm_scale, float logits_soft_cap, int32_t* status, void* stream);
 
 /* ---- GEMM-Q / GEMM-O ---------------------------------------------------------------------------
  * Workspace (device, caller-owned, 16-byte aligned) of fo_gemm_workspace_bytes(...) bytes, laid out

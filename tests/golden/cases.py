@@ -10,7 +10,7 @@ from flashomni_b200 import workloads as wl
 
 
 def attention_case(name):
-    group, D = 1, 128
+    group, D, causal = 1, 128, False
     if name == "attn_uniform":
         H, lens_q, lens_kv, density, seed = 2, [512], [512], 0.6, 101
     elif name == "attn_ragged":
@@ -23,6 +23,10 @@ def attention_case(name):
         H, lens_q, lens_kv, density, seed, D = 3, [300, 205], [256, 333], 0.7, 105, 64
     elif name == "attn_hd64_gqa":
         H, lens_q, lens_kv, density, seed, group, D = 4, [130, 256], [384, 130], 0.6, 106, 2, 64
+    elif name == "attn_causal":         # causal mask inside the kept blocks; kv longer than q (offset kv_len - q_len)
+        H, lens_q, lens_kv, density, seed, causal = 3, [300, 205], [428, 333], 0.7, 107, True
+    elif name == "attn_causal_gqa":
+        H, lens_q, lens_kv, density, seed, group, causal = 4, [130, 256], [384, 300], 0.6, 108, 2, True
     else:
         raise KeyError(name)
     Hkv = H // group
@@ -39,18 +43,19 @@ def attention_case(name):
         # the reference writes garbage-free output only if an active q-block keeps something; keep >= 1
         for qb in range(a.shape[0]):
             for h in range(Hkv):
-                if a[qb, h] and b[qb, h].sum() == 0:
-                    b[qb, h, 0] = 1
+                if a[qb, h] and (b[qb, h].sum() == 0 or causal):
+                    b[qb, h, 0] = 1     # causal: kv position 0 is visible to every token (kv_len >= q_len)
     m = wl.pack_masks(qa, kk)
     q = wl.randn_bf16((int(qo[-1]), H, D), seed + 1)
     k = wl.randn_bf16((int(kv[-1]), Hkv, D), seed + 2)
     v = wl.randn_bf16((int(kv[-1]), Hkv, D), seed + 3)
     prior = wl.randn_bf16((int(qo[-1]), H, D), seed + 4)
     return {"q": q, "k": k, "v": v, "qo": qo, "kv": kv, "masks": m, "prior": prior, "H": H, "Hkv": Hkv, "group": group,
-            "q_block_tokens": qtok, "D": D}
+            "q_block_tokens": qtok, "D": D, "causal": causal}
 
 
-ATTENTION_CASES = ("attn_uniform", "attn_ragged", "attn_gqa", "attn_gqa4", "attn_hd64", "attn_hd64_gqa")
+ATTENTION_CASES = ("attn_uniform", "attn_ragged", "attn_gqa", "attn_gqa4", "attn_hd64", "attn_hd64_gqa", "attn_causal",
+                   "attn_causal_gqa")
 
 
 def gemm_case(name):

@@ -31,7 +31,7 @@ def main(out_path):
         out = d(c["prior"]).clone()
         lse = torch.zeros(out.shape[0], c["H"], dtype=torch.float32, device=dev)
         ref_cuda.sparse_attention(d(c["q"]), d(c["k"]), d(c["v"]), d(c["qo"]), d(c["kv"]), d(m.sparse_info),
-                                  d(m.sparse_kv_info), d(m.info_indptr), d(m.kv_info_indptr), out, lse=lse)
+                                  d(m.sparse_kv_info), d(m.info_indptr), d(m.kv_info_indptr), out, lse=lse, causal=c["causal"])
         torch.cuda.synchronize()
         res[name + "_out"] = cases.bf16_bits(out)
         res[name + "_lse"] = lse.cpu().numpy()

@@ -30,7 +30,8 @@ def test_attention_oracle_vs_reference_kernel():
         c = cases.attention_case(name)
         m = c["masks"]
         out, lse = oa.sparse_attention(c["q"], c["k"], c["v"], c["qo"], c["kv"], m.sparse_info, m.sparse_kv_info,
-                                       m.info_indptr, m.kv_info_indptr, out_prior=c["prior"], return_lse=True)
+                                       m.info_indptr, m.kv_info_indptr, out_prior=c["prior"], return_lse=True,
+                                       causal=c["causal"])
         gold = cases.from_bits(GOLD[name + "_out"])
         # the reference output is itself bf16-rounded: same tolerance as for our kernels
         assert_close_bf16(gold, out, name)

@@ -413,6 +413,54 @@ def test_head_dim_64_flux_size(cuda_device):
         done += 1
 
 
+@pytest.mark.parametrize("H,Hkv,D,dtype,soft_cap", [(3, 3, 128, torch.bfloat16, 0.0), (4, 2, 128, torch.float16, 0.0),
+                                                    (3, 3, 64, torch.bfloat16, 0.0), (2, 2, 128, torch.bfloat16, 25.0)])
+def test_causal_mask(cuda_device, H, Hkv, D, dtype, soft_cap):
+    """plan(causal=True): inside the kept blocks kv position j is visible to q token i only if j <= i + kv_len - q_len
+    (the reference's MaskMode::kCausal). Requests with kv longer than q, equal, and SHORTER than q (their first
+    tokens then see nothing: zeros, lse -5e4), ragged tails, grouped heads, head_dim 64, soft cap."""
+    g = H // Hkv
+    qt = 128 // g
+    lens_q, lens_kv = [300, 205, 260], [428, 205, 200]
+    qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(lens_kv)]).astype(np.int32)
+    rng = np.random.default_rng(70 + H + D)
+    qa = [(rng.random((-(-a // qt), Hkv)) < 0.8).astype(np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // qt), Hkv, -(-b // 128))) < 0.7).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    m = wl.pack_masks(qa, kk)
+    q = wl.randn_bf16((int(qo[-1]), H, D), 71, dtype=dtype)
+    k = wl.randn_bf16((int(kv[-1]), Hkv, D), 72, dtype=dtype)
+    v = wl.randn_bf16((int(kv[-1]), Hkv, D), 73, dtype=dtype)
+    prior = wl.randn_bf16((int(qo[-1]), H, D), 74, dtype=dtype)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
+    w.plan(dev(qo, cuda_device), dev(kv, cuda_device), H, Hkv, D, causal=True, q_data_type=dtype,
+           logits_soft_cap=soft_cap if soft_cap > 0 else None)
+    si, skv, ip, kp = masks_to_device(m, cuda_device)
+    for _ in range(2):
+        o, lse = w.run(dev(q, cuda_device), dev(k, cuda_device), dev(v, cuda_device), si, skv, ip, kp,
+                       out=dev(prior, cuda_device).clone(), return_lse=True)
+    w.check_status()
+    ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                                       out_prior=prior, return_lse=True, logits_soft_cap=soft_cap, causal=True)
+    assert_close_bf16(o.cpu(), ref, f"causal H={H}/{Hkv} D={D} {dtype}")
+    act = torch.zeros(int(qo[-1]), H, dtype=torch.bool)
+    for b in range(len(lens_q)):
+        for qb in range(qa[b].shape[0]):
+            r0 = int(qo[b]) + qb * qt
+            r1 = min(r0 + qt, int(qo[b + 1]))
+            for hk in range(Hkv):
+                if qa[b][qb, hk]:
+                    act[r0:r1, hk * g:(hk + 1) * g] = True
+                else:
+                    assert torch.equal(o[r0:r1, hk * g:(hk + 1) * g].cpu(), prior[r0:r1, hk * g:(hk + 1) * g])
+    assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-3)
+    assert (ref_lse[act] == -5e4).any()          # the case does hold rows that see nothing
+    # and it differs from the unmasked result
+    full = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                               out_prior=prior)
+    assert (full - ref).abs().max() > 0.1
+
+
 def test_undersized_kept_list_is_reported_not_walked(cuda_device):
     """A C-ABI caller that compacts with a kv_idx capacity below the kept count: the compaction records it, and
     the attention launch that follows touches neither the lists nor the output and reports FO_DEV_BAD_INDEX."""

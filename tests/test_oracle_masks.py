@@ -103,9 +103,10 @@ def test_attention_units_cut_long_lists_only_when_items_are_few():
     for r, it in zip(u.tolist(), c["order"].tolist()):
         b, h, qb, nk = c["items"][it].tolist()
         assert r[0] == nk and r[1] == c["kv_indptr"][it] and r[2] == h and r[3] == qb * 128
-        assert r[4] == (128 if qb < 19 else 128 - 50) and r[5] == 0
+        assert (r[4] & 0xffff) == (128 if qb < 19 else 128 - 50) and r[5] == 0
         last_is_partial = nk > 0 and c["kv_idx"][c["kv_indptr"][it] + nk - 1] == 19
-        assert r[6] == (128 - 50 if last_is_partial else 0) and (r[7] & 0xffffffff) == 0xffff0001
+        assert (r[4] >> 16) == (128 - 50 if last_is_partial else 0) and (r[7] & 0xffffffff) == 0xffff0001
+        assert r[6] == qb * 128        # causal base: q and kv of the request have the same length
     # few items per stream: lists longer than chunk_max are cut into parts that tile the list without gaps
     u, slots, chunk = om.attn_units(c, qo, kv, num_streams=2 * n, min_chunk=6)
     assert chunk == max(6, -(-int(c["items"][:, 3].sum()) // (2 * n)))
@@ -129,7 +130,7 @@ def test_attention_units_cut_long_lists_only_when_items_are_few():
                 assert (w & 0xff) == n_parts and ((w >> 8) & 0xff) == p and (w >> 16) == used + p
             else:
                 assert w == 0xffff0001
-            assert r[6] == 0 or p == n_parts - 1          # only the last part can end with the partial block
+            assert (r[4] >> 16) == 0 or p == n_parts - 1   # only the last part can end with the partial block
             seen += 1
         assert off == int(c["kv_indptr"][it]) + nk           # the parts tile the list without gaps
         used += n_parts if n_parts > 1 else 0
