@@ -38,41 +38,83 @@ __device__ __forceinline__ uint32_t pack8(const uint8_t* p, int64_t avail, bool 
   return out;
 }
 
+// Four output bytes from 32 input bytes held in two 16-byte words: per 32-bit word the "byte is non-zero" flags are
+// gathered with one multiply (flag of byte i at bit 8 i; the product with 2^24 + 2^17 + 2^10 + 2^3 puts flag i at bit
+// 24 + i, all partial products land on distinct bits).
+__device__ __forceinline__ uint32_t nibble_of(uint32_t w) {
+  const uint32_t t = ((((w & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w) & 0x80808080u) >> 7;
+  return (t * 0x01020408u) >> 24;
+}
+__device__ __forceinline__ uint32_t pack32(const uint4& a, const uint4& b, bool little) {
+  uint32_t r = (nibble_of(a.x) | (nibble_of(a.y) << 4)) | ((nibble_of(a.z) | (nibble_of(a.w) << 4)) << 8) |
+               ((nibble_of(b.x) | (nibble_of(b.y) << 4)) << 16) | ((nibble_of(b.z) | (nibble_of(b.w) << 4)) << 24);
+  if (!little) r = __byte_perm(__brev(r), 0, 0x0123);  // reverse the bits inside every byte, keep the byte order
+  return r;
+}
+
+// One thread per four output bytes (32 inputs, two 16-byte loads in flight) where alignment and length allow it,
+// byte by byte otherwise.
 __global__ void packbits_kernel(const uint8_t* __restrict__ x, int64_t n, int little, uint8_t* __restrict__ y) {
   const int64_t nbytes = (n + 7) >> 3;
-  const bool base_aligned = (reinterpret_cast<uintptr_t>(x) & 7u) == 0;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nbytes;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    y[i] = static_cast<uint8_t>(pack8(x + i * 8, n - i * 8, little != 0, base_aligned));
+  const int64_t nwords = (nbytes + 3) >> 2;
+  const bool x16 = (reinterpret_cast<uintptr_t>(x) & 15u) == 0, y4 = (reinterpret_cast<uintptr_t>(y) & 3u) == 0;
+  const bool x8 = (reinterpret_cast<uintptr_t>(x) & 7u) == 0;
+  for (int64_t w = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; w < nwords;
+       w += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t i0 = w * 4;
+    if (x16 && y4 && (i0 + 4) * 8 <= n) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + i0 * 8), b = *reinterpret_cast<const uint4*>(x + i0 * 8 + 16);
+      *reinterpret_cast<uint32_t*>(y + i0) = pack32(a, b, little != 0);
+    } else {
+      for (int64_t i = i0; i < i0 + 4 && i < nbytes; ++i)
+        y[i] = static_cast<uint8_t>(pack8(x + i * 8, n - i * 8, little != 0, x8));
+    }
   }
 }
 
-// One thread per output byte; the segment of a byte is found by binary search over the byte indptr.
+// The same per segment; the segment of an output byte is found by binary search over the byte indptr.
+__device__ __forceinline__ int seg_of(const int32_t* __restrict__ new_indptr, int num_segments, int64_t i) {
+  int lo = 0, hi = num_segments;  // new_indptr[lo] <= i < new_indptr[lo + 1]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (static_cast<int64_t>(new_indptr[mid]) <= i) lo = mid; else hi = mid;
+  }
+  return lo;
+}
 __global__ void segment_packbits_kernel(const uint8_t* __restrict__ x, const int32_t* __restrict__ indptr,
                                         const int32_t* __restrict__ new_indptr, int num_segments,
                                         int64_t out_bytes, int little, uint8_t* __restrict__ y) {
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < out_bytes;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    int lo = 0, hi = num_segments;  // find seg with new_indptr[seg] <= i < new_indptr[seg+1]
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (static_cast<int64_t>(new_indptr[mid]) <= i) lo = mid; else hi = mid;
-    }
+  const int64_t nwords = (out_bytes + 3) >> 2;
+  const bool y4 = (reinterpret_cast<uintptr_t>(y) & 3u) == 0;
+  for (int64_t w = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; w < nwords;
+       w += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t i0 = w * 4;
+    const int lo = seg_of(new_indptr, num_segments, i0);
     const int64_t seg_in0 = indptr[lo], seg_in1 = indptr[lo + 1];
-    const int64_t k = i - new_indptr[lo];
-    const int64_t src = seg_in0 + k * 8;
-    const int64_t avail = seg_in1 - src;
-    if (avail <= 0) { y[i] = 0; continue; }
-    const bool aligned = (reinterpret_cast<uintptr_t>(x + src) & 7u) == 0;
-    y[i] = static_cast<uint8_t>(pack8(x + src, avail, little != 0, aligned));
+    const int64_t src0 = seg_in0 + (i0 - new_indptr[lo]) * 8;
+    // fast path: the four bytes lie in one segment, all 32 inputs exist, loads and the store are aligned
+    if (y4 && i0 + 4 <= out_bytes && i0 + 4 <= static_cast<int64_t>(new_indptr[lo + 1]) && src0 + 32 <= seg_in1 &&
+        (reinterpret_cast<uintptr_t>(x + src0) & 15u) == 0) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + src0), b = *reinterpret_cast<const uint4*>(x + src0 + 16);
+      *reinterpret_cast<uint32_t*>(y + i0) = pack32(a, b, little != 0);
+      continue;
+    }
+    for (int64_t i = i0; i < i0 + 4 && i < out_bytes; ++i) {
+      const int sg = seg_of(new_indptr, num_segments, i);
+      const int64_t src = static_cast<int64_t>(indptr[sg]) + (i - new_indptr[sg]) * 8;
+      const int64_t avail = static_cast<int64_t>(indptr[sg + 1]) - src;
+      if (avail <= 0) { y[i] = 0; continue; }
+      const bool aligned = (reinterpret_cast<uintptr_t>(x + src) & 7u) == 0;
+      y[i] = static_cast<uint8_t>(pack8(x + src, avail, little != 0, aligned));
+    }
   }
 }
 
 cudaError_t launch_packbits(const uint8_t* x, int64_t n, int little, uint8_t* y, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  const int64_t nbytes = (n + 7) >> 3;
+  const int64_t nwords = (((n + 7) >> 3) + 3) >> 2;
   const int threads = 256;
-  int64_t blocks = (nbytes + threads - 1) / threads;
+  int64_t blocks = (nwords + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   packbits_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(x, n, little, y);
   return cudaGetLastError();
@@ -82,8 +124,9 @@ cudaError_t launch_segment_packbits(const uint8_t* x, const int32_t* indptr, con
                                     int num_segments, int64_t out_bytes, int little, uint8_t* y,
                                     cudaStream_t stream) {
   if (out_bytes <= 0 || num_segments <= 0) return cudaSuccess;
+  const int64_t nwords = (out_bytes + 3) >> 2;
   const int threads = 256;
-  int64_t blocks = (out_bytes + threads - 1) / threads;
+  int64_t blocks = (nwords + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   segment_packbits_kernel<<<static_cast<int>(blocks), threads, 0, stream>>>(x, indptr, new_indptr, num_segments,
                                                                             out_bytes, little, y);

@@ -111,6 +111,11 @@ class PeerExchange:
             return
         try:
             import ctypes
+            import os
+            # Only unicast peer pointers are used here: ask torch not to bind the buffers to an NVLink multicast
+            # object (a rank that exits while bound to one can fault its peers). Unknown to a torch that has no such
+            # switch, where it changes nothing.
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as sm
             self._sm = sm
             pad = sm.empty((self.CHANNELS * self.world,), dtype=torch.int32, device=self.device)
