@@ -264,7 +264,7 @@ __global__ void compact_count_kernel(CompactArgs a) {
 // histogram in shared memory; bucket starts are (items of smaller keys) + (same bucket, earlier
 // slices); every warp then places its slice in ascending candidate order, 32 at a time.
 __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int sort_warps, int by_length, int heads_per_group) {
-  extern __shared__ int s_whist[];  // [sort_warps + 1][batch * head_count]
+  extern __shared__ __align__(16) int s_whist[];  // [sort_warps + 1][batch * head_count]; first the scan's staging
   __shared__ int s_warp_items[32];
   __shared__ long long s_warp_kept[32];
   __shared__ int s_carry_items;
@@ -275,11 +275,25 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
   __syncthreads();
   // kScanPer consecutive candidates per thread and pass: a thread scans its own run, the CTA scans the run totals
   constexpr int kScanPer = 8;
+  constexpr int kPassCand = 1024 * kScanPer, kPassPad = kPassCand + kPassCand / 32;
+  // staging of a pass, over the dynamic shared memory that the sort below uses afterwards
+  long long* s_off = reinterpret_cast<long long*>(s_whist);           // [kPassPad] kept-list offsets
+  int* s_val = reinterpret_cast<int*>(s_off + kPassPad);              // [kPassPad] candidate counts
+  int* s_pos = s_val + kPassPad;                                      // [kPassPad] item positions
   for (int64_t base = 0; base < a.n_cand; base += static_cast<int64_t>(blockDim.x) * kScanPer) {
     const int64_t c0 = base + static_cast<int64_t>(tid) * kScanPer;
+    // The counts of a pass come in with coalesced loads and the results leave with coalesced stores; between them
+    // they sit in shared memory, where a thread finds its eight consecutive entries (index i at i + i / 32: the
+    // accesses of a warp then fall on 32 different banks).
+    const int64_t pass_n = (a.n_cand - base) < kPassCand ? (a.n_cand - base) : kPassCand;
+    for (int i = tid; i < pass_n; i += blockDim.x) s_val[i + (i >> 5)] = a.cnt[base + i];
+    __syncthreads();
     int vals[kScanPer];
 #pragma unroll
-    for (int k = 0; k < kScanPer; ++k) vals[k] = (c0 + k < a.n_cand) ? a.cnt[c0 + k] : -1;
+    for (int k = 0; k < kScanPer; ++k) {
+      const int i = tid * kScanPer + k;
+      vals[k] = (c0 + k < a.n_cand) ? s_val[i + (i >> 5)] : -1;
+    }
     int run_i = 0;
     long long run_k = 0;
 #pragma unroll
@@ -316,13 +330,18 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
     for (int k = 0; k < kScanPer; ++k) {
       if (c0 + k < a.n_cand) {
         const bool flag = vals[k] >= 0;
-        a.item_pos[c0 + k] = flag ? pre_i : -1;
-        a.kv_off[c0 + k] = pre_k;
+        const int i = tid * kScanPer + k;
+        s_pos[i + (i >> 5)] = flag ? pre_i : -1;
+        s_off[i + (i >> 5)] = pre_k;
         pre_i += flag;
         pre_k += flag ? vals[k] : 0;
       }
     }
     __syncthreads();
+    for (int i = tid; i < pass_n; i += blockDim.x) {
+      a.item_pos[base + i] = s_pos[i + (i >> 5)];
+      a.kv_off[base + i] = s_off[i + (i >> 5)];
+    }
     if (tid == 0) {
       s_carry_items += s_warp_items[31];
       s_carry_kept += s_warp_kept[31];
@@ -585,8 +604,10 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
   int64_t sort_warps = nb > 0 ? (160 * 1024) / (nb * 4) - 1 : 0;
   if (sort_warps > 32) sort_warps = 32;
   if (sort_warps < 1) sort_warps = 0;
-  const size_t scan_smem = static_cast<size_t>((sort_warps + 1) * nb * 4) * (sort_warps > 0 ? 1 : 0);
-  if (scan_smem > 32 * 1024) {
+  size_t scan_smem = static_cast<size_t>((sort_warps + 1) * nb * 4) * (sort_warps > 0 ? 1 : 0);
+  const size_t stage_smem = static_cast<size_t>(8192 + 8192 / 32) * 16;   // the scan's staging: 8 + 4 + 4 bytes per candidate
+  if (scan_smem < stage_smem) scan_smem = stage_smem;
+  {
     cudaError_t ea = cudaFuncSetAttribute(compact_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
     if (ea != cudaSuccess) return ea;
   }
