@@ -369,6 +369,67 @@ __global__ void __launch_bounds__(1024) compact_scan_kernel(CompactArgs a, int s
     // Single heads with their q-blocks ascending: the candidates read in (request, head, q-block) order instead of
     // (request, q-block, head); the running count of active ones is the position. One more scan, no sort.
     build_cand_prefix(a, s_prefix);
+    if (a.head_count <= 512) {
+      // Threads laid out head-fastest: thread (chunk k, head h) walks the q-blocks of its chunk for its head, so the
+      // threads of a chunk read consecutive positions (one row of heads at a time). Count, prefix per head over the
+      // chunks and over the heads, then the same walk again writing the positions out.
+      int* s_cnt = reinterpret_cast<int*>(s_whist);          // [chunks][H] counts, then exclusive starts
+      const int H = a.head_count;
+      const int chunks = static_cast<int>(blockDim.x) / H;
+      int* s_tot = s_cnt + chunks * H;                       // [H] items of a head, then the head's start
+      const int h = tid % H, ck = tid / H;
+      int req_base = 0;
+      for (int b = 0; b < a.batch; ++b) {
+        const int64_t c_req = s_prefix[b];
+        const int nq = static_cast<int>((s_prefix[b + 1] - s_prefix[b]) / H);
+        const int qpc = (nq + chunks - 1) / chunks;
+        const int q0 = ck * qpc, q1 = (q0 + qpc < nq) ? q0 + qpc : nq;
+        int mine = 0;
+        if (ck < chunks)
+          for (int qb = q0; qb < q1; ++qb) mine += a.item_pos[c_req + static_cast<int64_t>(qb) * H + h] >= 0;
+        if (ck < chunks) s_cnt[ck * H + h] = mine;
+        __syncthreads();
+        if (tid < H) {   // exclusive prefix over the chunks of head `tid`
+          int run = 0;
+          for (int k = 0; k < chunks; ++k) {
+            const int t = s_cnt[k * H + tid];
+            s_cnt[k * H + tid] = run;
+            run += t;
+          }
+          s_tot[tid] = run;
+        }
+        __syncthreads();
+        if (warp == 0) {  // exclusive prefix over the heads
+          int carry = 0;
+          for (int h0 = 0; h0 < H; h0 += 32) {
+            const int v = (h0 + lane < H) ? s_tot[h0 + lane] : 0;
+            int x = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+              const int y = __shfl_up_sync(0xffffffffu, x, o);
+              if (lane >= o) x += y;
+            }
+            if (h0 + lane < H) s_tot[h0 + lane] = carry + x - v;
+            carry += __shfl_sync(0xffffffffu, x, 31);
+          }
+          if (lane == 0) s_carry_items = carry;   // items of this request
+        }
+        __syncthreads();
+        if (ck < chunks) {
+          int pos = req_base + s_tot[h] + s_cnt[ck * H + h];
+          for (int qb = q0; qb < q1; ++qb) {
+            const int ip = a.item_pos[c_req + static_cast<int64_t>(qb) * H + h];
+            if (ip >= 0) {
+              if (pos < a.max_items) a.order[pos] = ip;
+              ++pos;
+            }
+          }
+        }
+        req_base += s_carry_items;
+        __syncthreads();
+      }
+      return;
+    }
     if (tid == 0) s_carry_items = 0;
     __syncthreads();
     for (int64_t base = 0; base < a.n_cand; base += static_cast<int64_t>(blockDim.x) * kScanPer) {
