@@ -461,6 +461,61 @@ def test_causal_mask(cuda_device, H, Hkv, D, dtype, soft_cap):
     assert (full - ref).abs().max() > 0.1
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_random_configurations_against_the_oracle(cuda_device, seed):
+    """Seeded random draws over everything the wrapper takes at once: heads and grouping, head dimension, dtype, kv
+    layout, causal mask, soft cap, lse, batch, ragged q and kv lengths (empty requests included), mask densities
+    (rows that keep nothing included), prior contents of the output."""
+    rng = np.random.default_rng(1000 + seed)
+    g = int(rng.choice([1, 1, 2, 4]))
+    Hkv = int(rng.integers(1, 4))
+    H, D = Hkv * g, int(rng.choice([128, 128, 64]))
+    dtype = torch.bfloat16 if rng.random() < 0.6 else torch.float16
+    causal = bool(rng.random() < 0.35)
+    soft_cap = float(rng.choice([0.0, 0.0, 20.0]))
+    layout = "HND" if rng.random() < 0.3 else "NHD"
+    B = int(rng.integers(1, 4))
+    lens_q = [int(rng.integers(0, 420)) for _ in range(B)]
+    lens_kv = [int(rng.integers(1, 520)) if lq > 0 else int(rng.integers(0, 200)) for lq in lens_q]
+    if sum(lens_q) == 0:
+        lens_q[0], lens_kv[0] = 130, 257
+    qt = 128 // g
+    qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(lens_kv)]).astype(np.int32)
+    dq, dk = float(rng.uniform(0.3, 1.0)), float(rng.uniform(0.1, 1.0))
+    qa = [(rng.random((-(-a // qt), Hkv)) < dq).astype(np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // qt), Hkv, -(-b // 128))) < dk).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    m = wl.pack_masks(qa, kk)
+    Tq, Tkv = int(qo[-1]), max(int(kv[-1]), 1)
+    q = wl.randn_bf16((Tq, H, D), 2000 + seed, dtype=dtype)
+    k = wl.randn_bf16((Tkv, Hkv, D), 3000 + seed, dtype=dtype)
+    v = wl.randn_bf16((Tkv, Hkv, D), 4000 + seed, dtype=dtype)
+    prior = wl.randn_bf16((Tq, H, D), 5000 + seed, dtype=dtype)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device), layout)
+    w.plan(dev(qo, cuda_device), dev(kv, cuda_device), H, Hkv, D, causal=causal, q_data_type=dtype,
+           logits_soft_cap=soft_cap if soft_cap > 0 else None)
+    si, skv, ip, kp = masks_to_device(m, cuda_device)
+    kd, vd = dev(k, cuda_device), dev(v, cuda_device)
+    if layout == "HND":
+        kd, vd = kd.transpose(0, 1).contiguous(), vd.transpose(0, 1).contiguous()
+    o, lse = w.run(dev(q, cuda_device), kd, vd, si, skv, ip, kp, out=dev(prior, cuda_device).clone(), return_lse=True)
+    w.check_status()
+    ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                                       out_prior=prior, return_lse=True, logits_soft_cap=soft_cap, causal=causal)
+    what = f"seed {seed}: H={H}/{Hkv} D={D} {dtype} causal={causal} cap={soft_cap} {layout} q={lens_q} kv={lens_kv}"
+    assert_close_bf16(o.cpu(), ref, what)
+    act = torch.zeros(Tq, H, dtype=torch.bool)
+    for b in range(B):
+        for qb in range(qa[b].shape[0]):
+            r0 = int(qo[b]) + qb * qt
+            r1 = min(r0 + qt, int(qo[b + 1]))
+            for hk in range(Hkv):
+                if qa[b][qb, hk]:
+                    act[r0:r1, hk * g:(hk + 1) * g] = True
+    assert torch.equal(o.cpu()[~act], prior[~act]), what
+    assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-3), what
+
+
 def test_undersized_kept_list_is_reported_not_walked(cuda_device):
     """A C-ABI caller that compacts with a kv_idx capacity below the kept count: the compaction records it, and
     the attention launch that follows touches neither the lists nor the output and reports FO_DEV_BAD_INDEX."""
