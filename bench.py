@@ -231,13 +231,15 @@ def event_time(fn, steps, sync_each=False, before=None):
     return {"mean": ms, "median": ms, "min": ms}
 
 
-def graph_time(launch, device, reps=20):
+def graph_time(launch, device, reps=20, on_current=False):
     """Mean milliseconds of one call of launch(stream_handle) when `reps` calls are replayed from one CUDA graph
-    (for launches so short that eager calls would be bound by the host)."""
+    (for launches so short that eager calls would be bound by the host). `on_current`: the callable launches on
+    torch's current stream (which is the capture stream here) and ignores the handle."""
     cs = torch.cuda.Stream(device)
     cs.wait_stream(torch.cuda.current_stream(device))
     g = torch.cuda.CUDAGraph()
     with torch.cuda.stream(cs):
+        launch(cs.cuda_stream)
         launch(cs.cuda_stream)
         torch.cuda.synchronize()
         with torch.cuda.graph(g, stream=cs):
@@ -574,8 +576,24 @@ def run_flux(ctx, args, peaks):
 
     for _ in range(2):
         prep_masks(); k_gemm_q(); k_gemm_kv(); attn_run(); k_gemm_o()
-    kt = chain_time([("gemm_q", k_gemm_q), ("gemm_kv", k_gemm_kv), ("attention", attn_run), ("gemm_o", k_gemm_o)],
-                    args.steps, pre=prep_masks)
+    if world == 1:
+        kt = chain_time([("gemm_q", k_gemm_q), ("gemm_kv", k_gemm_kv), ("attention", attn_run), ("gemm_o", k_gemm_o)],
+                        args.steps, pre=prep_masks)
+    else:
+        # A rank's share of the step is too short for eager launches (the host's launch rate would set the intervals):
+        # every kernel is replayed alone from a CUDA graph of five launches. The lists are complete by now, so the
+        # GEMMs need not wait for them; the attention launch carries its list kernels, which are timed alone and
+        # taken off.
+        torch.cuda.synchronize()
+        q_list.event = None
+        o_list.event = None
+
+        def alone(fn):
+            return graph_time(lambda _s: fn(), device, reps=5, on_current=True)["mean"]
+
+        t_lists = alone(compact_only)
+        kt = {"gemm_q": alone(k_gemm_q), "gemm_kv": alone(k_gemm_kv), "attention": max(alone(attn_run) - t_lists, 0.0),
+              "gemm_o": alone(k_gemm_o)}
     kt["compact"] = event_time(compact_only, args.steps)["mean"]
     kt = {k: {"mean": v} for k, v in kt.items()}
     block.wrapper.check_status()
@@ -602,8 +620,8 @@ def run_flux(ctx, args, peaks):
     base = top["kernel"].split("<")[0]
     if world > 1:
         for e in kernels:
-            e["note"] = ("timed with events between eager launches; at this per-rank size the host's launch rate, not "
-                         "the GPU, sets these intervals: read the per-kernel figures at N = 1")
+            e["note"] = ("this rank's share, each kernel replayed alone from a CUDA graph of five launches (eager launches "
+                         "would be bound by the host at this size); at N = 1 the kernels are timed inside the step's chain")
     roofline = {"bound": "tensor", "kernel": top["kernel"], "achieved": top["achieved_tflops"], "peak": peaks["burst"],
                 "unit": "TFLOP/s", "frac": top["frac_of_peak"], "traffic": NCU_TRAFFIC.get(base),
                 "traffic_note": "dram read+write bytes per launch from the ncu captures summarised under profiles/",
