@@ -58,6 +58,11 @@ SIGNATURES = {
                                             c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                             c_int32, c_int32, _P, _P, _P,
                                             c_int64, c_int32, c_float, c_float, _P, _P]),
+    "fo_sparse_attn_fwd_custom_mask": (c_int32, [_P, _P, _P, _P, _P, c_int32,
+                                                 c_int64, c_int64, c_int32, c_int32, c_int32,
+                                                 c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                                 c_int32, c_int32, _P, _P, _P,
+                                                 c_int64, c_int32, c_float, c_float, _P, c_int64, _P, _P, _P, _P, _P]),
     "fo_gemm_workspace_bytes": (c_size_t, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "fo_gemm_dense_tile_rows": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32]),
     "fo_gemm_dense_tile_cols": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_int32, c_int32]),

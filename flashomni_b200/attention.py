@@ -149,8 +149,6 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         # Features of the FlashInfer lineage that the DiT path never enables (the reference's AOT build
         # only instantiates mask_mode 0, setup.py:38; pos-enc and fp16-qk-reduction are forced off,
         # csrc/batch_sparseFA_config.inc:42-43):
-        if custom_mask is not None or packed_custom_mask is not None:
-            raise NotImplementedError("flashomni_b200: custom attention masks are not implemented")
         if PosEncodingMode[pos_encoding_mode] != PosEncodingMode.NONE:
             raise NotImplementedError("flashomni_b200: in-kernel positional encoding is not implemented")
         if logits_soft_cap < 0:
@@ -223,6 +221,29 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         self._total_q = total_num_rows
         self._total_kv = int(kv_indptr_host[-1])
         self._causal = causal
+        # Custom mask (reference: flashomni/attention.py:524-533): per request a [q_len, kv_len] matrix of flags,
+        # flattened and concatenated; packed here with segment_packbits exactly as the reference packs it (every
+        # request's matrix starts at a byte boundary). A packed mask that the caller brings must be packed that way.
+        self._packed_custom_mask = None
+        self._mask_indptr = None
+        if custom_mask is not None or packed_custom_mask is not None:
+            elems = ql * kl
+            if packed_custom_mask is None:
+                from .quantization import segment_packbits
+                flat = custom_mask.contiguous().view(-1).to(self.device)
+                if flat.numel() != int(elems.sum()):
+                    raise ValueError("custom_mask must hold sum(q_len * kv_len) flags")
+                elem_indptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(elems, 0)]).to(
+                    self.device, dtype=torch.int32)
+                packed, byte_indptr = segment_packbits(flat, elem_indptr, bitorder="little")
+            else:
+                nbytes = (elems + 7) // 8
+                byte_indptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(nbytes, 0)])
+                packed = packed_custom_mask.to(self.device, dtype=torch.uint8).contiguous()
+                if packed.numel() < int(byte_indptr[-1]):
+                    raise ValueError("packed_custom_mask is shorter than sum(ceil(q_len * kv_len / 8)) bytes")
+            self._packed_custom_mask = packed
+            self._mask_indptr = byte_indptr.to(self.device, dtype=torch.int32)
         self._carve_workspace()
 
         self._sparse_block_size_for_q = sparse_block_size_for_q
@@ -291,7 +312,7 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             may_split, self._min_chunk, self._min_items = True, 2, 0
             self._num_streams = max(self._num_streams, self._n_cand, self._max_kept)
             extra_units = slots = self._max_kept // 2 + n + 1      # parts of at least two blocks
-        if self._causal:   # the causal instantiation handles whole items only
+        if self._causal or self._packed_custom_mask is not None:   # those instantiations handle whole items only
             may_split = False
         self._max_units = n + (extra_units if may_split else 0)
         self._partial_slots = slots if may_split else 0
@@ -412,7 +433,12 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
                     _native.ptr(ws["arrive"]), _native.ptr(self._partials), self._partial_slots,
                     self._mask_head_begin, float(sm_scale))
             cap = float(self._logits_soft_cap or 0.0)
-            if self._causal:  # whole items only: no partial-result scratch on this path
+            if self._packed_custom_mask is not None:  # the custom mask takes precedence over `causal`, as in the reference
+                rc = lib.fo_sparse_attn_fwd_custom_mask(
+                    *head[:25], self._mask_head_begin, float(sm_scale), cap, _native.ptr(self._packed_custom_mask),
+                    self._packed_custom_mask.numel(), _native.ptr(self._mask_indptr), _native.ptr(self._qo_indptr_buf),
+                    _native.ptr(self._kv_indptr_buf), _native.ptr(ws["status"]), stream)
+            elif self._causal:  # whole items only: no partial-result scratch on this path
                 rc = lib.fo_sparse_attn_fwd_causal(*head[:25], self._mask_head_begin, float(sm_scale), cap,
                                                    _native.ptr(ws["status"]), stream)
             elif cap > 0:  # logits = cap * tanh(q.k * sm_scale / cap), as the reference's variant does

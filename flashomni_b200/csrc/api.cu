@@ -192,6 +192,7 @@ int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes, const
   if (n_cand < 0 || max_nkv < 0 || max_items < n_cand || max_kept < 0)
     return fail(FO_ERR_INVALID_ARG, "fo_mask_compact: capacities must cover n_cand");
   if (batch > 1024) return fail(FO_ERR_UNSUPPORTED, "fo_mask_compact: batch > 1024");
+  if (num_heads > 65535) return fail(FO_ERR_UNSUPPORTED, "fo_mask_compact: more than 65535 heads");
   if (scratch == nullptr || scratch_bytes < fo_mask_compact_scratch_bytes(n_cand, max_nkv) || !aligned16(scratch))
     return fail(FO_ERR_WORKSPACE, "fo_mask_compact: scratch too small or misaligned");
   CompactArgs a;
@@ -285,7 +286,12 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
                      int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
                      const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t* arrive,
                      float* partials, int64_t partial_slots, int32_t head_begin, float sm_scale,
-                     float logits_soft_cap, int32_t causal, int32_t* status, void* stream) {
+                     float logits_soft_cap, int32_t mask_mode, const uint8_t* custom_mask, int64_t custom_mask_bytes,
+                     const int32_t* mask_indptr, const int32_t* qo_indptr, const int32_t* kv_indptr, int32_t* status,
+                     void* stream) {
+  if (mask_mode == 2 && (custom_mask == nullptr || mask_indptr == nullptr || qo_indptr == nullptr || kv_indptr == nullptr ||
+                         custom_mask_bytes <= 0))
+    return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd_custom_mask: mask, its indptr and the request indptrs are required");
   if (!(logits_soft_cap >= 0.f) || !(sm_scale > 0.f))
     return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: sm_scale must be positive and logits_soft_cap >= 0");
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr)
@@ -352,7 +358,12 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   a.partial_slots = static_cast<int>(partial_slots > 0x7fffffffLL ? 0x7fffffffLL : partial_slots);
   a.head_begin = head_begin;
   a.head_dim = head_dim;
-  a.causal = causal != 0;
+  a.mask_mode = mask_mode;
+  a.custom_mask = custom_mask;
+  a.custom_mask_bytes = custom_mask_bytes;
+  a.mask_indptr = mask_indptr;
+  a.qo_indptr = qo_indptr;
+  a.kv_indptr = kv_indptr;
   a.group_size = static_cast<int>(group);
   a.is_bf16 = dtype == FO_DTYPE_BF16;
   if (logits_soft_cap > 0.f) {
@@ -382,7 +393,7 @@ int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   return sparse_attn_impl(q, k, v, o, lse, dtype, total_q, total_kv, num_qo_heads, num_kv_heads, head_dim, q_stride_n,
                           q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, sbq, sbkv,
                           kv_idx, units, unit_counters, max_units, arrive, partials,
-                          partial_slots, head_begin, sm_scale, 0.f, 0, status, stream);
+                          partial_slots, head_begin, sm_scale, 0.f, 0, nullptr, 0, nullptr, nullptr, nullptr, status, stream);
 }
 
 int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
@@ -396,7 +407,7 @@ int fo_sparse_attn_fwd_softcap(const void* q, const void* k, const void* v, void
   return sparse_attn_impl(q, k, v, o, lse, dtype, total_q, total_kv, num_qo_heads, num_kv_heads, head_dim, q_stride_n,
                           q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, sbq, sbkv,
                           kv_idx, units, unit_counters, max_units, arrive, partials,
-                          partial_slots, head_begin, sm_scale, logits_soft_cap, 0, status, stream);
+                          partial_slots, head_begin, sm_scale, logits_soft_cap, 0, nullptr, 0, nullptr, nullptr, nullptr, status, stream);
 }
 
 int fo_sparse_attn_fwd_causal(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
@@ -409,7 +420,23 @@ int fo_sparse_attn_fwd_causal(const void* q, const void* k, const void* v, void*
   return sparse_attn_impl(q, k, v, o, lse, dtype, total_q, total_kv, num_qo_heads, num_kv_heads, head_dim, q_stride_n,
                           q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, sbq, sbkv,
                           kv_idx, units, unit_counters, max_units, nullptr, nullptr, 0, head_begin, sm_scale,
-                          logits_soft_cap, 1, status, stream);
+                          logits_soft_cap, 1, nullptr, 0, nullptr, nullptr, nullptr, status, stream);
+}
+
+int fo_sparse_attn_fwd_custom_mask(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                                   int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                                   int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                                   int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                                   int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
+                                   const int32_t* units, const int32_t* unit_counters, int64_t max_units,
+                                   int32_t head_begin, float sm_scale, float logits_soft_cap, const uint8_t* custom_mask,
+                                   int64_t custom_mask_bytes, const int32_t* mask_indptr, const int32_t* qo_indptr,
+                                   const int32_t* kv_indptr, int32_t* status, void* stream) {
+  return sparse_attn_impl(q, k, v, o, lse, dtype, total_q, total_kv, num_qo_heads, num_kv_heads, head_dim, q_stride_n,
+                          q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h, o_stride_n, o_stride_h, sbq, sbkv,
+                          kv_idx, units, unit_counters, max_units, nullptr, nullptr, 0, head_begin, sm_scale,
+                          logits_soft_cap, 2, custom_mask, custom_mask_bytes, mask_indptr, qo_indptr, kv_indptr, status,
+                          stream);
 }
 
 // ------------------------------------------------------------------------------------------ GEMMs

@@ -177,7 +177,7 @@ template <bool kWithKv>
 struct GroupSeq {
   ItemRead<true> src;
   const int32_t* kv;
-  int rot, kvb, kvb_next, causal_base;
+  int rot, kvb, kvb_next, causal_base, req;
   __device__ __forceinline__ int at(int jj) const {
     const int t = jj + rot;
     return t >= n ? t - n : t;
@@ -189,7 +189,7 @@ struct GroupSeq {
   __device__ __forceinline__ void init(Tail* tail, volatile int* abort_flag) {
     src.init(tail, abort_flag); n = 0; j = 0;
     h = q_row0 = q_valid = 0; ragged_j = -1; ragged_valid = 0; parts = 1;
-    kv = nullptr; rot = 0; kvb = kvb_next = 0; causal_base = 0;
+    kv = nullptr; rot = 0; kvb = kvb_next = 0; causal_base = 0; req = 0;
   }
   template <class F>
   __device__ __forceinline__ bool next(const AttnArgs& a, F&& on_empty) {
@@ -207,9 +207,10 @@ struct GroupSeq {
       // the unit's record: everything this role needs, in one 32-byte load
       const int4* up = reinterpret_cast<const int4*>(a.units + 8 * static_cast<int64_t>(pos));
       const int4 u0 = up[0], u1 = up[1];
-      if (u0.x <= 0) { on_empty(u0.w, u1.x & 0xffff, u0.z - a.head_begin); continue; }
+      if (u0.x <= 0) { on_empty(u0.w, u1.x & 0xffff, (u0.z & 0xffff) - a.head_begin); continue; }
       n = u0.x; j = 0;
-      h = u0.z - a.head_begin; q_row0 = u0.w; q_valid = u1.x & 0xffff; parts = u1.w;
+      h = (u0.z & 0xffff) - a.head_begin; q_row0 = u0.w; q_valid = u1.x & 0xffff; parts = u1.w;
+      req = u0.z >> 16;
       causal_base = u1.z;
       ragged_j = -1;
       if ((u1.x >> 16) != 0) {  // the unit's last entry is the request's partial kv block
@@ -262,9 +263,9 @@ struct BlockSeq {
       if (pos < 0) break;
       const int4* up = reinterpret_cast<const int4*>(a.units + 8 * static_cast<int64_t>(pos));
       const int4 u0 = up[0], u1 = up[1];
-      if (u0.x <= 0) { on_empty(u0.w, u1.x & 0xffff, u0.z - a.head_begin); continue; }
+      if (u0.x <= 0) { on_empty(u0.w, u1.x & 0xffff, (u0.z & 0xffff) - a.head_begin); continue; }
       n = u0.x; j = 0;
-      h = u0.z - a.head_begin; q_row0 = u0.w; kv_row0 = u1.y;
+      h = (u0.z & 0xffff) - a.head_begin; q_row0 = u0.w; kv_row0 = u1.y;
       kv = a.kv_idx + u0.y;
       rot = rot_of(q_row0 >> 7, n);
       kvb = kv[at(0)];
@@ -285,11 +286,31 @@ struct BlockSeq {
 
 // kParts: the launch may hold parts of split items (partial results and their merge in the epilogue); the
 // instantiation without carries none of that code.
+// Up to 64 bits of the little-endian bit stream `seg` starting at bit `pos` (nine independent byte loads; bytes at
+// or beyond `limit` read as zero), the bits from `nbits` on cleared.
+__device__ __forceinline__ uint64_t load_mask_bits64(const uint8_t* seg, int64_t pos, int64_t limit, int nbits) {
+  const int64_t byte0 = pos >> 3;
+  const int sh = static_cast<int>(pos & 7);
+  uint64_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t bi = byte0 + i;
+    const uint64_t v = (bi < limit) ? seg[bi] : 0u;
+    lo |= v << (8 * i);
+  }
+  if (byte0 + 8 < limit) hi = seg[byte0 + 8];
+  uint64_t r = sh ? ((lo >> sh) | (hi << (64 - sh))) : lo;
+  if (nbits < 64) r &= (1ull << nbits) - 1ull;
+  return r;
+}
+
 // kD: head dimension, 128 or 64. With 64 a tile is one 64-column half: the second TMA box, the upper four of the
 // eight Q K^T MMAs and the upper 64 columns of O are left out; everything else is the same code.
-// kCausal: a kv position is visible to a q token only up to token + kv_len - q_len (the reference's
-// MaskMode::kCausal, prefill.cuh:746-751); the softmax warps then also read the kv-block indices.
-template <bool kBf16, bool kSoftCap, bool kParts, int kD, bool kCausal>
+// kMask 1 (causal): a kv position is visible to a q token only up to token + kv_len - q_len (the reference's
+// MaskMode::kCausal, prefill.cuh:746-751). kMask 2 (custom): position (i, j) of a request is visible iff bit
+// i * kv_len + j of the request's packed mask is set (MaskMode::kCustom, variants.cuh:76-87). In both the softmax
+// warps also read the kv-block indices.
+template <bool kBf16, bool kSoftCap, bool kParts, int kD, int kMask>
 __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
   static_assert(kD == 128 || kD == 64, "head dimension");
   constexpr int kLoadBytes = 128 * kD * 2;   // bytes of one tile load
@@ -547,7 +568,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       }
     };
 
-    GroupSeq<kCausal> seq;
+    GroupSeq<kMask != 0> seq;
     seq.init(tail, abort_flag);
     uint32_t g = 0;          // global block index (both parities)
     uint32_t my_blocks = 0;  // blocks this group has processed
@@ -555,6 +576,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     float m_ref = -INFINITY; // the maximum this thread's partial sum refers to
     uint64_t l2a = 0, l2b = 0;  // partial row sum over this thread's columns of the group's blocks
     // an item whose statistics have been published and whose O is still being accumulated
+    int cm_kv_len = 0, cm_base = 0;   // custom mask: the request's kv length, byte offset of its matrix,
+    int64_t cm_row_bit = 0;           // and the bit offset of this thread's row inside it
     bool pend = false;
     uint32_t pend_item = 0;
     int pend_q_row0 = 0, pend_q_valid = 0, pend_h = 0, pend_parts = 1;
@@ -704,6 +727,12 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 
     while (ok && seq.next(a, on_empty)) {
       if (seq.first()) {
+        if constexpr (kMask == 2) {  // both groups: the row's bit offset inside the request's matrix
+          const int q0 = a.qo_indptr[seq.req];
+          cm_kv_len = a.kv_indptr[seq.req + 1] - a.kv_indptr[seq.req];
+          cm_base = a.mask_indptr[seq.req];
+          cm_row_bit = static_cast<int64_t>(seq.q_row0 - q0 + row / grp) * cm_kv_len;
+        }
         m_ref = -INFINITY;
         l2a = 0;
         l2b = 0;
@@ -714,11 +743,18 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (!mbar_wait(&tail->s_full[X], my_blocks & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         int valid = seq.valid() - static_cast<int>(64u * ch);  // of my columns, how many exist
-        if constexpr (kCausal) {
+        if constexpr (kMask == 1) {
           // ... and how many this row's token may attend to: kv positions up to causal_base + token
           const int lim = seq.causal_base + row / grp - seq.kvb * kBKV + 1;
           const int vc = (lim > kBKV ? kBKV : lim) - static_cast<int>(64u * ch);
           valid = valid < vc ? valid : vc;
+        }
+        uint64_t mbits = ~0ull;  // custom mask: one bit per column of this thread's half row
+        if constexpr (kMask == 2) {
+          const int col0 = seq.kvb * kBKV + static_cast<int>(64u * ch);
+          int nb = cm_kv_len - col0;
+          nb = nb > 64 ? 64 : nb;
+          mbits = nb > 0 ? load_mask_bits64(a.custom_mask + cm_base, cm_row_bit + col0, a.custom_mask_bytes - cm_base, nb) : 0ull;
         }
         float mx;
         {
@@ -732,6 +768,12 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 #pragma unroll
               for (int t = 0; t < 32; ++t)
                 if (32 * c + t >= valid) s[t] = 0xff800000u;  // -inf
+            }
+            if constexpr (kMask == 2) {
+              const uint32_t mb = static_cast<uint32_t>(mbits >> (32 * c));
+#pragma unroll
+              for (int t = 0; t < 32; ++t)
+                if (!((mb >> t) & 1u)) s[t] = 0xff800000u;
             }
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
@@ -812,6 +854,11 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           for (int t = 0; t < 64; ++t)
             if (t >= valid) s[t] = 0xff800000u;  // -inf: exp2 gives 0
         }
+        if constexpr (kMask == 2) {
+#pragma unroll
+          for (int t = 0; t < 64; ++t)
+            if (!((mbits >> t) & 1ull)) s[t] = 0xff800000u;
+        }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
@@ -888,20 +935,23 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
 
 
 namespace {
-template <bool kBf16, bool kSoftCap, bool kParts, int kD, bool kCausal = false>
+template <bool kBf16, bool kSoftCap, bool kParts, int kD, int kMask = 0>
 cudaError_t launch_one(const AttnArgs& a, int ctas, cudaStream_t stream) {
-  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap, kParts, kD, kCausal>,
+  const cudaError_t e = cudaFuncSetAttribute(attention_kernel<kBf16, kSoftCap, kParts, kD, kMask>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
-  attention_kernel<kBf16, kSoftCap, kParts, kD, kCausal><<<ctas, kThreads, kSmemBytes, stream>>>(a);
+  attention_kernel<kBf16, kSoftCap, kParts, kD, kMask><<<ctas, kThreads, kSmemBytes, stream>>>(a);
   return cudaGetLastError();
 }
 template <bool kBf16, bool kSoftCap>
 cudaError_t launch_two(const AttnArgs& a, int ctas, cudaStream_t stream) {
-  if (a.causal) {  // whole items only (the caller gives no room for partial results)
+  if (a.mask_mode != 0) {  // whole items only (the caller gives no room for partial results)
     if (a.partial_slots > 0) return cudaErrorInvalidValue;
-    return a.head_dim == 64 ? launch_one<kBf16, kSoftCap, false, 64, true>(a, ctas, stream)
-                            : launch_one<kBf16, kSoftCap, false, 128, true>(a, ctas, stream);
+    if (a.mask_mode == 1)
+      return a.head_dim == 64 ? launch_one<kBf16, kSoftCap, false, 64, 1>(a, ctas, stream)
+                              : launch_one<kBf16, kSoftCap, false, 128, 1>(a, ctas, stream);
+    return a.head_dim == 64 ? launch_one<kBf16, kSoftCap, false, 64, 2>(a, ctas, stream)
+                            : launch_one<kBf16, kSoftCap, false, 128, 2>(a, ctas, stream);
   }
   // room for partial results means that the unit builder may have cut lists: the instantiation with the merge
   if (a.head_dim == 64)

@@ -176,7 +176,12 @@ struct AttnArgs {
   float* partials;                 // partial results of split items: partial_slots x kPartialFloats floats
   int partial_slots;
   int head_dim;                    // 128 or 64
-  int causal;                      // kv position <= q token + kv_len - q_len only
+  int mask_mode;                   // 0: none; 1: causal (kv position <= q token + kv_len - q_len); 2: custom bit mask
+  const uint8_t* custom_mask;      // mode 2: per request a [q_len, kv_len] bit matrix, row-major, little-endian bits
+  int64_t custom_mask_bytes;
+  const int32_t* mask_indptr;      // mode 2: byte offset of each request's matrix [batch + 1]
+  const int32_t* qo_indptr;        // mode 2: request rows and lengths
+  const int32_t* kv_indptr;
   int head_begin;                  // tensor head = item head - head_begin
   int group_size;                  // H / Hkv
   int is_bf16;

@@ -685,7 +685,7 @@ cudaError_t launch_attn_compact(const CompactArgs& a, cudaStream_t stream) {
 // attention kernel's roles need (no chain of dependent loads at a unit boundary):
 //   [0] n          kv blocks of the unit (0: an active q-block that keeps nothing)
 //   [1] kv_off     offset of the unit's first entry in kv_idx
-//   [2] h          mask head
+//   [2] h | b << 16   mask head (< 65536), request (< 32768)
 //   [3] q_row0     first row of the q-block in the q / o tensors
 //   [4] q_valid | ragged << 16   rows (tokens) of the q-block that exist (1..sbq); columns of the request's partial
 //                  last kv block if the unit's list ends with it, else 0
@@ -769,7 +769,7 @@ __global__ void __launch_bounds__(1024) attn_units_kernel(UnitArgs a) {
         if (off_u + p < a.max_units) {
           int4* dst = reinterpret_cast<int4*>(a.units + 8 * static_cast<int64_t>(off_u + p));
           const int sp_word = np > 1 ? (((off_p + p) & 0xffff) << 16) | (p << 8) | np : (0xffff << 16) | 1;
-          dst[0] = make_int4(j1 - j0, kvp + j0, rec.y, q0 + rec.z * a.sbq);
+          dst[0] = make_int4(j1 - j0, kvp + j0, rec.y | (rec.x << 16), q0 + rec.z * a.sbq);
           dst[1] = make_int4(q_valid | ((p == np - 1 ? ragged : 0) << 16), k0, rec.z * a.sbq + kv_len - q_len, sp_word);
         }
       }
@@ -849,7 +849,7 @@ __global__ void __launch_bounds__(256) attn_units_whole_kernel(UnitArgs a) {
     const int tail_cols = kv_len % a.sbkv;
     if (tail_cols != 0 && n > 0 && a.kv_idx[kvp + n - 1] == kv_len / a.sbkv) ragged = tail_cols;
     int4* dst = reinterpret_cast<int4*>(a.units + 8 * pos);
-    dst[0] = make_int4(n, kvp, rec.y, q0 + rec.z * a.sbq);
+    dst[0] = make_int4(n, kvp, rec.y | (rec.x << 16), q0 + rec.z * a.sbq);
     dst[1] = make_int4(q_valid | (ragged << 16), k0, rec.z * a.sbq + kv_len - q_len, (0xffff << 16) | 1);
   }
 }

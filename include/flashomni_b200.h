@@ -105,7 +105,7 @@ FO_API int fo_mask_compact(const uint8_t* sparse_info, int64_t sparse_info_bytes
  * self-contained record of eight int32 per unit,
  *   [0] n         kv blocks of the unit (0: an active q-block that keeps nothing)
  *   [1] kv_off    offset of the unit's first entry in kv_idx
- *   [2] h         mask head
+ *   [2] h | b << 16   mask head (< 65536) and request (< 32768)
  *   [3] q_row0    first row of the q-block in the q / o tensors
  *   [4] q_valid | ragged << 16   rows of the q-block that exist (1..sbq); columns of the request's partial last kv
  *                 block if the unit's list ends with it, else 0
@@ -189,6 +189,22 @@ FO_API int fo_sparse_attn_fwd_causal(const void* q, const void* k, const void* v
                        int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
                        const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t head_begin,
                        float sm_scale, float logits_soft_cap, int32_t* status, void* stream);
+
+/* The same under a custom mask (the reference's MaskMode::kCustom with packed_custom_mask / mask_indptr,
+ * flashomni/attention.py:524-533, include/flashomni/attention/variants.cuh:76-87): inside the kept kv-blocks,
+ * position (i, j) of request b is visible iff bit i * kv_len_b + j of the request's matrix is set. custom_mask holds
+ * the matrices bit-packed (little-endian bits, as segment_packbits packs them), request b's starting at byte
+ * mask_indptr[b]; the same matrix serves all heads. qo_indptr / kv_indptr are the request indptrs of the plan. A row
+ * without any visible position gets zeros and lse = -5e4. Whole items only. logits_soft_cap = 0: no cap. */
+FO_API int fo_sparse_attn_fwd_custom_mask(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
+                       int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
+                       int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h, int64_t o_stride_n,
+                       int64_t o_stride_h, int32_t sbq, int32_t sbkv, const int32_t* kv_idx,
+                       const int32_t* units, const int32_t* unit_counters, int64_t max_units, int32_t head_begin,
+                       float sm_scale, float logits_soft_cap, const uint8_t* custom_mask, int64_t custom_mask_bytes,
+                       const int32_t* mask_indptr, const int32_t* qo_indptr, const int32_t* kv_indptr,
+                       int32_t* status, void* stream);
 
 /* ---- GEMM-Q / GEMM-O ---------------------------------------------------------------------------
  * Workspace (device, caller-owned, 16-byte aligned) of fo_gemm_workspace_bytes(...) bytes, laid out

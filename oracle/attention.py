@@ -31,14 +31,15 @@ def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info=None, sparse_kv_
                      info_indptr=None, kv_info_indptr=None, sbq: int = 128, sbkv: int = 128,
                      is_full: bool = False, sm_scale: float | None = None, out_prior=None,
                      lse_prior=None, return_lse: bool = False, head_begin: int = 0, num_mask_heads=None,
-                     dtype=torch.float32, logits_soft_cap: float = 0.0, causal: bool = False):
+                     dtype=torch.float32, logits_soft_cap: float = 0.0, causal: bool = False, custom_mask=None):
     """q [Tq, H, D], k/v [Tkv, Hkv, D] (any float dtype, computed in `dtype`). Returns fp32 `out`
     (and base-2 `lse`). With `logits_soft_cap` > 0 the logits are cap * tanh(q.k * sm_scale / cap)
     (include/flashomni/attention/variants.cuh:47-50,72-74). `out_prior` supplies the rows of skipped q-blocks (zeros if None, as
     flashomni/attention.py:778-781 allocates). With `causal`, kv position j of a request is visible to q token i only if
     j <= i + kv_len - q_len (prefill.cuh:746-751); a row without any visible kept position gives zeros and lse = -5e4
     (the reference fills masked logits with -5e4, not -inf, and would average V there: a degenerate case that the
-    golden cases avoid). kv head `hk` reads mask head `head_begin + hk` (of `num_mask_heads`)."""
+    golden cases avoid). `custom_mask`: per request a boolean [q_len, kv_len] array; position (i, j) is visible iff it
+    is set (MaskMode::kCustom, variants.cuh:76-87); it takes the place of `causal`. kv head `hk` reads mask head `head_begin + hk` (of `num_mask_heads`)."""
     Tq, H, D = q.shape
     Hkv = k.shape[1]
     group = H // Hkv
@@ -91,7 +92,10 @@ def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info=None, sparse_kv_
                     s = (qf[r0:r1, h] @ kf[cols_t, hk].T) * sm_scale
                     if logits_soft_cap > 0:
                         s = torch.tanh(s / logits_soft_cap) * logits_soft_cap
-                    if causal:
+                    if custom_mask is not None:
+                        cm = torch.from_numpy(np.asarray(custom_mask[b], dtype=bool)[r0 - q0:r1 - q0][:, cols - k0])
+                        s = s.masked_fill(~cm, float("-inf"))
+                    elif causal:
                         qi = torch.arange(r0 - q0, r1 - q0).view(-1, 1)
                         kj = torch.from_numpy(cols - k0).view(1, -1)
                         s = s.masked_fill(kj > qi + ((k1 - k0) - (q1 - q0)), float("-inf"))

@@ -167,7 +167,7 @@ def attn_units(lists: dict, qo_indptr, kv_indptr, num_streams: int, min_chunk: i
     """Canonical work units of the attention kernel, from the outputs of `compact` (`lists`): the items in
     processing order, one self-contained record of eight int32 per unit:
       [0] n kv blocks of the unit (0: an active q-block that keeps nothing)   [1] offset of its first entry in kv_idx
-      [2] mask head   [3] first row of the q-block in q / o
+      [2] mask head | request << 16   [3] first row of the q-block in q / o
       [4] existing rows of the q-block (1..sbq) | columns of the request's partial last kv block if the unit ends with it << 16
       [5] first kv row of the request   [6] qb * sbq + kv_len - q_len (last kv position the block's first token sees under a causal mask)
       [7] slot << 16 | part << 8 | n_parts   (a whole item: n_parts = 1, slot = 0xffff)
@@ -204,7 +204,7 @@ def attn_units(lists: dict, qo_indptr, kv_indptr, num_streams: int, min_chunk: i
             j0, j1 = n * p // n_parts, n * (p + 1) // n_parts
             word = (((slots + p) & 0xffff) << 16) | (p << 8) | n_parts if n_parts > 1 else (0xffff << 16) | 1
             word = word - (1 << 32) if word >= (1 << 31) else word
-            units.append((j1 - j0, int(kvp[it]) + j0, h, q0 + qb * sbq, q_valid | ((ragged if p == n_parts - 1 else 0) << 16), k0,
+            units.append((j1 - j0, int(kvp[it]) + j0, h | (b << 16), q0 + qb * sbq, q_valid | ((ragged if p == n_parts - 1 else 0) << 16), k0,
                           qb * sbq + kv_len - q_len, word))
         if n_parts > 1:
             slots += n_parts

@@ -27,7 +27,7 @@ def load():
     global _lib
     if _lib is None:
         _lib = ctypes.CDLL(LIB_PATH)
-        for n in ("ref_sparse_attn", "ref_sparse_attn_hd64", "ref_sparse_attn_causal", "ref_gemm_q", "ref_gemm_o", "ref_segment_packbits"):
+        for n in ("ref_sparse_attn", "ref_sparse_attn_hd64", "ref_sparse_attn_causal", "ref_sparse_attn_custom", "ref_gemm_q", "ref_gemm_o", "ref_segment_packbits"):
             getattr(_lib, n).restype = ctypes.c_int
     return _lib
 
@@ -58,7 +58,8 @@ def plan_unsplit(qo_indptr, kv_indptr, device, group=1):
 
 
 def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr,
-                     out, is_full=False, sm_scale=None, lse=None, plan=None, causal=False):
+                     out, is_full=False, sm_scale=None, lse=None, plan=None, causal=False, packed_custom_mask=None,
+                     mask_indptr=None):
     """q [Tq, H, D], k/v [Tkv, Hkv, D] (NHD, D = 128 or 64), `out` is written in place (only active q-blocks)."""
     dev = q.device
     if plan is None:
@@ -71,8 +72,14 @@ def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info, sparse_kv_info,
     if causal and q.shape[-1] != 128:
         raise ValueError("the harness instantiates the causal mask mode for head dimension 128 only")
     fn = load().ref_sparse_attn_causal if causal else (load().ref_sparse_attn if q.shape[-1] == 128 else load().ref_sparse_attn_hd64)
+    lead = ()
+    if packed_custom_mask is not None:   # byte indptr of the per-request matrices, as segment_packbits returns it
+        if q.shape[-1] != 128:
+            raise ValueError("the harness instantiates the custom mask mode for head dimension 128 only")
+        fn = load().ref_sparse_attn_custom
+        lead = (_p(packed_custom_mask), _p(mask_indptr))
     rc = fn(
-        _p(q), _p(k), _p(v), _p(out), _p(lse), _p(sparse_info), _p(sparse_kv_info), _p(info_indptr), _p(kv_info_indptr),
+        *lead, _p(q), _p(k), _p(v), _p(out), _p(lse), _p(sparse_info), _p(sparse_kv_info), _p(info_indptr), _p(kv_info_indptr),
         _p(qo_indptr), _p(kv_indptr), _p(plan["request"]), _p(plan["qo_tile"]), _p(plan["kv_tile"]), _p(plan["o_indptr"]),
         _p(plan["chunk"]), u(plan["n"]), u(q.shape[1]), u(k.shape[1]), u(q.stride(0)), u(q.stride(1)), u(k.stride(0)),
         u(k.stride(1)), u(v.stride(0)), u(v.stride(1)), ctypes.c_float(sm_scale), ctypes.c_int(1 if is_full else 0),

@@ -25,7 +25,7 @@
 using namespace flashomni;
 
 template <typename T, int HD, MaskMode MM = MaskMode::kNone>
-static int run_attn(void* q, void* k, void* v, void* o, float* lse, uint8_t* sparse_info, uint8_t* sparse_kv_info,
+static int run_attn(uint8_t* custom_mask, int32_t* mask_indptr, void* q, void* k, void* v, void* o, float* lse, uint8_t* sparse_info, uint8_t* sparse_kv_info,
                     int32_t* info_indptr, int32_t* kv_info_indptr, int32_t* q_indptr, int32_t* kv_indptr,
                     int32_t* request_indices, int32_t* qo_tile_indices, int32_t* kv_tile_indices, int32_t* o_indptr,
                     int32_t* kv_chunk_size_ptr, uint32_t padded_batch, uint32_t num_qo_heads, uint32_t num_kv_heads,
@@ -33,13 +33,15 @@ static int run_attn(void* q, void* k, void* v, void* o, float* lse, uint8_t* spa
                     uint32_t v_stride_n, uint32_t v_stride_h, float sm_scale, int is_full, uint32_t max_rows,
                     cudaStream_t stream) {
   using Params = BatchRaggedSparseFAParams<T, T, T, int32_t>;
-  using Variant = DefaultAttention</*use_custom_mask=*/false, /*use_logits_soft_cap=*/false, /*use_alibi=*/false>;
+  using Variant = DefaultAttention</*use_custom_mask=*/MM == MaskMode::kCustom, /*use_logits_soft_cap=*/false, /*use_alibi=*/false>;
   Params p;
   p.q = static_cast<T*>(q);
   p.k = static_cast<T*>(k);
   p.v = static_cast<T*>(v);
   p.o = static_cast<T*>(o);
   p.lse = lse;
+  p.maybe_custom_mask = custom_mask;
+  p.maybe_mask_indptr = mask_indptr;
   p.sparse_info = sparse_info;
   p.sparse_kv_info = sparse_kv_info;
   p.sparse_info_indptr = info_indptr;
@@ -89,11 +91,11 @@ __attribute__((visibility("default"))) int ref_sparse_attn(
     uint32_t max_rows, int is_bf16, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_bf16)
-    return run_attn<nv_bfloat16, 128>(q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr,
+    return run_attn<nv_bfloat16, 128>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr,
                                  kv_indptr, request_indices, qo_tile_indices, kv_tile_indices, o_indptr,
                                  kv_chunk_size_ptr, padded_batch, num_qo_heads, num_kv_heads, q_stride_n, q_stride_h,
                                  k_stride_n, k_stride_h, v_stride_n, v_stride_h, sm_scale, is_full, max_rows, st);
-  return run_attn<half, 128>(q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
+  return run_attn<half, 128>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
                         request_indices, qo_tile_indices, kv_tile_indices, o_indptr, kv_chunk_size_ptr, padded_batch,
                         num_qo_heads, num_kv_heads, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n,
                         v_stride_h, sm_scale, is_full, max_rows, st);
@@ -109,11 +111,11 @@ __attribute__((visibility("default"))) int ref_sparse_attn_hd64(
     uint32_t max_rows, int is_bf16, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_bf16)
-    return run_attn<nv_bfloat16, 64>(q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr,
+    return run_attn<nv_bfloat16, 64>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr,
                                  kv_indptr, request_indices, qo_tile_indices, kv_tile_indices, o_indptr,
                                  kv_chunk_size_ptr, padded_batch, num_qo_heads, num_kv_heads, q_stride_n, q_stride_h,
                                  k_stride_n, k_stride_h, v_stride_n, v_stride_h, sm_scale, is_full, max_rows, st);
-  return run_attn<half, 64>(q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
+  return run_attn<half, 64>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
                         request_indices, qo_tile_indices, kv_tile_indices, o_indptr, kv_chunk_size_ptr, padded_batch,
                         num_qo_heads, num_kv_heads, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n,
                         v_stride_h, sm_scale, is_full, max_rows, st);
@@ -129,11 +131,31 @@ __attribute__((visibility("default"))) int ref_sparse_attn_causal(
     uint32_t max_rows, int is_bf16, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_bf16)
-    return run_attn<nv_bfloat16, 128, MaskMode::kCausal>(q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr,
+    return run_attn<nv_bfloat16, 128, MaskMode::kCausal>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr,
                                  kv_indptr, request_indices, qo_tile_indices, kv_tile_indices, o_indptr,
                                  kv_chunk_size_ptr, padded_batch, num_qo_heads, num_kv_heads, q_stride_n, q_stride_h,
                                  k_stride_n, k_stride_h, v_stride_n, v_stride_h, sm_scale, is_full, max_rows, st);
-  return run_attn<half, 128, MaskMode::kCausal>(q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
+  return run_attn<half, 128, MaskMode::kCausal>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
+                        request_indices, qo_tile_indices, kv_tile_indices, o_indptr, kv_chunk_size_ptr, padded_batch,
+                        num_qo_heads, num_kv_heads, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n,
+                        v_stride_h, sm_scale, is_full, max_rows, st);
+}
+
+// Head dimension 128 under the reference's custom mask mode (MaskMode::kCustom, variants.cuh:76-87).
+__attribute__((visibility("default"))) int ref_sparse_attn_custom(
+    uint8_t* custom_mask, int32_t* mask_indptr, void* q, void* k, void* v, void* o, float* lse, uint8_t* sparse_info, uint8_t* sparse_kv_info,
+    int32_t* info_indptr, int32_t* kv_info_indptr, int32_t* q_indptr, int32_t* kv_indptr, int32_t* request_indices,
+    int32_t* qo_tile_indices, int32_t* kv_tile_indices, int32_t* o_indptr, int32_t* kv_chunk_size_ptr,
+    uint32_t padded_batch, uint32_t num_qo_heads, uint32_t num_kv_heads, uint32_t q_stride_n, uint32_t q_stride_h,
+    uint32_t k_stride_n, uint32_t k_stride_h, uint32_t v_stride_n, uint32_t v_stride_h, float sm_scale, int is_full,
+    uint32_t max_rows, int is_bf16, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    return run_attn<nv_bfloat16, 128, MaskMode::kCustom>(custom_mask, mask_indptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr,
+                                 kv_indptr, request_indices, qo_tile_indices, kv_tile_indices, o_indptr,
+                                 kv_chunk_size_ptr, padded_batch, num_qo_heads, num_kv_heads, q_stride_n, q_stride_h,
+                                 k_stride_n, k_stride_h, v_stride_n, v_stride_h, sm_scale, is_full, max_rows, st);
+  return run_attn<half, 128, MaskMode::kCustom>(custom_mask, mask_indptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
                         request_indices, qo_tile_indices, kv_tile_indices, o_indptr, kv_chunk_size_ptr, padded_batch,
                         num_qo_heads, num_kv_heads, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n,
                         v_stride_h, sm_scale, is_full, max_rows, st);

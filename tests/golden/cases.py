@@ -27,8 +27,13 @@ def attention_case(name):
         H, lens_q, lens_kv, density, seed, causal = 3, [300, 205], [428, 333], 0.7, 107, True
     elif name == "attn_causal_gqa":
         H, lens_q, lens_kv, density, seed, group, causal = 4, [130, 256], [384, 300], 0.6, 108, 2, True
+    elif name == "attn_custom_mask":     # a random element mask inside the kept blocks (column 0 always visible)
+        H, lens_q, lens_kv, density, seed = 3, [300, 205], [428, 333], 0.7, 109
+    elif name == "attn_custom_mask_gqa":
+        H, lens_q, lens_kv, density, seed, group = 4, [130, 256], [384, 300], 0.6, 110, 2
     else:
         raise KeyError(name)
+    custom = name.startswith("attn_custom_mask")
     Hkv = H // group
     qtok = 128 // group           # tokens per mask q-block (128 packed rows)
     qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
@@ -43,19 +48,30 @@ def attention_case(name):
         # the reference writes garbage-free output only if an active q-block keeps something; keep >= 1
         for qb in range(a.shape[0]):
             for h in range(Hkv):
-                if a[qb, h] and (b[qb, h].sum() == 0 or causal):
+                if a[qb, h] and (b[qb, h].sum() == 0 or causal or custom):
                     b[qb, h, 0] = 1     # causal: kv position 0 is visible to every token (kv_len >= q_len)
     m = wl.pack_masks(qa, kk)
     q = wl.randn_bf16((int(qo[-1]), H, D), seed + 1)
     k = wl.randn_bf16((int(kv[-1]), Hkv, D), seed + 2)
     v = wl.randn_bf16((int(kv[-1]), Hkv, D), seed + 3)
     prior = wl.randn_bf16((int(qo[-1]), H, D), seed + 4)
+    custom_mask = None
+    if custom:   # per request [q_len, kv_len] flags; kv position 0 stays visible so that no row is fully masked
+        crng = np.random.default_rng(seed + 50)
+        custom_mask = [crng.random((a, b)) < 0.6 for a, b in zip(lens_q, lens_kv)]
+        for cm in custom_mask:
+            cm[:, 0] = True
     return {"q": q, "k": k, "v": v, "qo": qo, "kv": kv, "masks": m, "prior": prior, "H": H, "Hkv": Hkv, "group": group,
-            "q_block_tokens": qtok, "D": D, "causal": causal}
+            "q_block_tokens": qtok, "D": D, "causal": causal, "custom_mask": custom_mask}
+
+
+def flat_custom_mask(case):
+    """The case's custom mask as the reference's plan() takes it: all matrices flattened and concatenated (bool)."""
+    return torch.from_numpy(np.concatenate([cm.reshape(-1) for cm in case["custom_mask"]]))
 
 
 ATTENTION_CASES = ("attn_uniform", "attn_ragged", "attn_gqa", "attn_gqa4", "attn_hd64", "attn_hd64_gqa", "attn_causal",
-                   "attn_causal_gqa")
+                   "attn_causal_gqa", "attn_custom_mask", "attn_custom_mask_gqa")
 
 
 def gemm_case(name):

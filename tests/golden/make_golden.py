@@ -30,8 +30,16 @@ def main(out_path):
         m = c["masks"]
         out = d(c["prior"]).clone()
         lse = torch.zeros(out.shape[0], c["H"], dtype=torch.float32, device=dev)
+        extra = {}
+        if c["custom_mask"] is not None:   # packed as the reference's plan() packs it (its segment_packbits kernel)
+            elems = np.asarray([cm.size for cm in c["custom_mask"]], dtype=np.int64)
+            ind = np.concatenate([[0], np.cumsum(elems)]).astype(np.int32)
+            new_ind = np.concatenate([[0], np.cumsum((elems + 7) // 8)]).astype(np.int32)
+            packed = ref_cuda.segment_packbits(d(cases.flat_custom_mask(c).to(torch.uint8)), d(ind), d(new_ind), True)
+            extra = {"packed_custom_mask": packed, "mask_indptr": d(new_ind)}
         ref_cuda.sparse_attention(d(c["q"]), d(c["k"]), d(c["v"]), d(c["qo"]), d(c["kv"]), d(m.sparse_info),
-                                  d(m.sparse_kv_info), d(m.info_indptr), d(m.kv_info_indptr), out, lse=lse, causal=c["causal"])
+                                  d(m.sparse_kv_info), d(m.info_indptr), d(m.kv_info_indptr), out, lse=lse, causal=c["causal"],
+                                  **extra)
         torch.cuda.synchronize()
         res[name + "_out"] = cases.bf16_bits(out)
         res[name + "_lse"] = lse.cpu().numpy()

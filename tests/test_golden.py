@@ -31,7 +31,7 @@ def test_attention_oracle_vs_reference_kernel():
         m = c["masks"]
         out, lse = oa.sparse_attention(c["q"], c["k"], c["v"], c["qo"], c["kv"], m.sparse_info, m.sparse_kv_info,
                                        m.info_indptr, m.kv_info_indptr, out_prior=c["prior"], return_lse=True,
-                                       causal=c["causal"])
+                                       causal=c["causal"], custom_mask=c["custom_mask"])
         gold = cases.from_bits(GOLD[name + "_out"])
         # the reference output is itself bf16-rounded: same tolerance as for our kernels
         assert_close_bf16(gold, out, name)

@@ -461,6 +461,61 @@ def test_causal_mask(cuda_device, H, Hkv, D, dtype, soft_cap):
     assert (full - ref).abs().max() > 0.1
 
 
+@pytest.mark.parametrize("H,Hkv,D,dtype,packed", [(3, 3, 128, torch.bfloat16, False), (4, 2, 128, torch.float16, True),
+                                                  (2, 2, 64, torch.bfloat16, False)])
+def test_custom_mask(cuda_device, H, Hkv, D, dtype, packed):
+    """plan(custom_mask=...) / plan(packed_custom_mask=...): inside the kept blocks position (i, j) of a request is
+    visible iff its flag is set (the reference's MaskMode::kCustom). Random flags with whole rows and whole blocks
+    switched off (rows that see nothing: zeros, lse -5e4), kv lengths that are no multiple of 8 (rows of the bit
+    matrix start at odd bit offsets), ragged tails, grouped heads, head_dim 64."""
+    g = H // Hkv
+    qt = 128 // g
+    lens_q, lens_kv = [300, 205, 77], [427, 205, 333]
+    qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
+    kv = np.concatenate([[0], np.cumsum(lens_kv)]).astype(np.int32)
+    rng = np.random.default_rng(90 + H + D)
+    qa = [(rng.random((-(-a // qt), Hkv)) < 0.8).astype(np.uint8) for a in lens_q]
+    kk = [(rng.random((-(-a // qt), Hkv, -(-b // 128))) < 0.7).astype(np.uint8) for a, b in zip(lens_q, lens_kv)]
+    m = wl.pack_masks(qa, kk)
+    cms = [rng.random((a, b)) < 0.5 for a, b in zip(lens_q, lens_kv)]
+    cms[0][5:9, :] = False                 # rows that see nothing
+    cms[0][:, 128:256] = False             # a whole kv block hidden
+    cms[1][:, :] = True                    # a request without restriction
+    flat = torch.from_numpy(np.concatenate([c.reshape(-1) for c in cms]))
+    q = wl.randn_bf16((int(qo[-1]), H, D), 91, dtype=dtype)
+    k = wl.randn_bf16((int(kv[-1]), Hkv, D), 92, dtype=dtype)
+    v = wl.randn_bf16((int(kv[-1]), Hkv, D), 93, dtype=dtype)
+    prior = wl.randn_bf16((int(qo[-1]), H, D), 94, dtype=dtype)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
+    if packed:   # packed by the caller, every request's matrix on its own byte boundary
+        elems = np.asarray([c.size for c in cms], dtype=np.int64)
+        ind = torch.from_numpy(np.concatenate([[0], np.cumsum(elems)]).astype(np.int32)).to(cuda_device)
+        pm, _ = fo.segment_packbits(flat.to(cuda_device), ind, bitorder="little")
+        w.plan(dev(qo, cuda_device), dev(kv, cuda_device), H, Hkv, D, packed_custom_mask=pm, q_data_type=dtype)
+    else:
+        w.plan(dev(qo, cuda_device), dev(kv, cuda_device), H, Hkv, D, custom_mask=flat.to(cuda_device), q_data_type=dtype)
+    si, skv, ip, kp = masks_to_device(m, cuda_device)
+    for _ in range(2):
+        o, lse = w.run(dev(q, cuda_device), dev(k, cuda_device), dev(v, cuda_device), si, skv, ip, kp,
+                       out=dev(prior, cuda_device).clone(), return_lse=True)
+    w.check_status()
+    ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
+                                       out_prior=prior, return_lse=True, custom_mask=cms)
+    assert_close_bf16(o.cpu(), ref, f"custom mask H={H}/{Hkv} D={D} {dtype}")
+    act = torch.zeros(int(qo[-1]), H, dtype=torch.bool)
+    for b in range(len(lens_q)):
+        for qb in range(qa[b].shape[0]):
+            r0 = int(qo[b]) + qb * qt
+            r1 = min(r0 + qt, int(qo[b + 1]))
+            for hk in range(Hkv):
+                if qa[b][qb, hk]:
+                    act[r0:r1, hk * g:(hk + 1) * g] = True
+                else:
+                    assert torch.equal(o[r0:r1, hk * g:(hk + 1) * g].cpu(), prior[r0:r1, hk * g:(hk + 1) * g])
+    assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-3)
+    assert (ref_lse[act] == -5e4).any()
+
+
 @pytest.mark.parametrize("seed", range(16))
 def test_random_configurations_against_the_oracle(cuda_device, seed):
     """Seeded random draws over everything the wrapper takes at once: heads and grouping, head dimension, dtype, kv

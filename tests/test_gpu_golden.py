@@ -32,7 +32,8 @@ def test_attention_vs_reference_kernel_output(cuda_device, name):
     m = c["masks"]
     w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
     w.plan(dev(c["qo"], cuda_device), dev(c["kv"], cuda_device), c["H"], c["Hkv"], c["D"], q_data_type=torch.bfloat16,
-           causal=c["causal"])
+           causal=c["causal"],
+           custom_mask=None if c["custom_mask"] is None else cases.flat_custom_mask(c).to(cuda_device))
     si, skv, ip, kp = masks_to_device(m, cuda_device)
     o, lse = w.run(dev(c["q"], cuda_device), dev(c["k"], cuda_device), dev(c["v"], cuda_device), si, skv, ip, kp,
                    out=dev(c["prior"], cuda_device).clone(), return_lse=True)
