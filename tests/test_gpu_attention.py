@@ -547,7 +547,12 @@ def test_random_configurations_against_the_oracle(cuda_device, seed):
     v = wl.randn_bf16((Tkv, Hkv, D), 4000 + seed, dtype=dtype)
     prior = wl.randn_bf16((Tq, H, D), 5000 + seed, dtype=dtype)
     w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device), layout)
-    w.plan(dev(qo, cuda_device), dev(kv, cuda_device), H, Hkv, D, causal=causal, q_data_type=dtype,
+    cms, flat = None, None
+    if seed % 4 == 3:   # every fourth draw: a custom element mask (it takes the place of `causal`)
+        cms = [rng.random((a, b)) < 0.6 for a, b in zip(lens_q, lens_kv)]
+        flat = torch.from_numpy(np.concatenate([c.reshape(-1) for c in cms] + [np.zeros(0, dtype=bool)])).to(cuda_device)
+        causal = False
+    w.plan(dev(qo, cuda_device), dev(kv, cuda_device), H, Hkv, D, causal=causal, q_data_type=dtype, custom_mask=flat,
            logits_soft_cap=soft_cap if soft_cap > 0 else None)
     si, skv, ip, kp = masks_to_device(m, cuda_device)
     kd, vd = dev(k, cuda_device), dev(v, cuda_device)
@@ -556,7 +561,8 @@ def test_random_configurations_against_the_oracle(cuda_device, seed):
     o, lse = w.run(dev(q, cuda_device), kd, vd, si, skv, ip, kp, out=dev(prior, cuda_device).clone(), return_lse=True)
     w.check_status()
     ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
-                                       out_prior=prior, return_lse=True, logits_soft_cap=soft_cap, causal=causal)
+                                       out_prior=prior, return_lse=True, logits_soft_cap=soft_cap, causal=causal,
+                                       custom_mask=cms)
     what = f"seed {seed}: H={H}/{Hkv} D={D} {dtype} causal={causal} cap={soft_cap} {layout} q={lens_q} kv={lens_kv}"
     assert_close_bf16(o.cpu(), ref, what)
     act = torch.zeros(Tq, H, dtype=torch.bool)
