@@ -43,6 +43,7 @@ SIGNATURES = {
     "fo_attn_units": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32,
                                 c_int32, c_int64, c_int64, _P, _P, _P, _P]),
     "fo_attn_partial_bytes": (c_size_t, [c_int64]),
+    "fo_cast_fp8": (c_int32, [_P, c_int64, c_int32, c_int32, _P, _P]),
     "fo_sparse_attn_fwd": (c_int32, [_P, _P, _P, _P, _P, c_int32,
                                      c_int64, c_int64, c_int32, c_int32, c_int32,
                                      c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,

@@ -42,6 +42,21 @@ def _compute_sparse_kv_info_indptr(qo_indptr: torch.Tensor, kv_indptr: torch.Ten
     return out
 
 
+_FP8_KINDS = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1}
+
+
+def _cast_fp8(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """An 8-bit float tensor as a new contiguous tensor of `dtype` (f16 / bf16), values unchanged."""
+    if not t.is_contiguous():
+        t = t.contiguous()
+    out = torch.empty(t.shape, dtype=dtype, device=t.device)
+    lib = _native.load()
+    with torch.cuda.device(t.device):
+        _native.check(lib.fo_cast_fp8(_native.ptr(t), t.numel(), _FP8_KINDS[t.dtype], native_dtype(dtype),
+                                      _native.ptr(out), _native.current_stream(t.device)), "fo_cast_fp8")
+    return out
+
+
 class BatchFlashOmniFAWithRaggedKVWrapper:
     r"""Prefill attention over ragged q/k/v with two bit-packed block masks: `sparse_info` selects the
     (q-block, head) pairs that are computed at all, `sparse_kv_info` the kv-blocks each of them attends
@@ -153,8 +168,10 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             raise NotImplementedError("flashomni_b200: in-kernel positional encoding is not implemented")
         if logits_soft_cap < 0:
             raise ValueError("logits_soft_cap must be >= 0 (0 disables it)")
-        if q_data_type != kv_data_type:
-            raise NotImplementedError("flashomni_b200: q and kv must share a dtype")
+        # 8-bit float K / V: the reference casts the fragments to the type of Q before the MMA, without scales
+        # (include/flashomni/attention/prefill.cuh:602-612); here run() casts the two tensors once (fo_cast_fp8)
+        if q_data_type != kv_data_type and kv_data_type not in _FP8_KINDS:
+            raise NotImplementedError("flashomni_b200: kv must have the dtype of q, float8_e4m3fn or float8_e5m2")
         native_dtype(q_data_type)
         if num_kv_heads <= 0 or num_qo_heads % num_kv_heads != 0:
             raise ValueError("num_qo_heads must be a multiple of num_kv_heads")
@@ -373,6 +390,10 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             raise RuntimeError("plan() must be called before run()")
         _native.require_cuda(q, k, v)
         _check_cached_qkv_data_type(q, k, self._cached_q_data_type, self._cached_kv_data_type)
+        if v.dtype != k.dtype:
+            raise ValueError(f"v has dtype {v.dtype}, k has {k.dtype}")
+        if k.dtype in _FP8_KINDS:
+            k, v = _cast_fp8(k, q.dtype), _cast_fp8(v, q.dtype)
         sm_scale = self._sm_scale
         if sm_scale is None:
             sm_scale = 1.0 / math.sqrt(q.size(-1))

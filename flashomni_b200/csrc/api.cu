@@ -439,6 +439,18 @@ int fo_sparse_attn_fwd_custom_mask(const void* q, const void* k, const void* v, 
                           stream);
 }
 
+int fo_cast_fp8(const void* src, int64_t n, int32_t fp8_kind, int32_t dtype, void* dst, void* stream) {
+  if (n < 0) return fail(FO_ERR_INVALID_ARG, "fo_cast_fp8: n < 0");
+  if (n == 0) return FO_OK;
+  if (src == nullptr || dst == nullptr || !aligned16(src) || !aligned16(dst))
+    return fail(FO_ERR_INVALID_ARG, "fo_cast_fp8: null or misaligned pointer (16 bytes)");
+  if ((fp8_kind != 0 && fp8_kind != 1) || (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16))
+    return fail(FO_ERR_INVALID_ARG, "fo_cast_fp8: fp8_kind must be 0 (e4m3) or 1 (e5m2), dtype f16 or bf16");
+  const cudaError_t e = launch_cast_fp8(src, n, fp8_kind, dtype == FO_DTYPE_BF16, dst, sm_count(), static_cast<cudaStream_t>(stream));
+  count_launches(1);
+  return e == cudaSuccess ? FO_OK : fail_cuda("fo_cast_fp8", e);
+}
+
 // ------------------------------------------------------------------------------------------ GEMMs
 int fo_gemm_dense_tile_rows(int32_t batch, int32_t m, int32_t n, int32_t k, int32_t has_full_init, int32_t sm_count) {
   if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;

@@ -5,6 +5,7 @@
 // Only loads cross the link; nothing here waits on another GPU (the callers order the steps with their
 // own barriers).
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "internal.h"
 
@@ -115,7 +116,58 @@ __global__ void __launch_bounds__(64) peer_barrier_kernel(const __grid_constant_
   __threadfence_system();
 }
 
+// 8-bit floating point (e4m3 or e5m2) to the 16-bit type the attention computes in: what the reference does to its
+// fp8 K / V fragments before the MMA (a plain cast, no scales; include/flashomni/attention/prefill.cuh:602-612),
+// done once per tensor here. Every fp8 value is exactly representable in f16 and in bf16.
+template <bool kE5m2, bool kBf16>
+__global__ void __launch_bounds__(256) cast_fp8_kernel(const uint8_t* __restrict__ src, int64_t n, uint16_t* __restrict__ dst) {
+  const int64_t nvec = n / 16;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 x = *reinterpret_cast<const uint4*>(src + i * 16);
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const __nv_fp8x2_storage_t p = static_cast<__nv_fp8x2_storage_t>((w[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(p, kE5m2 ? __NV_E5M2 : __NV_E4M3);
+      const __half2 h2 = *reinterpret_cast<const __half2*>(&hr);
+      o[j] = kBf16 ? pack_bf16x2(__low2float(h2), __high2float(h2)) : *reinterpret_cast<const uint32_t*>(&h2);
+    }
+    uint4* d = reinterpret_cast<uint4*>(dst + i * 16);
+    d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+  // tail of fewer than 16 values
+  if (blockIdx.x == 0) {
+    for (int64_t i = nvec * 16 + threadIdx.x; i < n; i += blockDim.x) {
+      const __half_raw hr = __nv_cvt_fp8_to_halfraw(src[i], kE5m2 ? __NV_E5M2 : __NV_E4M3);
+      const __half h = *reinterpret_cast<const __half*>(&hr);
+      if (kBf16) dst[i] = static_cast<uint16_t>(pack_bf16x2(__half2float(h), 0.f) & 0xffffu);
+      else dst[i] = *reinterpret_cast<const uint16_t*>(&h);
+    }
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_cast_fp8(const void* src, int64_t n, int e5m2, int is_bf16, void* dst, int sm_count, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  int64_t blocks = (n / 16 + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count) * 8;
+  blocks = blocks > cap ? cap : (blocks < 1 ? 1 : blocks);
+  const uint8_t* s = static_cast<const uint8_t*>(src);
+  uint16_t* d = static_cast<uint16_t*>(dst);
+  const unsigned g = static_cast<unsigned>(blocks);
+  if (e5m2) {
+    if (is_bf16) cast_fp8_kernel<true, true><<<g, 256, 0, stream>>>(s, n, d);
+    else cast_fp8_kernel<true, false><<<g, 256, 0, stream>>>(s, n, d);
+  } else {
+    if (is_bf16) cast_fp8_kernel<false, true><<<g, 256, 0, stream>>>(s, n, d);
+    else cast_fp8_kernel<false, false><<<g, 256, 0, stream>>>(s, n, d);
+  }
+  return cudaGetLastError();
+}
 
 cudaError_t launch_reduce_rows(const ReduceArgs& a, int is_bf16, int sm_count, cudaStream_t stream) {
   const int64_t total = a.rows * a.row_vecs;

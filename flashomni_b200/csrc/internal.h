@@ -73,6 +73,7 @@ struct UnitArgs {
   int32_t* arrive;           // [max_slots]
 };
 cudaError_t launch_attn_units(const UnitArgs& a, cudaStream_t stream);
+cudaError_t launch_cast_fp8(const void* src, int64_t n, int e5m2, int is_bf16, void* dst, int sm_count, cudaStream_t stream);
 cudaError_t launch_gemm_q_tiles(const GemmListArgs& a, cudaStream_t stream);
 cudaError_t launch_gemm_o_rows(const GemmListArgs& a, cudaStream_t stream);
 

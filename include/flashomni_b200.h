@@ -206,6 +206,12 @@ FO_API int fo_sparse_attn_fwd_custom_mask(const void* q, const void* k, const vo
                        const int32_t* mask_indptr, const int32_t* qo_indptr, const int32_t* kv_indptr,
                        int32_t* status, void* stream);
 
+/* K / V stored as 8-bit floats (the reference casts its fp8 K / V fragments to the type of Q before the MMA, no
+ * scales: include/flashomni/attention/prefill.cuh:602-612): n contiguous values of fp8_kind 0 (e4m3) or 1 (e5m2)
+ * are cast to dtype (exact: every fp8 value is representable in f16 and bf16) into dst; the attention then runs on
+ * the 16-bit copy. src and dst 16-byte aligned. */
+FO_API int fo_cast_fp8(const void* src, int64_t n, int32_t fp8_kind, int32_t dtype, void* dst, void* stream);
+
 /* ---- GEMM-Q / GEMM-O ---------------------------------------------------------------------------
  * Workspace (device, caller-owned, 16-byte aligned) of fo_gemm_workspace_bytes(...) bytes, laid out
  * as int32 words: [0..3] counters (count, aux, list status, two-block records), [4] kernel status (FO_DEV_*,

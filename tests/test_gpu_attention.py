@@ -577,6 +577,38 @@ def test_random_configurations_against_the_oracle(cuda_device, seed):
     assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-3), what
 
 
+@pytest.mark.parametrize("fp8", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("dtype,layout", [(torch.bfloat16, "NHD"), (torch.float16, "HND")])
+def test_fp8_kv_is_cast_to_the_type_of_q(cuda_device, fp8, dtype, layout):
+    """K / V stored as 8-bit floats: the cast is exact (every value of both formats, bit for bit against torch, with
+    a ragged tail), and the attention equals the oracle on the same values in fp32."""
+    codes = torch.arange(256, dtype=torch.uint8).repeat(3)[:256 * 3 - 5].to(cuda_device)
+    nan = codes.view(fp8).float().isnan()
+    got = fo.attention._cast_fp8(codes.view(fp8), dtype)
+    want = codes.view(fp8).to(dtype)
+    assert torch.equal(got[~nan].view(torch.int16), want[~nan].view(torch.int16))
+    assert bool(got[nan].isnan().all())
+
+    H, seq = 2, 512
+    inp = wl.attention_inputs(1, H, seq, 128, 0.6, seed=77, dtype=dtype)
+    k8, v8 = inp.k.to(fp8), inp.v.to(fp8)
+    w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device), layout)
+    w.plan(dev(inp.qo_indptr.numpy(), cuda_device), dev(inp.kv_indptr.numpy(), cuda_device), H, H, 128,
+           q_data_type=dtype, kv_data_type=fp8)
+    kd, vd = dev(k8, cuda_device), dev(v8, cuda_device)
+    if layout == "HND":
+        kd, vd = kd.transpose(0, 1).contiguous(), vd.transpose(0, 1).contiguous()
+    si, skv, ip, kp = masks_to_device(inp.masks, cuda_device)
+    o = w.run(dev(inp.q, cuda_device), kd, vd, si, skv, ip, kp)
+    w.check_status()
+    m = inp.masks
+    ref = oa.sparse_attention(inp.q, k8.float(), v8.float(), inp.qo_indptr.numpy(), inp.kv_indptr.numpy(),
+                              m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr)
+    assert_close_bf16(o, ref, f"fp8 kv {fp8} {dtype} {layout}")
+    with pytest.raises(ValueError):
+        w.run(dev(inp.q, cuda_device), kd.to(dtype), vd.to(dtype), si, skv, ip, kp)
+
+
 def test_undersized_kept_list_is_reported_not_walked(cuda_device):
     """A C-ABI caller that compacts with a kv_idx capacity below the kept count: the compaction records it, and
     the attention launch that follows touches neither the lists nor the output and reports FO_DEV_BAD_INDEX."""
