@@ -738,8 +738,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         l2b = 0;
       }
       if ((g & 1u) == X) {
-        // ---- pass 1: the maximum of this thread's half row of S[X], 32 columns at a time (the values are
-        // read again for the exponentials: holding them across the exchanges below would cost registers)
+        // ---- this thread's half row of S[X] goes to registers once and stays there until the exponentials; S[X] is
+        // handed back at once, so that the QK of this group's next block (about 1 800 clocks from here to a
+        // visible S while other batches are in the pipe) runs under this block's softmax
         if (!mbar_wait(&tail->s_full[X], my_blocks & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         int valid = seq.valid() - static_cast<int>(64u * ch);  // of my columns, how many exist
@@ -749,38 +750,36 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           const int vc = (lim > kBKV ? kBKV : lim) - static_cast<int>(64u * ch);
           valid = valid < vc ? valid : vc;
         }
-        uint64_t mbits = ~0ull;  // custom mask: one bit per column of this thread's half row
-        if constexpr (kMask == 2) {
+        uint32_t s[64];
+        tmem_ld_x32(tmem_s, s);
+        tmem_ld_x32(tmem_s + 32u, s + 32);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tail->s_free[X]);
+        if (valid < 64) {
+#pragma unroll
+          for (int t = 0; t < 64; ++t)
+            if (t >= valid) s[t] = 0xff800000u;  // -inf: exp2 gives 0
+        }
+        if constexpr (kMask == 2) {  // custom mask: one bit per column of this thread's half row
           const int col0 = seq.kvb * kBKV + static_cast<int>(64u * ch);
           int nb = cm_kv_len - col0;
           nb = nb > 64 ? 64 : nb;
-          mbits = nb > 0 ? load_mask_bits64(a.custom_mask + cm_base, cm_row_bit + col0, a.custom_mask_bytes - cm_base, nb) : 0ull;
+          const uint64_t mbits =
+              nb > 0 ? load_mask_bits64(a.custom_mask + cm_base, cm_row_bit + col0, a.custom_mask_bytes - cm_base, nb) : 0ull;
+#pragma unroll
+          for (int t = 0; t < 64; ++t)
+            if (!((mbits >> t) & 1ull)) s[t] = 0xff800000u;
         }
         float mx;
         {
           float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t s[32];
-            tmem_ld_x32(tmem_s + 32u * c, s);
-            tmem_wait_ld();
-            if (valid < 32 * c + 32) {
+          for (int t = 0; t < 8; ++t) {
 #pragma unroll
-              for (int t = 0; t < 32; ++t)
-                if (32 * c + t >= valid) s[t] = 0xff800000u;  // -inf
-            }
-            if constexpr (kMask == 2) {
-              const uint32_t mb = static_cast<uint32_t>(mbits >> (32 * c));
-#pragma unroll
-              for (int t = 0; t < 32; ++t)
-                if (!((mb >> t) & 1u)) s[t] = 0xff800000u;
-            }
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                mxs[i] = fmax3(mxs[i], __uint_as_float(s[8 * t + 2 * i]), __uint_as_float(s[8 * t + 2 * i + 1]));
-            }
+            for (int i = 0; i < 4; ++i)
+              mxs[i] = fmax3(mxs[i], __uint_as_float(s[8 * t + 2 * i]), __uint_as_float(s[8 * t + 2 * i + 1]));
           }
           mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
         }
@@ -805,23 +804,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (ch == 0u) tail->m_pub[X][row] = m_used;
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->m_ready[X]);
-        if (rescale) {
-          // O is rescaled only after the PV of block g-1 has completed; that PV may be the first of
-          // its item and wait for the previous item's epilogue, so this thread's share of it goes first
-          if (pend && !epilogue()) { ok = false; break; }
-          if (!mbar_wait(&tail->pv_done[Y], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
-          tc_fence_after_sync();
-          const float alpha = need ? ex2_approx(m_prev - m_new) : 1.0f;
-#pragma unroll
-          for (int c = 0; c < kD / 64; ++c) {  // this thread's half of the row of O: kD / 2 columns
-            uint32_t v[32];
-            tmem_ld_x32(tmem_o + static_cast<uint32_t>(kD / 2) * ch + 32u * c, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
-            tmem_st_x32(tmem_o + static_cast<uint32_t>(kD / 2) * ch + 32u * c, v);
-          }
-        }
         // this thread's partial sum follows the maximum in use
         if (m_ref != m_used) {
           const float beta = ex2_approx(m_ref - m_used);
@@ -837,27 +819,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
         const uint64_t scale2 = pack_f32x2(a.sm_scale_log2, a.sm_scale_log2);
         const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
-        uint32_t s[64];
-        tmem_ld_x32(tmem_s, s);
-        tmem_ld_x32(tmem_s + 32u, s + 32);
-        tmem_wait_ld();
-        // the QK of this group's next block may overwrite S[X]
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tail->s_free[X]);
         if constexpr (kSoftCap) {
 #pragma unroll
-          for (int t = 0; t < 64; ++t) s[t] = __float_as_uint(tanh_approx(__uint_as_float(s[t]) * a.soft_cap_pre));
-        }
-        if (valid < 64) {
-#pragma unroll
-          for (int t = 0; t < 64; ++t)
-            if (t >= valid) s[t] = 0xff800000u;  // -inf: exp2 gives 0
-        }
-        if constexpr (kMask == 2) {
-#pragma unroll
-          for (int t = 0; t < 64; ++t)
-            if (!((mbits >> t) & 1ull)) s[t] = 0xff800000u;
+          for (int t = 0; t < 64; ++t)  // masked columns stay at -inf
+            if (s[t] != 0xff800000u) s[t] = __float_as_uint(tanh_approx(__uint_as_float(s[t]) * a.soft_cap_pre));
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -875,6 +840,25 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           tmem_st_x16(tmem_p + 16u * c, pk);
         }
         tmem_wait_st();
+        if (rescale) {
+          // (after the exponentials, when S has left the registers, and before P is handed over: the PV of this
+          // block must see the rescaled O) O is rescaled only after the PV of block g-1 has completed; that PV may be the first of
+          // its item and wait for the previous item's epilogue, so this thread's share of it goes first
+          if (pend && !epilogue()) { ok = false; break; }
+          if (!mbar_wait(&tail->pv_done[Y], ((g - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const float alpha = need ? ex2_approx(m_prev - m_new) : 1.0f;
+#pragma unroll
+          for (int c = 0; c < kD / 64; ++c) {  // this thread's half of the row of O: kD / 2 columns
+            uint32_t v[32];
+            tmem_ld_x32(tmem_o + static_cast<uint32_t>(kD / 2) * ch + 32u * c, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
+            tmem_st_x32(tmem_o + static_cast<uint32_t>(kD / 2) * ch + 32u * c, v);
+          }
+          tmem_wait_st();
+        }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tail->p_full[X]);
