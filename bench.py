@@ -422,12 +422,33 @@ def run_flux(ctx, args, peaks):
             step()
         torch.cuda.synchronize()
 
+    # A model captures its layers back to back; one step of a GPU's share of the heads is launch-bound (the gap
+    # between two graph launches is about 9 us), so a graph holds as many steps as fit in about 0.65 ms: one at
+    # N = 1, several at N > 1. Every step inside a graph is the same full pass.
+    steps_per_graph, graph_many = 1, None
+    if graph is not None:
+        est = ctx.max_over_ranks([event_time(step, 3)["mean"]])[0]
+        want = args.steps_per_graph if args.steps_per_graph > 0 else int(0.65 / max(est, 1e-3))
+        steps_per_graph = max(1, min(8, want, args.steps))
+        if steps_per_graph > 1:
+            graph_many = torch.cuda.CUDAGraph()
+            cs.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(cs):
+                with torch.cuda.graph(graph_many, stream=cs):
+                    for _ in range(steps_per_graph):
+                        eager_step()
+            for _ in range(2):
+                graph_many.replay()
+            torch.cuda.synchronize()
+
     # ---- the timed region of `value`
     ctx.barrier()
     sampler = ClockSampler(ctx.local_rank).start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(args.steps // steps_per_graph):
+        (graph_many.replay if graph_many is not None else step)()
+    for _ in range(args.steps % steps_per_graph if graph_many is not None else 0):
         step()
     e1.record()
     torch.cuda.synchronize()
@@ -702,7 +723,7 @@ def run_flux(ctx, args, peaks):
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "flux_block: hidden 3072, H=24, D=128, S=4608, batch 2, block density 0.5 "
                                "(GEMM-Q sparse, GEMM-K/V dense, block-sparse attention, GEMM-O active heads + cache)",
-                   "parallelism": f"heads/{world}", "seed": SEED, "cuda_graph": bool(args.graph),
+                   "parallelism": f"heads/{world}", "seed": SEED, "cuda_graph": bool(args.graph), "steps_per_graph": steps_per_graph,
                    "schedule": args.schedule, "kv_projection": "one fused launch" if block.fuse_kv else "two launches",
                    "l2": "per-step working set (x, 4 weights, q/k/v, attention out, cache, y) is >200 MB per rank, "
                          "larger than the 126 MB L2; no explicit flush",
@@ -1240,6 +1261,8 @@ def main():
                     help="replay the step from a CUDA graph (device-resident leg; the default: at 8 GPUs a step is "
                          "about 100 us of kernels and eager launches are host-bound)")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="launch the step eagerly")
+    ap.add_argument("--steps-per-graph", type=int, default=0,
+                    help="steps captured in one CUDA graph (0: as many as fit in about 0.65 ms, at most 8)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
