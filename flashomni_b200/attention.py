@@ -178,8 +178,8 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         group = num_qo_heads // num_kv_heads
         if group not in (1, 2, 4, 8, 16):
             raise NotImplementedError("flashomni_b200: num_qo_heads / num_kv_heads must be 1, 2, 4, 8 or 16")
-        if head_dim_qk != head_dim_vo or head_dim_qk not in (64, 128):
-            raise NotImplementedError("flashomni_b200: head_dim 64 and 128 are implemented (qk and vo equal)")
+        if head_dim_qk != head_dim_vo or head_dim_qk not in (64, 128, 256):
+            raise NotImplementedError("flashomni_b200: head_dim 64, 128 and 256 are implemented (qk and vo equal)")
         if sparse_block_size_for_q != 128 or sparse_block_size_for_kv != 128:
             raise NotImplementedError("flashomni_b200: only 128-row sparse blocks are implemented")
 
@@ -329,7 +329,8 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
             may_split, self._min_chunk, self._min_items = True, 2, 0
             self._num_streams = max(self._num_streams, self._n_cand, self._max_kept)
             extra_units = slots = self._max_kept // 2 + n + 1      # parts of at least two blocks
-        if self._causal or self._packed_custom_mask is not None:   # those instantiations handle whole items only
+        # those instantiations handle whole items only
+        if self._causal or self._packed_custom_mask is not None or self._head_dim == 256:
             may_split = False
         self._max_units = n + (extra_units if may_split else 0)
         self._partial_slots = slots if may_split else 0

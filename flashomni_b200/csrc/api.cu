@@ -302,8 +302,10 @@ int sparse_attn_impl(const void* q, const void* k, const void* v, void* o, float
   if (partial_slots < 0 || (partial_slots > 0 && (partials == nullptr || !aligned16(partials) || arrive == nullptr)))
     return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: partial-result scratch missing or misaligned");
   if (dtype != FO_DTYPE_F16 && dtype != FO_DTYPE_BF16) return fail(FO_ERR_INVALID_ARG, "fo_sparse_attn_fwd: bad dtype");
-  if (head_dim != 128 && head_dim != 64)
-    return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: head_dim must be 128 or 64");
+  if (head_dim != 128 && head_dim != 64 && head_dim != 256)
+    return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: head_dim must be 64, 128 or 256");
+  if (head_dim == 256 && partial_slots > 0)
+    return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: head_dim 256 runs whole items only (partial_slots must be 0)");
   if (sbq != 128 || sbkv != 128)
     return fail(FO_ERR_UNSUPPORTED, "fo_sparse_attn_fwd: only 128-row q and kv sparse blocks are implemented");
   if (num_qo_heads <= 0 || num_kv_heads <= 0 || num_qo_heads % num_kv_heads != 0)

@@ -304,21 +304,32 @@ __device__ __forceinline__ uint64_t load_mask_bits64(const uint8_t* seg, int64_t
   return r;
 }
 
-// kD: head dimension, 128 or 64. With 64 a tile is one 64-column half: the second TMA box, the upper four of the
-// eight Q K^T MMAs and the upper 64 columns of O are left out; everything else is the same code.
+// kD: head dimension, 128, 64 or 256. With 64 a tile is one 64-column half: the second TMA box, the upper four of the
+// eight Q K^T MMAs and the upper 64 columns of O are left out; everything else is the same code. With 256 a tile
+// is four halves (64 KB), so Q, K and V have one slot each instead of two (a load waits for the MMA that read the
+// slot), Q K^T is sixteen MMAs, O takes 256 TMEM columns and P is written over the S it came from (S is in
+// registers by then): the QK of a group's next block waits for the PV of its previous one instead of for the
+// softmax. Correct and slower per FLOP than 128; whole items only.
 // kMask 1 (causal): a kv position is visible to a q token only up to token + kv_len - q_len (the reference's
 // MaskMode::kCausal, prefill.cuh:746-751). kMask 2 (custom): position (i, j) of a request is visible iff bit
 // i * kv_len + j of the request's packed mask is set (MaskMode::kCustom, variants.cuh:76-87). In both the softmax
 // warps also read the kv-block indices.
 template <bool kBf16, bool kSoftCap, bool kParts, int kD, int kMask>
 __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_constant__ AttnArgs a) {
-  static_assert(kD == 128 || kD == 64, "head dimension");
+  static_assert(kD == 128 || kD == 64 || kD == 256, "head dimension");
+  static_assert(!(kParts && kD == 256), "head dimension 256 runs whole items only");
   constexpr int kLoadBytes = 128 * kD * 2;   // bytes of one tile load
+  constexpr int kHalves = kD / 64;           // 64-column boxes per tile
+  constexpr bool kWide = kD == 256;
+  constexpr int kTB = kWide ? 2 * kTileBytes : kTileBytes;                               // bytes of a tile slot
+  constexpr int kQB = kWide ? 1 : kQBufs, kRK = kWide ? 1 : kRingK, kRV = kWide ? 1 : kRingV;   // slots of Q, K, V
+  static_assert((kQB + kRK + kRV) * kTB <= (kQBufs + kRing) * kTileBytes, "tile slots");
+  constexpr int kOW = kWide ? 64 : 32;       // columns of O per softmax thread in the epilogue
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   uint8_t* smem_q = smem;                           // kQBufs tiles
-  uint8_t* smem_ring = smem + kQBufs * kTileBytes;  // kRing tiles
+  uint8_t* smem_ring = smem + kQB * kTB;  // K slots, then V slots
   uint8_t* smem_ostage = smem + (kQBufs + kRing) * kTileBytes;  // output staging of the softmax warps
   Tail* tail = reinterpret_cast<Tail*>(smem_ostage + kSoftmaxWarps * kOutStageBytes);
   volatile int* abort_flag = &tail->abort_flag;
@@ -391,23 +402,23 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         const int hq = hk * a.group_size;     // group's q heads of 128 / group tokens, token-major
         if (seq.first()) {  // new item: its Q tile goes to buffer item_no & 1
           kv_row0 = seq.kv_row0;
-          const int qb_i = seq.item_no & 1;
+          const int qb_i = seq.item_no % kQB;
           if (!mbar_wait(&tail->q_empty[qb_i], (q_uses[qb_i] & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           ++q_uses[qb_i];
           const int q_row = seq.q_row0;
-          uint8_t* dst = smem_q + qb_i * kTileBytes;
+          uint8_t* dst = smem_q + qb_i * kTB;
           mbar_expect_tx(&tail->q_full[qb_i], kLoadBytes);
-          tma_load_3d(dst, &a.tmap_q, &tail->q_full[qb_i], 0, hq, q_row);
-          if constexpr (kD == 128) tma_load_3d(dst + kHalfBytes, &a.tmap_q, &tail->q_full[qb_i], 64, hq, q_row);
+#pragma unroll
+          for (int i = 0; i < kHalves; ++i) tma_load_3d(dst + i * kHalfBytes, &a.tmap_q, &tail->q_full[qb_i], 64 * i, hq, q_row);
         }
-        const int slot = static_cast<int>(nk % kRingK);
-        if (!mbar_wait(&tail->k_empty[slot], ((nk / kRingK) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        const int slot = static_cast<int>(nk % kRK);
+        if (!mbar_wait(&tail->k_empty[slot], ((nk / kRK) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         ++nk;
-        uint8_t* dst = smem_ring + slot * kTileBytes;
+        uint8_t* dst = smem_ring + slot * kTB;
         const int row = kv_row0 + seq.kvb * kBKV;
         mbar_expect_tx(&tail->k_full[slot], kLoadBytes);
-        tma_load_3d(dst, &a.tmap_k, &tail->k_full[slot], 0, hk, row);
-        if constexpr (kD == 128) tma_load_3d(dst + kHalfBytes, &a.tmap_k, &tail->k_full[slot], 64, hk, row);
+#pragma unroll
+        for (int i = 0; i < kHalves; ++i) tma_load_3d(dst + i * kHalfBytes, &a.tmap_k, &tail->k_full[slot], 64 * i, hk, row);
       }
     }
   } else if (warp == kWarpProducerV) {
@@ -422,14 +433,14 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       while (ok && seq.next(a, ignore_empty)) {
         const int hk = seq.h;
         if (seq.first()) kv_row0 = seq.kv_row0;
-        const int slot = static_cast<int>(nv % kRingV);
-        if (!mbar_wait(&tail->v_empty[slot], ((nv / kRingV) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        const int slot = static_cast<int>(nv % kRV);
+        if (!mbar_wait(&tail->v_empty[slot], ((nv / kRV) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         ++nv;
-        uint8_t* dst = smem_ring + (kRingK + slot) * kTileBytes;
+        uint8_t* dst = smem_ring + (kRK + slot) * kTB;
         const int row = kv_row0 + seq.kvb * kBKV;
         mbar_expect_tx(&tail->v_full[slot], kLoadBytes);
-        tma_load_3d(dst, &a.tmap_v, &tail->v_full[slot], 0, hk, row);
-        if constexpr (kD == 128) tma_load_3d(dst + kHalfBytes, &a.tmap_v, &tail->v_full[slot], 64, hk, row);
+#pragma unroll
+        for (int i = 0; i < kHalves; ++i) tma_load_3d(dst + i * kHalfBytes, &a.tmap_v, &tail->v_full[slot], 64 * i, hk, row);
       }
     }
   } else if (warp == kWarpQK) {
@@ -451,19 +462,20 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       bool ok = true;
       while (ok && seq.next(a, ignore_empty)) {
         const uint32_t sb = g & 1u;
-        const int qb_i = seq.item_no & 1;
-        // S[sb] is free once the softmax has copied block g-2 into registers
-        if (g >= 2u && !mbar_wait(&tail->s_free[sb], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        const int qb_i = seq.item_no % kQB;
+        // S[sb] is free once the softmax has copied block g-2 into registers (head dimension 256: once the PV of
+        // block g-2 has read the P that was written over it)
+        if (g >= 2u && !mbar_wait(kWide ? &tail->pv_done[sb] : &tail->s_free[sb], ((g - 2u) >> 1) & 1u, abort_flag)) { ok = false; break; }
         if (seq.first()) {
           if (!mbar_wait(&tail->q_full[qb_i], q_uses[qb_i] & 1u, abort_flag)) { ok = false; break; }
           ++q_uses[qb_i];
         }
-        const int slot = static_cast<int>(nk % kRingK);
-        if (!mbar_wait(&tail->k_full[slot], (nk / kRingK) & 1u, abort_flag)) { ok = false; break; }
+        const int slot = static_cast<int>(nk % kRK);
+        if (!mbar_wait(&tail->k_full[slot], (nk / kRK) & 1u, abort_flag)) { ok = false; break; }
         ++nk;
         tc_fence_after_sync();
-        const uint32_t q_lo = q_lo0 + static_cast<uint32_t>((qb_i * kTileBytes) >> 4);
-        const uint32_t k_lo = k_lo0 + static_cast<uint32_t>((slot * kTileBytes) >> 4);
+        const uint32_t q_lo = q_lo0 + static_cast<uint32_t>((qb_i * kTB) >> 4);
+        const uint32_t k_lo = k_lo0 + static_cast<uint32_t>((slot * kTB) >> 4);
         uint32_t la[8], lb[8];
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -472,8 +484,17 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
           la[kk] = q_lo + off;
           lb[kk] = k_lo + off;
         }
-        if constexpr (kD == 128) umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
+        if constexpr (kD >= 128) umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
         else umma_ss_x4(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 0u, la, lb);
+        if constexpr (kWide) {  // the other two 64-column halves of Q and K, accumulated onto the first two
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = static_cast<uint32_t>((((kk >> 2) + 2) * kHalfBytes + (kk & 3) * 32) >> 4);
+            la[kk] = q_lo + off;
+            lb[kk] = k_lo + off;
+          }
+          umma_ss_x8(tmem_base + kColS + sb * 128u, hi, hi, idesc_qk, 1u, la, lb);
+        }
         umma_commit(&tail->s_full[sb]);
         umma_commit(&tail->k_empty[slot]);
         if (seq.last()) umma_commit(&tail->q_empty[qb_i]);
@@ -485,7 +506,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     if (lane == 0) {
       constexpr uint32_t idesc_pv = make_idesc_f16(kBQ, kD, kBf16, 0, 1);
       // V is MN-major: its two 64-column halves are 16 KB apart (leading byte offset)
-      const uint64_t d0 = make_smem_desc_sw128(smem_u32(smem_ring + kRingK * kTileBytes), kHalfBytes, 1024);
+      const uint64_t d0 = make_smem_desc_sw128(smem_u32(smem_ring + kRK * kTB), kHalfBytes, 1024);
       const uint32_t hi = static_cast<uint32_t>(d0 >> 32), v_lo0 = static_cast<uint32_t>(d0);
       BlockSeq<ItemRead<false>> seq;
       seq.init();
@@ -498,12 +519,12 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         if (seq.first() && items_started > 0) {  // O must have been drained by the previous item's epilogue
           if (!mbar_wait(&tail->o_free, (items_started - 1u) & 1u, abort_flag)) { ok = false; break; }
         }
-        const int slot = static_cast<int>(nv % kRingV);
-        if (!mbar_wait(&tail->v_full[slot], (nv / kRingV) & 1u, abort_flag)) { ok = false; break; }
+        const int slot = static_cast<int>(nv % kRV);
+        if (!mbar_wait(&tail->v_full[slot], (nv / kRV) & 1u, abort_flag)) { ok = false; break; }
         ++nv;
         tc_fence_after_sync();
-        const uint32_t tmem_p = tmem_base + kColP + sb * 64u;
-        const uint32_t v_lo = v_lo0 + static_cast<uint32_t>((slot * kTileBytes) >> 4);
+        const uint32_t tmem_p = tmem_base + (kWide ? kColS + sb * 128u : kColP + sb * 64u);
+        const uint32_t v_lo = v_lo0 + static_cast<uint32_t>((slot * kTB) >> 4);
         uint32_t ta[8], lb[8];
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -532,9 +553,9 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
     const int quad = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tmem_s = tmem_base + lane_base + kColS + X * 128u + ch * 64u;
-    const uint32_t tmem_p = tmem_base + lane_base + kColP + X * 64u + ch * 32u;
+    const uint32_t tmem_p = tmem_base + lane_base + (kWide ? kColS + X * 128u : kColP + X * 64u) + ch * 32u;
     const uint32_t tmem_o = tmem_base + lane_base + kColO;
-    const uint32_t ocol = 64u * X + 32u * ch;  // this thread's quarter of O in the epilogue
+    const uint32_t ocol = static_cast<uint32_t>(kOW) * (2u * X + ch);  // this thread's quarter of O in the epilogue
     const bool has_cols = ocol < static_cast<uint32_t>(kD);  // head_dim 64: the second group's threads own no column of O
     const int row = quad * 32 + lane;
     uint64_t* pair_bar = &tail->pair_bar[X][quad];
@@ -563,7 +584,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       if (c.row_ok && has_cols) {
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(c.orow)[i] = z;
+        for (int i = 0; i < kOW / 8; ++i) reinterpret_cast<uint4*>(c.orow)[i] = z;
         if (c.lse != nullptr) *c.lse = -5e4f;
       }
     };
@@ -606,8 +627,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
       if (!mbar_wait(&tail->o_full, pend_item & 1u, abort_flag)) return false;
       tc_fence_after_sync();
       uint32_t v[32];
+      [[maybe_unused]] uint32_t v_hi[kWide ? 32 : 1];  // head dimension 256: the thread's second 32 columns
       if (has_cols) {
         tmem_ld_x32(tmem_o + ocol, v);
+        if constexpr (kWide) tmem_ld_x32(tmem_o + ocol + 32u, v_hi);
         tmem_wait_ld();
       } else {
 #pragma unroll
@@ -679,46 +702,53 @@ __global__ void __launch_bounds__(kThreads, 1) attention_kernel(const __grid_con
         }
       }
       const float inv_out = l_out > 0.f ? __frcp_rn(l_out) : 0.f;
-      uint4 outv[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t w[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float x0 = __uint_as_float(v[8 * q + 2 * t]) * inv_out;
-          const float x1 = __uint_as_float(v[8 * q + 2 * t + 1]) * inv_out;
-          w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
-        }
-        outv[q] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
       const bool whole = pend_q_valid * grp == kBQ;  // no row of the q-block is past the request
-      if (!has_cols) {
-        // head_dim 64: this thread's quarter of O does not exist
-      } else if (whole) {
-        // Through a 1 KB staging area per warp (16 rows x 64 bytes, plain row-major) and a TMA store of one
-        // 16-row x 32-column box: a store instruction of a warp would otherwise write 32 scattered 16-byte pieces.
-        uint8_t* stg = smem_ostage + warp * kOutStageBytes;
-        const int grow0 = pend_q_row0 + (quad * 32) / grp;
 #pragma unroll
-        for (int ph = 0; ph < 2; ++ph) {
-          if (lane == 0) tma_store_wait_read<0>();  // the staging area is free once its last store has read it
-          __syncwarp();
-          if ((lane >> 4) == ph) {
-            const int r = lane & 15;
+      for (int hh = 0; hh < kOW / 32; ++hh) {  // 32 columns at a time
+        uint4 outv[4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(stg + r * 64 + c * 16) = outv[c];
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            uint32_t r0 = v[8 * q + 2 * t], r1 = v[8 * q + 2 * t + 1];
+            if constexpr (kWide) {
+              if (hh == 1) { r0 = v_hi[8 * q + 2 * t]; r1 = v_hi[8 * q + 2 * t + 1]; }
+            }
+            const float x0 = __uint_as_float(r0) * inv_out;
+            const float x1 = __uint_as_float(r1) * inv_out;
+            w[t] = kBf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_3d(&a.tmap_o16, stg, static_cast<int>(ocol), pend_h * grp, grow0 + (ph * 16) / grp);
-            tma_store_commit();
-          }
+          outv[q] = make_uint4(w[0], w[1], w[2], w[3]);
         }
-      } else if (pend_ctx.row_ok) {
-        uint4* dst = reinterpret_cast<uint4*>(pend_ctx.orow);
+        if (!has_cols) {
+          // head_dim 64: this thread's quarter of O does not exist
+        } else if (whole) {
+          // Through a 1 KB staging area per warp (16 rows x 64 bytes, plain row-major) and a TMA store of one
+          // 16-row x 32-column box: a store instruction of a warp would otherwise write 32 scattered 16-byte pieces.
+          uint8_t* stg = smem_ostage + warp * kOutStageBytes;
+          const int grow0 = pend_q_row0 + (quad * 32) / grp;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) dst[q] = outv[q];
+          for (int ph = 0; ph < 2; ++ph) {
+            if (lane == 0) tma_store_wait_read<0>();  // the staging area is free once its last store has read it
+            __syncwarp();
+            if ((lane >> 4) == ph) {
+              const int r = lane & 15;
+#pragma unroll
+              for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(stg + r * 64 + c * 16) = outv[c];
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&a.tmap_o16, stg, static_cast<int>(ocol) + 32 * hh, pend_h * grp, grow0 + (ph * 16) / grp);
+              tma_store_commit();
+            }
+          }
+        } else if (pend_ctx.row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(pend_ctx.orow) + 4 * hh;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) dst[q] = outv[q];
+        }
       }
       if (pend_ctx.row_ok && pend_ctx.lse != nullptr) *pend_ctx.lse = (l_out > 0.f) ? (log2f(l_out) + m_out) : -5e4f;
       pend = false;
@@ -929,6 +959,12 @@ cudaError_t launch_one(const AttnArgs& a, int ctas, cudaStream_t stream) {
 }
 template <bool kBf16, bool kSoftCap>
 cudaError_t launch_two(const AttnArgs& a, int ctas, cudaStream_t stream) {
+  if (a.head_dim == 256) {  // whole items only
+    if (a.partial_slots > 0) return cudaErrorInvalidValue;
+    if (a.mask_mode == 1) return launch_one<kBf16, kSoftCap, false, 256, 1>(a, ctas, stream);
+    if (a.mask_mode == 2) return launch_one<kBf16, kSoftCap, false, 256, 2>(a, ctas, stream);
+    return launch_one<kBf16, kSoftCap, false, 256>(a, ctas, stream);
+  }
   if (a.mask_mode != 0) {  // whole items only (the caller gives no room for partial results)
     if (a.partial_slots > 0) return cudaErrorInvalidValue;
     if (a.mask_mode == 1)

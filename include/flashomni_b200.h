@@ -154,7 +154,8 @@ FO_API size_t fo_attn_partial_bytes(int64_t partial_slots);
  * [1] (unit cursor: units are handed to the CTAs dynamically) and [2] (count of finished CTAs) are used by
  * the kernel and are zero again when it ends, so launches that share the words (or `arrive`, `partials`) must
  * not overlap; [3] is reserved.
- * This build implements D = 128 and D = 64 with 128-row q and kv blocks. */
+ * This build implements D = 64, 128 and 256 with 128-row q and kv blocks (D = 256: whole items only,
+ * partial_slots = 0). */
 FO_API int fo_sparse_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int32_t dtype,
                        int64_t total_q, int64_t total_kv, int32_t num_qo_heads, int32_t num_kv_heads,
                        int32_t head_dim, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,

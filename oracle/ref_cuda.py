@@ -27,7 +27,7 @@ def load():
     global _lib
     if _lib is None:
         _lib = ctypes.CDLL(LIB_PATH)
-        for n in ("ref_sparse_attn", "ref_sparse_attn_hd64", "ref_sparse_attn_causal", "ref_sparse_attn_custom", "ref_gemm_q", "ref_gemm_o", "ref_segment_packbits"):
+        for n in ("ref_sparse_attn", "ref_sparse_attn_hd64", "ref_sparse_attn_hd256", "ref_sparse_attn_causal", "ref_sparse_attn_custom", "ref_gemm_q", "ref_gemm_o", "ref_segment_packbits"):
             getattr(_lib, n).restype = ctypes.c_int
     return _lib
 
@@ -40,15 +40,15 @@ def _stream(dev):
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
-def plan_unsplit(qo_indptr, kv_indptr, device, group=1):
+def plan_unsplit(qo_indptr, kv_indptr, device, group=1, cta_tile_q=128):
     """Work arrays of the reference planner for the un-split case (scheduler.cuh:67-168 with
-    cta_tile_q = 128 and kv_chunk_size >= every kv length): one entry per (request, q tile of 128 packed rows),
+    kv_chunk_size >= every kv length): one entry per (request, q tile of `cta_tile_q` packed rows),
     a request having qo_len * group packed rows (scheduler.cuh:82)."""
     qo = np.asarray(qo_indptr, dtype=np.int64)
     kv = np.asarray(kv_indptr, dtype=np.int64)
     req, tile = [], []
     for b in range(len(qo) - 1):
-        for t in range(int(-(-((qo[b + 1] - qo[b]) * group) // 128))):
+        for t in range(int(-(-((qo[b + 1] - qo[b]) * group) // cta_tile_q))):
             req.append(b)
             tile.append(t)
     mk = lambda a: torch.tensor(a, dtype=torch.int32, device=device)
@@ -60,18 +60,20 @@ def plan_unsplit(qo_indptr, kv_indptr, device, group=1):
 def sparse_attention(q, k, v, qo_indptr, kv_indptr, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr,
                      out, is_full=False, sm_scale=None, lse=None, plan=None, causal=False, packed_custom_mask=None,
                      mask_indptr=None):
-    """q [Tq, H, D], k/v [Tkv, Hkv, D] (NHD, D = 128 or 64), `out` is written in place (only active q-blocks)."""
+    """q [Tq, H, D], k/v [Tkv, Hkv, D] (NHD, D = 64, 128 or 256), `out` is written in place (only active q-blocks)."""
     dev = q.device
     if plan is None:
-        plan = plan_unsplit(qo_indptr.cpu().numpy(), kv_indptr.cpu().numpy(), dev, q.shape[1] // k.shape[1])
+        plan = plan_unsplit(qo_indptr.cpu().numpy(), kv_indptr.cpu().numpy(), dev, q.shape[1] // k.shape[1],
+                            cta_tile_q=64 if q.shape[-1] == 256 else 128)   # the harness runs head dimension 256 with 64-row tiles
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
     u = ctypes.c_uint32
-    if q.shape[-1] not in (64, 128):
-        raise ValueError("the harness instantiates the reference kernel for head dimensions 64 and 128")
+    if q.shape[-1] not in (64, 128, 256):
+        raise ValueError("the harness instantiates the reference kernel for head dimensions 64, 128 and 256")
     if causal and q.shape[-1] != 128:
         raise ValueError("the harness instantiates the causal mask mode for head dimension 128 only")
-    fn = load().ref_sparse_attn_causal if causal else (load().ref_sparse_attn if q.shape[-1] == 128 else load().ref_sparse_attn_hd64)
+    fn = load().ref_sparse_attn_causal if causal else {128: load().ref_sparse_attn, 64: load().ref_sparse_attn_hd64,
+                                                       256: load().ref_sparse_attn_hd256}[q.shape[-1]]
     lead = ()
     if packed_custom_mask is not None:   # byte indptr of the per-request matrices, as segment_packbits returns it
         if q.shape[-1] != 128:

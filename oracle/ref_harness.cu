@@ -24,7 +24,9 @@
 
 using namespace flashomni;
 
-template <typename T, int HD, MaskMode MM = MaskMode::kNone>
+// TQ: the kernel's q tile (CTA_TILE_Q). The reference has no 128-row configuration for head dimension 256
+// (prefill.cuh:1601 rejects it), so that one runs with 64-row tiles, as the reference's own dispatch would.
+template <typename T, int HD, MaskMode MM = MaskMode::kNone, int TQ = 128>
 static int run_attn(uint8_t* custom_mask, int32_t* mask_indptr, void* q, void* k, void* v, void* o, float* lse, uint8_t* sparse_info, uint8_t* sparse_kv_info,
                     int32_t* info_indptr, int32_t* kv_info_indptr, int32_t* q_indptr, int32_t* kv_indptr,
                     int32_t* request_indices, int32_t* qo_tile_indices, int32_t* kv_tile_indices, int32_t* o_indptr,
@@ -75,7 +77,7 @@ static int run_attn(uint8_t* custom_mask, int32_t* mask_indptr, void* q, void* k
   p.total_num_rows = nullptr;
   p.padded_batch_size = padded_batch;
   p.partition_kv = false;
-  cudaError_t e = BatchSparseFAWithRaggedKVDispatched<128, HD, HD, PosEncodingMode::kNone, false, MM,
+  cudaError_t e = BatchSparseFAWithRaggedKVDispatched<TQ, HD, HD, PosEncodingMode::kNone, false, MM,
                                                       Variant, Params>(p, nullptr, nullptr, stream);
   return static_cast<int>(e);
 }
@@ -116,6 +118,26 @@ __attribute__((visibility("default"))) int ref_sparse_attn_hd64(
                                  kv_chunk_size_ptr, padded_batch, num_qo_heads, num_kv_heads, q_stride_n, q_stride_h,
                                  k_stride_n, k_stride_h, v_stride_n, v_stride_h, sm_scale, is_full, max_rows, st);
   return run_attn<half, 64>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
+                        request_indices, qo_tile_indices, kv_tile_indices, o_indptr, kv_chunk_size_ptr, padded_batch,
+                        num_qo_heads, num_kv_heads, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n,
+                        v_stride_h, sm_scale, is_full, max_rows, st);
+}
+
+// The same with head dimension 256 (one of the reference's AOT head dimensions, setup.py:30), q tiles of 64 rows.
+__attribute__((visibility("default"))) int ref_sparse_attn_hd256(
+    void* q, void* k, void* v, void* o, float* lse, uint8_t* sparse_info, uint8_t* sparse_kv_info,
+    int32_t* info_indptr, int32_t* kv_info_indptr, int32_t* q_indptr, int32_t* kv_indptr, int32_t* request_indices,
+    int32_t* qo_tile_indices, int32_t* kv_tile_indices, int32_t* o_indptr, int32_t* kv_chunk_size_ptr,
+    uint32_t padded_batch, uint32_t num_qo_heads, uint32_t num_kv_heads, uint32_t q_stride_n, uint32_t q_stride_h,
+    uint32_t k_stride_n, uint32_t k_stride_h, uint32_t v_stride_n, uint32_t v_stride_h, float sm_scale, int is_full,
+    uint32_t max_rows, int is_bf16, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    return run_attn<nv_bfloat16, 256, MaskMode::kNone, 64>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr,
+                                 kv_indptr, request_indices, qo_tile_indices, kv_tile_indices, o_indptr,
+                                 kv_chunk_size_ptr, padded_batch, num_qo_heads, num_kv_heads, q_stride_n, q_stride_h,
+                                 k_stride_n, k_stride_h, v_stride_n, v_stride_h, sm_scale, is_full, max_rows, st);
+  return run_attn<half, 256, MaskMode::kNone, 64>(nullptr, nullptr, q, k, v, o, lse, sparse_info, sparse_kv_info, info_indptr, kv_info_indptr, q_indptr, kv_indptr,
                         request_indices, qo_tile_indices, kv_tile_indices, o_indptr, kv_chunk_size_ptr, padded_batch,
                         num_qo_heads, num_kv_heads, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n,
                         v_stride_h, sm_scale, is_full, max_rows, st);

@@ -23,6 +23,10 @@ def attention_case(name):
         H, lens_q, lens_kv, density, seed, D = 3, [300, 205], [256, 333], 0.7, 105, 64
     elif name == "attn_hd64_gqa":
         H, lens_q, lens_kv, density, seed, group, D = 4, [130, 256], [384, 130], 0.6, 106, 2, 64
+    elif name == "attn_hd256":   # head dimension 256, ragged
+        H, lens_q, lens_kv, density, seed, D = 3, [300, 205], [256, 333], 0.7, 111, 256
+    elif name == "attn_hd256_gqa":
+        H, lens_q, lens_kv, density, seed, group, D = 4, [130, 256], [384, 130], 0.6, 112, 2, 256
     elif name == "attn_causal":         # causal mask inside the kept blocks; kv longer than q (offset kv_len - q_len)
         H, lens_q, lens_kv, density, seed, causal = 3, [300, 205], [428, 333], 0.7, 107, True
     elif name == "attn_causal_gqa":
@@ -70,7 +74,7 @@ def flat_custom_mask(case):
     return torch.from_numpy(np.concatenate([cm.reshape(-1) for cm in case["custom_mask"]]))
 
 
-ATTENTION_CASES = ("attn_uniform", "attn_ragged", "attn_gqa", "attn_gqa4", "attn_hd64", "attn_hd64_gqa", "attn_causal",
+ATTENTION_CASES = ("attn_uniform", "attn_ragged", "attn_gqa", "attn_gqa4", "attn_hd64", "attn_hd64_gqa", "attn_hd256", "attn_hd256_gqa", "attn_causal",
                    "attn_causal_gqa", "attn_custom_mask", "attn_custom_mask_gqa")
 
 

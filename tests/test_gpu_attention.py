@@ -348,10 +348,12 @@ def test_grouped_query_attention(cuda_device, H, Hkv):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("soft_cap", [0.0, 30.0])
-def test_head_dim_64(cuda_device, dtype, soft_cap):
-    """Head dimension 64 (second instantiation of the kernel: half tiles, four Q K^T MMAs, 64 columns of O): ragged
-    requests, an active q-block that keeps nothing, lse, rows of switched-off blocks kept, with and without the cap."""
-    H, D = 3, 64
+@pytest.mark.parametrize("D", [64, 256])
+def test_head_dim_64_and_256(cuda_device, dtype, soft_cap, D):
+    """Head dimension 64 (half tiles, four Q K^T MMAs, 64 columns of O) and 256 (four-half tiles in single slots,
+    sixteen Q K^T MMAs, 256 columns of O, P written over S): ragged requests, an active q-block that keeps nothing,
+    lse, rows of switched-off blocks kept, with and without the cap."""
+    H = 3
     lens_q, lens_kv = [300, 205, 128], [256, 333, 70]
     qo = np.concatenate([[0], np.cumsum(lens_q)]).astype(np.int32)
     kv = np.concatenate([[0], np.cumsum(lens_kv)]).astype(np.int32)
@@ -373,7 +375,7 @@ def test_head_dim_64(cuda_device, dtype, soft_cap):
     w.check_status()
     ref, ref_lse = oa.sparse_attention(q, k, v, qo, kv, m.sparse_info, m.sparse_kv_info, m.info_indptr, m.kv_info_indptr,
                                        out_prior=prior, return_lse=True, logits_soft_cap=soft_cap)
-    assert_close_bf16(o.cpu(), ref, f"head_dim 64 {dtype} cap {soft_cap}")
+    assert_close_bf16(o.cpu(), ref, f"head_dim {D} {dtype} cap {soft_cap}")
     act = torch.zeros(int(qo[-1]), H, dtype=torch.bool)
     for b in range(len(lens_q)):
         for qb in range(qa[b].shape[0]):
@@ -516,7 +518,7 @@ def test_custom_mask(cuda_device, H, Hkv, D, dtype, packed):
     assert (ref_lse[act] == -5e4).any()
 
 
-@pytest.mark.parametrize("seed", range(16))
+@pytest.mark.parametrize("seed", range(24))
 def test_random_configurations_against_the_oracle(cuda_device, seed):
     """Seeded random draws over everything the wrapper takes at once: heads and grouping, head dimension, dtype, kv
     layout, causal mask, soft cap, lse, batch, ragged q and kv lengths (empty requests included), mask densities
@@ -525,6 +527,8 @@ def test_random_configurations_against_the_oracle(cuda_device, seed):
     g = int(rng.choice([1, 1, 2, 4]))
     Hkv = int(rng.integers(1, 4))
     H, D = Hkv * g, int(rng.choice([128, 128, 64]))
+    if seed >= 16:   # the last eight draws run head dimension 256
+        D = 256
     dtype = torch.bfloat16 if rng.random() < 0.6 else torch.float16
     causal = bool(rng.random() < 0.35)
     soft_cap = float(rng.choice([0.0, 0.0, 20.0]))
