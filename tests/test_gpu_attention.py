@@ -389,9 +389,11 @@ def test_head_dim_64_and_256(cuda_device, dtype, soft_cap, D):
     assert torch.allclose(lse.cpu()[act], ref_lse[act], atol=2e-2, rtol=1e-3)
 
 
-def test_head_dim_64_flux_size(cuda_device):
-    """24 heads of dimension 64 over 4608 tokens at density 0.5 against the oracle on sampled (head, q-block) rows."""
-    H, S, D = 24, 4608, 64
+@pytest.mark.parametrize("H,D", [(24, 64), (12, 256)])
+def test_head_dim_64_and_256_flux_size(cuda_device, H, D):
+    """24 heads of dimension 64 / 12 of dimension 256 over 4608 tokens at density 0.5 (several items per CTA, lists of
+    about 18 blocks) against the fp32 computation on sampled (head, q-block) rows."""
+    S = 4608
     inp = wl.attention_inputs(1, H, S, D, 0.5, seed=97)
     w = fo.BatchFlashOmniFAWithRaggedKVWrapper(torch.empty(1 << 20, dtype=torch.uint8, device=cuda_device))
     ind = inp.qo_indptr.to(cuda_device)
@@ -411,7 +413,7 @@ def test_head_dim_64_flux_size(cuda_device):
         cols = torch.from_numpy(np.concatenate([np.arange(b * 128, b * 128 + 128) for b in kept]))
         s_ = (inp.q[qb * 128:(qb + 1) * 128, h].float() @ inp.k[cols, h].float().T) / math.sqrt(D)
         ref = torch.softmax(s_, -1) @ inp.v[cols, h].float()
-        assert_close_bf16(o[qb * 128:(qb + 1) * 128, h].cpu(), ref, f"head_dim 64 head {h} q-block {qb}")
+        assert_close_bf16(o[qb * 128:(qb + 1) * 128, h].cpu(), ref, f"head_dim {D} head {h} q-block {qb}")
         done += 1
 
 
