@@ -423,13 +423,13 @@ def run_flux(ctx, args, peaks):
         torch.cuda.synchronize()
 
     # A model captures its layers back to back; a step of a small share of the heads is launch-bound (the gap
-    # between two graph launches is about 9 us), so when a step lasts under 0.25 ms a graph holds as many steps as
+    # between two graph launches is about 9 us), so when a step lasts under 0.27 ms a graph holds as many steps as
     # fit in about 0.65 ms (three at N = 4, four or five at N = 8; at N = 1 and 2 one step per graph measured the
     # same or faster). Every step inside a graph is the same full pass.
     steps_per_graph, graph_many = 1, None
     if graph is not None:
         est = ctx.max_over_ranks([event_time(step, 3)["mean"]])[0]
-        want = args.steps_per_graph if args.steps_per_graph > 0 else (int(0.65 / max(est, 1e-3)) if est < 0.25 else 1)
+        want = args.steps_per_graph if args.steps_per_graph > 0 else (int(0.65 / max(est, 1e-3)) if est < 0.27 else 1)
         steps_per_graph = max(1, min(8, want, args.steps))
         if steps_per_graph > 1:
             graph_many = torch.cuda.CUDAGraph()
@@ -1263,7 +1263,7 @@ def main():
                          "about 100 us of kernels and eager launches are host-bound)")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="launch the step eagerly")
     ap.add_argument("--steps-per-graph", type=int, default=0,
-                    help="steps captured in one CUDA graph (0: one, or as many as fit in about 0.65 ms when a step is under 0.25 ms)")
+                    help="steps captured in one CUDA graph (0: one, or as many as fit in about 0.65 ms when a step is under 0.27 ms)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
