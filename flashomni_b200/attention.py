@@ -172,6 +172,9 @@ class BatchFlashOmniFAWithRaggedKVWrapper:
         # (include/flashomni/attention/prefill.cuh:602-612); here run() casts the two tensors once (fo_cast_fp8)
         if q_data_type != kv_data_type and kv_data_type not in _FP8_KINDS:
             raise NotImplementedError("flashomni_b200: kv must have the dtype of q, float8_e4m3fn or float8_e5m2")
+        if kv_data_type in _FP8_KINDS:   # the reference warns in the same words where it casts (attention.py:787-794)
+            logging.warning("flashomni_b200: the attention kernel takes 16-bit inputs; float8 k / v are cast to the dtype "
+                            "of q before every run, which costs one more pass over them")
         native_dtype(q_data_type)
         if num_kv_heads <= 0 or num_qo_heads % num_kv_heads != 0:
             raise ValueError("num_qo_heads must be a multiple of num_kv_heads")

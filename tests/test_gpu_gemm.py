@@ -1,6 +1,5 @@
 """GPU: GEMM-Q and GEMM-O through the public API against the fp32 oracle."""
 
-import numpy as np
 import pytest
 import torch
 

@@ -6,7 +6,6 @@ sources local, and the peer barrier's bounded wait (a peer that never arrives gi
 import os
 import socket
 
-import numpy as np
 import pytest
 import torch
 
