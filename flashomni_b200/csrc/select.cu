@@ -83,36 +83,105 @@ __device__ __forceinline__ void select_row(const float* __restrict__ x, int len,
 }
 
 // t2i[b][j] = sum over heads (outer) and text rows (inner) of score[b][h][q][t2t + j], sequential fp32.
-__global__ void select_t2i_kernel(SelectArgs a) {
+// A CTA takes 32 columns j: its 256 threads fetch the (head, text row) values of those columns 8 pairs at a time
+// into shared memory (every load of a pass in flight together), then one warp adds them up per column in the
+// stated order, pass after pass.
+constexpr int kT2iPairs = 64;   // (head, text row) pairs per pass
+__global__ void __launch_bounds__(256) select_t2i_kernel(SelectArgs a) {
+  __shared__ float s_v[kT2iPairs][33];
   const int n_img = a.n - a.t2t;
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
-  if (j >= n_img) return;
+  const int j0 = blockIdx.x * 32;
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;   // 8 groups of 32 columns' worth of threads
+  const int pairs = a.heads * a.t2t;
   float acc = 0.f;
-  for (int h = 0; h < a.heads; ++h)
-    for (int q = 0; q < a.t2t; ++q)
-      acc = __fadd_rn(acc, a.score[((static_cast<int64_t>(b) * a.heads + h) * a.n + q) * a.n + a.t2t + j]);
-  a.t2i[static_cast<int64_t>(b) * a.n + j] = acc;
+  for (int p0 = 0; p0 < pairs; p0 += kT2iPairs) {
+#pragma unroll
+    for (int u = 0; u < kT2iPairs / 8; ++u) {
+      const int p = p0 + u * 8 + grp;
+      const int h = p / a.t2t, q = p - h * a.t2t;
+      float v = 0.f;
+      if (p < pairs && j0 + lane < n_img)
+        v = a.score[((static_cast<int64_t>(b) * a.heads + h) * a.n + q) * a.n + a.t2t + j0 + lane];
+      s_v[u * 8 + grp][lane] = v;
+    }
+    __syncthreads();
+    if (grp == 0) {
+      const int np = pairs - p0 < kT2iPairs ? pairs - p0 : kT2iPairs;
+      for (int u = 0; u < np; ++u) acc = __fadd_rn(acc, s_v[u][lane]);
+    }
+    __syncthreads();
+  }
+  if (grp == 0 && j0 + lane < n_img) a.t2i[static_cast<int64_t>(b) * a.n + j0 + lane] = acc;
 }
 
-// One warp per request: which image q-blocks stay on (bytes q_keep[b][qb], text blocks always 1).
-__global__ void __launch_bounds__(kSelWarps * 32) select_q_kernel(SelectArgs a) {
-  __shared__ uint32_t s_mass[kSelWarps][kSelMaxBlocks];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x * kSelWarps + warp;
-  if (b >= a.batch) return;
+// One CTA per request: which image q-blocks stay on (bytes q_keep[b][qb], text blocks always 1). The same
+// integer arithmetic as select_row, with the sums taken over the whole CTA (exact, so the order does not matter).
+constexpr int kSelQThreads = 128;
+// `round` alternates between two sets of partials, so one barrier per sum is enough: a set is rewritten two sums
+// later, after a barrier that every reader of it has passed.
+__device__ __forceinline__ unsigned long long cta_sum_u64(unsigned long long v, unsigned long long (*s_part)[kSelQThreads / 32],
+                                                          int round) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  unsigned long long* part = s_part[round & 1];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  unsigned long long t = 0;
+#pragma unroll
+  for (int w = 0; w < kSelQThreads / 32; ++w) t += part[w];
+  return t;
+}
+__global__ void __launch_bounds__(kSelQThreads) select_q_kernel(SelectArgs a) {
+  __shared__ uint32_t s_mass[kSelMaxBlocks];
+  __shared__ unsigned long long s_part[2][kSelQThreads / 32];
+  __shared__ float s_max[kSelQThreads / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = blockIdx.x;
   uint8_t* keep = a.q_keep + static_cast<int64_t>(b) * a.n;
-  for (int q = lane; q < a.t2t && q < a.n; q += 32) keep[q] = 1;
+  for (int q = tid; q < a.t2t && q < a.n; q += kSelQThreads) keep[q] = 1;
   const int n_img = a.n - a.t2t;
   if (n_img <= 0) return;
   if (a.t2t == 0) {  // no text rows to score the image blocks with: everything stays on
-    for (int q = lane; q < a.n; q += 32) keep[q] = 1;
+    for (int q = tid; q < a.n; q += kSelQThreads) keep[q] = 1;
     return;
   }
-  select_row(a.t2i + static_cast<int64_t>(b) * a.n, n_img, a.q_thr[b], s_mass[warp], [&](int k, uint32_t word) {
-    const int j = k * 32 + lane;
-    if (j < n_img) keep[a.t2t + j] = static_cast<uint8_t>((word >> lane) & 1u);
-  });
+  const float* x = a.t2i + static_cast<int64_t>(b) * a.n;
+  const float threshold = a.q_thr[b];
+  float mx = -INFINITY;
+  for (int j = tid; j < n_img; j += kSelQThreads) mx = fmaxf(mx, x[j]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) s_max[warp] = mx;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < kSelQThreads / 32; ++w) mx = fmaxf(mx, s_max[w]);
+  unsigned long long mine = 0;
+  for (int j = tid; j < n_img; j += kSelQThreads) {
+    const uint32_t m = det_exp2_mass(x[j], mx);
+    s_mass[j] = m;
+    mine += m;
+  }
+  const unsigned long long total = cta_sum_u64(mine, s_part, 0);
+  unsigned long long K = 0;
+  const bool any_off = threshold >= 0.f;
+  if (any_off) {
+    const unsigned long long limit = __double2ull_rd(__dmul_rn(static_cast<double>(threshold), static_cast<double>(total)));
+    for (int bit = 47; bit >= 0; --bit) {
+      const unsigned long long cand = K | (1ull << bit);
+      unsigned long long m_le = 0;
+      for (int j = tid; j < n_img; j += kSelQThreads) {
+        const unsigned long long key = (static_cast<unsigned long long>(s_mass[j]) << 16) | static_cast<unsigned>(j);
+        if (key <= cand) m_le += s_mass[j];
+      }
+      m_le = cta_sum_u64(m_le, s_part, bit);   // 47 first: the other set than the total's
+      if (m_le <= limit) K = cand;
+    }
+  }
+  for (int j = tid; j < n_img; j += kSelQThreads) {
+    const unsigned long long key = (static_cast<unsigned long long>(s_mass[j]) << 16) | static_cast<unsigned>(j);
+    keep[a.t2t + j] = static_cast<uint8_t>((any_off && key <= K) ? 0 : 1);
+  }
 }
 
 // sparse_info bytes (bit qb * H + h = q_keep[b][qb]) and the two byte indptrs.
@@ -173,10 +242,10 @@ cudaError_t launch_select_blocks(const SelectArgs& a, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   const int n_img = a.n - a.t2t;
   if (n_img > 0 && a.t2t > 0) {
-    dim3 g((n_img + 255) / 256, a.batch);
+    dim3 g((n_img + 31) / 32, a.batch);
     select_t2i_kernel<<<g, 256, 0, stream>>>(a);
   }
-  select_q_kernel<<<(a.batch + kSelWarps - 1) / kSelWarps, kSelWarps * 32, 0, stream>>>(a);
+  select_q_kernel<<<a.batch, kSelQThreads, 0, stream>>>(a);
   const int64_t info_bytes = static_cast<int64_t>(a.batch) * a.info_seg_bytes;
   const int64_t threads = info_bytes > a.batch + 1 ? info_bytes : a.batch + 1;
   select_pack_q_kernel<<<static_cast<int>((threads + 255) / 256), 256, 0, stream>>>(a);
